@@ -1,0 +1,156 @@
+/*
+ * pla_b200 — C ABI of the B200 (sm_100a) linear-attention hot path.
+ *
+ * Every entry point takes one plain-old-data argument struct (device pointers,
+ * element strides, sizes, small enums) and a CUDA stream handle passed as
+ * `void*` (a `cudaStream_t`; NULL = legacy default stream), launches its
+ * kernels on that stream and returns immediately. No torch type appears here;
+ * the library links only against the CUDA runtime.
+ *
+ * Return value: PLA_B200_OK, or a negative PLA_B200_E_* code for a host-side
+ * contract violation (nothing is launched in that case).
+ * `pla_b200_last_error()` returns a thread-local message for the last failure.
+ *
+ * Device-detected metadata problems (negative sequence offsets, an interval
+ * longer than t_max, a tree parent that points forward) never trap: the CTA
+ * that sees one ORs a PLA_B200_DEV_* bit into `*status` (when `status` is not
+ * NULL), writes zeros to its output rows and returns.
+ *
+ * Reference interfaces are cited by their path inside t-head/pla.
+ */
+#ifndef PLA_B200_H_
+#define PLA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PLA_B200_ABI_VERSION 1
+
+/* ---- return codes ------------------------------------------------------ */
+#define PLA_B200_OK 0
+#define PLA_B200_E_INVALID (-1)     /* bad shape / stride / enum             */
+#define PLA_B200_E_ALIGN (-2)       /* pointer or pitch not 16-byte aligned  */
+#define PLA_B200_E_UNSUPPORTED (-3) /* valid in the reference, not built     */
+#define PLA_B200_E_CUDA (-4)        /* the CUDA runtime reported an error    */
+#define PLA_B200_E_TOO_LARGE (-5)   /* exceeds a fixed capacity              */
+
+/* ---- device status bits (OR-ed into *status) ---------------------------- */
+#define PLA_B200_DEV_BAD_INTERVAL 1 /* cu_seqlens interval invalid or > t_max */
+#define PLA_B200_DEV_BAD_PARENT 2   /* tree parent index >= its own step      */
+#define PLA_B200_DEV_WAIT_TIMEOUT 4 /* a bounded wait on a bulk copy ran out  */
+#define PLA_B200_DEV_BAD_SLOT 8     /* slot index outside the pool            */
+
+/* ---- enums ---------------------------------------------------------------- */
+enum pla_b200_dtype { PLA_B200_BF16 = 0, PLA_B200_F16 = 1, PLA_B200_F32 = 2 };
+/* Decay gate form. SOFTPLUS: g = -exp(A_log) * softplus(x + dt_bias).
+ * SAFE: g = lower_bound * sigmoid(exp(A_log) * (x + dt_bias)).
+ * (src/pla_device_helpers.cuh:215-246) */
+enum pla_b200_gate { PLA_B200_GATE_SOFTPLUS = 0, PLA_B200_GATE_SAFE = 1 };
+/* Which slot ids are padding: SGLANG: slot < 0; VLLM: slot <= 0.
+ * (src/decode/k-last/fused_sigmoid_gating_k_last_kernel.cuh:166-169, :232-248) */
+enum pla_b200_pad { PLA_B200_PAD_SGLANG = 0, PLA_B200_PAD_VLLM = 1 };
+
+const char* pla_b200_last_error(void);
+int pla_b200_abi_version(void);
+
+/* ======================================================================== *
+ * k-last decode / MTP verify
+ * Replaces the launcher behind
+ *   pla.decode.fused_sigmoid_gating_delta_rule_forward_k_last         and
+ *   pla.decode.fused_sigmoid_gating_delta_rule_forward_k_last_packed
+ * (src/decode/k-last/fused_sigmoid_gating.cpp:164-203, host entry
+ *  src/decode/k-last/fused_sigmoid_gating_cuda_k_last.cpp:239-435, launcher
+ *  prototype src/decode/k-last/generated/fused_sigmoid_gating_dispatch_k_last.h:37-56).
+ *
+ * State pool: [slots, HV, V=128, K=128], K contiguous, slot pitch
+ * `state_slot_stride` elements (>= HV*16384). Activations: q,k [tokens,H,128],
+ * v [tokens,HV,128], o [tokens,HV,128] (o is dense), `*_tok_stride` in
+ * elements. The packed form is the same call with q,k,v pointing into one
+ * mixed_qkv row. All strides are in elements of the tensor's dtype.
+ * ======================================================================== */
+typedef struct pla_b200_klast_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* a;       /* gate logits: [tokens,HV] (GDN) or [tokens,HV,128] (KDA) */
+  const void* b;       /* beta logits: [tokens,HV] */
+  void* o;             /* [tokens,HV,128] dense, activation dtype */
+  int64_t q_tok_stride, k_tok_stride, v_tok_stride, a_tok_stride, b_tok_stride;
+  const void* A_log;   /* [HV] */
+  const void* dt_bias; /* [HV] (GDN) or [HV,128] (KDA) */
+  int32_t act_dtype;      /* pla_b200_dtype: BF16 or F16 */
+  int32_t A_log_dtype;    /* any pla_b200_dtype */
+  int32_t dt_bias_dtype;  /* any pla_b200_dtype */
+  int32_t state_dtype;    /* F32 or BF16 */
+
+  void* state;               /* pool base */
+  int64_t state_slot_stride; /* elements between slots */
+  int64_t num_slots;         /* slots addressable in the pool (bounds check; 0 = unchecked) */
+  const int32_t* slot_indices; /* [B] or [B, S] */
+  int32_t slot_row_stride;     /* 0: 1-D table; >0: row stride of the vLLM 2-D table */
+  int32_t slot_cols;           /* S of the 2-D table (0 for 1-D) */
+  const int32_t* num_accepted; /* [B] or NULL (2-D table: start column = max(acc,1)-1) */
+  const int32_t* cu_seqlens;   /* [B+1] or NULL (then request n owns tokens [n*t_max,(n+1)*t_max)) */
+
+  /* SGLang per-step snapshot cache [cache_rows, cache_steps, HV,128,128], same dtype as the pool */
+  void* cache;
+  const int32_t* cache_indices; /* [B] or NULL */
+  int32_t cache_steps;          /* allocated step dimension of `cache` */
+  /* EAGLE-tree parents; NULL = chain */
+  const void* parents;
+  int32_t parents_wide;         /* 0: int32, 1: int64 */
+  int64_t parents_seq_stride, parents_tok_stride;
+
+  int32_t B, t_max, H, HV;
+  float scale;
+  float softplus_beta, softplus_threshold, lower_bound;
+  int32_t gate;            /* pla_b200_gate */
+  int32_t is_kda;          /* per-key-channel gate */
+  int32_t use_qk_l2norm;
+  int32_t disable_state_update;
+  int32_t pad;             /* pla_b200_pad */
+  int32_t rows_per_cta;    /* 0 = pick; else 32, 64 or 128 state rows per CTA */
+  int32_t* status;         /* device word or NULL */
+} pla_b200_klast_args;
+
+int pla_b200_decode_klast(const pla_b200_klast_args* args, void* stream);
+
+/* ======================================================================== *
+ * v-last GDN decode (single token per request)
+ * Replaces pla::v_last::Args + pla_v_last_{small,big}batch_h*
+ * (src/decode/v-last/v_last_args.h:79-106, v_last_dispatch.cuh:43-67, host
+ *  src/decode/v-last/fused_sigmoid_gating_v_last.cpp:133-235).
+ * State pool [slots,HV,K=128,V=128] fp32, V contiguous, dense. All activation
+ * tensors dense. A slot < 0 leaves the request's `o` rows untouched; a request
+ * whose interval is not exactly one token is skipped.
+ * ======================================================================== */
+typedef struct pla_b200_vlast_args {
+  const void* q;  /* [B,H,128] */
+  const void* k;  /* [B,H,128] */
+  const void* v;  /* [B,HV,128] */
+  const void* a;  /* [B,HV] */
+  const void* b;  /* [B,HV] */
+  void* o;        /* [B,HV,128] */
+  const void* A_log;
+  const void* dt_bias; /* [HV], activation dtype */
+  int32_t act_dtype;
+  int32_t A_log_dtype;
+  float* state;
+  int64_t num_slots;
+  const int32_t* slot_indices; /* [>=B] */
+  const int32_t* cu_seqlens;   /* [B+1] or NULL */
+  int32_t B, H, HV;
+  float scale, softplus_beta, softplus_threshold;
+  int32_t use_qk_l2norm;
+  int32_t* status;
+} pla_b200_vlast_args;
+
+int pla_b200_decode_vlast(const pla_b200_vlast_args* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PLA_B200_H_ */

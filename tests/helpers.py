@@ -1,0 +1,34 @@
+"""Comparison helpers shared by the tests."""
+from __future__ import annotations
+
+import torch
+
+# Parity bars of the target: bf16/fp16 outputs within 2e-2 max-abs and 1e-2
+# relative L2; fp32 states within 1e-3 relative L2.
+OUT_MAX_ABS = 2e-2
+OUT_REL_L2 = 1e-2
+STATE_REL_L2 = 1e-3
+
+
+def rel_l2(x: torch.Tensor, ref: torch.Tensor) -> float:
+    x, ref = x.double(), ref.double()
+    den = ref.norm().item()
+    return (x - ref).norm().item() / max(den, 1e-30)
+
+
+def assert_out_close(out, ref, what="out"):
+    out, ref = out.float().cpu(), ref.float().cpu()
+    assert out.shape == ref.shape, (out.shape, ref.shape)
+    assert torch.isfinite(out).all(), f"{what}: non-finite values"
+    max_abs = (out - ref).abs().max().item() if out.numel() else 0.0
+    r = rel_l2(out, ref) if out.numel() else 0.0
+    assert max_abs <= OUT_MAX_ABS, f"{what}: max-abs {max_abs:.3e} > {OUT_MAX_ABS}"
+    assert r <= OUT_REL_L2, f"{what}: rel-L2 {r:.3e} > {OUT_REL_L2}"
+
+
+def assert_state_close(state, ref, what="state", tol=STATE_REL_L2):
+    state, ref = state.float().cpu(), ref.float().cpu()
+    assert state.shape == ref.shape, (state.shape, ref.shape)
+    assert torch.isfinite(state).all(), f"{what}: non-finite values"
+    r = rel_l2(state, ref)
+    assert r <= tol, f"{what}: rel-L2 {r:.3e} > {tol}"
