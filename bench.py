@@ -1,0 +1,331 @@
+#!/usr/bin/env python
+"""Headline benchmark: GDN single-token decode at production batch (B=256, Hqk=16, HV=32,
+d=128, fp32 k-last state pool of 1024 slots) — state traffic in GB/s against the HBM peak.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One process per GPU (torchrun for N>1). With N GPUs the value heads (and the matching
+q/k heads and pool shard) are split across ranks; there is no data-path collective, only
+the barrier that brackets the timed region. A "step" is one decode step of the whole
+batch: every (request, value head) 128x128 fp32 state is read once and written once.
+
+value : steps timed back to back with inputs resident in HBM (CUDA events on the launch stream).
+e2e   : the same step through the public op with the step's activations (packed q|k|v, a, b)
+        copied from pinned host memory and the output rows copied back, every step, and a
+        stream synchronise per step. The state pool is the engine's resident cache, not a
+        per-step input, so it stays in HBM in both measurements.
+roofline.achieved : algorithmic state bytes per launch (2 * B * HV_local * 65536) / average
+        launch time. cpu_baseline: the CPU oracle (a port of the reference's fp32 PyTorch
+        recurrence) timed on the host cores on a bounded sample of the same requests.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+B, HQK, HV, D, SLOTS = 256, 16, 32, 128, 1024
+TILE_BYTES = D * D * 4
+SEED = 20261125 + 1
+METRIC = "gdn_decode_state_bandwidth_B256"
+UNIT = "GB/s"
+WORKLOAD = "config1: GDN decode B=256 Hqk=16 HV=32 d=128, fp32 k-last pool 1024 slots, random non-consecutive slots"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
+# profiles/ (captured at B=64 and scaled by the tiles processed); None until captured.
+TRAFFIC_BYTES_PER_TILE = None
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_inputs(hv_lo: int, hv_hi: int, device):
+    """Seeded synthetic inputs of config 1 restricted to value heads [hv_lo, hv_hi)."""
+    g = torch.Generator().manual_seed(SEED)
+    ratio = HV // HQK
+    h_lo, h_hi = hv_lo // ratio, (hv_hi + ratio - 1) // ratio
+    q = torch.nn.functional.normalize(torch.randn(B, HQK, D, generator=g), dim=-1)
+    k = torch.nn.functional.normalize(torch.randn(B, HQK, D, generator=g), dim=-1)
+    v = torch.randn(B, HV, D, generator=g)
+    a = torch.randn(B, HV, generator=g)
+    b = torch.randn(B, HV, generator=g)
+    A_log = torch.rand(HV, generator=g) * math.log(16.0)
+    dt_bias = torch.randn(HV, generator=g) * 0.1
+    perm = torch.randperm(SLOTS - 1, generator=g) + 1          # slot 0 left out (padding under the vLLM rule)
+    slot_sets = [perm[i * B:(i + 1) * B].to(torch.int32) for i in range((SLOTS - 1) // B)]
+    hl = h_hi - h_lo
+    hvl = hv_hi - hv_lo
+    mixed = torch.cat([q[:, h_lo:h_hi].reshape(B, hl * D), k[:, h_lo:h_hi].reshape(B, hl * D),
+                       v[:, hv_lo:hv_hi].reshape(B, hvl * D)], dim=1).bfloat16()
+    host = dict(mixed=mixed, a=a[:, hv_lo:hv_hi].contiguous().bfloat16(), b=b[:, hv_lo:hv_hi].contiguous().bfloat16())
+    const = dict(A_log=A_log[hv_lo:hv_hi].contiguous(), dt_bias=dt_bias[hv_lo:hv_hi].contiguous().bfloat16())
+    return host, const, slot_sets, hl, hvl
+
+
+def run_ours(args):
+    from pla_b200.decode import fused_sigmoid_gating_delta_rule_forward_k_last_packed as packed
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    assert HV % world == 0
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    hv_lo, hv_hi = rank * HV // world, (rank + 1) * HV // world
+    host, const, slot_sets, hl, hvl = make_inputs(hv_lo, hv_hi, dev)
+    pinned = {k_: v_.pin_memory() for k_, v_ in host.items()}
+    dev_in = {k_: v_.to(dev) for k_, v_ in host.items()}
+    const = {k_: v_.to(dev) for k_, v_ in const.items()}
+    g = torch.Generator(device=dev).manual_seed(SEED + rank)
+    pool = torch.empty(SLOTS, hvl, D, D, device=dev)
+    pool.normal_(0.0, 0.02, generator=g)
+    slot_sets = [s.to(dev) for s in slot_sets]
+    cu = torch.arange(B + 1, dtype=torch.int32, device=dev)
+    out = torch.empty(B, 1, hvl, D, dtype=torch.bfloat16, device=dev)
+    out_host = torch.empty(B, 1, hvl, D, dtype=torch.bfloat16).pin_memory()
+    scale = D ** -0.5
+    stream = torch.cuda.current_stream()
+
+    def step(i, inp):
+        packed(inp["mixed"], inp["a"], inp["b"], const["A_log"], const["dt_bias"], 1.0, 20.0, scale, pool,
+               slot_sets[i % len(slot_sets)], out, True, cu, False, True, rows_per_cta=args.rows)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ----
+    for i in range(args.warmup):
+        step(i, dev_in)
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for i in range(args.steps):
+        step(i, dev_in)
+    e1.record(stream)
+    barrier()
+    ms_dev = e0.elapsed_time(e1)
+
+    # ---- end to end: pinned host activations in, output rows out, every step ----
+    stage = {k_: torch.empty_like(v_) for k_, v_ in dev_in.items()}
+
+    def e2e_step(i):
+        for k_ in stage:
+            stage[k_].copy_(pinned[k_], non_blocking=True)
+        step(i, stage)
+        out_host.copy_(out, non_blocking=True)
+        stream.synchronize()
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    barrier()
+    e2 = torch.cuda.Event(enable_timing=True)
+    e3 = torch.cuda.Event(enable_timing=True)
+    e2.record(stream)
+    for i in range(args.steps):
+        e2e_step(i)
+    e3.record(stream)
+    barrier()
+    ms_e2e = e2.elapsed_time(e3)   # events span the host-side gaps too: every step ends in a stream sync
+    clocks = sampler.stop() if rank == 0 else None
+
+    times = torch.tensor([ms_dev, ms_e2e], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_dev, ms_e2e = times.tolist()
+
+    total_state_bytes = 2 * B * HV * TILE_BYTES                      # whole job, per step
+    local_state_bytes = 2 * B * hvl * TILE_BYTES                     # this GPU's launch
+    value = total_state_bytes * args.steps / (ms_dev * 1e-3) / 1e9
+    e2e_value = total_state_bytes * args.steps / (ms_e2e * 1e-3) / 1e9
+    peak, peak_src = measured_peaks()
+    per_launch_s = ms_dev * 1e-3 / args.steps
+    achieved = local_state_bytes / per_launch_s / 1e9
+    h2d = sum(v_.numel() * v_.element_size() for v_ in host.values())
+    d2h = out_host.numel() * out_host.element_size()
+
+    line = None
+    if rank == 0:
+        cpu = None if args.no_cpu else cpu_baseline_sample()
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_dev / args.steps, 5), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layout": "k-last packed-QKV op", "sharding": f"value heads / {world}",
+                       "l2": "each step touches 1 GiB/n_gpus of state; slot sets rotate over 3 disjoint sets of 256",
+                       "frac_of_nominal_8TBps": round(achieved / 8000.0, 4)},
+            "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": h2d * world,
+                    "d2h_bytes_per_step": d2h * world, "ms_per_step": round(ms_e2e / args.steps, 5)},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "peak_source": f"of {peak_src}",
+                         "traffic": (None if TRAFFIC_BYTES_PER_TILE is None else TRAFFIC_BYTES_PER_TILE * B * hvl),
+                         "algorithmic_bytes_per_launch": local_state_bytes},
+            "cpu_baseline": cpu,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return line
+
+
+def cpu_oracle_step(n_req: int, reps: int):
+    """Times the CPU oracle on the first ``n_req`` requests of the workload (all 32 value heads)."""
+    from oracle import decode as odec
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    host, const, slot_sets, hl, hvl = make_inputs(0, HV, "cpu")
+    mixed = host["mixed"][:n_req]
+    q = mixed[:, : HQK * D].reshape(n_req, HQK, D)
+    k = mixed[:, HQK * D: 2 * HQK * D].reshape(n_req, HQK, D)
+    v = mixed[:, 2 * HQK * D:].reshape(n_req, HV, D)
+    g = torch.Generator().manual_seed(SEED)
+    pool = torch.randn(n_req, HV, D, D, generator=g) * 0.02      # pool pre-gathered to the active slots
+    idx = list(range(n_req))
+    best = float("inf")
+    for _ in range(reps + 1):                                    # first pass is warm-up
+        t0 = time.perf_counter()
+        odec.klast_forward(q=q, k=k, v=v, a=host["a"][:n_req], b=host["b"][:n_req], A_log=const["A_log"],
+                           dt_bias=const["dt_bias"], state=pool, slot_indices=idx, lengths=[1] * n_req,
+                           scale=D ** -0.5)
+        best = min(best, time.perf_counter() - t0)
+    gbs = 2 * n_req * HV * TILE_BYTES / best / 1e9
+    return gbs, best, threads
+
+
+def cpu_baseline_sample():
+    n_req, reps = 32, 3
+    gbs, sec, threads = cpu_oracle_step(n_req, reps)
+    return {"value": round(gbs, 3), "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"CPU oracle (fp32 torch recurrence) on {n_req} of the 256 requests, best of {reps}; "
+                      f"{sec * 1e3:.1f} ms per sample step; state pre-gathered to the active slots"}
+
+
+def run_reference(args):
+    """Reference arm: the reference's own CPU implementation of the path — its fp32 PyTorch
+    recurrence, restated in oracle/ because the reference tree is not on the GPU box — on all
+    host threads. Rank 0 only."""
+    if int(os.environ.get("RANK", 0)) != 0:
+        return
+    n_req = 32 if args.steps <= 200 else 8           # keeps the whole run within a few minutes
+    threads = os.cpu_count() or 1
+    for _ in range(args.warmup):
+        cpu_oracle_step(n_req, 0)
+    total = 0.0
+    for _ in range(args.steps):
+        _, sec, threads = cpu_oracle_step(n_req, 0)
+        total += sec
+    value = 2 * n_req * HV * TILE_BYTES * args.steps / total / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(total / args.steps * 1e3, 3),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": f"{n_req} of 256 requests per step"},
+        "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{n_req} of the 256 requests per step, all host threads"},
+        "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=0, help="state rows per CTA (0 = library default)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample (tuning runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        if args.warmup < 3:
+            args.warmup = 3
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
