@@ -231,7 +231,7 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": round(ms_dev / args.steps, 5), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "layout": "k-last packed-QKV op", "sharding": f"value heads / {world}",
-                       "l2": "each step touches 1 GiB/n_gpus of state; slot sets rotate over 3 disjoint sets of 256",
+                       "l2": "each step touches 1 GiB/n_gpus of state; slot sets rotate over disjoint sets of B slots",
                        "frac_of_nominal_8TBps": round(achieved / 8000.0, 4)},
             "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": h2d * world,
                     "d2h_bytes_per_step": d2h * world, "ms_per_step": round(ms_e2e / args.steps, 5)},
@@ -311,14 +311,20 @@ def run_reference(args):
 
 
 def main():
+    global B, SLOTS, WORKLOAD
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=0, help="state rows per CTA (0 = library default)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample (tuning runs)")
+    ap.add_argument("--batch", type=int, default=B, help="requests per step (profiling aid; the metric is quoted at 256)")
+    ap.add_argument("--slots", type=int, default=SLOTS, help="pool slots (profiling aid; default 1024)")
     args = ap.parse_args()
+    if (args.batch, args.slots) != (B, SLOTS):
+        B, SLOTS = args.batch, args.slots
+        WORKLOAD = f"REDUCED (not the headline): GDN decode B={B} Hqk=16 HV=32 d=128, fp32 k-last pool {SLOTS} slots"
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -18,6 +18,7 @@
 #include <stdio.h>
 
 #include "common.cuh"
+#include "decode_klast.h"
 
 namespace pla {
 
@@ -25,10 +26,6 @@ namespace {
 
 constexpr int D = 128;          // K = V = 128
 constexpr int TILE = D * D;     // elements of one (slot, hv) state
-
-struct KlastDev {
-  pla_b200_klast_args a;
-};
 
 template <int BV, int TS, bool IS_KDA>
 struct KlastSmem {
@@ -191,8 +188,8 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
       // Bounded wait for the state block; on timeout flag it, give the copy a
       // second bounded chance to land (shared memory must not be released
       // under it) and leave without touching global memory.
-      bool ok = mbar_wait(bar, 0);
-      if (!ok) {
+      const bool ok = mbar_wait(bar, 0);
+      if (__syncthreads_or(!ok)) {  // CTA-uniform decision
         if (tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_WAIT_TIMEOUT);
         (void)mbar_wait(bar, 0);
         return;
@@ -338,7 +335,7 @@ int launch_shape(const pla_b200_klast_args& a, cudaStream_t stream) {
       case 128: return launch_one<act_t, 128, 256, 1, IS_KDA>(a, stream);
     }
   }
-  PLA_REQUIRE(false, PLA_B200_E_INVALID, "rows_per_cta must be 0, 32, 64 or 128 (got %d)", rows);
+  PLA_REQUIRE(false, PLA_B200_E_INVALID, "rows_per_cta must be 0, 16, 32, 64 or 128 (got %d)", rows);
 }
 
 }  // namespace
@@ -381,6 +378,12 @@ extern "C" int pla_b200_decode_klast(const pla_b200_klast_args* args, void* stre
   PLA_REQUIRE(a.parents == nullptr || a.cache != nullptr, PLA_B200_E_INVALID,
               "a parent table needs the snapshot cache");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // rows_per_cta: 0 = pick (streaming kernel when the call qualifies), 16 = streaming kernel or error,
+  // 32/64/128 = the one-block-per-CTA kernel.
+  if (a.rows_per_cta == 16)
+    PLA_REQUIRE(klast_stream_eligible(a), PLA_B200_E_INVALID,
+                "rows_per_cta=16 selects the streaming decode kernel, which needs a plain single-token call");
+  if ((a.rows_per_cta == 0 || a.rows_per_cta == 16) && klast_stream_eligible(a)) return launch_klast_stream(a, s);
   if (a.act_dtype == PLA_B200_BF16)
     return a.is_kda ? launch_shape<__nv_bfloat16, true>(a, s) : launch_shape<__nv_bfloat16, false>(a, s);
   return a.is_kda ? launch_shape<__half, true>(a, s) : launch_shape<__half, false>(a, s);
