@@ -150,6 +150,109 @@ typedef struct pla_b200_vlast_args {
 
 int pla_b200_decode_vlast(const pla_b200_vlast_args* args, void* stream);
 
+/* ======================================================================== *
+ * KDA ReplaySSM: verify (read-only checkpoint, replay records out) and commit
+ * (integer plan, exact fold of the accepted prefix, conv-window scatter).
+ * Replaces launch_verify_native / launch_commit_plan / launch_fold_native /
+ * launch_conv_native (src/decode/kda_replayssm/kda_mtp_abi.h:127-150,
+ * src/decode/kda_replayssm_vllm/commit_plan.h:7-14).
+ * ======================================================================== */
+
+/* A 1-D index vector as the caller holds it: int32 or int64, possibly strided
+ * (src/decode/kda_replayssm/kda_mtp_abi.h:101-105). */
+typedef struct pla_b200_index {
+  const void* data;
+  int32_t wide;   /* 0: int32 elements, 1: int64 elements */
+  int64_t stride; /* elements between consecutive entries */
+} pla_b200_index;
+
+/* Strides (elements) of one conv-history tensor addressed [slot, channel, tap]. */
+typedef struct pla_b200_conv_strides {
+  int64_t slot, channel, tap;
+} pla_b200_conv_strides;
+
+/* Strides (elements) of one conv-window record tensor addressed [row, step, channel, tap]. */
+typedef struct pla_b200_window_strides {
+  int64_t row, step, channel, tap;
+} pla_b200_window_strides;
+
+typedef struct pla_b200_kda_verify_args {
+  /* pre-conv activations, bf16, one row per token; q|k|v may be thirds of one mixed_qkv row */
+  const void* x_q;
+  const void* x_k;
+  const void* x_v;
+  int64_t xq_tok_stride, xk_tok_stride, xv_tok_stride;
+  const void* raw_g;    /* [T, H*128] bf16 view */
+  const void* raw_beta; /* [T, H] bf16 view */
+  int64_t g_tok_stride, beta_tok_stride;
+  const float* w_q;     /* [H*128, 4] causal-conv taps, tap 3 multiplies the current token */
+  const float* w_k;
+  const float* w_v;
+  const void* cs_q;     /* persistent conv history (bf16), first three taps are read */
+  const void* cs_k;
+  const void* cs_v;
+  pla_b200_conv_strides cs_q_strides, cs_k_strides, cs_v_strides;
+  const float* A_log;   /* [H] */
+  const float* dt_bias; /* [H*128] */
+  const float* state;   /* checkpoint pool [slots, H, 128(V), 128(K)], read only */
+  int64_t state_slot_stride;
+  int32_t slots;
+  void* out;            /* [T, H*128] bf16, dense */
+  /* replay records; record row = request row (row_by_slot = 0) or = state slot (row_by_slot = 1) */
+  void* rec_rawv;       /* [R, H, Q, 128] bf16: post-conv, pre-norm v */
+  void* rec_rawk;       /* [R, H, Q, 128] bf16: post-conv, pre-norm k */
+  float* rec_g;         /* [R, H, Q, 128] log-decay (pre-exp) */
+  float* rec_beta;      /* [R, H, Q] */
+  void* win_q;          /* conv windows after consuming each token, bf16 */
+  void* win_k;
+  void* win_v;
+  pla_b200_window_strides win_q_strides, win_k_strides, win_v_strides;
+  pla_b200_index slot_idx;    /* [N] */
+  pla_b200_index cu;          /* [N+1] query_start_loc */
+  pla_b200_index scratch_idx; /* [N] window row per request (row_by_slot = 1); data NULL -> request row */
+  int32_t H, N, Q, T;         /* heads, requests, record steps, token capacity */
+  int32_t null_block_id;      /* slots <= this are padding: their output interval is zeroed */
+  int32_t row_by_slot;
+  int32_t gate;               /* pla_b200_gate */
+  float scale, lower_bound, softplus_beta, softplus_threshold;
+  int32_t* status;
+} pla_b200_kda_verify_args;
+
+int pla_b200_kda_replay_verify(const pla_b200_kda_verify_args* args, void* stream);
+
+/* Columns of the per-layer descriptor table (int64 [layers, 11], device memory)
+ * (src/decode/kda_replayssm/kda_mtp_abi.h:115-118). */
+enum pla_b200_replay_column {
+  PLA_B200_COL_STATE = 0, PLA_B200_COL_STATE_STRIDE, PLA_B200_COL_CONV, PLA_B200_COL_CONV_SLOT,
+  PLA_B200_COL_CONV_CHANNEL, PLA_B200_COL_CONV_TAP, PLA_B200_COL_RAWV, PLA_B200_COL_RAWK,
+  PLA_B200_COL_GATE, PLA_B200_COL_BETA, PLA_B200_COL_WINDOWS, PLA_B200_REPLAY_COLUMNS
+};
+
+typedef struct pla_b200_kda_commit_args {
+  const int64_t* layers;      /* device table [n_layers, PLA_B200_REPLAY_COLUMNS] */
+  int32_t n_layers;
+  int32_t* candidate;         /* device int32 [4, capacity] scratch owned by the context */
+  int32_t* plan;              /* device int32 [4, capacity]: commit_len, final, boundary, boundary_len */
+  pla_b200_index sampled;     /* accepted-token counts per sampler row */
+  pla_b200_index source;      /* [N] source checkpoint slot per request */
+  pla_b200_index cu;          /* [N+1] */
+  pla_b200_index mapping;     /* [N] request -> sampler row, data NULL = identity */
+  pla_b200_index computed;    /* tokens already in the cache per sampler row (align mode) */
+  pla_b200_index blocks;      /* block table base (align mode), addressed with the two strides below */
+  int64_t block_row_stride, block_col_stride;
+  int64_t block_size;         /* 0 = no alignment */
+  int32_t block_rows, block_cols;
+  int32_t N, capacity, sampler_rows;
+  int32_t H, slots, Q, null_block_id;
+  int64_t token_capacity;
+  int32_t* status;
+} pla_b200_kda_commit_args;
+
+/* Plan only (bit-exact integer semantics of commit_plan.cu:18-115). */
+int pla_b200_kda_replay_plan(const pla_b200_kda_commit_args* args, void* stream);
+/* Plan, then fold + conv scatter of every layer in one more launch. */
+int pla_b200_kda_replay_commit(const pla_b200_kda_commit_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

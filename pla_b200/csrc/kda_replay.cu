@@ -1,0 +1,592 @@
+// KDA ReplaySSM for sm_100a: verify, commit plan, exact fold + conv scatter.
+//
+// verify  (src/decode/kda_replayssm/kda_mtp_verify.cu:235-583): per request row and head, for
+//   every token of the window: causal conv (4 taps) + SiLU on q/k/v, gate, records (post-conv
+//   pre-norm k and v in bf16, log-decay and beta in fp32, the 3-tap window after the token),
+//   L2-norm q (times scale) and k, one delta-rule step on a PRIVATE copy of the checkpoint.
+//   The checkpoint is read once (one bulk copy per CTA) and never written.
+// plan    (src/decode/kda_replayssm_vllm/commit_plan.cu:18-115): integer, bit-exact.
+// fold    (src/decode/kda_replayssm/kda_mtp_fold.cu:254-529): replay the accepted prefix from the
+//   records (division-form norm of the recorded k), store to the final slot and, when the
+//   prefix crosses a block boundary, to the boundary slot after `bc` steps.
+// scatter (kda_mtp_fold.cu:828-894): conv_state[final, :, 0:3] <- records.conv[row, n-1], exact.
+//
+// CTA layout for verify and fold: one (row, head, 32-row slice of the 128x128 state); 128
+// threads; the slice (16 KiB, contiguous) lives in shared memory, is fetched with one bulk copy
+// and (fold) written back with one bulk store. Window steps are staged four at a time.
+#include <limits.h>
+
+#include "common.cuh"
+
+namespace pla {
+namespace {
+
+constexpr int D = 128;
+constexpr int TILE = D * D;
+constexpr int BV = 32;            // state rows per CTA
+constexpr int NVS = D / BV;
+constexpr int NT = 128;
+constexpr int NW = NT / 32;
+constexpr int TS = 4;             // steps staged per chunk
+constexpr uint32_t kSliceBytes = BV * D * 4;
+
+struct Smem {
+  float state[BV * D];
+  float q[TS][D];
+  float k[TS][D];
+  float gam[TS][D];
+  float v[TS][BV];
+  float o[TS][BV];
+  float part[TS][2][NW];
+  float beta[TS];
+  uint64_t bar;
+};
+
+__device__ __forceinline__ int64_t idx_at(const pla_b200_index& a, int64_t i) {
+  return a.wide ? static_cast<const int64_t*>(a.data)[i * a.stride]
+                : static_cast<const int32_t*>(a.data)[i * a.stride];
+}
+
+__device__ __forceinline__ float silu(float x) { return x * sigmoidf_fast(x); }
+
+// One delta-rule step on the CTA's 32 rows held in shared memory. 8 lanes per row.
+// WITH_OUT: also form o = S q. `snap` (optional) receives the updated rows.
+template <bool WITH_OUT>
+__device__ __forceinline__ void kda_step(float* s_state, const float* sk, const float* sq, const float* sgam,
+                                         const float* sv, float kr, float qr, float beta, float* so,
+                                         float* snap, int warp, int lane) {
+  const int row = warp * 8 + (lane >> 3) * 2;  // two consecutive rows per lane group
+  const int j = lane & 7;
+  float4 kk[4], qq[4], gg[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    kk[i] = reinterpret_cast<const float4*>(sk)[i * 8 + j];
+    kk[i].x *= kr; kk[i].y *= kr; kk[i].z *= kr; kk[i].w *= kr;
+    gg[i] = reinterpret_cast<const float4*>(sgam)[i * 8 + j];
+    if constexpr (WITH_OUT) {
+      qq[i] = reinterpret_cast<const float4*>(sq)[i * 8 + j];
+      qq[i].x *= qr; qq[i].y *= qr; qq[i].z *= qr; qq[i].w *= qr;
+    }
+  }
+#pragma unroll
+  for (int pp = 0; pp < 2; ++pp) {
+    float4* srow = reinterpret_cast<float4*>(s_state + (row + pp) * D);
+    float4 st[4];
+    float d = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      st[i] = srow[i * 8 + j];
+      st[i].x *= gg[i].x; st[i].y *= gg[i].y; st[i].z *= gg[i].z; st[i].w *= gg[i].w;
+      d += dot4(st[i], kk[i]);
+    }
+    d += __shfl_xor_sync(0xffffffffu, d, 1);
+    d += __shfl_xor_sync(0xffffffffu, d, 2);
+    d += __shfl_xor_sync(0xffffffffu, d, 4);
+    const float vn = (sv[row + pp] - d) * beta;
+    float oacc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      st[i].x = fmaf(vn, kk[i].x, st[i].x);
+      st[i].y = fmaf(vn, kk[i].y, st[i].y);
+      st[i].z = fmaf(vn, kk[i].z, st[i].z);
+      st[i].w = fmaf(vn, kk[i].w, st[i].w);
+      if constexpr (WITH_OUT) oacc += dot4(st[i], qq[i]);
+      srow[i * 8 + j] = st[i];
+      if (snap != nullptr) *reinterpret_cast<float4*>(snap + (row + pp) * D + (i * 8 + j) * 4) = st[i];
+    }
+    if constexpr (WITH_OUT) {
+      oacc += __shfl_xor_sync(0xffffffffu, oacc, 1);
+      oacc += __shfl_xor_sync(0xffffffffu, oacc, 2);
+      oacc += __shfl_xor_sync(0xffffffffu, oacc, 4);
+      if (j == 0) so[row + pp] = oacc;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ verify
+__global__ void __launch_bounds__(NT) kda_verify_kernel(const pla_b200_kda_verify_args p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  Smem& sh = *reinterpret_cast<Smem*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int vs = blockIdx.x % NVS;
+  const int h = (blockIdx.x / NVS) % p.H;
+  const int n = blockIdx.x / (NVS * p.H);
+  const int row0 = vs * BV;
+  const bool writer = vs == 0;  // q/k/gate/beta records are written once per (row, head)
+
+  const int64_t begin = idx_at(p.cu, n), end = idx_at(p.cu, n + 1);
+  const int64_t slot = idx_at(p.slot_idx, n);
+  // rows whose metadata is unusable are left completely alone
+  if (idx_at(p.cu, 0) != 0 || begin < 0 || end < begin || end > p.T || end - begin > p.Q || slot >= p.slots ||
+      begin == end)
+    return;
+  const int n_tok = static_cast<int>(end - begin);
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(h) * D + row0;
+  const int64_t out_stride = static_cast<int64_t>(p.H) * D;
+  if (slot <= p.null_block_id) {  // padding row: zero its output interval, touch nothing else
+    for (int i = tid; i < n_tok * BV; i += NT)
+      out[(begin + i / BV) * out_stride + (i % BV)] = __float2bfloat16(0.0f);
+    return;
+  }
+
+  if (tid == 0) {
+    mbar_init(&sh.bar, 1);
+    fence_mbar_init();
+    mbar_expect_tx(&sh.bar, kSliceBytes);
+    bulk_load(sh.state, p.state + slot * p.state_slot_stride + static_cast<int64_t>(h) * TILE + row0 * D,
+              kSliceBytes, &sh.bar);
+  }
+
+  const int64_t rec_row = p.row_by_slot ? slot : n;
+  const int64_t win_row = (p.row_by_slot && p.scratch_idx.data != nullptr) ? idx_at(p.scratch_idx, n) : n;
+  const int ch = h * D + tid;          // q/k/gate channel of this thread
+  const int chv = h * D + row0 + tid;  // v channel (threads < BV)
+  const __nv_bfloat16* xq = static_cast<const __nv_bfloat16*>(p.x_q);
+  const __nv_bfloat16* xk = static_cast<const __nv_bfloat16*>(p.x_k);
+  const __nv_bfloat16* xv = static_cast<const __nv_bfloat16*>(p.x_v);
+  const __nv_bfloat16* gin = static_cast<const __nv_bfloat16*>(p.raw_g);
+  const __nv_bfloat16* bin = static_cast<const __nv_bfloat16*>(p.raw_beta);
+
+  // conv taps and the sliding 3-tap history, all in registers
+  float wq[4], wk[4], wv[4], hq[3], hk[3], hv3[3];
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    wq[w] = p.w_q[ch * 4 + w];
+    wk[w] = p.w_k[ch * 4 + w];
+    wv[w] = (tid < BV) ? p.w_v[chv * 4 + w] : 0.0f;
+  }
+  {
+    const __nv_bfloat16* cq = static_cast<const __nv_bfloat16*>(p.cs_q);
+    const __nv_bfloat16* ck = static_cast<const __nv_bfloat16*>(p.cs_k);
+    const __nv_bfloat16* cv = static_cast<const __nv_bfloat16*>(p.cs_v);
+#pragma unroll
+    for (int w = 0; w < 3; ++w) {
+      hq[w] = __bfloat162float(cq[slot * p.cs_q_strides.slot + ch * p.cs_q_strides.channel + w * p.cs_q_strides.tap]);
+      hk[w] = __bfloat162float(ck[slot * p.cs_k_strides.slot + ch * p.cs_k_strides.channel + w * p.cs_k_strides.tap]);
+      hv3[w] = (tid < BV) ? __bfloat162float(cv[slot * p.cs_v_strides.slot + chv * p.cs_v_strides.channel +
+                                                w * p.cs_v_strides.tap])
+                          : 0.0f;
+    }
+  }
+  const float A_log = p.A_log[h];
+  const float dtb = p.dt_bias[ch];
+  __nv_bfloat16* wqo = static_cast<__nv_bfloat16*>(p.win_q);
+  __nv_bfloat16* wko = static_cast<__nv_bfloat16*>(p.win_k);
+  __nv_bfloat16* wvo = static_cast<__nv_bfloat16*>(p.win_v);
+  __nv_bfloat16* rrk = static_cast<__nv_bfloat16*>(p.rec_rawk);
+  __nv_bfloat16* rrv = static_cast<__nv_bfloat16*>(p.rec_rawv);
+
+  bool loaded = false;
+  for (int t0 = 0; t0 < n_tok; t0 += TS) {
+    const int nt = min(TS, n_tok - t0);
+    if (t0 > 0) __syncthreads();
+    for (int s = 0; s < nt; ++s) {
+      const int t = t0 + s;
+      const int64_t tok = begin + t;
+      const int64_t rec = ((rec_row * p.H + h) * p.Q + t) * D;
+      const __nv_bfloat16 bq = xq[tok * p.xq_tok_stride + ch], bk = xk[tok * p.xk_tok_stride + ch];
+      const float fq = __bfloat162float(bq), fk = __bfloat162float(bk);
+      float cq = fq * wq[3], ck = fk * wk[3];
+#pragma unroll
+      for (int w = 0; w < 3; ++w) {
+        cq += hq[w] * wq[w];
+        ck += hk[w] * wk[w];
+      }
+      cq = silu(cq);
+      ck = silu(ck);
+      const float x = __bfloat162float(gin[tok * p.g_tok_stride + ch]) + dtb;
+      const float gk = log_decay(x, A_log, p.gate, p.softplus_beta, p.softplus_threshold, p.lower_bound);
+      hq[0] = hq[1]; hq[1] = hq[2]; hq[2] = fq;
+      hk[0] = hk[1]; hk[1] = hk[2]; hk[2] = fk;
+      if (writer) {
+        rrk[rec + tid] = __float2bfloat16(ck);
+        p.rec_g[rec + tid] = gk;
+        const int64_t iq = win_row * p.win_q_strides.row + t * p.win_q_strides.step + ch * p.win_q_strides.channel;
+        const int64_t ik = win_row * p.win_k_strides.row + t * p.win_k_strides.step + ch * p.win_k_strides.channel;
+#pragma unroll
+        for (int w = 0; w < 3; ++w) {
+          wqo[iq + w * p.win_q_strides.tap] = __float2bfloat16(hq[w]);  // exact: the values came from bf16
+          wko[ik + w * p.win_k_strides.tap] = __float2bfloat16(hk[w]);
+        }
+      }
+      sh.q[s][tid] = cq;
+      sh.k[s][tid] = ck;
+      sh.gam[s][tid] = __expf(gk);
+      const float sq = warp_sum(cq * cq), sk = warp_sum(ck * ck);
+      if (lane == 0) {
+        sh.part[s][0][warp] = sq;
+        sh.part[s][1][warp] = sk;
+      }
+      if (tid < BV) {
+        const __nv_bfloat16 bvv = xv[tok * p.xv_tok_stride + chv];
+        const float fv = __bfloat162float(bvv);
+        float cv = fv * wv[3];
+#pragma unroll
+        for (int w = 0; w < 3; ++w) cv += hv3[w] * wv[w];
+        cv = silu(cv);
+        hv3[0] = hv3[1]; hv3[1] = hv3[2]; hv3[2] = fv;
+        sh.v[s][tid] = cv;
+        rrv[rec + row0 + tid] = __float2bfloat16(cv);
+        const int64_t iv = win_row * p.win_v_strides.row + t * p.win_v_strides.step + chv * p.win_v_strides.channel;
+#pragma unroll
+        for (int w = 0; w < 3; ++w) wvo[iv + w * p.win_v_strides.tap] = __float2bfloat16(hv3[w]);
+      }
+      if (tid == 0) {
+        const float beta = sigmoidf_fast(__bfloat162float(bin[tok * p.beta_tok_stride + h]));
+        sh.beta[s] = beta;
+        if (writer) p.rec_beta[(rec_row * p.H + h) * p.Q + t] = beta;
+      }
+    }
+    __syncthreads();
+    if (!loaded) {
+      const bool ok = mbar_wait(&sh.bar, 0);
+      if (__syncthreads_or(!ok)) {
+        if (tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_WAIT_TIMEOUT);
+        (void)mbar_wait(&sh.bar, 0);
+        return;
+      }
+      loaded = true;
+    }
+    for (int s = 0; s < nt; ++s) {
+      float sq = 0.f, sk = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        sq += sh.part[s][0][w];
+        sk += sh.part[s][1][w];
+      }
+      const float qr = rsqrtf(sq + 1e-6f) * p.scale, kr = rsqrtf(sk + 1e-6f);
+      kda_step<true>(sh.state, sh.k[s], sh.q[s], sh.gam[s], sh.v[s], kr, qr, sh.beta[s], sh.o[s], nullptr, warp,
+                     lane);
+    }
+    __syncthreads();
+    for (int i = tid; i < nt * BV; i += NT)
+      out[(begin + t0 + i / BV) * out_stride + (i % BV)] = __float2bfloat16(sh.o[i / BV][i % BV]);
+  }
+}
+
+// -------------------------------------------------------------------- plan
+struct PlanView {
+  pla_b200_kda_commit_args a;
+};
+
+__device__ __forceinline__ bool valid_slot(int64_t slot, const pla_b200_kda_commit_args& p) {
+  return slot > p.null_block_id && slot >= 0 && slot < p.slots;
+}
+__device__ __forceinline__ bool valid_interval(int64_t b, int64_t e, const pla_b200_kda_commit_args& p) {
+  return b >= 0 && e > b && e <= p.token_capacity && e - b <= p.Q;
+}
+
+// Candidate plan of row b: (count, final, boundary, boundary_len); zeros when the row commits nothing.
+__device__ void plan_row(const pla_b200_kda_commit_args& p, int b, int* cand) {
+  int64_t count = 0, final_slot = 0, boundary = 0, bc = 0;
+  if (b < p.N) {
+    const int64_t row = p.mapping.data != nullptr ? idx_at(p.mapping, b) : b;
+    const int64_t source = idx_at(p.source, b);
+    const int64_t begin = idx_at(p.cu, b), end = idx_at(p.cu, b + 1);
+    if (idx_at(p.cu, 0) == 0 && row >= 0 && row < p.sampler_rows && valid_slot(source, p) &&
+        valid_interval(begin, end, p)) {
+      const int64_t sampled = idx_at(p.sampled, row);
+      const int64_t len = end - begin;
+      count = sampled <= 0 ? 0 : (sampled > len ? len : sampled);
+      final_slot = source;
+      if (count != 0 && p.block_size != 0) {
+        if (row >= p.block_rows) {
+          count = 0;
+        } else {
+          const int64_t pos = idx_at(p.computed, row);
+          if (pos < 0 || pos > LLONG_MAX - p.Q) {
+            count = 0;
+          } else {
+            int64_t col = (pos + count - 1) / p.block_size;
+            if (col >= p.block_cols) col = p.block_cols - 1;
+            const int64_t f = idx_at(p.blocks, row * p.block_row_stride + col * p.block_col_stride);
+            if (!valid_slot(f, p)) count = 0;
+            else final_slot = f;
+            const int64_t distance = p.block_size - pos % p.block_size;  // tokens left in the current block
+            if (count != 0 && count >= distance) {
+              const int64_t bcol = pos / p.block_size;
+              if (bcol >= p.block_cols) {
+                count = 0;
+              } else {
+                const int64_t dest = idx_at(p.blocks, row * p.block_row_stride + bcol * p.block_col_stride);
+                if (!valid_slot(dest, p) || (dest == final_slot && distance != count)) {
+                  count = 0;
+                } else {
+                  boundary = dest;
+                  bc = distance;
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  const int R = p.capacity;
+  cand[b] = static_cast<int>(count);
+  cand[R + b] = count ? static_cast<int>(final_slot) : 0;
+  cand[2 * R + b] = count ? static_cast<int>(boundary) : 0;
+  cand[3 * R + b] = count ? static_cast<int>(bc) : 0;
+}
+
+// One warp per row: a row is dropped when one of its destinations is another row's source,
+// final or boundary slot, or its source is another row's destination. Symmetric by construction.
+__device__ void protect_row(const pla_b200_kda_commit_args& p, int b, int lane, const int* cand, int* plan) {
+  const int R = p.capacity;
+  bool conflict = false;
+  if (cand[b] != 0) {
+    const int64_t source = idx_at(p.source, b);
+    const int f = cand[R + b], d = cand[2 * R + b];
+    const bool has_d = cand[3 * R + b] > 0;
+    for (int other = lane; other < p.N; other += 32) {
+      if (other == b) continue;
+      const int64_t os = idx_at(p.source, other);
+      const int64_t ob = idx_at(p.cu, other), oe = idx_at(p.cu, other + 1);
+      // a real query that commits nothing still owns its source checkpoint
+      if (valid_slot(os, p) && valid_interval(ob, oe, p)) conflict |= (f == os) || (has_d && d == os);
+      if (cand[other] == 0) continue;
+      const int of = cand[R + other], od = cand[2 * R + other];
+      const bool has_od = cand[3 * R + other] > 0;
+      conflict |= (f == os) || (f == of) || (has_od && f == od) ||
+                  (has_d && (d == os || d == of || (has_od && d == od))) || (source == of) ||
+                  (has_od && source == od);
+    }
+  }
+  conflict = __any_sync(0xffffffffu, conflict);
+  if (lane == 0) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) plan[c * R + b] = conflict ? 0 : cand[c * R + b];
+  }
+}
+
+__global__ void plan_build_kernel(const pla_b200_kda_commit_args p) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < p.capacity) plan_row(p, b, p.candidate);
+}
+__global__ void plan_protect_kernel(const pla_b200_kda_commit_args p) {
+  const int b = blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
+  if (b < p.capacity) protect_row(p, b, threadIdx.x & 31, p.candidate, p.plan);
+}
+// Small batches: both phases in one CTA.
+__global__ void __launch_bounds__(1024) plan_fused_kernel(const pla_b200_kda_commit_args p) {
+  for (int b = threadIdx.x; b < p.capacity; b += blockDim.x) plan_row(p, b, p.candidate);
+  __threadfence_block();
+  __syncthreads();
+  for (int b = threadIdx.x >> 5; b < p.capacity; b += blockDim.x / 32)
+    protect_row(p, b, threadIdx.x & 31, p.candidate, p.plan);
+}
+
+// ----------------------------------------------------------- fold + scatter
+struct FoldGrid {
+  int fold_ctas;     // N * layers * H * NVS
+  int conv_tiles;    // CTAs per (row, layer) of the scatter part
+};
+
+__device__ void fold_cta(const pla_b200_kda_commit_args& p, int cta, Smem& sh) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int vs = cta % NVS;
+  const int hl = (cta / NVS) % (p.n_layers * p.H);
+  const int b = cta / (NVS * p.n_layers * p.H);
+  const int layer = hl / p.H, h = hl % p.H;
+  const int R = p.capacity;
+  const int n_commit = p.plan[b];
+  if (n_commit <= 0) return;
+  const int64_t slot = idx_at(p.source, b);
+  if (slot <= p.null_block_id || slot >= p.slots) return;
+  const int final_slot = p.plan[R + b], boundary = p.plan[2 * R + b], bc = p.plan[3 * R + b];
+  const int64_t* L = p.layers + static_cast<int64_t>(layer) * PLA_B200_REPLAY_COLUMNS;
+  float* pool = reinterpret_cast<float*>(L[PLA_B200_COL_STATE]);
+  const int64_t slot_stride = L[PLA_B200_COL_STATE_STRIDE];
+  const __nv_bfloat16* rawv = reinterpret_cast<const __nv_bfloat16*>(L[PLA_B200_COL_RAWV]);
+  const __nv_bfloat16* rawk = reinterpret_cast<const __nv_bfloat16*>(L[PLA_B200_COL_RAWK]);
+  const float* gate = reinterpret_cast<const float*>(L[PLA_B200_COL_GATE]);
+  const float* beta = reinterpret_cast<const float*>(L[PLA_B200_COL_BETA]);
+  const int row0 = vs * BV;
+  const int64_t tile_off = static_cast<int64_t>(h) * TILE + row0 * D;
+
+  if (tid == 0) {
+    mbar_init(&sh.bar, 1);
+    fence_mbar_init();
+    mbar_expect_tx(&sh.bar, kSliceBytes);
+    bulk_load(sh.state, pool + slot * slot_stride + tile_off, kSliceBytes, &sh.bar);
+  }
+  bool loaded = false;
+  const int64_t rec0 = (static_cast<int64_t>(b) * p.H + h) * p.Q;
+  for (int t0 = 0; t0 < n_commit; t0 += TS) {
+    const int nt = min(TS, n_commit - t0);
+    if (t0 > 0) __syncthreads();
+    for (int s = 0; s < nt; ++s) {
+      const int64_t rec = (rec0 + t0 + s) * D;
+      const float kf = __bfloat162float(rawk[rec + tid]);
+      sh.k[s][tid] = kf;
+      sh.gam[s][tid] = __expf(gate[rec + tid]);
+      const float sk = warp_sum(kf * kf);
+      if (lane == 0) sh.part[s][1][warp] = sk;
+      if (tid < BV) sh.v[s][tid] = __bfloat162float(rawv[rec + row0 + tid]);
+      if (tid == 0) sh.beta[s] = beta[rec0 + t0 + s];
+    }
+    __syncthreads();
+    if (!loaded) {
+      const bool ok = mbar_wait(&sh.bar, 0);
+      if (__syncthreads_or(!ok)) {
+        if (tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_WAIT_TIMEOUT);
+        (void)mbar_wait(&sh.bar, 0);
+        return;
+      }
+      loaded = true;
+    }
+    for (int s = 0; s < nt; ++s) {
+      float sk = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) sk += sh.part[s][1][w];
+      const float kinv = 1.0f / sqrtf(sk + 1e-6f);  // division form, as the records are replayed
+      float* snap = nullptr;
+      if (bc > 0 && t0 + s == bc - 1 && boundary > p.null_block_id && boundary < p.slots)
+        snap = pool + static_cast<int64_t>(boundary) * slot_stride + tile_off;
+      kda_step<false>(sh.state, sh.k[s], nullptr, sh.gam[s], sh.v[s], kinv, 0.f, sh.beta[s], nullptr, snap, warp,
+                      lane);
+    }
+  }
+  if (final_slot > p.null_block_id && final_slot < p.slots) {
+    fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      bulk_store(pool + static_cast<int64_t>(final_slot) * slot_stride + tile_off, sh.state, kSliceBytes);
+      bulk_commit();
+      bulk_wait_read<0>();
+    }
+  }
+}
+
+__device__ void scatter_cta(const pla_b200_kda_commit_args& p, int cta, int tiles) {
+  const int tile = cta % tiles;
+  const int layer = (cta / tiles) % p.n_layers;
+  const int b = cta / (tiles * p.n_layers);
+  const int R = p.capacity;
+  const int count = p.plan[b];
+  if (count <= 0) return;
+  const int final_slot = p.plan[R + b], boundary = p.plan[2 * R + b], bc = p.plan[3 * R + b];
+  const int64_t* L = p.layers + static_cast<int64_t>(layer) * PLA_B200_REPLAY_COLUMNS;
+  uint16_t* dst = reinterpret_cast<uint16_t*>(L[PLA_B200_COL_CONV]);
+  const uint16_t* src = reinterpret_cast<const uint16_t*>(L[PLA_B200_COL_WINDOWS]);
+  const int64_t s_slot = L[PLA_B200_COL_CONV_SLOT], s_ch = L[PLA_B200_COL_CONV_CHANNEL], s_tap = L[PLA_B200_COL_CONV_TAP];
+  const int dim = 3 * p.H * D;
+  const bool final_ok = final_slot > p.null_block_id && final_slot < p.slots;
+  const bool bound_ok = bc > 0 && boundary > p.null_block_id && boundary < p.slots;
+  const int64_t fsrc = (static_cast<int64_t>(b) * p.Q + count - 1) * dim * 3;
+  const int64_t bsrc = (static_cast<int64_t>(b) * p.Q + bc - 1) * dim * 3;
+  for (int i = tile * NT + threadIdx.x; i < dim * 3; i += tiles * NT) {
+    const int c = i / 3, w = i % 3;
+    const int64_t off = static_cast<int64_t>(c) * s_ch + w * s_tap;
+    if (bound_ok) dst[static_cast<int64_t>(boundary) * s_slot + off] = src[bsrc + i];
+    if (final_ok) dst[static_cast<int64_t>(final_slot) * s_slot + off] = src[fsrc + i];
+  }
+}
+
+__global__ void __launch_bounds__(NT) fold_scatter_kernel(const pla_b200_kda_commit_args p, const FoldGrid g) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  if (static_cast<int>(blockIdx.x) < g.fold_ctas)
+    fold_cta(p, blockIdx.x, *reinterpret_cast<Smem*>(smem_raw));
+  else
+    scatter_cta(p, blockIdx.x - g.fold_ctas, g.conv_tiles);
+}
+
+int check_commit(const pla_b200_kda_commit_args& a) {
+  PLA_REQUIRE(a.null_block_id == -1 || a.null_block_id == 0, PLA_B200_E_INVALID, "null_block_id must be -1 or 0");
+  PLA_REQUIRE(a.capacity >= 0 && a.N >= 0 && a.N <= a.capacity, PLA_B200_E_INVALID,
+              "commit query count exceeds capacity");
+  PLA_REQUIRE(a.Q >= 1 && a.Q <= 32 && a.H > 0 && a.slots > 0, PLA_B200_E_INVALID, "invalid commit plan dimensions");
+  PLA_REQUIRE(a.token_capacity >= 0 && a.token_capacity <= INT_MAX, PLA_B200_E_INVALID,
+              "token_capacity must be between 0 and INT32_MAX");
+  if (a.capacity == 0) return PLA_B200_OK;
+  PLA_REQUIRE(a.candidate && a.plan && a.sampled.data && a.source.data && a.cu.data, PLA_B200_E_INVALID,
+              "plan buffers and index vectors are required");
+  PLA_REQUIRE((a.block_size != 0) == (a.blocks.data != nullptr) && (a.block_size != 0) == (a.computed.data != nullptr),
+              PLA_B200_E_INVALID, "align arguments must be supplied together");
+  PLA_REQUIRE(a.block_size == 0 || (a.block_size >= a.Q && a.block_cols > 0), PLA_B200_E_INVALID,
+              "invalid align table/count/block size");
+  return PLA_B200_OK;
+}
+
+int launch_plan(const pla_b200_kda_commit_args& a, cudaStream_t s) {
+  if (a.capacity == 0) return PLA_B200_OK;
+  if (a.capacity <= 256) {
+    plan_fused_kernel<<<1, 1024, 0, s>>>(a);
+  } else {
+    plan_build_kernel<<<(a.capacity + 127) / 128, 128, 0, s>>>(a);
+    plan_protect_kernel<<<(a.capacity + 3) / 4, 128, 0, s>>>(a);
+  }
+  PLA_CUDA_OK(cudaGetLastError());
+  return PLA_B200_OK;
+}
+
+}  // namespace
+}  // namespace pla
+
+extern "C" int pla_b200_kda_replay_verify(const pla_b200_kda_verify_args* args, void* stream) {
+  using namespace pla;
+  PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
+  const pla_b200_kda_verify_args& a = *args;
+  PLA_REQUIRE(a.null_block_id == -1 || a.null_block_id == 0 || a.row_by_slot, PLA_B200_E_INVALID,
+              "null_block_id must be -1 or 0");
+  PLA_REQUIRE(a.H > 0 && a.N >= 0 && a.Q >= 1 && a.Q <= 32 && a.T >= 0 && a.slots > 0, PLA_B200_E_INVALID,
+              "verify requires H > 0, N >= 0, Q in [1, 32], slots > 0");
+  if (a.N == 0) return PLA_B200_OK;
+  PLA_REQUIRE(a.x_q && a.x_k && a.x_v && a.raw_g && a.raw_beta && a.w_q && a.w_k && a.w_v && a.cs_q && a.cs_k &&
+                  a.cs_v && a.A_log && a.dt_bias && a.state && a.out && a.rec_rawv && a.rec_rawk && a.rec_g &&
+                  a.rec_beta && a.win_q && a.win_k && a.win_v && a.slot_idx.data && a.cu.data,
+              PLA_B200_E_INVALID, "verify: a required pointer is NULL");
+  PLA_REQUIRE(aligned16(a.state) && a.state_slot_stride % 4 == 0 &&
+                  a.state_slot_stride >= static_cast<int64_t>(a.H) * 16384,
+              PLA_B200_E_ALIGN, "state must be float4-aligned fp32 [slots,H,128,128] with contiguous pages");
+  PLA_REQUIRE(a.gate == PLA_B200_GATE_SOFTPLUS || a.lower_bound < 0.0f, PLA_B200_E_INVALID,
+              "scale/lower_bound must be finite fp32; bound < 0");
+  static bool configured[64] = {};
+  int dev = 0;
+  PLA_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    PLA_CUDA_OK(cudaFuncSetAttribute(kda_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(Smem)));
+    configured[dev] = true;
+  }
+  const int64_t ctas = static_cast<int64_t>(a.N) * a.H * NVS;
+  PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "N*H exceeds the grid limit");
+  kda_verify_kernel<<<static_cast<unsigned>(ctas), NT, sizeof(Smem), static_cast<cudaStream_t>(stream)>>>(a);
+  PLA_CUDA_OK(cudaGetLastError());
+  return PLA_B200_OK;
+}
+
+extern "C" int pla_b200_kda_replay_plan(const pla_b200_kda_commit_args* args, void* stream) {
+  using namespace pla;
+  PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
+  const int rc = check_commit(*args);
+  if (rc != PLA_B200_OK) return rc;
+  return launch_plan(*args, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int pla_b200_kda_replay_commit(const pla_b200_kda_commit_args* args, void* stream) {
+  using namespace pla;
+  PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
+  const pla_b200_kda_commit_args& a = *args;
+  int rc = check_commit(a);
+  if (rc != PLA_B200_OK) return rc;
+  PLA_REQUIRE(a.layers != nullptr && a.n_layers > 0, PLA_B200_E_INVALID, "invalid layer pointer table");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  rc = launch_plan(a, s);
+  if (rc != PLA_B200_OK || a.N == 0) return rc;
+  static bool configured[64] = {};
+  int dev = 0;
+  PLA_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    PLA_CUDA_OK(cudaFuncSetAttribute(fold_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(Smem)));
+    configured[dev] = true;
+  }
+  FoldGrid g;
+  const int64_t fold = static_cast<int64_t>(a.N) * a.n_layers * a.H * NVS;
+  g.conv_tiles = (3 * a.H * D * 3 + NT * 8 - 1) / (NT * 8);
+  const int64_t total = fold + static_cast<int64_t>(a.N) * a.n_layers * g.conv_tiles;
+  PLA_REQUIRE(total < (1ll << 31), PLA_B200_E_TOO_LARGE, "commit grid too large");
+  g.fold_ctas = static_cast<int>(fold);
+  fold_scatter_kernel<<<static_cast<unsigned>(total), NT, sizeof(Smem), s>>>(a, g);
+  PLA_CUDA_OK(cudaGetLastError());
+  return PLA_B200_OK;
+}

@@ -108,3 +108,163 @@ def oracle_kwargs(args, lengths, state_ids, cache_ids):
         disable_state_update=args["disable_state_update"], cache=args["intermediate_states_buffer"],
         cache_indices=cache_ids, parents=args["retrieve_parent_token"],
     )
+
+
+# --------------------------------------------------------------------------- KDA ReplaySSM
+from types import SimpleNamespace  # noqa: E402
+
+
+def replay_layer(rs, slots, heads, q, layout, padding=256, history=None, conv_offset=0, device="cpu"):
+    """One layer's paged cache in the geometry the reference tests use
+    (tests/test_kda_replayssm_vllm.py:45-63 describes it): every page holds the bf16 conv
+    history, then (16-byte aligned) the fp32 [H,128,128] checkpoint, then padding bytes; the
+    whole buffer is pre-filled with 0x5A so that stray writes show up."""
+    c = 3 * heads * D
+    history = q + 2 if history is None else history
+    conv_shape = (c, history) if layout == "DS" else (history, c)
+    conv_bytes = c * history * 2
+    state_bytes = heads * D * D * 4
+    state_offset = -(-(conv_offset + conv_bytes) // 16) * 16
+    page_bytes = -(-(state_offset + state_bytes + padding) // 16) * 16
+    raw = torch.full((slots * page_bytes,), 0x5A, dtype=torch.uint8)
+    conv = raw.view(torch.bfloat16).as_strided((slots, *conv_shape),
+                                                (page_bytes // 2, conv_shape[1], 1), conv_offset // 2)
+    state = raw.view(torch.float32).as_strided((slots, heads, D, D), (page_bytes // 4, D * D, D, 1),
+                                               state_offset // 4)
+    conv.copy_(_t(rs, *conv.shape, dtype=torch.bfloat16, scale=0.2))
+    state.copy_(_t(rs, *state.shape, dtype=torch.float32, scale=0.01))
+    raw = raw.to(device)
+    conv = raw.view(torch.bfloat16).as_strided(conv.shape, conv.stride(), conv_offset // 2)
+    state = raw.view(torch.float32).as_strided(state.shape, state.stride(), state_offset // 4)
+    return SimpleNamespace(raw=raw, kv_cache=(conv, state), heads=heads, q=q, layout=layout, page_bytes=page_bytes)
+
+
+def replay_inputs(rs, heads, capacity, offset=2, softplus=False, device="cpu"):
+    """Projection rows [.., q|k|v|g|beta|pad] carved out of a larger buffer (token stride > width,
+    nonzero storage offset), conv taps, gate parameters."""
+    c = heads * D
+    storage = _t(rs, offset + capacity + 2, 4 * c + heads + 3, dtype=torch.bfloat16, scale=0.4).to(device)
+    rows = storage[offset:offset + capacity]
+    x = dict(mixed_qkv=rows[:, :3 * c], raw_g=rows[:, 3 * c:4 * c], raw_beta=rows[:, 4 * c:4 * c + heads],
+             storage=storage, conv_weight=_t(rs, 3 * c, 4, dtype=torch.float32, scale=0.2).to(device),
+             A_log=_t(rs, heads, dtype=torch.float32, scale=0.1).to(device),
+             dt_bias=_t(rs, c, dtype=torch.float32, scale=0.2).to(device), lower_bound=None if softplus else -5.0)
+    return x
+
+
+def blank_records(rows, heads, q, device="cpu"):
+    shape = (rows, heads, q, D)
+    return SimpleNamespace(
+        rawv=torch.full(shape, -7, dtype=torch.bfloat16, device=device),
+        rawk=torch.full(shape, -7, dtype=torch.bfloat16, device=device),
+        g=torch.full(shape, -7.0, device=device), beta=torch.full(shape[:-1], -7.0, device=device),
+        conv=torch.full((rows, q, 3 * heads * D, 3), -7, dtype=torch.bfloat16, device=device))
+
+
+def conv_ds(layer):
+    c = layer.kv_cache[0]
+    return c if layer.layout == "DS" else c.transpose(-1, -2)
+
+
+# name -> (layout, q, heads): request lengths [q, q-2, 0, 1, 1], slots [7, 2, 5, 0, -1] on 12 pages
+REPLAY_VERIFY_CASES = {
+    "sd_q4_h2": ("SD", 4, 2), "ds_q4_h2": ("DS", 4, 2), "sd_q1_h1": ("SD", 1, 1), "ds_q5_h1": ("DS", 5, 1),
+    "sd_q8_h1": ("SD", 8, 1),
+}
+
+
+def replay_verify_case(name, device="cpu"):
+    layout, q, heads = REPLAY_VERIFY_CASES[name]
+    rs = _rs(4100 + sum(map(ord, name)))
+    lengths = [q, max(q - 2, 0), 0, 1, 1]
+    offsets = [0]
+    for n in lengths:
+        offsets.append(offsets[-1] + n)
+    slots = [7, 2, 5, 0, -1]
+    layer = replay_layer(rs, 12, heads, q, layout, device=device)
+    x = replay_inputs(rs, heads, len(slots) * q + 3, device=device)
+    return layer, x, offsets, slots, lengths
+
+
+# Commit scenarios: 3 request rows on 24 pages, 2 layers, Q = 5, heads = 2.
+REPLAY_COMMIT_CASES = {
+    "plain_t0": dict(align=False, turn=0), "plain_t1": dict(align=False, turn=1),
+    "align_t0": dict(align=True, turn=0), "align_t2": dict(align=True, turn=2),
+    "align_t3": dict(align=True, turn=3),
+}
+
+
+def replay_commit_case(name, layout="SD", device="cpu"):
+    """Metadata of one commit round: request lengths, sampler mapping, accepted counts and (align
+    mode) a block table with 8-token blocks, after the scenario family of the reference's commit
+    test (tests/test_kda_replayssm_vllm.py:489-520)."""
+    cfg = REPLAY_COMMIT_CASES[name]
+    q, heads, rows = 5, 2, 3
+    rs = _rs(5700 + sum(map(ord, name)))
+    layers = [replay_layer(rs, 24, heads, q, layout, 256 + i * 64, device=device) for i in range(2)]
+    x = replay_inputs(rs, heads, rows * q + 2, device=device)
+    turn, align = cfg["turn"], cfg["align"]
+    lengths = [q, 3, 1] if turn % 2 == 0 else [1, q, 0]
+    offsets = [0, lengths[0], sum(lengths[:2]), sum(lengths)]
+    mapping = [2, 0, 3]
+    counts = ([2, 777, q, 0], [-3, 777, 1, q + 10], [q, 777, 0, 1], [q + 10, 777, 1, 0])[turn % 4]
+    table = [[1 + r * 6 + j for j in range(4)] for r in range(4)]
+    computed = [6, 1, 7, 8]
+    order = [2, 9, 16]
+    order = order[(turn + 1) % 3:] + order[:(turn + 1) % 3]
+    slots = [table[mapping[b]][(computed[mapping[b]] - 1) // 8] for b in range(rows)] if align else order
+    return dict(layers=layers, x=x, q=q, heads=heads, rows=rows, offsets=offsets, slots=slots, mapping=mapping,
+                counts=counts, table=table if align else None, computed=computed if align else None,
+                block_size=8 if align else None)
+
+
+def plan_scenarios():
+    """Conflict-masking scenarios with their expected plans
+    (after tests/test_kda_replayssm_vllm.py:980-1160: a destination equal to another row's source,
+    duplicate finals, a boundary slot owned by another row, int64 sources beyond int32, and the
+    block-table known answer)."""
+    out = []
+    for batch in (2, 5, 40):
+        for align in (True, False):
+            q, capacity = 4, batch + 3
+            names = (("c0_owner", "empty_owner", "duplicate_final", "boundary_source", "reverse_source", "disjoint",
+                      "wide_source") if align else
+                     ("c0_owner", "empty_owner", "duplicate_final", "disjoint", "wide_source", "wide_length"))
+            for variant in names:
+                sources = list(range(1, batch + 1))
+                offsets = [i * q for i in range(batch + 1)]
+                counts = [0] * batch
+                counts[0] = 1
+                table = [[batch + 1 + i, batch + 1 + i] for i in range(batch)]
+                positions = [8] * batch
+                if variant in ("c0_owner", "empty_owner"):
+                    table[0][1] = sources[-1]
+                    if variant == "empty_owner":
+                        offsets[-1] = offsets[-2]
+                elif variant == "duplicate_final":
+                    counts[-1] = 1
+                    table[-1][1] = table[0][1]
+                elif variant == "boundary_source":
+                    counts[0], counts[-1], positions[0] = 2, 1, 7
+                    table[0][0] = sources[-1]
+                elif variant == "reverse_source":
+                    counts[-1] = 1
+                    table[-1][1] = sources[0]
+                elif variant == "disjoint":
+                    counts[0], counts[-1] = 2, 1
+                else:
+                    sources[-1] = 2 ** 32 + table[0][1]
+                if not align:
+                    if variant in ("c0_owner", "empty_owner", "duplicate_final", "wide_length"):
+                        sources[-1] = sources[0]
+                    elif variant == "wide_source":
+                        sources[-1] = 2 ** 32 + sources[0]
+                    if variant == "wide_length":
+                        offsets[-1] += 2 ** 32
+                out.append(dict(name=f"{variant}_b{batch}_{'align' if align else 'plain'}", sources=sources,
+                                offsets=offsets, counts=counts, table=table if align else None,
+                                positions=positions if align else None, block_size=8 if align else 0, q=q,
+                                capacity=capacity, slots=2 * batch + 8, token_capacity=batch * q,
+                                blocked=variant in ("c0_owner", "duplicate_final", "boundary_source",
+                                                    "reverse_source")))
+    return out

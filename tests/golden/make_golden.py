@@ -45,6 +45,68 @@ def make_klast():
         print("klast", name, {k: getattr(v, "shape", None) for k, v in blob.items()})
 
 
+def load_replay_reference():
+    """The reference's vLLM replay test module: its fp64 oracle adapters are plain functions
+    (the PPU extension is only imported inside the functions that launch kernels)."""
+    import importlib.util
+    sys.dont_write_bytecode = True
+    sys.path.insert(0, str(REF / "tests"))
+    spec = importlib.util.spec_from_file_location("ref_replay_test", REF / "tests" / "test_kda_replayssm_vllm.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def make_replay():
+    ref = load_replay_reference()
+    import json
+    for name in cases.REPLAY_VERIFY_CASES:
+        layer, x, offsets, slots, lengths = cases.replay_verify_case(name)
+        records = cases.blank_records(len(slots), layer.heads, layer.q)
+        out = torch.full((x["mixed_qkv"].shape[0], layer.heads * 128), -11, dtype=torch.bfloat16)
+        want_out, want = ref.oracle_verify(layer, x, offsets, slots, records, out, 0)
+        np.savez_compressed(HERE / f"replay_verify_{name}.npz", out=want_out.float().numpy(),
+                            rawv=want.rawv.float().numpy(), rawk=want.rawk.float().numpy(), g=want.g.numpy(),
+                            beta=want.beta.numpy(), conv=want.conv.float().numpy())
+        print("replay verify", name, tuple(want_out.shape))
+    for name in cases.REPLAY_COMMIT_CASES:
+        c = cases.replay_commit_case(name)
+        blob = {}
+        for li, layer in enumerate(c["layers"]):
+            records = cases.blank_records(c["rows"], c["heads"], c["q"])
+            out = torch.full((c["x"]["mixed_qkv"].shape[0], c["heads"] * 128), -11, dtype=torch.bfloat16)
+            _, want = ref.oracle_verify(layer, c["x"], c["offsets"], c["slots"], records, out, 0)
+            state, conv, plan = ref.oracle_commit(layer, want, c["offsets"], c["slots"], c["counts"], c["mapping"],
+                                                  c["table"], c["computed"], c["block_size"])
+            touched = sorted({s for n, f, b, bc in zip(*plan) if n for s in ([f, b] if bc else [f])})
+            blob[f"state_l{li}"] = cases.subsample(state[touched]) if touched else np.zeros((0,), np.float32)
+            blob[f"conv_l{li}"] = conv[touched][:, :, :3].float().numpy() if touched else np.zeros((0,), np.float32)
+            blob["touched"] = np.array(touched, dtype=np.int64)
+            blob["plan"] = np.array(plan, dtype=np.int64)
+        np.savez_compressed(HERE / f"replay_commit_{name}.npz", **blob)
+        print("replay commit", name, blob["plan"].tolist())
+    plans = {}
+    for sc in cases.plan_scenarios():
+        layer = cases.replay_layer(np.random.RandomState(1), sc["slots"], 1, sc["q"], "DS")
+        rec = cases.blank_records(sc["capacity"], 1, sc["q"])
+        for key, val in (("rawv", .1), ("rawk", .2), ("g", -.1), ("beta", .5), ("conv", .3)):
+            getattr(rec, key).fill_(val)
+        batch = len(sc["sources"])
+        expected_counts = [0] * batch if sc["blocked"] else sc["counts"]
+        _, _, plan = ref.oracle_commit(layer, rec, sc["offsets"], sc["sources"], expected_counts,
+                                       block_table=sc["table"], computed=sc["positions"],
+                                       block_size=sc["block_size"] or None)
+        plans[sc["name"]] = [col + [0] * (sc["capacity"] - batch) for col in plan]
+    # known answer stated by the reference for block_table=[[3,4]], computed=[7], block 8, 4 sampled of Q=4
+    plans["known_answer_block_boundary"] = [[2], [4], [3], [1]]
+    (HERE / "replay_plans.json").write_text(json.dumps(plans, indent=0))
+    print("plans", len(plans))
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
-    make_klast()
+    which = sys.argv[2] if len(sys.argv) > 2 else "all"
+    if which in ("all", "klast"):
+        make_klast()
+    if which in ("all", "replay"):
+        make_replay()
