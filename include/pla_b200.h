@@ -112,11 +112,29 @@ typedef struct pla_b200_klast_args {
   int32_t use_qk_l2norm;
   int32_t disable_state_update;
   int32_t pad;             /* pla_b200_pad */
-  int32_t rows_per_cta;    /* 0 = pick; else 32, 64 or 128 state rows per CTA */
+  int32_t rows_per_cta;    /* 0 = pick; 16 = streaming decode kernel; else 32, 64 or 128 state rows per CTA */
   int32_t* status;         /* device word or NULL */
+
+  /* ---- extensions used by the token-recurrent prefill (all zero / NULL for decode) ---- */
+  void* state_out;                  /* NULL: the final state goes back into `state` at the request's slot */
+  int64_t state_out_slot_stride;
+  const int32_t* state_out_indices; /* NULL: request index n */
+  int32_t state_by_request;         /* 1: slot_indices may be NULL, request n then uses slot n */
+  int32_t state_init_zero;          /* start from a zero state; `state` is not read */
+  int32_t state_transposed;         /* slots hold [K,V] (V contiguous) instead of [V,K] */
+  int32_t gate_activated;           /* a = fp32 log-decay, b = fp32 beta, both already activated */
+  int64_t o_total_rows;             /* > 0: rows [cu_seqlens[B], o_total_rows) of o are set to zero */
 } pla_b200_klast_args;
 
 int pla_b200_decode_klast(const pla_b200_klast_args* args, void* stream);
+
+/* Chunk-free prefill: the same recurrence token by token over packed varlen sequences
+ * (needs cu_seqlens; t_max = longest sequence). Serves
+ *   pla.prefill.flashqla.chunk_gated_delta_rule_fwd / gdn_prefill_packed_qkv_fwd
+ *   (pla/prefill/flashqla/ops.py:225-738) and pla.prefill.flashkdapro.flashkda_fwd
+ *   (pla/prefill/flashkdapro/ops.py:66-219)
+ * with exact fp32 state arithmetic; q/k/v/gate rows may be only 2-byte aligned. */
+int pla_b200_prefill_recurrent(const pla_b200_klast_args* args, void* stream);
 
 /* ======================================================================== *
  * v-last GDN decode (single token per request)

@@ -41,6 +41,27 @@ struct KlastSmem {
   static constexpr int kBytes = kBar + 8;
 };
 
+// 4 consecutive state elements of a pool that is fp32 or bf16.
+__device__ __forceinline__ float4 load_state4(const void* base, int64_t off, bool f32) {
+  if (f32) return *reinterpret_cast<const float4*>(static_cast<const float*>(base) + off);
+  const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(base) + off);
+  const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+  return make_float4(__bfloat162float(e[0]), __bfloat162float(e[1]), __bfloat162float(e[2]), __bfloat162float(e[3]));
+}
+__device__ __forceinline__ void store_state4(void* base, int64_t off, const float4& v, bool f32) {
+  if (f32) {
+    *reinterpret_cast<float4*>(static_cast<float*>(base) + off) = v;
+  } else {
+    __nv_bfloat16 e[4] = {__float2bfloat16_rn(v.x), __float2bfloat16_rn(v.y), __float2bfloat16_rn(v.z),
+                          __float2bfloat16_rn(v.w)};
+    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(base) + off) = *reinterpret_cast<const uint2*>(e);
+  }
+}
+template <typename T>
+__device__ __forceinline__ float4 load4_scalar(const T* p) {
+  return make_float4(to_f32(p[0]), to_f32(p[1]), to_f32(p[2]), to_f32(p[3]));
+}
+
 template <typename act_t, int BV, int NT, int TS, bool IS_KDA>
 __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) {
   using L = KlastSmem<BV, TS, IS_KDA>;
@@ -65,6 +86,18 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
   const int HV = p.HV, H = p.H;
 
   const unsigned bid = blockIdx.x;
+  const unsigned work_ctas = static_cast<unsigned>(p.B) * HV * NVS;
+  if (bid >= work_ctas) {
+    // Trailing CTAs: physical token rows past the last sequence get zero output.
+    const int64_t first = p.cu_seqlens != nullptr ? p.cu_seqlens[p.B] : static_cast<int64_t>(p.B) * p.t_max;
+    const int64_t words = (p.o_total_rows - first) * HV * (D / 2);  // 16-bit outputs, two per word
+    if (first < 0 || words <= 0) return;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(static_cast<act_t*>(p.o) + first * HV * D);
+    for (int64_t i = static_cast<int64_t>(bid - work_ctas) * NT + tid; i < words;
+         i += static_cast<int64_t>(gridDim.x - work_ctas) * NT)
+      dst[i] = 0u;
+    return;
+  }
   const int vs = bid % NVS;
   const int hv = (bid / NVS) % HV;
   const int n = bid / (NVS * HV);
@@ -94,10 +127,12 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
     int col = acc > 0 ? acc - 1 : 0;
     if (col >= p.slot_cols) col = p.slot_cols - 1;
     slot = p.slot_indices[static_cast<int64_t>(n) * p.slot_row_stride + col];
-  } else {
+  } else if (p.slot_indices != nullptr) {
     slot = p.slot_indices[n];
+  } else {
+    slot = n;  // state_by_request
   }
-  const bool is_pad = (p.pad == PLA_B200_PAD_SGLANG) ? (slot < 0) : (slot <= 0);
+  const bool is_pad = p.slot_indices != nullptr && ((p.pad == PLA_B200_PAD_SGLANG) ? (slot < 0) : (slot <= 0));
   const bool oob = !is_pad && p.num_slots > 0 && slot >= p.num_slots;
   act_t* o_base = static_cast<act_t*>(p.o) + hv * D + row0;
   if (is_pad || oob) {
@@ -109,26 +144,47 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
     return;
   }
 
-  float* g_tile = static_cast<float*>(p.state) + static_cast<int64_t>(slot) * p.state_slot_stride +
-                  static_cast<int64_t>(hv) * TILE + row0 * D;
+  // Element offset of this CTA's rows inside a slot: contiguous for [V,K] slots; for
+  // transposed [K,V] slots the rows are columns and are gathered by hand.
+  const int64_t tile_off = static_cast<int64_t>(hv) * TILE + (p.state_transposed ? row0 : row0 * D);
+  const int64_t in_off = static_cast<int64_t>(slot) * p.state_slot_stride + tile_off;
+  const bool f32_state = p.state_dtype == PLA_B200_F32;
+  const bool bulk_io = f32_state && !p.state_transposed;
+  float* g_tile = static_cast<float*>(p.state) + in_off;  // only dereferenced when bulk_io
   constexpr uint32_t kBlockBytes = BV * D * 4;
+  const bool bulk_in = bulk_io && !p.state_init_zero;
 
-  if (tid == 0) {
-    mbar_init(bar, 1);
-    fence_mbar_init();
-    mbar_expect_tx(bar, kBlockBytes);
-    bulk_load(s_state, g_tile, kBlockBytes, bar);
+  if (bulk_in) {
+    if (tid == 0) {
+      mbar_init(bar, 1);
+      fence_mbar_init();
+      mbar_expect_tx(bar, kBlockBytes);
+      bulk_load(s_state, g_tile, kBlockBytes, bar);
+    }
+  } else {
+    // zero start, 16-bit pool or transposed slots: fill shared memory by hand (once per sequence)
+    for (int i = tid; i < BV * D; i += NT) {
+      float x = 0.0f;
+      if (!p.state_init_zero) {
+        const int r = p.state_transposed ? (i % BV) : (i / D);
+        const int c = p.state_transposed ? (i / BV) : (i % D);
+        const int64_t e = in_off + (p.state_transposed ? static_cast<int64_t>(c) * D + r : static_cast<int64_t>(r) * D + c);
+        x = load_any(p.state, p.state_dtype, e);
+        s_state[r * D + c] = x;
+      } else {
+        s_state[i] = 0.0f;
+      }
+    }
   }
 
   // ---- snapshot destinations ----
   int cache_idx = -1;
   if (p.cache != nullptr && p.cache_indices != nullptr && p.pad == PLA_B200_PAD_SGLANG)
     cache_idx = p.cache_indices[n];
-  float* cache_rows = (cache_idx >= 0)
-                          ? static_cast<float*>(p.cache) +
-                                static_cast<int64_t>(cache_idx) * p.cache_steps * HV * TILE +
-                                static_cast<int64_t>(hv) * TILE + row0 * D
-                          : nullptr;
+  // element offset of this CTA's rows in step 0 of the request's snapshot row, or -1
+  const int64_t cache_off = (cache_idx >= 0) ? static_cast<int64_t>(cache_idx) * p.cache_steps * HV * TILE +
+                                                   static_cast<int64_t>(hv) * TILE + row0 * D
+                                             : -1;
 
   const act_t* gq = static_cast<const act_t*>(p.q) + h * D;
   const act_t* gk = static_cast<const act_t*>(p.k) + h * D;
@@ -140,6 +196,13 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
   const int r_in_pass = warp * 4 + (lane >> 3);  // row inside a pass
   const int j = lane & 7;                        // lane inside the row
   bool loaded = false;
+  // 8-byte vector loads of q/k/gate rows need aligned rows; sliced projection
+  // buffers may be only 2-byte aligned and then take element loads.
+  const auto al8 = [](const void* ptr, int64_t stride) {
+    return ((reinterpret_cast<uintptr_t>(ptr) & 7) == 0) && (stride % 4 == 0);
+  };
+  const bool io_vec = al8(p.q, p.q_tok_stride) && al8(p.k, p.k_tok_stride) &&
+                      (!IS_KDA || p.gate_activated || al8(p.a, p.a_tok_stride));
 
   for (int t0 = 0; t0 < T; t0 += TS) {
     const int nt = min(TS, T - t0);
@@ -148,8 +211,8 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
     // ---- per-step parameters, one warp per step ----
     for (int s = warp; s < nt; s += NW) {
       const int64_t tok = bos + t0 + s;
-      float4 qv = load4(gq + tok * p.q_tok_stride + lane * 4);
-      float4 kv = load4(gk + tok * p.k_tok_stride + lane * 4);
+      float4 qv = io_vec ? load4(gq + tok * p.q_tok_stride + lane * 4) : load4_scalar(gq + tok * p.q_tok_stride + lane * 4);
+      float4 kv = io_vec ? load4(gk + tok * p.k_tok_stride + lane * 4) : load4_scalar(gk + tok * p.k_tok_stride + lane * 4);
       float qr = p.scale, kr = 1.0f;
       if (p.use_qk_l2norm) {
         const float qs = warp_sum(dot4(qv, qv));
@@ -159,8 +222,23 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
       }
       reinterpret_cast<float4*>(s_q + s * D)[lane] = make_float4(qv.x * qr, qv.y * qr, qv.z * qr, qv.w * qr);
       reinterpret_cast<float4*>(s_k + s * D)[lane] = make_float4(kv.x * kr, kv.y * kr, kv.z * kr, kv.w * kr);
+      if (p.gate_activated) {
+        // a holds fp32 log-decays, b fp32 betas: nothing left to activate
+        const float* fa = static_cast<const float*>(p.a);
+        if constexpr (IS_KDA) {
+          const float* row = fa + tok * p.a_tok_stride + hv * D + lane * 4;
+          reinterpret_cast<float4*>(s_gam + s * D)[lane] =
+              make_float4(__expf(row[0]), __expf(row[1]), __expf(row[2]), __expf(row[3]));
+        } else if (lane == 0) {
+          s_gam[s] = __expf(fa[tok * p.a_tok_stride + hv]);
+        }
+        if (lane == 0) s_beta[s] = static_cast<const float*>(p.b)[tok * p.b_tok_stride + hv];
+        for (int i = lane; i < BV; i += 32) s_v[s * BV + i] = to_f32(gv[tok * p.v_tok_stride + i]);
+        continue;
+      }
       if constexpr (IS_KDA) {
-        const float4 av = load4(ga + tok * p.a_tok_stride + hv * D + lane * 4);
+        const float4 av = io_vec ? load4(ga + tok * p.a_tok_stride + hv * D + lane * 4)
+                                 : load4_scalar(ga + tok * p.a_tok_stride + hv * D + lane * 4);
         const int64_t c = static_cast<int64_t>(hv) * D + lane * 4;
         float4 g;
         g.x = __expf(log_decay(av.x + load_any(p.dt_bias, p.dt_bias_dtype, c + 0), A_log, p.gate,
@@ -184,7 +262,7 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
     // by thread 0 before anybody polls it.
     __syncthreads();
 
-    if (!loaded) {
+    if (!loaded && bulk_in) {
       // Bounded wait for the state block; on timeout flag it, give the copy a
       // second bounded chance to land (shared memory must not be released
       // under it) and leave without touching global memory.
@@ -211,21 +289,26 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
       const float beta = s_beta[s];
 
       // where this step's state snapshot goes (NULL: nowhere)
-      float* snap = nullptr;
-      if (cache_rows != nullptr) {
-        if (t < p.cache_steps) snap = cache_rows + static_cast<int64_t>(t) * HV * TILE;
+      void* snap_base = nullptr;
+      int64_t snap_off = 0;
+      if (cache_off >= 0) {
+        if (t < p.cache_steps) {
+          snap_base = p.cache;
+          snap_off = cache_off + static_cast<int64_t>(t) * HV * TILE;
+        }
       } else if (table2d && p.pad == PLA_B200_PAD_VLLM && t < p.slot_cols) {
         const int step_slot = p.slot_indices[static_cast<int64_t>(n) * p.slot_row_stride + t];
-        if (step_slot > 0 && (p.num_slots <= 0 || step_slot < p.num_slots))
-          snap = static_cast<float*>(p.state) + static_cast<int64_t>(step_slot) * p.state_slot_stride +
-                 static_cast<int64_t>(hv) * TILE + row0 * D;
+        if (step_slot > 0 && (p.num_slots <= 0 || step_slot < p.num_slots)) {
+          snap_base = p.state;
+          snap_off = static_cast<int64_t>(step_slot) * p.state_slot_stride + static_cast<int64_t>(hv) * TILE + row0 * D;
+        }
       }
 
       // EAGLE tree: continue from the parent's snapshot instead of step t-1.
       // The snapshot rows were written by these same threads earlier in this
       // launch, so plain loads observe them without a fence.
-      const float* reload = nullptr;
-      if (p.parents != nullptr && t != 0 && cache_rows != nullptr) {
+      int64_t reload_off = -1;
+      if (p.parents != nullptr && t != 0 && cache_off >= 0) {
         const int64_t pi = static_cast<int64_t>(n) * p.parents_seq_stride + static_cast<int64_t>(t) * p.parents_tok_stride;
         const int64_t parent = p.parents_wide ? static_cast<const int64_t*>(p.parents)[pi]
                                               : static_cast<const int32_t*>(p.parents)[pi];
@@ -233,7 +316,7 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
           if (tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_BAD_PARENT);
           return;
         }
-        if (parent >= 0 && parent != t - 1) reload = cache_rows + parent * static_cast<int64_t>(HV) * TILE;
+        if (parent >= 0 && parent != t - 1) reload_off = cache_off + parent * static_cast<int64_t>(HV) * TILE;
       }
 
 #pragma unroll
@@ -243,8 +326,8 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
         float4 st[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          if (reload != nullptr)
-            st[i] = *reinterpret_cast<const float4*>(reload + row * D + (i * 8 + j) * 4);
+          if (reload_off >= 0)
+            st[i] = load_state4(p.cache, reload_off + row * D + (i * 8 + j) * 4, f32_state);
           else
             st[i] = srow[i * 8 + j];
         }
@@ -268,7 +351,7 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
           st[i].x += kk[i].x * vn; st[i].y += kk[i].y * vn; st[i].z += kk[i].z * vn; st[i].w += kk[i].w * vn;
           oacc += dot4(st[i], qq[i]);
           srow[i * 8 + j] = st[i];
-          if (snap != nullptr) *reinterpret_cast<float4*>(snap + row * D + (i * 8 + j) * 4) = st[i];
+          if (snap_base != nullptr) store_state4(snap_base, snap_off + row * D + (i * 8 + j) * 4, st[i], f32_state);
         }
         oacc += __shfl_xor_sync(0xffffffffu, oacc, 1);
         oacc += __shfl_xor_sync(0xffffffffu, oacc, 2);
@@ -284,13 +367,31 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
   }
 
   if (!p.disable_state_update) {
-    // generic-proxy writes to s_state -> visible to the bulk-copy engine
-    fence_async_smem();
-    __syncthreads();
-    if (tid == 0) {
-      bulk_store(g_tile, s_state, kBlockBytes);
-      bulk_commit();
-      bulk_wait_read<0>();  // shared memory must stay valid until the engine has read it
+    void* dst_base = p.state;
+    int64_t dst_off = in_off;
+    if (p.state_out != nullptr) {
+      const int64_t oslot = p.state_out_indices != nullptr ? p.state_out_indices[n] : n;
+      dst_base = p.state_out;
+      dst_off = oslot * p.state_out_slot_stride + tile_off;
+    }
+    if (bulk_io) {
+      // generic-proxy writes to s_state -> visible to the bulk-copy engine
+      fence_async_smem();
+      __syncthreads();
+      if (tid == 0) {
+        bulk_store(static_cast<float*>(dst_base) + dst_off, s_state, kBlockBytes);
+        bulk_commit();
+        bulk_wait_read<0>();  // shared memory must stay valid until the engine has read it
+      }
+    } else {
+      __syncthreads();
+      for (int i = tid; i < BV * D; i += NT) {
+        const int r = p.state_transposed ? (i % BV) : (i / D);
+        const int c = p.state_transposed ? (i / BV) : (i % D);
+        const int64_t e = dst_off + (p.state_transposed ? static_cast<int64_t>(c) * D + r : static_cast<int64_t>(r) * D + c);
+        if (f32_state) static_cast<float*>(dst_base)[e] = s_state[r * D + c];
+        else static_cast<__nv_bfloat16*>(dst_base)[e] = __float2bfloat16_rn(s_state[r * D + c]);
+      }
     }
   }
 }
@@ -306,7 +407,8 @@ int launch_one(const pla_b200_klast_args& a, cudaStream_t stream) {
     PLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     configured[dev] = true;
   }
-  const int64_t ctas = static_cast<int64_t>(a.B) * a.HV * (D / BV);
+  int64_t ctas = static_cast<int64_t>(a.B) * a.HV * (D / BV);
+  if (a.o_total_rows > 0) ctas += 64;  // CTAs that zero the padded output suffix
   PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "B*HV*(128/rows_per_cta) exceeds the grid limit");
   kern<<<static_cast<unsigned>(ctas), NT, L::kBytes, stream>>>(a);
   PLA_CUDA_OK(cudaGetLastError());
@@ -352,24 +454,24 @@ extern "C" int pla_b200_decode_klast(const pla_b200_klast_args* args, void* stre
               "HV must be a positive multiple of H, got H=%d, HV=%d", a.H, a.HV);
   PLA_REQUIRE(a.q && a.k && a.v && a.a && a.b && a.o && a.A_log && a.dt_bias, PLA_B200_E_INVALID,
               "q, k, v, a, b, o, A_log and dt_bias are required");
-  PLA_REQUIRE(a.state != nullptr && a.slot_indices != nullptr, PLA_B200_E_INVALID,
-              "the state pool and its slot indices are required");
+  PLA_REQUIRE((a.state != nullptr || a.state_init_zero) && (a.slot_indices != nullptr || a.state_by_request),
+              PLA_B200_E_INVALID, "the state pool and its slot indices are required");
+  PLA_REQUIRE(a.state != nullptr || a.state_out != nullptr || a.disable_state_update, PLA_B200_E_INVALID,
+              "a final state needs somewhere to go");
   PLA_REQUIRE(a.act_dtype == PLA_B200_BF16 || a.act_dtype == PLA_B200_F16, PLA_B200_E_INVALID,
               "activation dtype must be bf16 or fp16");
   PLA_REQUIRE(a.state_dtype == PLA_B200_F32 || a.state_dtype == PLA_B200_BF16, PLA_B200_E_INVALID,
               "state dtype must be fp32 or bf16");
-  PLA_REQUIRE(a.state_dtype == PLA_B200_F32, PLA_B200_E_UNSUPPORTED, "bf16 state pools are not built yet");
-  PLA_REQUIRE(a.state_slot_stride >= static_cast<int64_t>(a.HV) * 16384, PLA_B200_E_INVALID,
+  PLA_REQUIRE(a.state == nullptr || a.state_slot_stride >= static_cast<int64_t>(a.HV) * 16384, PLA_B200_E_INVALID,
               "state slot pitch must cover HV*128*128 elements");
-  PLA_REQUIRE(aligned16(a.state) && a.state_slot_stride % 4 == 0, PLA_B200_E_ALIGN,
+  PLA_REQUIRE(a.state == nullptr || (aligned16(a.state) && a.state_slot_stride % 4 == 0), PLA_B200_E_ALIGN,
               "state pool base and slot pitch must be 16-byte aligned");
+  PLA_REQUIRE(a.state_out == nullptr || (aligned16(a.state_out) && a.state_out_slot_stride % 4 == 0 &&
+                                         a.state_out_slot_stride >= static_cast<int64_t>(a.HV) * 16384),
+              PLA_B200_E_ALIGN, "final-state base and slot pitch must be 16-byte aligned and cover HV*128*128");
   PLA_REQUIRE(a.cache == nullptr || aligned16(a.cache), PLA_B200_E_ALIGN, "snapshot cache must be 16-byte aligned");
-  PLA_REQUIRE((reinterpret_cast<uintptr_t>(a.q) & 7) == 0 && (reinterpret_cast<uintptr_t>(a.k) & 7) == 0 &&
-                  a.q_tok_stride % 4 == 0 && a.k_tok_stride % 4 == 0,
-              PLA_B200_E_ALIGN, "q/k rows must be 8-byte aligned");
-  if (a.is_kda)
-    PLA_REQUIRE((reinterpret_cast<uintptr_t>(a.a) & 7) == 0 && a.a_tok_stride % 4 == 0, PLA_B200_E_ALIGN,
-                "KDA gate rows must be 8-byte aligned");
+  PLA_REQUIRE(a.o_total_rows == 0 || (reinterpret_cast<uintptr_t>(a.o) & 3) == 0, PLA_B200_E_ALIGN,
+              "o must be 4-byte aligned");
   PLA_REQUIRE(a.gate == PLA_B200_GATE_SOFTPLUS || (a.gate == PLA_B200_GATE_SAFE && a.is_kda), PLA_B200_E_INVALID,
               "lower_bound is only supported for KDA");
   PLA_REQUIRE(a.slot_row_stride == 0 || a.pad == PLA_B200_PAD_VLLM, PLA_B200_E_INVALID,
@@ -387,4 +489,16 @@ extern "C" int pla_b200_decode_klast(const pla_b200_klast_args* args, void* stre
   if (a.act_dtype == PLA_B200_BF16)
     return a.is_kda ? launch_shape<__nv_bfloat16, true>(a, s) : launch_shape<__nv_bfloat16, false>(a, s);
   return a.is_kda ? launch_shape<__half, true>(a, s) : launch_shape<__half, false>(a, s);
+}
+
+extern "C" int pla_b200_prefill_recurrent(const pla_b200_klast_args* args, void* stream) {
+  using namespace pla;
+  PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
+  PLA_REQUIRE(args->cu_seqlens != nullptr, PLA_B200_E_INVALID, "prefill needs cu_seqlens");
+  PLA_REQUIRE(args->slot_row_stride == 0 && args->cache == nullptr && args->parents == nullptr,
+              PLA_B200_E_INVALID, "prefill takes no snapshot cache, parent table or 2-D slot table");
+  pla_b200_klast_args a = *args;
+  if (a.rows_per_cta == 0 || a.rows_per_cta == 16) a.rows_per_cta = 32;  // most CTAs per sequence
+  if (a.t_max < 2) a.t_max = 2;                                         // always the multi-step kernel
+  return pla_b200_decode_klast(&a, stream);
 }

@@ -351,7 +351,11 @@ bool klast_stream_eligible(const pla_b200_klast_args& a) {
   const auto al4 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3) == 0; };
   return a.t_max == 1 && a.slot_row_stride == 0 && a.cache == nullptr && a.parents == nullptr &&
          !a.disable_state_update && a.state_dtype == PLA_B200_F32 && al4(a.v) && a.v_tok_stride % 2 == 0 &&
-         al4(a.o);
+         al4(a.o) && a.slot_indices != nullptr && a.state_out == nullptr && !a.state_init_zero &&
+         !a.state_transposed && !a.gate_activated && a.o_total_rows == 0 &&
+         (reinterpret_cast<uintptr_t>(a.q) & 7) == 0 && (reinterpret_cast<uintptr_t>(a.k) & 7) == 0 &&
+         a.q_tok_stride % 4 == 0 && a.k_tok_stride % 4 == 0 &&
+         (!a.is_kda || ((reinterpret_cast<uintptr_t>(a.a) & 7) == 0 && a.a_tok_stride % 4 == 0));
 }
 
 int launch_klast_stream(const pla_b200_klast_args& a, cudaStream_t stream) {

@@ -1,0 +1,160 @@
+// Host layer of the prefill ops: tensor contracts of
+//   pla.prefill.flashqla.chunk_gated_delta_rule_fwd / gdn_prefill_packed_qkv_fwd (pla/prefill/flashqla/ops.py:225-738)
+//   pla.prefill.flashkdapro.flashkda_fwd                                          (pla/prefill/flashkdapro/ops.py:66-219)
+// mapped onto the token-recurrent prefill entry of the C ABI. No sync, no D2H.
+#include "ops_common.h"
+
+namespace pla_ops {
+namespace {
+
+using Optional = std::optional<at::Tensor>;
+
+void rows_ok(const at::Tensor& t, int64_t heads, const char* name) {
+  TORCH_CHECK(t.dim() == 3 && t.size(1) == heads && t.size(2) == 128, name, " must be [tokens, heads, 128]");
+  TORCH_CHECK(t.stride(2) == 1 && t.stride(1) == 128, name, ": features inside one token must be contiguous");
+}
+
+void state_ok(const at::Tensor& t, int64_t H, const at::Tensor& ref, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.device() == ref.device(), name, " must be on q's device");
+  TORCH_CHECK(t.scalar_type() == at::kFloat || t.scalar_type() == at::kBFloat16, name, " must be fp32 or bf16");
+  TORCH_CHECK(t.dim() == 4 && t.size(1) == H && t.size(2) == 128 && t.size(3) == 128, name,
+              " must be [slots, H, 128, 128]");
+  TORCH_CHECK(t.stride(3) == 1 && t.stride(2) == 128 && t.stride(1) == 128 * 128 && t.stride(0) >= H * 16384, name,
+              ": the [H,128,128] block of a slot must be contiguous");
+}
+
+void prefill_recurrent(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& gate,
+                       const at::Tensor& beta, const Optional& A_log, const Optional& dt_bias, at::Tensor out,
+                       const at::Tensor& cu_seqlens, const Optional& state_in, const Optional& in_indices,
+                       const Optional& state_out, const Optional& out_indices, bool transposed, bool is_kda,
+                       bool normalize_qk, double scale, std::optional<double> lower_bound, bool gate_activated,
+                       bool update_in_place, const Optional& status) {
+  check_cuda(q, "q");
+  const int64_t T = q.size(0);
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3, "q, k, v must be [tokens, heads, 128]");
+  const int64_t Hg = k.size(1), H = v.size(1);
+  rows_ok(q, Hg, "q");
+  rows_ok(k, Hg, "k");
+  rows_ok(v, H, "v");
+  TORCH_CHECK(Hg > 0 && H % Hg == 0, "the value-head count must be a multiple of the q/k head count");
+  TORCH_CHECK(k.size(0) == T && v.size(0) == T, "q, k, v token counts must match");
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 || q.scalar_type() == at::kHalf, "q must be fp16 or bf16");
+  TORCH_CHECK(k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type() &&
+                  out.scalar_type() == q.scalar_type(),
+              "q, k, v and out must share a dtype");
+  TORCH_CHECK(out.is_contiguous() && out.numel() == T * H * 128, "out must be contiguous [tokens, H, 128]");
+  TORCH_CHECK(cu_seqlens.scalar_type() == at::kInt && cu_seqlens.dim() == 1 && cu_seqlens.is_contiguous() &&
+                  cu_seqlens.numel() >= 2 && cu_seqlens.device() == q.device(),
+              "cu_seqlens must be contiguous int32 [batch+1] on q's device");
+  const int64_t N = cu_seqlens.numel() - 1;
+  c10::cuda::CUDAGuard guard(q.device());
+
+  pla_b200_klast_args g{};
+  g.q = q.data_ptr();
+  g.k = k.data_ptr();
+  g.v = v.data_ptr();
+  g.o = out.data_ptr();
+  g.q_tok_stride = q.stride(0);
+  g.k_tok_stride = k.stride(0);
+  g.v_tok_stride = v.stride(0);
+  g.act_dtype = dtype_tag(q, "q");
+  const int64_t gate_w = is_kda ? H * 128 : H;
+  TORCH_CHECK(gate.size(0) == T && gate.numel() == T * gate_w && gate.stride(-1) == 1,
+              "gate must be [tokens, H] (GDN) or [tokens, H, 128] (KDA) with contiguous rows");
+  if (gate.dim() == 3) TORCH_CHECK(gate.stride(1) == 128, "KDA gate heads must be contiguous");
+  TORCH_CHECK(beta.dim() == 2 && beta.size(0) == T && beta.size(1) == H && beta.stride(1) == 1,
+              "beta must be [tokens, H] with contiguous heads");
+  if (gate_activated) {
+    TORCH_CHECK(gate.scalar_type() == at::kFloat && beta.scalar_type() == at::kFloat,
+                "activated gates (log-decay g, beta) must be fp32");
+  } else {
+    TORCH_CHECK(gate.scalar_type() == q.scalar_type() && beta.scalar_type() == q.scalar_type(),
+                "raw gate inputs must share q's dtype");
+    TORCH_CHECK(A_log.has_value() && dt_bias.has_value(), "raw gating needs A_log and dt_bias");
+    TORCH_CHECK(A_log->scalar_type() == at::kFloat && dt_bias->scalar_type() == at::kFloat && A_log->is_contiguous() &&
+                    dt_bias->is_contiguous() && A_log->numel() == H && dt_bias->numel() == gate_w,
+                "A_log [H] and dt_bias must be contiguous fp32");
+    g.A_log = A_log->data_ptr();
+    g.dt_bias = dt_bias->data_ptr();
+  }
+  if (gate_activated) {  // never read, but the entry insists on non-NULL pointers
+    g.A_log = gate.data_ptr();
+    g.dt_bias = gate.data_ptr();
+  }
+  g.A_log_dtype = PLA_B200_F32;
+  g.dt_bias_dtype = PLA_B200_F32;
+  g.a = gate.data_ptr();
+  g.b = beta.data_ptr();
+  g.a_tok_stride = gate.stride(0);
+  g.b_tok_stride = beta.stride(0);
+  g.gate_activated = gate_activated;
+
+  g.state_dtype = PLA_B200_F32;
+  if (state_in.has_value()) {
+    state_ok(*state_in, H, q, "initial state");
+    g.state = state_in->data_ptr();
+    g.state_slot_stride = state_in->stride(0);
+    g.num_slots = state_in->size(0);
+    g.state_dtype = dtype_tag(*state_in, "initial state");
+  } else {
+    g.state_init_zero = 1;
+  }
+  if (in_indices.has_value()) {
+    TORCH_CHECK(state_in.has_value(), "state indices need a state");
+    TORCH_CHECK(in_indices->scalar_type() == at::kInt && in_indices->is_contiguous() && in_indices->dim() == 1 &&
+                    in_indices->numel() == N && in_indices->device() == q.device(),
+                "state indices must be contiguous int32 [batch] on q's device");
+    g.slot_indices = in_indices->data_ptr<int32_t>();
+  } else {
+    g.state_by_request = 1;
+    if (state_in.has_value()) TORCH_CHECK(state_in->size(0) >= N, "the initial state needs one slot per sequence");
+  }
+  if (state_out.has_value()) {
+    state_ok(*state_out, H, q, "final state");
+    if (state_in.has_value())
+      TORCH_CHECK(state_out->scalar_type() == state_in->scalar_type(), "initial and final state dtypes must match");
+    g.state_out = state_out->data_ptr();
+    g.state_out_slot_stride = state_out->stride(0);
+    g.state_dtype = dtype_tag(*state_out, "final state");
+    if (out_indices.has_value()) {
+      TORCH_CHECK(out_indices->scalar_type() == at::kInt && out_indices->is_contiguous() && out_indices->numel() == N,
+                  "final-state indices must be contiguous int32 [batch]");
+      g.state_out_indices = out_indices->data_ptr<int32_t>();
+    } else {
+      TORCH_CHECK(state_out->size(0) >= N, "the final state needs one slot per sequence");
+    }
+  }
+  TORCH_CHECK(!(update_in_place && state_out.has_value()), "in-place update and a separate final state are exclusive");
+  TORCH_CHECK(!update_in_place || state_in.has_value(), "an in-place update needs the state pool");
+  g.disable_state_update = !(state_out.has_value() || update_in_place);
+  g.state_transposed = transposed;
+  g.cu_seqlens = cu_seqlens.data_ptr<int32_t>();
+  g.B = static_cast<int32_t>(N);
+  g.t_max = static_cast<int32_t>(std::max<int64_t>(T, 2));
+  g.H = static_cast<int32_t>(Hg);
+  g.HV = static_cast<int32_t>(H);
+  g.scale = static_cast<float>(scale);
+  g.softplus_beta = 1.0f;
+  g.softplus_threshold = 20.0f;
+  g.lower_bound = static_cast<float>(lower_bound.value_or(0.0));
+  g.gate = lower_bound.has_value() ? PLA_B200_GATE_SAFE : PLA_B200_GATE_SOFTPLUS;
+  TORCH_CHECK(!lower_bound.has_value() || is_kda, "lower_bound is only supported for KDA");
+  g.is_kda = is_kda;
+  g.use_qk_l2norm = normalize_qk;
+  g.pad = PLA_B200_PAD_SGLANG;
+  g.o_total_rows = T;
+  g.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
+  check_abi(pla_b200_prefill_recurrent(&g, stream_of(q)), "prefill");
+}
+
+}  // namespace
+}  // namespace pla_ops
+
+TORCH_LIBRARY_FRAGMENT(pla_b200, m) {
+  m.def(
+      "prefill_recurrent(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor? A_log, Tensor? dt_bias, "
+      "Tensor(a!) out, Tensor cu_seqlens, Tensor(b!)? state_in, Tensor? in_indices, Tensor(c!)? state_out, "
+      "Tensor? out_indices, bool transposed, bool is_kda, bool normalize_qk, float scale, float? lower_bound, "
+      "bool gate_activated, bool update_in_place, Tensor(d!)? status) -> ()",
+      &pla_ops::prefill_recurrent);
+}

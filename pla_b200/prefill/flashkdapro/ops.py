@@ -1,0 +1,89 @@
+"""KDA prefill entry point with the reference's signature (pla/prefill/flashkdapro/ops.py:66-219)."""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from ..._ops import ops
+
+DK = 128
+DV = 128
+
+
+def _rows(t: torch.Tensor) -> torch.Tensor:
+    """[tokens, H, 128] readable in place when one token's features are contiguous; else materialised."""
+    return t if (t.stride(2) == 1 and t.stride(1) == 128) else t.contiguous()
+
+
+def flashkda_fwd(
+    q: torch.Tensor,                       # [total_tokens, H, DK] bf16
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,                       # [total_tokens, H, DK] bf16 raw gate
+    beta: torch.Tensor,                    # [total_tokens, H] bf16 raw
+    A_log: torch.Tensor,                   # [H] fp32
+    dt_bias: torch.Tensor,                 # [H, DK] fp32
+    out: torch.Tensor,                     # [total_tokens, H, DV] bf16 (written)
+    scale: Optional[float] = None,
+    lower_bound: Optional[float] = -5.0,
+    initial_state: Optional[torch.Tensor] = None,   # [N, H, DV, DK]
+    final_state: Optional[torch.Tensor] = None,     # [N, H, DV, DK] (written)
+    cu_seqlens: Optional[torch.Tensor] = None,
+    state_pool: Optional[torch.Tensor] = None,      # [slots, H, DV, DK] (in place)
+    state_indices: Optional[torch.Tensor] = None,
+    raw_cu_seqlens: Optional[Tuple[int, ...]] = None,
+) -> None:
+    """KDA prefill over packed varlen tokens; writes ``out`` in full (rows past ``cu_seqlens[-1]``
+    zero) and ``final_state`` or the pool slots. The gate is the safe gate
+    ``lower_bound * sigmoid(exp(A_log) * (g + dt_bias))``; ``lower_bound=None`` (an extension)
+    selects ``-exp(A_log) * softplus(g + dt_bias)``. ``None`` initial state starts from zero.
+    """
+    if not q.is_cuda:
+        raise ValueError("q must be a CUDA tensor")
+    for name, t in (("k", k), ("v", v), ("g", g), ("beta", beta), ("A_log", A_log), ("dt_bias", dt_bias),
+                    ("out", out)):
+        if t.device != q.device:
+            raise ValueError(f"{name} must be on {q.device}, got {t.device}")
+    for name, t in (("initial_state", initial_state), ("final_state", final_state), ("cu_seqlens", cu_seqlens),
+                    ("state_pool", state_pool), ("state_indices", state_indices)):
+        if t is not None and t.device != q.device:
+            raise ValueError(f"{name} must be on {q.device}, got {t.device}")
+    in_idx = out_idx = None
+    in_place = False
+    if state_pool is not None:
+        if initial_state is not None or final_state is not None:
+            raise ValueError("state_pool is mutually exclusive with initial_state/final_state")
+        if state_indices is None:
+            raise ValueError("state_pool requires state_indices")
+        initial_state, in_idx, in_place = state_pool, state_indices, True
+    elif state_indices is not None:
+        if initial_state is None and final_state is None:
+            raise ValueError("state_indices requires state_pool, initial_state, or final_state")
+        in_idx = state_indices if initial_state is not None else None
+        out_idx = state_indices if final_state is not None else None
+    if initial_state is not None and final_state is not None and initial_state.dtype != final_state.dtype:
+        raise ValueError("initial_state and final_state dtypes must match")
+    if q.ndim != 3 or q.size(2) != DK:
+        raise ValueError("q must be [total_tokens, H, 128]")
+    T, H = q.size(0), q.size(1)
+    if scale is None:
+        scale = q.size(-1) ** -0.5
+    if cu_seqlens is None:
+        cu32 = torch.tensor(raw_cu_seqlens if raw_cu_seqlens is not None else (0, T), dtype=torch.int32,
+                            device=q.device)
+    else:
+        if cu_seqlens.dtype not in (torch.int32, torch.int64):
+            raise ValueError("cu_seqlens must be int32 or int64")
+        cu32 = cu_seqlens.to(torch.int32).contiguous()
+    if raw_cu_seqlens is not None and len(raw_cu_seqlens) != cu32.numel():
+        raise ValueError("raw_cu_seqlens must have N+1 entries")
+    if not out.is_contiguous() or tuple(out.shape) != (T, H, DV):
+        raise ValueError("out must be contiguous [total_tokens, H, DV]")
+    bet = beta if beta.stride(-1) == 1 else beta.contiguous()
+    gg = g if (g.stride(2) == 1 and g.stride(1) == 128) else g.contiguous()
+    ops.prefill_recurrent(
+        _rows(q), _rows(k), _rows(v), gg, bet, A_log.contiguous(), dt_bias.contiguous(), out, cu32,
+        initial_state, in_idx, None if in_place else final_state, out_idx, False, True, True, float(scale),
+        None if lower_bound is None else float(lower_bound), False, in_place, None)
+    return None

@@ -1,0 +1,195 @@
+"""GDN prefill entry points with the reference's signatures
+(pla/prefill/flashqla/ops.py:225-738).
+
+State contract: an indexed pool ``[slots, H, DV, DK]`` (k-last) with int32 ``initial_state_indices``
+is updated in place, even when ``output_final_state`` is false; the legacy layout
+``[N, H, DK, DV]`` is read (or a zero state assumed) and a new final state of that layout returned.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence, Tuple, Union
+
+import torch
+
+from ..._ops import ops
+
+DK = 128
+DV = 128
+CHUNK_SIZE = 64
+_STATE_DTYPES = (torch.float32, torch.bfloat16)
+
+
+def _offsets(cu_seqlens, num_tokens, raw_cu_seqlens, device):
+    if raw_cu_seqlens is not None:
+        if isinstance(raw_cu_seqlens, torch.Tensor):
+            if (raw_cu_seqlens.device.type != "cpu" or raw_cu_seqlens.ndim != 1
+                    or raw_cu_seqlens.dtype not in (torch.int32, torch.int64)):
+                raise ValueError("raw_cu_seqlens must be a 1-D CPU int32 or int64 tensor")
+            raw_cu_seqlens = raw_cu_seqlens.tolist()
+        raw_cu_seqlens = tuple(int(x) for x in raw_cu_seqlens)
+        if (len(raw_cu_seqlens) < 2 or raw_cu_seqlens[0] != 0 or raw_cu_seqlens[-1] > num_tokens
+                or any(b < a for a, b in zip(raw_cu_seqlens, raw_cu_seqlens[1:]))):
+            raise ValueError("raw_cu_seqlens must be monotonic offsets starting at zero within the token count")
+    if cu_seqlens is None:
+        if raw_cu_seqlens is None:
+            raw_cu_seqlens = (0, num_tokens)
+        cu_seqlens = torch.tensor(raw_cu_seqlens, dtype=torch.int32, device=device)
+    cu32 = cu_seqlens.to(device=device, dtype=torch.int32).contiguous()
+    if cu32.ndim != 1:
+        raise ValueError("cu_seqlens must be a rank-1 tensor")
+    if raw_cu_seqlens is not None and len(raw_cu_seqlens) != cu32.numel():
+        raise ValueError("raw_cu_seqlens must have batch+1 entries")
+    return cu32
+
+
+def chunk_gated_delta_rule_fwd(
+    q: torch.Tensor,                       # [1, T, Hg, DK]
+    k: torch.Tensor,                       # [1, T, Hg, DK]
+    v: torch.Tensor,                       # [1, T, H, DV]
+    g: Optional[torch.Tensor],             # [1, T, H] fp32 log gate
+    beta: Optional[torch.Tensor],          # [1, T, H] fp32 activated beta
+    scale: Optional[float] = None,
+    initial_state: Optional[torch.Tensor] = None,
+    initial_state_indices: Optional[torch.Tensor] = None,
+    cu_seqlens: Optional[torch.Tensor] = None,
+    output_final_state: bool = True,
+    auto_cp: bool = True,
+    overlap_warmup_threshold: Optional[float] = None,
+    force_tc01_cp_candidate: bool = False,
+    normalize_qk: bool = False,
+    raw_cu_seqlens: Optional[Union[Sequence[int], torch.Tensor]] = None,
+    raw_gate_a: Optional[torch.Tensor] = None,   # [T,H] 16-bit
+    raw_beta_b: Optional[torch.Tensor] = None,   # [T,H] 16-bit
+    A_log: Optional[torch.Tensor] = None,        # [H] fp32
+    dt_bias: Optional[torch.Tensor] = None,      # [H] fp32
+    final_state_dtype: Optional[torch.dtype] = None,
+) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor], torch.Tensor, None, Optional[torch.Tensor]]:
+    """Returns ``(g_cum, A, O, None, final_state)``.
+
+    ``O`` has the physical token shape; rows past ``cu_seqlens[-1]`` are zero and never touch the
+    state. With raw gating (``raw_gate_a``, ``raw_beta_b``, ``A_log``, ``dt_bias``) the gate
+    ``g = -exp(A_log) * softplus(a + dt_bias)`` and ``beta = sigmoid(b)`` are formed in the kernel.
+    The by-products ``g_cum`` / ``A`` of the reference's chunk pipeline are not produced by the
+    token-recurrent evaluation and are returned as ``None``; ``auto_cp``,
+    ``overlap_warmup_threshold`` and ``force_tc01_cp_candidate`` tune the reference's intra-card
+    planner and are accepted and ignored.
+    """
+    if not q.is_cuda:
+        raise ValueError("q must be a CUDA tensor")
+    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4 or q.size(0) != 1:
+        raise ValueError("q, k, v must be [1, T, heads, 128]")
+    raw = (raw_gate_a, raw_beta_b, A_log, dt_bias)
+    use_raw = any(t is not None for t in raw)
+    if use_raw and (any(t is None for t in raw) or g is not None or beta is not None):
+        raise ValueError("raw gating needs raw_gate_a, raw_beta_b, A_log and dt_bias, and excludes g/beta")
+    if not use_raw and (g is None or beta is None):
+        raise ValueError("g and beta are required without raw gating")
+    T, Hg, H = q.size(1), k.size(2), v.size(2)
+    if q.size(3) != DK or v.size(3) != DV:
+        raise ValueError("head dimensions must be 128")
+    if scale is None:
+        scale = q.size(-1) ** -0.5
+    cu32 = _offsets(cu_seqlens, T, raw_cu_seqlens, q.device)
+    batch = cu32.numel() - 1
+    indexed = initial_state_indices is not None
+    if indexed:
+        if initial_state is None or initial_state.dtype not in _STATE_DTYPES or not initial_state.is_contiguous():
+            raise ValueError("indexed initial_state must be contiguous fp32 or bf16")
+        if initial_state.ndim != 4 or tuple(initial_state.shape[1:]) != (H, DV, DK):
+            raise ValueError("indexed initial_state must be [num_slots,H,DV,DK]")
+        if (initial_state_indices.device != q.device or initial_state_indices.dtype != torch.int32
+                or not initial_state_indices.is_contiguous() or initial_state_indices.ndim != 1
+                or initial_state_indices.numel() != batch):
+            raise ValueError("initial_state_indices must be contiguous int32 [batch] on q.device")
+    elif initial_state is not None:
+        if initial_state.dtype not in _STATE_DTYPES or not initial_state.is_contiguous():
+            raise ValueError("initial_state must be contiguous fp32 or bf16")
+        if (initial_state.ndim != 4 or initial_state.size(0) < batch
+                or tuple(initial_state.shape[1:]) != (H, DK, DV)):
+            raise ValueError("initial_state must be [num_states>=batch,H,DK,DV]")
+    if final_state_dtype is None:
+        state_dtype = initial_state.dtype if initial_state is not None else torch.float32
+    else:
+        if final_state_dtype not in _STATE_DTYPES:
+            raise ValueError("final_state_dtype must be fp32 or bf16")
+        if initial_state is not None and final_state_dtype != initial_state.dtype:
+            raise ValueError("final_state_dtype must match the initial_state dtype")
+        state_dtype = final_state_dtype
+
+    o = torch.empty((1, T, H, DV), dtype=q.dtype, device=q.device)
+    if use_raw:
+        gate, bet = raw_gate_a.reshape(T, H) if raw_gate_a.ndim != 2 else raw_gate_a, \
+            raw_beta_b.reshape(T, H) if raw_beta_b.ndim != 2 else raw_beta_b
+    else:
+        gate, bet = g.reshape(T, H), beta.reshape(T, H)
+    final_state = None
+    state_out = None
+    if not indexed and output_final_state:
+        state_out = torch.empty((batch, H, DK, DV), dtype=state_dtype, device=q.device)
+        final_state = state_out
+    ops.prefill_recurrent(
+        q[0], k[0], v[0], gate, bet, A_log, dt_bias, o[0], cu32, initial_state,
+        initial_state_indices if indexed else None, state_out, None, not indexed, False, bool(normalize_qk),
+        float(scale), None, not use_raw, indexed, None)
+    if indexed and output_final_state:
+        final_state = initial_state[initial_state_indices.long()]
+    return None, None, o, None, final_state
+
+
+def gdn_prefill_packed_qkv_fwd(
+    packed_qkv: torch.Tensor,                # [T, 2*Hg*DK + H*DV]
+    raw_gate_a: torch.Tensor,                # [T,H]
+    raw_beta_b: torch.Tensor,                # [T,H]
+    A_log: torch.Tensor,                     # [H] fp32
+    dt_bias: torch.Tensor,                   # [H] fp32
+    cu_seqlens: torch.Tensor,                # [batch+1] int32
+    *,
+    num_qk_heads: int,
+    num_v_heads: int,
+    scale: Optional[float] = None,
+    initial_state: Optional[torch.Tensor] = None,
+    initial_state_indices: Optional[torch.Tensor] = None,
+    output_final_state: bool = True,
+    auto_cp: bool = True,
+    overlap_warmup_threshold: Optional[float] = None,
+    force_tc01_cp_candidate: bool = False,
+    raw_cu_seqlens: Optional[Union[Sequence[int], torch.Tensor]] = None,
+    final_state_dtype: Optional[torch.dtype] = None,
+):
+    """GDN prefill directly on a post-convolution ``[T, Q|K|V]`` buffer: features of one token are
+    contiguous, the token stride may exceed the row width and the view may start at any element
+    (Q/K/V are consumed in place as aliases of the buffer). Same return contract as
+    :func:`chunk_gated_delta_rule_fwd`."""
+    if not packed_qkv.is_cuda:
+        raise ValueError("packed_qkv must be a CUDA tensor")
+    if packed_qkv.ndim != 2:
+        raise ValueError("packed_qkv must be rank-2 [T,QKV]")
+    if packed_qkv.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("packed_qkv must be fp16 or bf16")
+    if packed_qkv.stride(1) != 1:
+        raise ValueError("packed_qkv features must be contiguous")
+    if num_qk_heads <= 0 or num_v_heads <= 0:
+        raise ValueError("num_qk_heads and num_v_heads must be positive")
+    T = packed_qkv.size(0)
+    if T == 0:
+        raise ValueError("GDN packed prefill does not support an empty token dimension")
+    Hg, H = int(num_qk_heads), int(num_v_heads)
+    qk_width = Hg * DK
+    width = 2 * qk_width + H * DV
+    if packed_qkv.size(1) != width:
+        raise ValueError(f"packed_qkv width must be {width} for H={H}, Hg={Hg}, got {packed_qkv.size(1)}")
+    pitch = packed_qkv.stride(0)
+    if pitch < width:
+        raise ValueError("packed_qkv token stride must cover the complete Q|K|V row")
+    off = packed_qkv.storage_offset()
+    batch_stride = max(T, 1) * pitch
+    q = packed_qkv.as_strided((1, T, Hg, DK), (batch_stride, pitch, DK, 1), off)
+    k = packed_qkv.as_strided((1, T, Hg, DK), (batch_stride, pitch, DK, 1), off + qk_width)
+    v = packed_qkv.as_strided((1, T, H, DV), (batch_stride, pitch, DV, 1), off + 2 * qk_width)
+    return chunk_gated_delta_rule_fwd(
+        q, k, v, None, None, scale=scale, initial_state=initial_state,
+        initial_state_indices=initial_state_indices, cu_seqlens=cu_seqlens,
+        output_final_state=output_final_state, auto_cp=auto_cp,
+        overlap_warmup_threshold=overlap_warmup_threshold, force_tc01_cp_candidate=force_tc01_cp_candidate,
+        normalize_qk=True, raw_cu_seqlens=raw_cu_seqlens, raw_gate_a=raw_gate_a, raw_beta_b=raw_beta_b,
+        A_log=A_log, dt_bias=dt_bias, final_state_dtype=final_state_dtype)

@@ -268,3 +268,66 @@ def plan_scenarios():
                                 blocked=variant in ("c0_owner", "duplicate_final", "boundary_source",
                                                     "reverse_source")))
     return out
+
+
+# --------------------------------------------------------------------------- prefill
+PREFILL_CASES = {
+    # name: (lengths, padded_tokens, Hg, H)
+    "gdn_two_seqs": ([97, 50], 3, 1, 2),
+    "gdn_chunk_edges": ([64, 1, 129], 0, 2, 4),
+}
+
+
+def gdn_prefill_case(name, device="cpu"):
+    """Packed varlen GDN prefill inputs: a [T, Q|K|V] buffer cut out of a wider one (row pitch
+    +64 elements, first column 17 -> rows are only 2-byte aligned), raw gates as two column
+    slices of one [T, 2H] buffer, fp32 A_log ~ U(0, log 16) and dt_bias ~ N(0, 0.1), an indexed
+    fp32 pool [16, H, DV, DK] ~ N(0, 0.02) with non-consecutive slots."""
+    lengths, pad, Hg, H = PREFILL_CASES[name]
+    rs = _rs(7300 + sum(map(ord, name)))
+    T = sum(lengths) + pad
+    width = 2 * Hg * D + H * D
+    storage = _t(rs, T, width + 64, dtype=torch.bfloat16).to(device)
+    packed = storage[:, 17:17 + width]
+    gates = _t(rs, T, 2 * H, dtype=torch.bfloat16).to(device)
+    A_log = torch.from_numpy(rs.uniform(0.0, np.log(16.0), H).astype(np.float32)).to(device)
+    dt_bias = _t(rs, H, dtype=torch.float32, scale=0.1).to(device)
+    pool = _t(rs, 16, H, D, D, dtype=torch.float32, scale=0.02).to(device)
+    slots = [11, 2, 7, 14][:len(lengths)]
+    cu = [0]
+    for n in lengths:
+        cu.append(cu[-1] + n)
+    return dict(packed=packed, storage=storage, a=gates[:, :H], b=gates[:, H:], A_log=A_log, dt_bias=dt_bias,
+                pool=pool, slots=slots, cu=cu, lengths=lengths, T=T, Hg=Hg, H=H)
+
+
+def gdn_prefill_oracle_kwargs(c):
+    """The case as ``oracle.decode.klast_forward`` keywords (token-level fp32 recurrence)."""
+    Hg, H = c["Hg"], c["H"]
+    p = c["packed"]
+    T = c["T"]
+    q = p[:, : Hg * D].reshape(T, Hg, D)
+    k = p[:, Hg * D: 2 * Hg * D].reshape(T, Hg, D)
+    v = p[:, 2 * Hg * D:].reshape(T, H, D)
+    return dict(q=q, k=k, v=v, a=c["a"], b=c["b"], A_log=c["A_log"], dt_bias=c["dt_bias"], state=c["pool"],
+                slot_indices=c["slots"], lengths=c["lengths"], scale=D ** -0.5, use_qk_l2norm=True)
+
+
+KDA_PREFILL_CASES = {"kda_two_seqs": ([70, 41], 2, 2), "kda_one_seq": ([130], 0, 1)}
+
+
+def kda_prefill_case(name, softplus=False, device="cpu"):
+    lengths, pad, H = KDA_PREFILL_CASES[name]
+    rs = _rs(8100 + sum(map(ord, name)))
+    T = sum(lengths) + pad
+    mk = lambda *s, sc=1.0: _t(rs, *s, dtype=torch.bfloat16, scale=sc).to(device)  # noqa: E731
+    q, k, v, g = mk(T, H, D), mk(T, H, D), mk(T, H, D), mk(T, H, D)
+    beta = mk(T, H)
+    A_log = _t(rs, H, dtype=torch.float32, scale=0.3).to(device)
+    dt_bias = _t(rs, H, D, dtype=torch.float32, scale=0.2).to(device)
+    init = _t(rs, len(lengths), H, D, D, dtype=torch.float32, scale=0.02).to(device)
+    cu = [0]
+    for n in lengths:
+        cu.append(cu[-1] + n)
+    return dict(q=q, k=k, v=v, g=g, beta=beta, A_log=A_log, dt_bias=dt_bias, init=init, cu=cu, lengths=lengths, T=T,
+                H=H, lower_bound=None if softplus else -5.0)

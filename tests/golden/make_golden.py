@@ -103,6 +103,60 @@ def make_replay():
     print("plans", len(plans))
 
 
+def make_prefill():
+    """GDN: the vendored chunked torch reference the reference's own prefill tests compare with
+    (scripts/prefill/flashqla/private/ref_gdr.py, chunk 64, called per sequence as in
+    tests/prefill_utils.py:272-283). KDA: naive_recurrent_kda with the gate helpers of
+    scripts/decode/_kda_reference.py."""
+    import importlib.util
+    sys.path.insert(0, str(REF / "scripts" / "prefill" / "flashqla"))
+    from private import ref_gdr
+    for name in cases.PREFILL_CASES:
+        c = cases.gdn_prefill_case(name)
+        kw = cases.gdn_prefill_oracle_kwargs(c)
+        q = kw["q"].float() * torch.rsqrt(kw["q"].float().square().sum(-1, keepdim=True) + 1e-6)
+        k = kw["k"].float() * torch.rsqrt(kw["k"].float().square().sum(-1, keepdim=True) + 1e-6)
+        g = -c["A_log"].exp() * F.softplus(c["a"].float() + c["dt_bias"])
+        beta = torch.sigmoid(c["b"].float())
+        outs, finals = [], []
+        for i, n in enumerate(c["lengths"]):
+            sl = slice(c["cu"][i], c["cu"][i + 1])
+            h0 = c["pool"][c["slots"][i]].transpose(-1, -2)[None].float()       # [1,H,DK,DV]
+            _, o_i, _, _, h_i = ref_gdr.chunk_gated_delta_rule_fwd(
+                q[None, sl], k[None, sl], kw["v"][None, sl].float(), g[None, sl], beta[None, sl],
+                cu_seqlens=torch.tensor([0, n]), initial_state=h0, chunk_size=64)
+            outs.append(o_i.reshape(n, c["H"], 128))
+            finals.append(h_i.reshape(c["H"], 128, 128).transpose(-1, -2))
+        np.savez_compressed(HERE / f"prefill_{name}.npz", out=torch.cat(outs).float().numpy(),
+                            final=cases.subsample(torch.stack(finals)))
+        print("prefill", name, torch.cat(outs).shape)
+    spec = importlib.util.spec_from_file_location("ref_kda", REF / "scripts" / "decode" / "_kda_reference.py")
+    kda = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(kda)
+    for name in cases.KDA_PREFILL_CASES:
+        for softplus in (False, True):
+            c = cases.kda_prefill_case(name, softplus=softplus)
+            if softplus:
+                g = kda.naive_kda_gate(c["g"], c["A_log"], c["dt_bias"])
+            else:
+                g = kda.naive_kda_lowerbound_gate(c["g"], c["A_log"], c["dt_bias"], lower_bound=-5.0)
+            qn = c["q"].float() * torch.rsqrt(c["q"].float().square().sum(-1, keepdim=True) + 1e-6)
+            kn = c["k"].float() * torch.rsqrt(c["k"].float().square().sum(-1, keepdim=True) + 1e-6)
+            outs, finals = [], []
+            for i, n in enumerate(c["lengths"]):
+                sl = slice(c["cu"][i], c["cu"][i + 1])
+                o_i, S = kda.naive_recurrent_kda(qn[None, sl], kn[None, sl], c["v"][None, sl].float(), g[None, sl],
+                                                 torch.sigmoid(c["beta"][None, sl].float()),
+                                                 initial_state=c["init"][i].transpose(-1, -2)[None],
+                                                 output_final_state=True)
+                outs.append(o_i[0])
+                finals.append(S[0].transpose(-1, -2))
+            tag = "softplus" if softplus else "safe"
+            np.savez_compressed(HERE / f"prefill_{name}_{tag}.npz", out=torch.cat(outs).float().numpy(),
+                                final=cases.subsample(torch.stack(finals)))
+            print("prefill", name, tag)
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     which = sys.argv[2] if len(sys.argv) > 2 else "all"
@@ -110,3 +164,5 @@ if __name__ == "__main__":
         make_klast()
     if which in ("all", "replay"):
         make_replay()
+    if which in ("all", "prefill"):
+        make_prefill()

@@ -1,0 +1,145 @@
+"""Prefill: CPU oracle against reference fixtures (not gpu), and the GPU ops against both (gpu)."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from helpers import assert_out_close, assert_state_close
+from oracle import decode as odec
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+D = 128
+
+
+def kda_oracle(c):
+    return odec.klast_forward(
+        q=c["q"], k=c["k"], v=c["v"], a=c["g"], b=c["beta"], A_log=c["A_log"], dt_bias=c["dt_bias"], state=c["init"],
+        slot_indices=list(range(len(c["lengths"]))), lengths=c["lengths"], scale=D ** -0.5, use_qk_l2norm=True,
+        is_kda=True, lower_bound=c["lower_bound"])
+
+
+@pytest.mark.parametrize("name", sorted(cases.PREFILL_CASES))
+def test_gdn_token_recurrence_matches_chunked_reference(name):
+    c = cases.gdn_prefill_case(name)
+    out, state, _ = odec.klast_forward(**cases.gdn_prefill_oracle_kwargs(c))
+    gold = np.load(GOLDEN / f"prefill_{name}.npz")
+    n_real = c["cu"][-1]
+    np.testing.assert_allclose(out[:n_real].float().numpy(), gold["out"], rtol=2e-2, atol=2e-3)
+    assert torch.count_nonzero(out[n_real:]) == 0
+    np.testing.assert_allclose(cases.subsample(state[c["slots"]]), gold["final"], rtol=1e-3, atol=1e-5)
+
+
+@pytest.mark.parametrize("softplus", [False, True])
+@pytest.mark.parametrize("name", sorted(cases.KDA_PREFILL_CASES))
+def test_kda_token_recurrence_matches_reference(name, softplus):
+    c = cases.kda_prefill_case(name, softplus=softplus)
+    out, state, _ = kda_oracle(c)
+    gold = np.load(GOLDEN / f"prefill_{name}_{'softplus' if softplus else 'safe'}.npz")
+    n_real = c["cu"][-1]
+    np.testing.assert_allclose(out[:n_real].float().numpy(), gold["out"], rtol=2e-2, atol=2e-3)
+    np.testing.assert_allclose(cases.subsample(state), gold["final"], rtol=1e-3, atol=1e-5)
+
+
+# ------------------------------------------------------------------------------------------ GPU
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(cases.PREFILL_CASES))
+def test_gdn_packed_prefill_indexed_pool(native_built, name):
+    from pla_b200.prefill.flashqla import gdn_prefill_packed_qkv_fwd
+    c = cases.gdn_prefill_case(name, device="cuda")
+    cpu = cases.gdn_prefill_case(name)
+    exp_out, exp_state, _ = odec.klast_forward(**cases.gdn_prefill_oracle_kwargs(cpu))
+    assert c["packed"].data_ptr() % 4 != 0          # rows are only 2-byte aligned
+    idx = torch.tensor(c["slots"], dtype=torch.int32, device="cuda")
+    cu = torch.tensor(c["cu"], dtype=torch.int32, device="cuda")
+    storage_before = c["storage"].clone()
+    g_cum, A, o, none, final = gdn_prefill_packed_qkv_fwd(
+        c["packed"], c["a"], c["b"], c["A_log"], c["dt_bias"], cu, num_qk_heads=c["Hg"], num_v_heads=c["H"],
+        initial_state=c["pool"], initial_state_indices=idx, raw_cu_seqlens=tuple(c["cu"]))
+    torch.cuda.synchronize()
+    assert none is None and o.shape == (1, c["T"], c["H"], D)
+    n_real = c["cu"][-1]
+    assert_out_close(o[0, :n_real], exp_out[:n_real])
+    assert torch.count_nonzero(o[0, n_real:]) == 0                       # padded suffix exactly zero
+    assert_state_close(c["pool"].cpu(), exp_state)
+    assert torch.equal(final, c["pool"][idx.long()])
+    for s in range(16):
+        if s not in c["slots"]:
+            assert torch.equal(c["pool"][s].cpu(), cpu["pool"][s])
+    assert torch.equal(c["storage"], storage_before)
+    gold = np.load(GOLDEN / f"prefill_{name}.npz")
+    assert_out_close(o[0, :n_real], torch.from_numpy(gold["out"]), "out vs chunked reference fixture")
+    assert_state_close(torch.from_numpy(cases.subsample(c["pool"][idx.long()].cpu())), torch.from_numpy(gold["final"]),
+                       "state vs chunked reference fixture")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("state_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("with_state", [False, True])
+def test_gdn_legacy_state_and_activated_gates(native_built, with_state, state_dtype):
+    """Legacy [N,H,DK,DV] state (transposed w.r.t. the pool), pre-activated fp32 g / beta, q/k already normalised."""
+    from pla_b200.prefill.flashqla import chunk_gated_delta_rule_fwd
+    cpu = cases.gdn_prefill_case("gdn_two_seqs")
+    kw = cases.gdn_prefill_oracle_kwargs(cpu)
+    T, H = cpu["T"], cpu["H"]
+    g = (-cpu["A_log"].exp() * torch.nn.functional.softplus(cpu["a"].float() + cpu["dt_bias"])).contiguous()
+    beta = torch.sigmoid(cpu["b"].float()).contiguous()
+    init = cpu["pool"][cpu["slots"]].to(state_dtype)                      # [N,H,DV,DK]
+    kw["q"] = torch.nn.functional.normalize(kw["q"].float(), dim=-1).bfloat16()
+    kw["k"] = torch.nn.functional.normalize(kw["k"].float(), dim=-1).bfloat16()
+    exp_out, exp_state, _ = odec.klast_forward(
+        q=kw["q"], k=kw["k"], v=kw["v"], a=cpu["a"], b=cpu["b"], A_log=cpu["A_log"], dt_bias=cpu["dt_bias"],
+        state=(init.float() if with_state else torch.zeros_like(init, dtype=torch.float32)),
+        slot_indices=[0, 1], lengths=cpu["lengths"], scale=D ** -0.5, use_qk_l2norm=False)
+    legacy = init.transpose(-1, -2).contiguous().cuda() if with_state else None
+    cu = torch.tensor(cpu["cu"], dtype=torch.int32, device="cuda")
+    _, _, o, _, final = chunk_gated_delta_rule_fwd(
+        kw["q"].contiguous().cuda()[None], kw["k"].contiguous().cuda()[None], kw["v"].contiguous().cuda()[None],
+        g.cuda()[None], beta.cuda()[None], initial_state=legacy, cu_seqlens=cu, final_state_dtype=state_dtype)
+    torch.cuda.synchronize()
+    n_real = cpu["cu"][-1]
+    assert_out_close(o[0, :n_real], exp_out[:n_real])
+    assert final.shape == (2, H, D, D) and final.dtype == state_dtype
+    assert_state_close(final.float().cpu().transpose(-1, -2), exp_state,
+                       tol=1e-3 if state_dtype == torch.float32 else 8e-3)
+    if with_state:
+        assert torch.equal(legacy.cpu(), init.transpose(-1, -2))         # the incoming legacy state is not modified
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("softplus", [False, True])
+@pytest.mark.parametrize("name", sorted(cases.KDA_PREFILL_CASES))
+def test_kda_prefill(native_built, name, softplus):
+    from pla_b200.prefill.flashkdapro import flashkda_fwd
+    cpu = cases.kda_prefill_case(name, softplus=softplus)
+    c = cases.kda_prefill_case(name, softplus=softplus, device="cuda")
+    exp_out, exp_state, _ = kda_oracle(cpu)
+    out = torch.full((c["T"], c["H"], D), 3.0, dtype=torch.bfloat16, device="cuda")
+    final = torch.empty_like(c["init"])
+    init_before = c["init"].clone()
+    flashkda_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"], c["A_log"], c["dt_bias"], out,
+                 lower_bound=c["lower_bound"], initial_state=c["init"], final_state=final,
+                 cu_seqlens=torch.tensor(c["cu"], dtype=torch.int64, device="cuda"))
+    torch.cuda.synchronize()
+    n_real = c["cu"][-1]
+    assert_out_close(out[:n_real], exp_out[:n_real])
+    assert torch.count_nonzero(out[n_real:]) == 0
+    assert_state_close(final.cpu(), exp_state)
+    assert torch.equal(c["init"], init_before)
+    gold = np.load(GOLDEN / f"prefill_{name}_{'softplus' if softplus else 'safe'}.npz")
+    assert_out_close(out[:n_real], torch.from_numpy(gold["out"]), "out vs reference fixture")
+    # pool form: in place, by slot
+    pool = torch.zeros(6, c["H"], D, D, device="cuda")
+    slots = torch.tensor([4, 1][:len(c["lengths"])], dtype=torch.int32, device="cuda")
+    pool[slots.long()] = c["init"]
+    out2 = torch.empty_like(out)
+    flashkda_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"], c["A_log"], c["dt_bias"], out2,
+                 lower_bound=c["lower_bound"], cu_seqlens=torch.tensor(c["cu"], dtype=torch.int32, device="cuda"),
+                 state_pool=pool, state_indices=slots)
+    torch.cuda.synchronize()
+    assert torch.equal(out2, out)
+    assert torch.equal(pool[slots.long()], final)
+    with pytest.raises(ValueError, match="mutually exclusive"):
+        flashkda_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"], c["A_log"], c["dt_bias"], out2, state_pool=pool,
+                     state_indices=slots, final_state=final)
