@@ -271,6 +271,23 @@ int pla_b200_kda_replay_plan(const pla_b200_kda_commit_args* args, void* stream)
 /* Plan, then fold + conv scatter of every layer in one more launch. */
 int pla_b200_kda_replay_commit(const pla_b200_kda_commit_args* args, void* stream);
 
+/* The commit plan for a caller that cannot allocate device memory. No counterpart in the
+ * reference: there the candidate buffer always comes from the framework's allocator.
+ *
+ * Same inputs, same `plan` output and same bit-exact semantics as pla_b200_kda_replay_plan, but
+ * `args->candidate` is ignored: the two plan phases exchange their candidates through a fixed
+ * 64 KiB array that lives inside the library on every GPU that loads it. Meant for runners that
+ * set their commit context up after all free device memory has been given to their cache pools,
+ * or from a place where their allocator may not be called.
+ *   - at most 4096 request rows (`capacity`); more returns PLA_B200_E_TOO_LARGE;
+ *   - the array is shared by all calls on a device and keeps the previous call's contents (each
+ *     call rewrites every entry it reads, so nothing needs clearing); calls that overlap on the
+ *     GPU without a stream / event dependency between them race on it;
+ *   - the first call on each device looks up the array's device address, so issue it before any
+ *     stream capture starts;
+ *   - it never calls cudaMalloc / cudaFree or any allocating routine. */
+int pla_b200_kda_replay_plan_static(const pla_b200_kda_commit_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

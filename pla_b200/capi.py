@@ -36,7 +36,7 @@ def load() -> ctypes.CDLL:
         raise ImportError(f"{LIB_PATH} is not built; run `python -m pla_b200.build`")
     lib = ctypes.CDLL(str(LIB_PATH))
     lib.pla_b200_last_error.restype = ctypes.c_char_p
-    for name in ("pla_b200_kda_replay_plan", "pla_b200_kda_replay_commit"):
+    for name in ("pla_b200_kda_replay_plan", "pla_b200_kda_replay_commit", "pla_b200_kda_replay_plan_static"):
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [ctypes.POINTER(KdaCommitArgs), ctypes.c_void_p]

@@ -265,10 +265,6 @@ __global__ void __launch_bounds__(NT) kda_verify_kernel(const pla_b200_kda_verif
 }
 
 // -------------------------------------------------------------------- plan
-struct PlanView {
-  pla_b200_kda_commit_args a;
-};
-
 __device__ __forceinline__ bool valid_slot(int64_t slot, const pla_b200_kda_commit_args& p) {
   return slot > p.null_block_id && slot >= 0 && slot < p.slots;
 }
@@ -589,4 +585,53 @@ extern "C" int pla_b200_kda_replay_commit(const pla_b200_kda_commit_args* args, 
   fold_scatter_kernel<<<static_cast<unsigned>(total), NT, sizeof(Smem), s>>>(a, g);
   PLA_CUDA_OK(cudaGetLastError());
   return PLA_B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Commit plan for callers that must not allocate.
+//
+// The plan is built in two phases (candidates, then conflict masking) and the phases talk through a
+// [4, capacity] int32 candidate buffer that a KDAReplayCommitContext normally allocates when it is
+// created. A runner that builds its context late -- after it has handed every free byte of the
+// device to its cache pools, or inside a region where its allocator is frozen -- has nowhere to get
+// that buffer from. For it the library carries the buffer itself: a fixed array in device memory
+// that exists on every GPU that loads the library, for as long as the process lives.
+//
+// Limit: kStaticPlanRows request rows (64 KiB per GPU). Larger capacities are refused.
+// Sharing: every call on a device uses the SAME array. Calls are safe back to back on one stream;
+// two calls that overlap on the GPU (different streams, no dependency) race on it. Nothing has to be
+// cleared between calls: the first phase rewrites all 4 * capacity entries it later reads.
+// First call per device: looks up the array's device address (no allocation, but a runtime call
+// that is not a stream operation), so make that call before any stream capture begins.
+namespace pla {
+namespace {
+constexpr int kStaticPlanRows = 4096;
+static __device__ __align__(256) int32_t g_plan_candidates[4 * kStaticPlanRows];
+}  // namespace
+}  // namespace pla
+
+extern "C" int pla_b200_kda_replay_plan_static(const pla_b200_kda_commit_args* args, void* stream) {
+  using namespace pla;
+  PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
+  PLA_REQUIRE(args->capacity <= kStaticPlanRows, PLA_B200_E_TOO_LARGE,
+              "plan capacity %d exceeds the %d rows of the built-in candidate buffer; use "
+              "pla_b200_kda_replay_plan with a caller-provided buffer",
+              args->capacity, kStaticPlanRows);
+  // In host code the array's name is only a handle; the kernel needs the address the symbol has on
+  // the CURRENT device, looked up once per device.
+  static int32_t* device_address[64] = {};
+  int dev = 0;
+  PLA_CUDA_OK(cudaGetDevice(&dev));
+  PLA_REQUIRE(dev >= 0 && dev < 64, PLA_B200_E_INVALID, "device ordinal %d out of range", dev);
+  if (device_address[dev] == nullptr) {
+    void* ptr = nullptr;
+    PLA_CUDA_OK(cudaGetSymbolAddress(&ptr, g_plan_candidates));
+    PLA_REQUIRE(ptr != nullptr, PLA_B200_E_CUDA, "the built-in candidate buffer has no device address");
+    device_address[dev] = static_cast<int32_t*>(ptr);
+  }
+  pla_b200_kda_commit_args a = *args;
+  a.candidate = device_address[dev];
+  const int rc = check_commit(a);
+  if (rc != PLA_B200_OK) return rc;
+  return launch_plan(a, static_cast<cudaStream_t>(stream));
 }
