@@ -310,9 +310,102 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def _time_steps(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_prefill(args):
+    """Secondary line (not the headline metric): config 3, GDN packed varlen prefill, 8 sequences with
+    lengths ~U[512, 8192], Hqk=16, HV=32, indexed fp32 pool; Mtok/s on one GPU."""
+    from pla_b200.prefill.flashqla import gdn_prefill_packed_qkv_fwd
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(20261125 + 3)
+    lengths = torch.randint(512, 8193, (8,), generator=g).tolist()
+    T = sum(lengths)
+    width = 2 * HQK * D + HV * D
+    storage = torch.empty(T, width + 64, dtype=torch.bfloat16, device=dev)
+    packed = storage[:, 17:17 + width]
+    gd = torch.Generator(device=dev).manual_seed(5)
+    packed.normal_(0.0, 1.0, generator=gd)
+    for lo in (0, HQK * D):   # q, k L2-normalised per head, as in config 0
+        blk = packed[:, lo:lo + HQK * D].float().view(T, HQK, D)
+        packed[:, lo:lo + HQK * D] = torch.nn.functional.normalize(blk, dim=-1).view(T, HQK * D).bfloat16()
+    gates = torch.randn(T, 2 * HV, generator=g).bfloat16().to(dev)
+    A_log = (torch.rand(HV, generator=g) * math.log(16.0)).to(dev)
+    dt_bias = (torch.randn(HV, generator=g) * 0.1).to(dev)
+    pool = (torch.randn(16, HV, D, D, generator=g) * 0.02).to(dev)
+    idx = torch.tensor([1, 3, 5, 7, 9, 11, 13, 15], dtype=torch.int32, device=dev)
+    offs = [0]
+    for n in lengths:
+        offs.append(offs[-1] + n)
+    cu = torch.tensor(offs, dtype=torch.int32, device=dev)
+
+    def step():
+        gdn_prefill_packed_qkv_fwd(packed, gates[:, :HV], gates[:, HV:], A_log, dt_bias, cu, num_qk_heads=HQK,
+                                   num_v_heads=HV, initial_state=pool, initial_state_indices=idx,
+                                   output_final_state=False, raw_cu_seqlens=tuple(offs))
+
+    ms = _time_steps(step, args.steps, max(args.warmup, 3))
+    flops = T * (HV * 133803 + HQK * 32768)
+    print(json.dumps({"metric": "gdn_prefill_throughput_32K_varlen", "value": round(T / ms / 1e3, 3), "unit": "Mtok/s",
+                      "n_gpus": 1, "steps": args.steps, "ms_per_step": round(ms, 4), "higher_is_better": True,
+                      "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": f"config3: 8 sequences {lengths}, T={T}, Hqk=16 HV=32, token-recurrent",
+                                 "chunk_equivalent_tflops": round(flops / ms / 1e9, 2)}}), flush=True)
+
+
+def run_replay(args):
+    """Secondary line: config 2, KDA ReplaySSM verify + commit, 32 heads, 64 rows x 4 tokens, 512 pages."""
+    import numpy as np
+    sys.path.insert(0, str(ROOT / "tests" / "golden"))
+    import cases
+    from pla_b200.decode.kda_replayssm_vllm import KDAReplayCommitContext, KDAReplayRecords, kda_replay_verify
+    H, N, Q, pages = 32, 64, 4, 512
+    rs = np.random.RandomState(20261125 + 2)
+    layer = cases.replay_layer(rs, pages, H, Q, "SD", device="cuda")
+    x = cases.replay_inputs(rs, H, N * Q, device="cuda")
+    layer.replay_records = KDAReplayRecords.allocate(N, H, Q, "cuda")
+    slots = torch.tensor((rs.permutation(pages - 1)[:N] + 1).astype("int32"), device="cuda")
+    cu = torch.arange(0, N * Q + 1, Q, dtype=torch.int32, device="cuda")
+    sampled = torch.tensor(rs.randint(1, Q + 1, N).astype("int32"), device="cuda")
+    out = torch.empty(N * Q, H * D, dtype=torch.bfloat16, device="cuda")
+    ctx = KDAReplayCommitContext.create([layer], Q, N, conv_state_layout="SD")
+    kw = {k_: v_ for k_, v_ in x.items() if k_ != "storage"}
+
+    def verify():
+        kda_replay_verify(**kw, conv_state=layer.kv_cache[0], checkpoint_state=layer.kv_cache[1],
+                          records=layer.replay_records, query_start_loc=cu, state_indices=slots,
+                          conv_state_layout="SD", out=out)
+
+    def commit():
+        ctx.commit(sampled, slots, cu, token_capacity=N * Q)
+
+    ms_v = _time_steps(verify, args.steps, max(args.warmup, 3))
+    ms_c = _time_steps(commit, args.steps, max(args.warmup, 3))
+    state_v, state_c = N * H * TILE_BYTES, 2 * N * H * TILE_BYTES
+    print(json.dumps({"metric": "kda_replay_verify_commit_state_bandwidth", "unit": "GB/s",
+                      "value": round((state_v + state_c) / ((ms_v + ms_c) * 1e-3) / 1e9, 1),
+                      "n_gpus": 1, "steps": args.steps, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "config2: H=32, 64 rows x 4 tokens, 512 pages, accepted ~U{1..4}",
+                                 "verify_ms": round(ms_v, 4), "commit_ms": round(ms_c, 4),
+                                 "verify_GBps": round(state_v / ms_v / 1e6, 1),
+                                 "commit_GBps": round(state_c / ms_c / 1e6, 1)}}), flush=True)
+
+
 def main():
     global B, SLOTS, WORKLOAD
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "replay"],
+                    help="decode = the headline metric; prefill / replay print secondary lines (1 GPU)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=10)
@@ -325,6 +418,11 @@ def main():
     if (args.batch, args.slots) != (B, SLOTS):
         B, SLOTS = args.batch, args.slots
         WORKLOAD = f"REDUCED (not the headline): GDN decode B={B} Hqk=16 HV=32 d=128, fp32 k-last pool {SLOTS} slots"
+    if args.workload != "decode":
+        if int(os.environ.get("RANK", 0)) == 0:
+            args.steps = min(args.steps, 50)
+            (run_prefill if args.workload == "prefill" else run_replay)(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:
