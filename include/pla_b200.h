@@ -169,6 +169,59 @@ typedef struct pla_b200_vlast_args {
 int pla_b200_decode_vlast(const pla_b200_vlast_args* args, void* stream);
 
 /* ======================================================================== *
+ * Chunked GDN prefill (chunk 64, WY/UT transform) on the tcgen05 tensor cores.
+ * Replaces the stage chain chunk_local_cumsum_qk_norm_gated -> kkt_solve -> fused_fwd behind
+ * pla.prefill.flashqla.chunk_gated_delta_rule_fwd (pla/prefill/flashqla/ops.py:501-642,
+ * src/prefill/flashqla/host/torch_extension_cute.cc:253, :546, :1008).
+ * Two launches: "prepare" (per chunk and q/k head: normalised K/Q operands, K K^T and Q K^T on the
+ * tensor cores, gate cumsum, the unit-lower-triangular inverse) writes operand images into
+ * `workspace`; "chain" (per sequence and value head) walks the chunks with the state resident in
+ * tensor memory. q/k/v/gate rows may be only 2-byte aligned. State arguments as in
+ * pla_b200_klast_args' prefill extensions.
+ * ======================================================================== */
+typedef struct pla_b200_gdn_chunk_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  int64_t q_tok_stride, k_tok_stride, v_tok_stride;
+  int32_t act_dtype;       /* BF16 or F16 */
+  int32_t gate_activated;  /* 0: gate/beta are raw 16-bit logits; 1: fp32 log-decay and fp32 beta */
+  const void* gate;        /* [T, HV] */
+  const void* beta;        /* [T, HV] */
+  int64_t gate_tok_stride, beta_tok_stride;
+  const float* A_log;      /* [HV] (raw gating) */
+  const float* dt_bias;    /* [HV] (raw gating) */
+  void* o;                 /* [T, HV, 128] dense, activation dtype; rows >= cu_seqlens[N] are zeroed */
+  float* g_cum;            /* optional [T, HV]: chunk-local cumulative log decay */
+  void* state;             /* initial state pool or NULL with state_init_zero */
+  int32_t state_dtype;     /* F32 or BF16 */
+  int32_t state_init_zero;
+  int32_t state_transposed;   /* slots hold [K,V] instead of [V,K] */
+  int32_t state_by_request;   /* slot_indices may be NULL: sequence n uses slot n */
+  int64_t state_slot_stride;
+  int64_t num_slots;
+  const int32_t* slot_indices;
+  void* state_out;            /* NULL: final state goes back into `state` (when write_state) */
+  int64_t state_out_slot_stride;
+  const int32_t* state_out_indices;
+  int32_t write_state;
+  int32_t N;                  /* sequences */
+  const int32_t* cu_seqlens;  /* [N+1] device */
+  int64_t T_total;            /* physical token rows of q/k/v/o */
+  int32_t max_chunks;         /* upper bound on sum_n ceil(len_n / 64), e.g. T_total/64 + N */
+  int32_t H, HV;
+  float scale;
+  int32_t normalize_qk;
+  int32_t stage;              /* 0: prepare + chain; 1: prepare only (tests) */
+  void* workspace;            /* device scratch of pla_b200_gdn_chunk_workspace_bytes() bytes, 128-byte aligned */
+  int64_t workspace_bytes;
+  int32_t* status;
+} pla_b200_gdn_chunk_args;
+
+int64_t pla_b200_gdn_chunk_workspace_bytes(int32_t max_chunks, int32_t H, int32_t HV);
+int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args, void* stream);
+
+/* ======================================================================== *
  * KDA ReplaySSM: verify (read-only checkpoint, replay records out) and commit
  * (integer plan, exact fold of the accepted prefix, conv-window scatter).
  * Replaces launch_verify_native / launch_commit_plan / launch_fold_native /

@@ -147,10 +147,138 @@ void prefill_recurrent(const at::Tensor& q, const at::Tensor& k, const at::Tenso
   check_abi(pla_b200_prefill_recurrent(&g, stream_of(q)), "prefill");
 }
 
+// Chunked (chunk 64) GDN prefill on the tensor cores. Returns the scratch workspace it allocated
+// from the caching allocator (callers normally drop it; tests inspect the operand images).
+at::Tensor gdn_prefill_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& gate,
+                               const at::Tensor& beta, const Optional& A_log, const Optional& dt_bias, at::Tensor out,
+                               const Optional& g_cum, const at::Tensor& cu_seqlens, const Optional& state_in,
+                               const Optional& in_indices, const Optional& state_out, const Optional& out_indices,
+                               bool transposed, bool normalize_qk, double scale, bool gate_activated,
+                               bool update_in_place, int64_t max_chunks, int64_t stage, const Optional& status) {
+  check_cuda(q, "q");
+  const int64_t T = q.size(0);
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3, "q, k, v must be [tokens, heads, 128]");
+  const int64_t Hg = k.size(1), H = v.size(1);
+  rows_ok(q, Hg, "q");
+  rows_ok(k, Hg, "k");
+  rows_ok(v, H, "v");
+  TORCH_CHECK(Hg > 0 && H % Hg == 0, "the value-head count must be a multiple of the q/k head count");
+  TORCH_CHECK(k.size(0) == T && v.size(0) == T, "q, k, v token counts must match");
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 || q.scalar_type() == at::kHalf, "q must be fp16 or bf16");
+  TORCH_CHECK(k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type() &&
+                  out.scalar_type() == q.scalar_type(),
+              "q, k, v and out must share a dtype");
+  TORCH_CHECK(out.is_contiguous() && out.numel() == T * H * 128, "out must be contiguous [tokens, H, 128]");
+  TORCH_CHECK(cu_seqlens.scalar_type() == at::kInt && cu_seqlens.dim() == 1 && cu_seqlens.is_contiguous() &&
+                  cu_seqlens.numel() >= 2 && cu_seqlens.device() == q.device(),
+              "cu_seqlens must be contiguous int32 [batch+1] on q's device");
+  const int64_t N = cu_seqlens.numel() - 1;
+  TORCH_CHECK(max_chunks >= 0 && max_chunks <= T / 64 + N, "max_chunks out of range");
+  c10::cuda::CUDAGuard guard(q.device());
+
+  pla_b200_gdn_chunk_args g{};
+  g.q = q.data_ptr();
+  g.k = k.data_ptr();
+  g.v = v.data_ptr();
+  g.o = out.data_ptr();
+  g.q_tok_stride = q.stride(0);
+  g.k_tok_stride = k.stride(0);
+  g.v_tok_stride = v.stride(0);
+  g.act_dtype = dtype_tag(q, "q");
+  TORCH_CHECK(gate.dim() == 2 && gate.size(0) == T && gate.size(1) == H && gate.stride(1) == 1,
+              "gate must be [tokens, H] with contiguous heads");
+  TORCH_CHECK(beta.dim() == 2 && beta.size(0) == T && beta.size(1) == H && beta.stride(1) == 1,
+              "beta must be [tokens, H] with contiguous heads");
+  if (gate_activated) {
+    TORCH_CHECK(gate.scalar_type() == at::kFloat && beta.scalar_type() == at::kFloat,
+                "activated gates (log-decay g, beta) must be fp32");
+  } else {
+    TORCH_CHECK(gate.scalar_type() == q.scalar_type() && beta.scalar_type() == q.scalar_type(),
+                "raw gate inputs must share q's dtype");
+    TORCH_CHECK(A_log.has_value() && dt_bias.has_value(), "raw gating needs A_log and dt_bias");
+    TORCH_CHECK(A_log->scalar_type() == at::kFloat && dt_bias->scalar_type() == at::kFloat && A_log->is_contiguous() &&
+                    dt_bias->is_contiguous() && A_log->numel() == H && dt_bias->numel() == H,
+                "A_log [H] and dt_bias [H] must be contiguous fp32");
+    g.A_log = A_log->data_ptr<float>();
+    g.dt_bias = dt_bias->data_ptr<float>();
+  }
+  g.gate = gate.data_ptr();
+  g.beta = beta.data_ptr();
+  g.gate_tok_stride = gate.stride(0);
+  g.beta_tok_stride = beta.stride(0);
+  g.gate_activated = gate_activated;
+  if (g_cum.has_value()) {
+    TORCH_CHECK(g_cum->scalar_type() == at::kFloat && g_cum->is_contiguous() && g_cum->numel() == T * H,
+                "g_cum must be contiguous fp32 [tokens, H]");
+    g.g_cum = g_cum->data_ptr<float>();
+  }
+  g.state_dtype = PLA_B200_F32;
+  if (state_in.has_value()) {
+    state_ok(*state_in, H, q, "initial state");
+    g.state = state_in->data_ptr();
+    g.state_slot_stride = state_in->stride(0);
+    g.num_slots = state_in->size(0);
+    g.state_dtype = dtype_tag(*state_in, "initial state");
+  } else {
+    g.state_init_zero = 1;
+  }
+  if (in_indices.has_value()) {
+    TORCH_CHECK(state_in.has_value(), "state indices need a state");
+    TORCH_CHECK(in_indices->scalar_type() == at::kInt && in_indices->is_contiguous() && in_indices->dim() == 1 &&
+                    in_indices->numel() == N && in_indices->device() == q.device(),
+                "state indices must be contiguous int32 [batch] on q's device");
+    g.slot_indices = in_indices->data_ptr<int32_t>();
+  } else {
+    g.state_by_request = 1;
+    if (state_in.has_value()) TORCH_CHECK(state_in->size(0) >= N, "the initial state needs one slot per sequence");
+  }
+  if (state_out.has_value()) {
+    state_ok(*state_out, H, q, "final state");
+    if (state_in.has_value())
+      TORCH_CHECK(state_out->scalar_type() == state_in->scalar_type(), "initial and final state dtypes must match");
+    g.state_out = state_out->data_ptr();
+    g.state_out_slot_stride = state_out->stride(0);
+    g.state_dtype = dtype_tag(*state_out, "final state");
+    if (out_indices.has_value()) {
+      TORCH_CHECK(out_indices->scalar_type() == at::kInt && out_indices->is_contiguous() && out_indices->numel() == N,
+                  "final-state indices must be contiguous int32 [batch]");
+      g.state_out_indices = out_indices->data_ptr<int32_t>();
+    } else {
+      TORCH_CHECK(state_out->size(0) >= N, "the final state needs one slot per sequence");
+    }
+  }
+  TORCH_CHECK(!(update_in_place && state_out.has_value()), "in-place update and a separate final state are exclusive");
+  TORCH_CHECK(!update_in_place || state_in.has_value(), "an in-place update needs the state pool");
+  g.write_state = state_out.has_value() || update_in_place;
+  g.state_transposed = transposed;
+  g.cu_seqlens = cu_seqlens.data_ptr<int32_t>();
+  g.N = static_cast<int32_t>(N);
+  g.T_total = T;
+  g.max_chunks = static_cast<int32_t>(max_chunks);
+  g.H = static_cast<int32_t>(Hg);
+  g.HV = static_cast<int32_t>(H);
+  g.scale = static_cast<float>(scale);
+  g.normalize_qk = normalize_qk;
+  g.stage = static_cast<int32_t>(stage);
+  const int64_t bytes = pla_b200_gdn_chunk_workspace_bytes(g.max_chunks, g.H, g.HV);
+  at::Tensor workspace = at::empty({std::max<int64_t>(bytes, 16)}, q.options().dtype(at::kByte));
+  g.workspace = workspace.data_ptr();
+  g.workspace_bytes = bytes;
+  g.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
+  check_abi(pla_b200_gdn_prefill_chunked(&g, stream_of(q)), "gdn chunked prefill");
+  return workspace;
+}
+
 }  // namespace
 }  // namespace pla_ops
 
 TORCH_LIBRARY_FRAGMENT(pla_b200, m) {
+  m.def(
+      "gdn_prefill_chunked(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor? A_log, Tensor? dt_bias, "
+      "Tensor(a!) out, Tensor(e!)? g_cum, Tensor cu_seqlens, Tensor(b!)? state_in, Tensor? in_indices, "
+      "Tensor(c!)? state_out, Tensor? out_indices, bool transposed, bool normalize_qk, float scale, "
+      "bool gate_activated, bool update_in_place, int max_chunks, int stage, Tensor(d!)? status) -> Tensor",
+      &pla_ops::gdn_prefill_chunked);
   m.def(
       "prefill_recurrent(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor? A_log, Tensor? dt_bias, "
       "Tensor(a!) out, Tensor cu_seqlens, Tensor(b!)? state_in, Tensor? in_indices, Tensor(c!)? state_out, "

@@ -28,7 +28,7 @@ def test_null_args_are_rejected_without_a_gpu(native_built):
     lib = ctypes.CDLL(str(build.NATIVE_LIB))
     lib.pla_b200_last_error.restype = ctypes.c_char_p
     for name in declared_symbols():
-        if name in ("pla_b200_last_error", "pla_b200_abi_version"):
+        if name in ("pla_b200_last_error", "pla_b200_abi_version") or name.endswith("_bytes"):
             continue
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int

@@ -1,0 +1,95 @@
+"""Chunked (chunk 64) tensor-core GDN prefill: the prepare stage's operand images against fp32 torch,
+and the whole op against the CPU oracle and the chunked reference fixtures."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from helpers import assert_out_close, assert_state_close
+from oracle import decode as odec
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+D, C = 128, 64
+KQ_BYTES, KNT_BYTES, TM_BYTES, PM_BYTES, VEC_BYTES = 128 * 128 * 4, 128 * 64 * 4, 64 * 64 * 4, 64 * 64 * 4, 512
+HBLOB, VBLOB = KQ_BYTES + KNT_BYTES, TM_BYTES + PM_BYTES + VEC_BYTES
+
+
+def image_to_tile(img, rows, kdim):
+    """Operand image [K/4][rows][4] -> [rows, K]."""
+    return img.view(kdim // 4, rows, 4).permute(1, 0, 2).reshape(rows, kdim)
+
+
+def run_op(c, stage, state=True):
+    from pla_b200._ops import ops
+    Hg, H, T = c["Hg"], c["H"], c["T"]
+    p = c["packed"]
+    q = p.as_strided((T, Hg, D), (p.stride(0), D, 1), p.storage_offset())
+    k = p.as_strided((T, Hg, D), (p.stride(0), D, 1), p.storage_offset() + Hg * D)
+    v = p.as_strided((T, H, D), (p.stride(0), D, 1), p.storage_offset() + 2 * Hg * D)
+    out = torch.full((T, H, D), 7.0, dtype=torch.bfloat16, device="cuda")
+    g_cum = torch.zeros(T, H, device="cuda")
+    cu = torch.tensor(c["cu"], dtype=torch.int32, device="cuda")
+    idx = torch.tensor(c["slots"], dtype=torch.int32, device="cuda")
+    max_chunks = sum((n + C - 1) // C for n in c["lengths"])
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ws = ops.gdn_prefill_chunked(q, k, v, c["a"], c["b"], c["A_log"], c["dt_bias"], out, g_cum, cu,
+                                 c["pool"] if state else None, idx if state else None, None, None, False, True,
+                                 D ** -0.5, False, state, max_chunks, stage, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    return ws, out, g_cum, max_chunks
+
+
+@pytest.mark.parametrize("name", sorted(cases.PREFILL_CASES))
+def test_prepare_stage_operand_images(native_built, name):
+    c = cases.gdn_prefill_case(name, device="cuda")
+    cpu = cases.gdn_prefill_case(name)
+    ws, _, g_cum, max_chunks = run_op(c, stage=1)
+    ws = ws.cpu()
+    kw = cases.gdn_prefill_oracle_kwargs(cpu)
+    Hg, H = cpu["Hg"], cpu["H"]
+    R = H // Hg
+    qn = odec.l2norm(kw["q"].float()) * D ** -0.5
+    kn = odec.l2norm(kw["k"].float())
+    g = odec.log_decay(cpu["a"].float() + cpu["dt_bias"], cpu["A_log"][None], None)      # [T,H]
+    beta = torch.sigmoid(cpu["b"].float())
+    gc = 0
+    for s, n_seq in enumerate(cpu["lengths"]):
+        for ci in range((n_seq + C - 1) // C):
+            t0 = cpu["cu"][s] + ci * C
+            n = min(C, n_seq - ci * C)
+            for h in range(Hg):
+                blob = ws[(gc * Hg + h) * HBLOB:(gc * Hg + h + 1) * HBLOB]
+                kq = image_to_tile(blob[:KQ_BYTES].view(torch.float32), 128, 128)
+                knt = image_to_tile(blob[KQ_BYTES:].view(torch.float32), 128, 64)
+                Kn = torch.zeros(C, D); Qn = torch.zeros(C, D)
+                Kn[:n] = kn[t0:t0 + n, h]; Qn[:n] = qn[t0:t0 + n, h]
+                torch.testing.assert_close(kq[:64], Kn, rtol=1e-3, atol=1e-4)
+                torch.testing.assert_close(kq[64:], Qn, rtol=1e-3, atol=1e-5)
+                assert torch.equal(knt, kq[:64].t())
+                A = Kn @ Kn.t()
+                QK = Qn @ Kn.t()
+                for r in range(R):
+                    hv = h * R + r
+                    off = max_chunks * Hg * HBLOB + (gc * H + hv) * VBLOB
+                    vb = ws[off:off + VBLOB]
+                    Tm = image_to_tile(vb[:TM_BYTES].view(torch.float32), 64, 64)
+                    Pm = image_to_tile(vb[TM_BYTES:TM_BYTES + PM_BYTES].view(torch.float32), 64, 64)
+                    vec = vb[TM_BYTES + PM_BYTES:].view(torch.float32)
+                    G = torch.zeros(C); b = torch.zeros(C)
+                    G[:n] = torch.cumsum(g[t0:t0 + n, hv], 0); G[n:] = G[n - 1]
+                    b[:n] = beta[t0:t0 + n, hv]
+                    torch.testing.assert_close(vec[:64], G, rtol=1e-4, atol=1e-5)
+                    torch.testing.assert_close(vec[64:], b, rtol=1e-4, atol=1e-6)
+                    torch.testing.assert_close(g_cum[t0:t0 + n, hv].cpu(), G[:n], rtol=1e-4, atol=1e-5)
+                    Gam = torch.exp(G[:, None] - G[None, :])
+                    L = torch.tril(b[:, None] * A * Gam, -1)
+                    T_ref = torch.linalg.solve_triangular(torch.eye(C) + L, torch.eye(C), upper=False)
+                    P_ref = torch.tril(QK * Gam)
+                    P_ref[n:] = 0
+                    torch.testing.assert_close(Tm, T_ref, rtol=5e-3, atol=2e-3)
+                    torch.testing.assert_close(Pm, P_ref, rtol=5e-3, atol=1e-4)
+            gc += 1
