@@ -37,7 +37,7 @@ constexpr int KQ_BYTES = 128 * D * 4;   // rows 0-63 Kn, rows 64-127 Qn*scale; K
 constexpr int KNT_BYTES = D * C * 4;    // rows = feature k (128), K = token (64)
 constexpr int TM_BYTES = C * C * 4;     // T: rows = token i, K = token j
 constexpr int PM_BYTES = C * C * 4;     // P: rows = token i, K = token j
-constexpr int VEC_BYTES = 2 * C * 4;    // G[64] then beta[64]
+constexpr int VEC_BYTES = 4 * C * 4;    // G[64], beta[64], exp(G)[64], exp(G_last - G)[64]
 constexpr int HBLOB = KQ_BYTES + KNT_BYTES;            // per (chunk, q/k head)
 constexpr int VBLOB = TM_BYTES + PM_BYTES + VEC_BYTES;  // per (chunk, value head)
 
@@ -320,6 +320,8 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
         float* vec = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv) + TM_BYTES + PM_BYTES);
         vec[col] = sh.G[s][col];
         vec[C + col] = sh.beta[s][col];
+        vec[2 * C + col] = __expf(sh.G[s][col]);
+        vec[3 * C + col] = __expf(sh.G[s][C - 1] - sh.G[s][col]);
       }
     }
     __syncthreads();  // L / G / beta are rewritten by the next pair of heads
@@ -336,6 +338,347 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
   tc05::fence_before_sync();
   __syncthreads();
   if (warp == 0) tc05::tmem_dealloc(tbase, 64);
+}
+
+// ================================================================================================
+// chain: one CTA per (sequence, value head), chunks in order, state resident in tensor memory
+// ================================================================================================
+// Orientation: every accumulator is [128 lanes = value index v] x [columns = token or key index],
+// i.e. the transposes of the matrices in the header comment, so that a thread of the epilogue
+// group owns one v row and writes the next A operand straight back into TMEM:
+//   MMA1  D1[v, 0:64 | 64:128] = S^T(TMEM, fp32 read as tf32) x [Kn; Qn]^T       -> (Kn S)^T | (Qn S)^T
+//   E1    W^T[v, c] = beta_c (V[c, v] - e^{G_c} (Kn S)^T[v, c])                   -> over D1[:, 0:64]
+//   MMA2  D2[v, i]  = W^T(TMEM) x T^T                                             -> V'^T
+//   E2    A3 = V'^T (over D2),  A4[v, c] = e^{G_C - G_c} V'^T[v, c] (over D1[:, 0:64]);  S *= e^{G_C}
+//   MMA3  D3[v, i]  = A3(TMEM) x P^T                                              -> intra-chunk output
+//   MMA4  S[v, k]  += A4(TMEM) x Kn^T-image                                       -> state update
+//   E3    O[i, v]   = e^{G_i} (Qn S)^T[v, i] + D3[v, i]
+// D1 is double-buffered across chunks so that E3 of chunk c overlaps MMA1 of chunk c+1.
+// TMEM columns: S 0..127, D1[0] 128..255, D1[1] 256..383, D2 384..447, D3 448..511.
+// Warps: 0 = bulk-copy producer, 1 = MMA issuer (and TMEM owner), 2..5 = epilogue group.
+constexpr uint32_t COL_S = 0, COL_D1 = 128, COL_D2 = 384, COL_D3 = 448;
+constexpr uint32_t kWaitLimit = 1u << 20;
+
+struct ChainSmem {
+  alignas(1024) float kq[KQ_BYTES / 4];
+  alignas(1024) float knt[KNT_BYTES / 4];
+  alignas(1024) float tm[TM_BYTES / 4];
+  alignas(1024) float pm[PM_BYTES / 4];
+  alignas(16) float vec[2][VEC_BYTES / 4];
+  alignas(8) uint64_t full_kq, full_t, full_pk, full_vec[2];
+  uint64_t mma1_done, mma2_done, mma34_done;
+  uint64_t s_ready, a2_ready, a34_ready, e_done;
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+// Bounded wait that also gives up when another role has already given up.
+__device__ __forceinline__ bool chain_wait(ChainSmem& sh, uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u && sh.abort) return false;
+  }
+  sh.abort = 1;
+  return false;
+}
+
+template <typename act_t>
+__global__ void __launch_bounds__(192, 1) gdn_chunk_chain_kernel(const pla_b200_gdn_chunk_args p) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem_raw = smem_dyn + ((1024u - (smem_addr(smem_dyn) & 1023u)) & 1023u);
+  ChainSmem& sh = *reinterpret_cast<ChainSmem*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  const unsigned chains = static_cast<unsigned>(p.N) * p.HV;
+  if (blockIdx.x >= chains) {
+    // trailing CTAs: physical token rows past the last sequence get zero output
+    const int64_t first = p.cu_seqlens[p.N];
+    const int64_t words = (p.T_total - first) * p.HV * (D / 2);
+    if (first < 0 || words <= 0) return;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(static_cast<act_t*>(p.o) + first * p.HV * D);
+    for (int64_t i = static_cast<int64_t>(blockIdx.x - chains) * 192 + tid; i < words;
+         i += static_cast<int64_t>(gridDim.x - chains) * 192)
+      dst[i] = 0u;
+    return;
+  }
+  const int seq = blockIdx.x / p.HV, hv = blockIdx.x % p.HV;
+  const int h = hv / (p.HV / p.H);
+  const int64_t bos = p.cu_seqlens[seq];
+  const int len = p.cu_seqlens[seq + 1] - static_cast<int>(bos);
+  if (bos < 0 || len <= 0) return;
+  const int nch = (len + C - 1) / C;
+  const int gc0 = first_chunk_of(p.cu_seqlens, seq);
+
+  int slot = seq;
+  if (p.slot_indices != nullptr) slot = p.slot_indices[seq];
+  act_t* o_col = static_cast<act_t*>(p.o) + static_cast<int64_t>(hv) * D;  // + tok*HV*D + v
+  if (p.slot_indices != nullptr && (slot < 0 || (p.num_slots > 0 && slot >= p.num_slots))) {
+    if (slot >= 0 && tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_BAD_SLOT);
+    for (int i = tid; i < len * D; i += 192) o_col[(bos + i / D) * p.HV * D + (i % D)] = from_f32<act_t>(0.f);
+    return;
+  }
+
+  if (tid == 0) {
+    mbar_init(&sh.full_kq, 1);
+    mbar_init(&sh.full_t, 1);
+    mbar_init(&sh.full_pk, 1);
+    mbar_init(&sh.full_vec[0], 1);
+    mbar_init(&sh.full_vec[1], 1);
+    mbar_init(&sh.mma1_done, 1);
+    mbar_init(&sh.mma2_done, 1);
+    mbar_init(&sh.mma34_done, 1);
+    mbar_init(&sh.s_ready, 128);
+    mbar_init(&sh.a2_ready, 128);
+    mbar_init(&sh.a34_ready, 128);
+    mbar_init(&sh.e_done, 128);
+    sh.abort = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) tc05::tmem_alloc(&sh.tmem_base, 512);
+  tc05::fence_before_sync();
+  __syncthreads();
+  tc05::fence_after_sync();
+  const uint32_t tb = sh.tmem_base;
+  const unsigned char* ws = static_cast<const unsigned char*>(p.workspace);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      auto load_kq = [&](int c) {
+        mbar_expect_tx(&sh.full_kq, KQ_BYTES);
+        bulk_load(sh.kq, ws + ws_hblob(gc0 + c, h, p.H), KQ_BYTES, &sh.full_kq);
+      };
+      auto load_t = [&](int c) {
+        mbar_expect_tx(&sh.full_t, TM_BYTES);
+        bulk_load(sh.tm, ws + ws_vblob(p.max_chunks, p.H, p.HV, gc0 + c, hv), TM_BYTES, &sh.full_t);
+      };
+      auto load_pk = [&](int c) {
+        mbar_expect_tx(&sh.full_pk, PM_BYTES + KNT_BYTES);
+        bulk_load(sh.pm, ws + ws_vblob(p.max_chunks, p.H, p.HV, gc0 + c, hv) + TM_BYTES, PM_BYTES, &sh.full_pk);
+        bulk_load(sh.knt, ws + ws_hblob(gc0 + c, h, p.H) + KQ_BYTES, KNT_BYTES, &sh.full_pk);
+      };
+      auto load_vec = [&](int c) {
+        mbar_expect_tx(&sh.full_vec[c & 1], VEC_BYTES);
+        bulk_load(sh.vec[c & 1], ws + ws_vblob(p.max_chunks, p.H, p.HV, gc0 + c, hv) + TM_BYTES + PM_BYTES, VEC_BYTES,
+                  &sh.full_vec[c & 1]);
+      };
+      load_vec(0);
+      load_kq(0);
+      load_t(0);
+      load_pk(0);
+      if (nch > 1) load_vec(1);
+      for (int c = 1; c < nch; ++c) {
+        const uint32_t prev = (c - 1) & 1;
+        if (!chain_wait(sh, &sh.mma1_done, prev)) break;
+        load_kq(c);
+        if (!chain_wait(sh, &sh.mma2_done, prev)) break;
+        load_t(c);
+        if (!chain_wait(sh, &sh.mma34_done, prev)) break;
+        load_pk(c);
+        if (!chain_wait(sh, &sh.e_done, prev)) break;
+        if (c + 1 < nch) load_vec(c + 1);
+      }
+      if (sh.abort) {
+        // copies may still be in flight into this CTA's shared memory: bounded wait for each
+        (void)mbar_wait(&sh.full_kq, 0, 1u << 16);
+        (void)mbar_wait(&sh.full_kq, 1, 1u << 16);
+        (void)mbar_wait(&sh.full_pk, 0, 1u << 16);
+        (void)mbar_wait(&sh.full_pk, 1, 1u << 16);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint64_t kq_desc = tc05::smem_desc(sh.kq, 128 * 16, 128);
+      const uint64_t t_desc = tc05::smem_desc(sh.tm, 64 * 16, 128);
+      const uint64_t p_desc = tc05::smem_desc(sh.pm, 64 * 16, 128);
+      const uint64_t knt_desc = tc05::smem_desc(sh.knt, 128 * 16, 128);
+      constexpr uint32_t i128 = tc05::idesc_tf32(128, 128), i64 = tc05::idesc_tf32(128, 64);
+      bool ok = chain_wait(sh, &sh.s_ready, 0);
+      for (int c = 0; c < nch && ok; ++c) {
+        const uint32_t ph = c & 1;
+        const uint32_t d1 = tb + COL_D1 + ph * 128;
+        if (!(ok = chain_wait(sh, &sh.full_kq, ph))) break;
+        tc05::fence_after_sync();
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j)
+          tc05::mma_tf32_ts(d1, tb + COL_S + j * 8, tc05::desc_advance(kq_desc, j * 2 * 128 * 16), i128, j > 0);
+        tc05::mma_commit(&sh.mma1_done);
+        if (!(ok = chain_wait(sh, &sh.a2_ready, ph) && chain_wait(sh, &sh.full_t, ph))) break;
+        tc05::fence_after_sync();
+#pragma unroll
+        for (int j = 0; j < C / 8; ++j)
+          tc05::mma_tf32_ts(tb + COL_D2, d1 + j * 8, tc05::desc_advance(t_desc, j * 2 * 64 * 16), i64, j > 0);
+        tc05::mma_commit(&sh.mma2_done);
+        if (!(ok = chain_wait(sh, &sh.a34_ready, ph) && chain_wait(sh, &sh.full_pk, ph))) break;
+        tc05::fence_after_sync();
+#pragma unroll
+        for (int j = 0; j < C / 8; ++j)
+          tc05::mma_tf32_ts(tb + COL_D3, tb + COL_D2 + j * 8, tc05::desc_advance(p_desc, j * 2 * 64 * 16), i64, j > 0);
+#pragma unroll
+        for (int j = 0; j < C / 8; ++j)
+          tc05::mma_tf32_ts(tb + COL_S, d1 + j * 8, tc05::desc_advance(knt_desc, j * 2 * 128 * 16), i128, true);
+        tc05::mma_commit(&sh.mma34_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue group (128 threads)
+    const int quad = warp & 3;
+    const int m = quad * 32 + lane;               // value index v owned by this thread
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t tS = tb + lane_base + COL_S, tD2 = tb + lane_base + COL_D2, tD3 = tb + lane_base + COL_D3;
+    const bool f32_state = p.state_dtype == PLA_B200_F32;
+
+    // initial state row v = m -> TMEM (fp32)
+    {
+      const int64_t in_base = static_cast<int64_t>(slot) * p.state_slot_stride + static_cast<int64_t>(hv) * TILE;
+#pragma unroll 1
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float s[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int kx = q4 * 32 + j;
+          s[j] = p.state_init_zero ? 0.0f
+                                   : load_any(p.state, p.state_dtype,
+                                              in_base + (p.state_transposed ? static_cast<int64_t>(kx) * D + m
+                                                                            : static_cast<int64_t>(m) * D + kx));
+        }
+        tc05::tmem_st32(tS + q4 * 32, s);
+      }
+      tc05::wait_st();
+      tc05::fence_before_sync();
+      mbar_arrive(&sh.s_ready);
+    }
+
+    // V column of this thread for one chunk, 16-bit pairs packed
+    uint32_t vpk[C / 2];
+    auto fetch_v = [&](int c) {
+      const int n = min(C, len - c * C);
+      const unsigned short* col = reinterpret_cast<const unsigned short*>(p.v) + static_cast<int64_t>(hv) * D + m;
+      const int64_t t0 = bos + static_cast<int64_t>(c) * C;
+#pragma unroll
+      for (int i = 0; i < C / 2; ++i) {
+        const unsigned lo = (2 * i < n) ? col[(t0 + 2 * i) * p.v_tok_stride] : 0u;
+        const unsigned hi = (2 * i + 1 < n) ? col[(t0 + 2 * i + 1) * p.v_tok_stride] : 0u;
+        vpk[i] = lo | (hi << 16);
+      }
+    };
+    auto v_at = [&](int i) -> float {
+      const unsigned short raw = static_cast<unsigned short>((i & 1) ? (vpk[i >> 1] >> 16) : (vpk[i >> 1] & 0xffffu));
+      return to_f32(*reinterpret_cast<const act_t*>(&raw));
+    };
+    fetch_v(0);
+
+    bool ok = true;
+    for (int c = 0; c < nch && ok; ++c) {
+      const uint32_t ph = c & 1;
+      const uint32_t tD1 = tb + lane_base + COL_D1 + ph * 128;
+      const int n = min(C, len - c * C);
+      const float* vec = sh.vec[ph];
+      if (!(ok = chain_wait(sh, &sh.full_vec[ph], (c >> 1) & 1))) break;
+      if (!(ok = chain_wait(sh, &sh.mma1_done, ph))) break;
+      tc05::fence_after_sync();
+      // ---- E1: W^T over (Kn S)^T ----
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float x[32];
+        tc05::tmem_ld32(tD1 + half * 32, x);
+        tc05::wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int i = half * 32 + j;
+          x[j] = tc05::to_tf32(vec[C + i] * (v_at(i) - vec[2 * C + i] * x[j]));
+        }
+        tc05::tmem_st32(tD1 + half * 32, x);
+      }
+      tc05::wait_st();
+      tc05::fence_before_sync();
+      mbar_arrive(&sh.a2_ready);
+      if (c + 1 < nch) fetch_v(c + 1);  // lands while the rest of this chunk runs
+      // ---- S *= e^{G_C} (MMA1 has consumed S; MMA4 comes after a34_ready) ----
+      {
+        const float gC = vec[2 * C + C - 1];
+#pragma unroll 1
+        for (int q4 = 0; q4 < 4; ++q4) {
+          float s[32];
+          tc05::tmem_ld32(tS + q4 * 32, s);
+          tc05::wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) s[j] *= gC;
+          tc05::tmem_st32(tS + q4 * 32, s);
+        }
+      }
+      if (!(ok = chain_wait(sh, &sh.mma2_done, ph))) break;
+      tc05::fence_after_sync();
+      // ---- E2: A3 = V'^T in place, A4 = decayed copy over W^T ----
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float x[32], y[32];
+        tc05::tmem_ld32(tD2 + half * 32, x);
+        tc05::wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          y[j] = tc05::to_tf32(vec[3 * C + half * 32 + j] * x[j]);
+          x[j] = tc05::to_tf32(x[j]);
+        }
+        tc05::tmem_st32(tD2 + half * 32, x);
+        tc05::tmem_st32(tD1 + half * 32, y);
+      }
+      tc05::wait_st();
+      tc05::fence_before_sync();
+      mbar_arrive(&sh.a34_ready);
+      if (!(ok = chain_wait(sh, &sh.mma34_done, ph))) break;
+      tc05::fence_after_sync();
+      // ---- E3: output rows of this chunk ----
+      {
+        act_t* orow = o_col + (bos + static_cast<int64_t>(c) * C) * p.HV * D + m;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float qs[32], d3[32];
+          tc05::tmem_ld32(tD1 + 64 + half * 32, qs);
+          tc05::tmem_ld32(tD3 + half * 32, d3);
+          tc05::wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int i = half * 32 + j;
+            if (i < n) orow[static_cast<int64_t>(i) * p.HV * D] = from_f32<act_t>(vec[2 * C + i] * qs[j] + d3[j]);
+          }
+        }
+      }
+      tc05::fence_before_sync();
+      mbar_arrive(&sh.e_done);
+    }
+
+    // ---- final state ----
+    if (ok && p.write_state) {
+      void* dst = p.state;
+      int64_t base = static_cast<int64_t>(slot) * p.state_slot_stride;
+      if (p.state_out != nullptr) {
+        const int64_t oslot = p.state_out_indices != nullptr ? p.state_out_indices[seq] : seq;
+        dst = p.state_out;
+        base = oslot * p.state_out_slot_stride;
+      }
+      base += static_cast<int64_t>(hv) * TILE;
+#pragma unroll 1
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float s[32];
+        tc05::tmem_ld32(tS + q4 * 32, s);
+        tc05::wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int kx = q4 * 32 + j;
+          const int64_t e = base + (p.state_transposed ? static_cast<int64_t>(kx) * D + m : static_cast<int64_t>(m) * D + kx);
+          if (f32_state) static_cast<float*>(dst)[e] = s[j];
+          else static_cast<__nv_bfloat16*>(dst)[e] = __float2bfloat16_rn(s[j]);
+        }
+      }
+    }
+  }
+
+  if (sh.abort && tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_WAIT_TIMEOUT);
+  tc05::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tc05::tmem_dealloc(tb, 512);
 }
 
 }  // namespace
@@ -381,5 +724,26 @@ extern "C" int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args,
   int rc = a.act_dtype == PLA_B200_BF16 ? launch_prepare(gdn_chunk_prepare_kernel<__nv_bfloat16>)
                                         : launch_prepare(gdn_chunk_prepare_kernel<__half>);
   if (rc != PLA_B200_OK || a.stage == 1) return rc;
-  PLA_REQUIRE(false, PLA_B200_E_UNSUPPORTED, "the chain stage is not built yet");
+  PLA_REQUIRE(a.state_init_zero || a.state != nullptr, PLA_B200_E_INVALID, "an initial state or state_init_zero is required");
+  PLA_REQUIRE(a.slot_indices != nullptr || a.state_by_request, PLA_B200_E_INVALID, "slot indices are required");
+  PLA_REQUIRE(!a.write_state || a.state_out != nullptr || a.state != nullptr, PLA_B200_E_INVALID,
+              "a final state needs somewhere to go");
+  PLA_REQUIRE((reinterpret_cast<uintptr_t>(a.o) & 3) == 0, PLA_B200_E_ALIGN, "o must be 4-byte aligned");
+  auto launch_chain = [&](auto kern) -> int {
+    static bool configured[64] = {};
+    int dev = 0;
+    PLA_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 64 && !configured[dev]) {
+      PLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(sizeof(ChainSmem) + 1024)));
+      configured[dev] = true;
+    }
+    const int64_t ctas = static_cast<int64_t>(a.N) * a.HV + 32;
+    PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "N*HV exceeds the grid limit");
+    kern<<<static_cast<unsigned>(ctas), 192, sizeof(ChainSmem) + 1024, s>>>(a);
+    PLA_CUDA_OK(cudaGetLastError());
+    return PLA_B200_OK;
+  };
+  return a.act_dtype == PLA_B200_BF16 ? launch_chain(gdn_chunk_chain_kernel<__nv_bfloat16>)
+                                      : launch_chain(gdn_chunk_chain_kernel<__half>);
 }

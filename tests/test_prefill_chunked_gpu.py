@@ -13,7 +13,7 @@ from oracle import decode as odec
 pytestmark = pytest.mark.gpu
 GOLDEN = Path(__file__).resolve().parent / "golden"
 D, C = 128, 64
-KQ_BYTES, KNT_BYTES, TM_BYTES, PM_BYTES, VEC_BYTES = 128 * 128 * 4, 128 * 64 * 4, 64 * 64 * 4, 64 * 64 * 4, 512
+KQ_BYTES, KNT_BYTES, TM_BYTES, PM_BYTES, VEC_BYTES = 128 * 128 * 4, 128 * 64 * 4, 64 * 64 * 4, 64 * 64 * 4, 1024
 HBLOB, VBLOB = KQ_BYTES + KNT_BYTES, TM_BYTES + PM_BYTES + VEC_BYTES
 
 
@@ -83,7 +83,7 @@ def test_prepare_stage_operand_images(native_built, name):
                     G[:n] = torch.cumsum(g[t0:t0 + n, hv], 0); G[n:] = G[n - 1]
                     b[:n] = beta[t0:t0 + n, hv]
                     torch.testing.assert_close(vec[:64], G, rtol=1e-4, atol=1e-5)
-                    torch.testing.assert_close(vec[64:], b, rtol=1e-4, atol=1e-6)
+                    torch.testing.assert_close(vec[64:128], b, rtol=1e-4, atol=1e-6)
                     torch.testing.assert_close(g_cum[t0:t0 + n, hv].cpu(), G[:n], rtol=1e-4, atol=1e-5)
                     Gam = torch.exp(G[:, None] - G[None, :])
                     L = torch.tril(b[:, None] * A * Gam, -1)
@@ -93,3 +93,31 @@ def test_prepare_stage_operand_images(native_built, name):
                     torch.testing.assert_close(Tm, T_ref, rtol=5e-3, atol=2e-3)
                     torch.testing.assert_close(Pm, P_ref, rtol=5e-3, atol=1e-4)
             gc += 1
+
+
+@pytest.mark.parametrize("with_state", [True, False])
+@pytest.mark.parametrize("name", sorted(cases.PREFILL_CASES))
+def test_chunked_prefill_matches_oracle_and_fixture(native_built, name, with_state):
+    c = cases.gdn_prefill_case(name, device="cuda")
+    cpu = cases.gdn_prefill_case(name)
+    kw = cases.gdn_prefill_oracle_kwargs(cpu)
+    if not with_state:
+        kw["state"] = torch.zeros_like(cpu["pool"])
+    exp_out, exp_state, _ = odec.klast_forward(**kw)
+    pool_before = c["pool"].clone()
+    _, out, _, _ = run_op(c, stage=0, state=with_state)
+    n_real = cpu["cu"][-1]
+    assert_out_close(out[:n_real], exp_out[:n_real])
+    assert torch.count_nonzero(out[n_real:]) == 0
+    if with_state:
+        assert_state_close(c["pool"].cpu(), exp_state)
+        for s in range(16):
+            if s not in cpu["slots"]:
+                assert torch.equal(c["pool"][s], pool_before[s])
+        gold = np.load(GOLDEN / f"prefill_{name}.npz")
+        assert_out_close(out[:n_real], torch.from_numpy(gold["out"]), "out vs chunked reference fixture")
+        idx = torch.tensor(cpu["slots"])
+        assert_state_close(torch.from_numpy(cases.subsample(c["pool"].cpu()[idx])), torch.from_numpy(gold["final"]),
+                           "state vs chunked reference fixture")
+    else:
+        assert torch.equal(c["pool"], pool_before)          # no state given: nothing written
