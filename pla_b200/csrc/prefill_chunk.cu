@@ -84,8 +84,7 @@ constexpr int L_STRIDE = 68;  // padded row of the fp32 L matrix (floats); rows 
 
 struct PrepSmem {
   alignas(1024) float kq[KQ_BYTES / 4];
-  alignas(1024) float knt[KNT_BYTES / 4];
-  alignas(16) float L[2][C * L_STRIDE];
+  alignas(16) float L[2][C * L_STRIDE];  // phase A reuses this space to stage the raw rows
   float G[2][C];
   float beta[2][C];
   alignas(8) uint64_t bar;
@@ -135,44 +134,71 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
     fence_mbar_init();
   }
 
-  // ---- phase A: normalised rows -> tf32 operand images ----
+  // ---- phase A1: coalesced copy of the chunk's 64 k rows and 64 q rows (any alignment) to shared memory ----
+  constexpr int STG = 65;  // staged row pitch in 32-bit words (odd: row-per-thread reads are conflict-free)
+  static_assert(128 * STG * 4 <= sizeof(PrepSmem::L), "row staging must fit into the L buffers");
+  uint32_t* stg = reinterpret_cast<uint32_t*>(sh.L);
+  for (int r = warp; r < 128; r += 4) {
+    const int c = r & 63;
+    if (c >= pos.n) continue;
+    const act_t* base = static_cast<const act_t*>(r >= 64 ? p.q : p.k);
+    const act_t* row = base + (pos.tok0 + c) * (r >= 64 ? p.q_tok_stride : p.k_tok_stride) + h * D;
+    if ((reinterpret_cast<uintptr_t>(row) & 3) == 0) {
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(row);
+      stg[r * STG + lane] = w[lane];
+      stg[r * STG + 32 + lane] = w[32 + lane];
+    } else {
+      const unsigned short* e = reinterpret_cast<const unsigned short*>(row);
+      unsigned short* d16 = reinterpret_cast<unsigned short*>(stg + r * STG);
+#pragma unroll
+      for (int t = 0; t < 4; ++t) d16[lane + 32 * t] = e[lane + 32 * t];
+    }
+  }
+  __syncthreads();
+  // ---- phase A2: one thread per row: L2 norm, tf32 rounding, operand images ----
   {
     const int c = tid & 63;
     const bool is_q = tid >= 64;
     float4* kq4 = reinterpret_cast<float4*>(sh.kq);
+    float* knt_g = reinterpret_cast<float*>(static_cast<unsigned char*>(p.workspace) + ws_hblob(gc, h, p.H) + KQ_BYTES);
     if (c < pos.n) {
-      const act_t* base = static_cast<const act_t*>(is_q ? p.q : p.k);
-      const int64_t stride = is_q ? p.q_tok_stride : p.k_tok_stride;
-      const act_t* row = base + (pos.tok0 + c) * stride + h * D;
-      const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+      const uint32_t* srow = stg + tid * STG;
       float r = is_q ? p.scale : 1.0f;
-      if (p.normalize_qk) r *= rsqrtf(row_sumsq(row, vec) + 1e-6f);
-#pragma unroll 2
-      for (int i = 0; i < D / 8; ++i) {
-        float x[8];
-        if (vec) {
-          const uint4 raw = reinterpret_cast<const uint4*>(row)[i];
-          const act_t* e = reinterpret_cast<const act_t*>(&raw);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) x[j] = tc05::to_tf32(to_f32(e[j]) * r);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) x[j] = tc05::to_tf32(to_f32(row[i * 8 + j]) * r);
+      if (p.normalize_qk) {
+        float ss = 0.f;
+#pragma unroll 8
+        for (int i = 0; i < D / 2; ++i) {
+          const uint32_t w = srow[i];
+          const act_t* e = reinterpret_cast<const act_t*>(&w);
+          const float x0 = to_f32(e[0]), x1 = to_f32(e[1]);
+          ss = fmaf(x0, x0, fmaf(x1, x1, ss));
         }
-        kq4[(2 * i) * 128 + tid] = make_float4(x[0], x[1], x[2], x[3]);
-        kq4[(2 * i + 1) * 128 + tid] = make_float4(x[4], x[5], x[6], x[7]);
+        r *= rsqrtf(ss + 1e-6f);
+      }
+#pragma unroll 4
+      for (int kc = 0; kc < D / 4; ++kc) {
+        const uint32_t w0 = srow[2 * kc], w1 = srow[2 * kc + 1];
+        const act_t* e0 = reinterpret_cast<const act_t*>(&w0);
+        const act_t* e1 = reinterpret_cast<const act_t*>(&w1);
+        const float4 x = make_float4(tc05::to_tf32(to_f32(e0[0]) * r), tc05::to_tf32(to_f32(e0[1]) * r),
+                                     tc05::to_tf32(to_f32(e1[0]) * r), tc05::to_tf32(to_f32(e1[1]) * r));
+        kq4[kc * 128 + tid] = x;
         if (!is_q) {
-          // transposed copy: rows = feature, K = token
-#pragma unroll
-          for (int j = 0; j < 8; ++j) sh.knt[(c >> 2) * (D * 4) + (i * 8 + j) * 4 + (c & 3)] = x[j];
+          // transposed image (rows = feature, K = token) straight to the workspace
+          float* dst = knt_g + (c >> 2) * (D * 4) + (kc * 4) * 4 + (c & 3);
+          dst[0] = x.x;
+          dst[4] = x.y;
+          dst[8] = x.z;
+          dst[12] = x.w;
         }
       }
     } else {
       for (int i = 0; i < D / 4; ++i) kq4[i * 128 + tid] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (!is_q)
-        for (int kk = 0; kk < D; ++kk) sh.knt[(c >> 2) * (D * 4) + kk * 4 + (c & 3)] = 0.f;
+        for (int kk = 0; kk < D; ++kk) knt_g[(c >> 2) * (D * 4) + kk * 4 + (c & 3)] = 0.f;
     }
   }
+  __syncthreads();  // staging (aliased with L) fully consumed
   fence_async_smem();   // the images are read by the tensor core and by bulk stores (async proxy)
   tc05::fence_before_sync();
   __syncthreads();
@@ -294,7 +320,12 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
 
     // ---- T = (I + L)^-1: thread = one column, rows by forward substitution, all in registers ----
     {
-      const int s = tid >> 6, col = tid & 63;
+      // Columns are dealt to threads in 16-wide blocks; a column of block cb is zero above row
+      // 16*cb and only needs rows/terms from its own block on. Blocks {0,3} share one warp and
+      // {1,2} the other, which evens out the two warps' work.
+      const int s = tid >> 6, t6 = tid & 63;
+      const int cb = (t6 < 32) ? ((t6 & 16) ? 3 : 0) : ((t6 & 16) ? 2 : 1);
+      const int col = cb * 16 + (t6 & 15);
       if (s < heads_now) {
         const int hv = h * R + r0 + s;
         float Tcol[C];
@@ -302,17 +333,24 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
         for (int i = 0; i < C; ++i) Tcol[i] = 0.0f;
 #pragma unroll
         for (int i = 0; i < C; ++i) {
-          const float4* Lrow = reinterpret_cast<const float4*>(sh.L[s] + i * L_STRIDE);
-          float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+          if (cb <= (i >> 4)) {
+            const float4* Lrow = reinterpret_cast<const float4*>(sh.L[s] + i * L_STRIDE);
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-          for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
-            const float4 l = Lrow[j4];  // entries at j >= i are zero
-            a0 = fmaf(l.x, Tcol[4 * j4 + 0], a0);
-            a1 = fmaf(l.y, Tcol[4 * j4 + 1], a1);
-            a2 = fmaf(l.z, Tcol[4 * j4 + 2], a2);
-            a3 = fmaf(l.w, Tcol[4 * j4 + 3], a3);
+            for (int jb = 0; jb <= (i >> 4); ++jb) {
+              if (cb <= jb) {
+#pragma unroll
+                for (int j4 = jb * 4; j4 < jb * 4 + 4 && j4 < (i + 3) / 4; ++j4) {
+                  const float4 l = Lrow[j4];  // entries at j >= i are zero
+                  a0 = fmaf(l.x, Tcol[4 * j4 + 0], a0);
+                  a1 = fmaf(l.y, Tcol[4 * j4 + 1], a1);
+                  a2 = fmaf(l.z, Tcol[4 * j4 + 2], a2);
+                  a3 = fmaf(l.w, Tcol[4 * j4 + 3], a3);
+                }
+              }
+            }
+            Tcol[i] = ((i == col) ? 1.0f : 0.0f) - ((a0 + a1) + (a2 + a3));
           }
-          Tcol[i] = ((i == col) ? 1.0f : 0.0f) - ((a0 + a1) + (a2 + a3));
         }
         float* Timg = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv));
 #pragma unroll
@@ -327,11 +365,10 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
     __syncthreads();  // L / G / beta are rewritten by the next pair of heads
   }
 
-  // ---- Kn|Qn and Kn^T images -> workspace (bulk stores straight from shared memory) ----
+  // ---- Kn|Qn image -> workspace (bulk store straight from shared memory) ----
   if (tid == 0) {
     unsigned char* dst = ws + ws_hblob(gc, h, p.H);
     bulk_store(dst, sh.kq, KQ_BYTES);
-    bulk_store(dst + KQ_BYTES, sh.knt, KNT_BYTES);
     bulk_commit();
     bulk_wait_read<0>();
   }
@@ -355,9 +392,12 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
 //   E3    O[i, v]   = e^{G_i} (Qn S)^T[v, i] + D3[v, i]
 // D1 is double-buffered across chunks so that E3 of chunk c overlaps MMA1 of chunk c+1.
 // TMEM columns: S 0..127, D1[0] 128..255, D1[1] 256..383, D2 384..447, D3 448..511.
-// Warps: 0 = bulk-copy producer, 1 = MMA issuer (and TMEM owner), 2..5 = epilogue group.
+// Warps: 0 = bulk-copy producer, 1 = MMA issuer (and TMEM owner), 2..9 = two epilogue warpgroups that
+// split the columns of every accumulator between them (a warp may only touch TMEM lanes 32*(warp%4)..+31).
 constexpr uint32_t COL_S = 0, COL_D1 = 128, COL_D2 = 384, COL_D3 = 448;
 constexpr uint32_t kWaitLimit = 1u << 20;
+constexpr int CHAIN_THREADS = 320;
+constexpr int E_THREADS = 256;
 
 struct ChainSmem {
   alignas(1024) float kq[KQ_BYTES / 4];
@@ -383,7 +423,7 @@ __device__ __forceinline__ bool chain_wait(ChainSmem& sh, uint64_t* bar, uint32_
 }
 
 template <typename act_t>
-__global__ void __launch_bounds__(192, 1) gdn_chunk_chain_kernel(const pla_b200_gdn_chunk_args p) {
+__global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const pla_b200_gdn_chunk_args p) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem_raw = smem_dyn + ((1024u - (smem_addr(smem_dyn) & 1023u)) & 1023u);
   ChainSmem& sh = *reinterpret_cast<ChainSmem*>(smem_raw);
@@ -396,8 +436,8 @@ __global__ void __launch_bounds__(192, 1) gdn_chunk_chain_kernel(const pla_b200_
     const int64_t words = (p.T_total - first) * p.HV * (D / 2);
     if (first < 0 || words <= 0) return;
     uint32_t* dst = reinterpret_cast<uint32_t*>(static_cast<act_t*>(p.o) + first * p.HV * D);
-    for (int64_t i = static_cast<int64_t>(blockIdx.x - chains) * 192 + tid; i < words;
-         i += static_cast<int64_t>(gridDim.x - chains) * 192)
+    for (int64_t i = static_cast<int64_t>(blockIdx.x - chains) * CHAIN_THREADS + tid; i < words;
+         i += static_cast<int64_t>(gridDim.x - chains) * CHAIN_THREADS)
       dst[i] = 0u;
     return;
   }
@@ -414,7 +454,7 @@ __global__ void __launch_bounds__(192, 1) gdn_chunk_chain_kernel(const pla_b200_
   act_t* o_col = static_cast<act_t*>(p.o) + static_cast<int64_t>(hv) * D;  // + tok*HV*D + v
   if (p.slot_indices != nullptr && (slot < 0 || (p.num_slots > 0 && slot >= p.num_slots))) {
     if (slot >= 0 && tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_BAD_SLOT);
-    for (int i = tid; i < len * D; i += 192) o_col[(bos + i / D) * p.HV * D + (i % D)] = from_f32<act_t>(0.f);
+    for (int i = tid; i < len * D; i += CHAIN_THREADS) o_col[(bos + i / D) * p.HV * D + (i % D)] = from_f32<act_t>(0.f);
     return;
   }
 
@@ -427,10 +467,10 @@ __global__ void __launch_bounds__(192, 1) gdn_chunk_chain_kernel(const pla_b200_
     mbar_init(&sh.mma1_done, 1);
     mbar_init(&sh.mma2_done, 1);
     mbar_init(&sh.mma34_done, 1);
-    mbar_init(&sh.s_ready, 128);
-    mbar_init(&sh.a2_ready, 128);
-    mbar_init(&sh.a34_ready, 128);
-    mbar_init(&sh.e_done, 128);
+    mbar_init(&sh.s_ready, E_THREADS);
+    mbar_init(&sh.a2_ready, E_THREADS);
+    mbar_init(&sh.a34_ready, E_THREADS);
+    mbar_init(&sh.e_done, E_THREADS);
     sh.abort = 0;
     fence_mbar_init();
   }
@@ -522,9 +562,11 @@ __global__ void __launch_bounds__(192, 1) gdn_chunk_chain_kernel(const pla_b200_
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue group (128 threads)
+    // ------------------------------------------------------------------ epilogue warpgroups (2 x 128 threads)
     const int quad = warp & 3;
     const int m = quad * 32 + lane;               // value index v owned by this thread
+    const int wg = (warp - 2) >> 2;               // 0: token columns 0..31 and key columns 0..63; 1: the rest
+    const int cg = wg * 32;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t tS = tb + lane_base + COL_S, tD2 = tb + lane_base + COL_D2, tD3 = tb + lane_base + COL_D3;
     const bool f32_state = p.state_dtype == PLA_B200_F32;
@@ -533,7 +575,7 @@ __global__ void __launch_bounds__(192, 1) gdn_chunk_chain_kernel(const pla_b200_
     {
       const int64_t in_base = static_cast<int64_t>(slot) * p.state_slot_stride + static_cast<int64_t>(hv) * TILE;
 #pragma unroll 1
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q4 = 2 * wg; q4 < 2 * wg + 2; ++q4) {
         float s[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -550,23 +592,17 @@ __global__ void __launch_bounds__(192, 1) gdn_chunk_chain_kernel(const pla_b200_
       mbar_arrive(&sh.s_ready);
     }
 
-    // V column of this thread for one chunk, 16-bit pairs packed
-    uint32_t vpk[C / 2];
+    // this thread's V values for its 32 tokens of one chunk (raw 16-bit; the loads stay in flight
+    // until E1 of that chunk touches them)
+    unsigned short vraw[32];
     auto fetch_v = [&](int c) {
       const int n = min(C, len - c * C);
-      const unsigned short* col = reinterpret_cast<const unsigned short*>(p.v) + static_cast<int64_t>(hv) * D + m;
-      const int64_t t0 = bos + static_cast<int64_t>(c) * C;
+      const unsigned short* col = reinterpret_cast<const unsigned short*>(p.v) + static_cast<int64_t>(hv) * D + m +
+                                  (bos + static_cast<int64_t>(c) * C + cg) * p.v_tok_stride;
 #pragma unroll
-      for (int i = 0; i < C / 2; ++i) {
-        const unsigned lo = (2 * i < n) ? col[(t0 + 2 * i) * p.v_tok_stride] : 0u;
-        const unsigned hi = (2 * i + 1 < n) ? col[(t0 + 2 * i + 1) * p.v_tok_stride] : 0u;
-        vpk[i] = lo | (hi << 16);
-      }
+      for (int j = 0; j < 32; ++j) vraw[j] = (cg + j < n) ? col[static_cast<int64_t>(j) * p.v_tok_stride] : 0;
     };
-    auto v_at = [&](int i) -> float {
-      const unsigned short raw = static_cast<unsigned short>((i & 1) ? (vpk[i >> 1] >> 16) : (vpk[i >> 1] & 0xffffu));
-      return to_f32(*reinterpret_cast<const act_t*>(&raw));
-    };
+    auto v_at = [&](int j) -> float { return to_f32(*reinterpret_cast<const act_t*>(&vraw[j])); };
     fetch_v(0);
 
     bool ok = true;
@@ -579,17 +615,16 @@ __global__ void __launch_bounds__(192, 1) gdn_chunk_chain_kernel(const pla_b200_
       if (!(ok = chain_wait(sh, &sh.mma1_done, ph))) break;
       tc05::fence_after_sync();
       // ---- E1: W^T over (Kn S)^T ----
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         float x[32];
-        tc05::tmem_ld32(tD1 + half * 32, x);
+        tc05::tmem_ld32(tD1 + cg, x);
         tc05::wait_ld();
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          const int i = half * 32 + j;
-          x[j] = tc05::to_tf32(vec[C + i] * (v_at(i) - vec[2 * C + i] * x[j]));
+          const int i = cg + j;
+          x[j] = tc05::to_tf32(vec[C + i] * (v_at(j) - vec[2 * C + i] * x[j]));
         }
-        tc05::tmem_st32(tD1 + half * 32, x);
+        tc05::tmem_st32(tD1 + cg, x);
       }
       tc05::wait_st();
       tc05::fence_before_sync();
@@ -599,7 +634,7 @@ __global__ void __launch_bounds__(192, 1) gdn_chunk_chain_kernel(const pla_b200_
       {
         const float gC = vec[2 * C + C - 1];
 #pragma unroll 1
-        for (int q4 = 0; q4 < 4; ++q4) {
+        for (int q4 = 2 * wg; q4 < 2 * wg + 2; ++q4) {
           float s[32];
           tc05::tmem_ld32(tS + q4 * 32, s);
           tc05::wait_ld();
@@ -611,18 +646,17 @@ __global__ void __launch_bounds__(192, 1) gdn_chunk_chain_kernel(const pla_b200_
       if (!(ok = chain_wait(sh, &sh.mma2_done, ph))) break;
       tc05::fence_after_sync();
       // ---- E2: A3 = V'^T in place, A4 = decayed copy over W^T ----
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         float x[32], y[32];
-        tc05::tmem_ld32(tD2 + half * 32, x);
+        tc05::tmem_ld32(tD2 + cg, x);
         tc05::wait_ld();
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          y[j] = tc05::to_tf32(vec[3 * C + half * 32 + j] * x[j]);
+          y[j] = tc05::to_tf32(vec[3 * C + cg + j] * x[j]);
           x[j] = tc05::to_tf32(x[j]);
         }
-        tc05::tmem_st32(tD2 + half * 32, x);
-        tc05::tmem_st32(tD1 + half * 32, y);
+        tc05::tmem_st32(tD2 + cg, x);
+        tc05::tmem_st32(tD1 + cg, y);
       }
       tc05::wait_st();
       tc05::fence_before_sync();
@@ -631,19 +665,14 @@ __global__ void __launch_bounds__(192, 1) gdn_chunk_chain_kernel(const pla_b200_
       tc05::fence_after_sync();
       // ---- E3: output rows of this chunk ----
       {
-        act_t* orow = o_col + (bos + static_cast<int64_t>(c) * C) * p.HV * D + m;
+        act_t* orow = o_col + (bos + static_cast<int64_t>(c) * C + cg) * p.HV * D + m;
+        float qs[32], d3[32];
+        tc05::tmem_ld32(tD1 + 64 + cg, qs);
+        tc05::tmem_ld32(tD3 + cg, d3);
+        tc05::wait_ld();
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          float qs[32], d3[32];
-          tc05::tmem_ld32(tD1 + 64 + half * 32, qs);
-          tc05::tmem_ld32(tD3 + half * 32, d3);
-          tc05::wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int i = half * 32 + j;
-            if (i < n) orow[static_cast<int64_t>(i) * p.HV * D] = from_f32<act_t>(vec[2 * C + i] * qs[j] + d3[j]);
-          }
-        }
+        for (int j = 0; j < 32; ++j)
+          if (cg + j < n) orow[static_cast<int64_t>(j) * p.HV * D] = from_f32<act_t>(vec[2 * C + cg + j] * qs[j] + d3[j]);
       }
       tc05::fence_before_sync();
       mbar_arrive(&sh.e_done);
@@ -660,7 +689,7 @@ __global__ void __launch_bounds__(192, 1) gdn_chunk_chain_kernel(const pla_b200_
       }
       base += static_cast<int64_t>(hv) * TILE;
 #pragma unroll 1
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q4 = 2 * wg; q4 < 2 * wg + 2; ++q4) {
         float s[32];
         tc05::tmem_ld32(tS + q4 * 32, s);
         tc05::wait_ld();
@@ -740,7 +769,7 @@ extern "C" int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args,
     }
     const int64_t ctas = static_cast<int64_t>(a.N) * a.HV + 32;
     PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "N*HV exceeds the grid limit");
-    kern<<<static_cast<unsigned>(ctas), 192, sizeof(ChainSmem) + 1024, s>>>(a);
+    kern<<<static_cast<unsigned>(ctas), CHAIN_THREADS, sizeof(ChainSmem) + 1024, s>>>(a);
     PLA_CUDA_OK(cudaGetLastError());
     return PLA_B200_OK;
   };

@@ -69,8 +69,10 @@ def chunk_gated_delta_rule_fwd(
     ``O`` has the physical token shape; rows past ``cu_seqlens[-1]`` are zero and never touch the
     state. With raw gating (``raw_gate_a``, ``raw_beta_b``, ``A_log``, ``dt_bias``) the gate
     ``g = -exp(A_log) * softplus(a + dt_bias)`` and ``beta = sigmoid(b)`` are formed in the kernel.
-    The by-products ``g_cum`` / ``A`` of the reference's chunk pipeline are not produced by the
-    token-recurrent evaluation and are returned as ``None``; ``auto_cp``,
+    Evaluated chunk-wise (chunk 64, WY/UT transform) on the tensor cores. ``g_cum`` is the
+    chunk-local cumulative log decay ``[1, T, H]`` fp32 at chunk size 64 (the reference uses 32);
+    the reference's ``A`` by-product is not materialised in its layout and is returned as
+    ``None`` (nothing downstream of inference reads it); ``auto_cp``,
     ``overlap_warmup_threshold`` and ``force_tc01_cp_candidate`` tune the reference's intra-card
     planner and are accepted and ignored.
     """
@@ -127,13 +129,20 @@ def chunk_gated_delta_rule_fwd(
     if not indexed and output_final_state:
         state_out = torch.empty((batch, H, DK, DV), dtype=state_dtype, device=q.device)
         final_state = state_out
-    ops.prefill_recurrent(
-        q[0], k[0], v[0], gate, bet, A_log, dt_bias, o[0], cu32, initial_state,
-        initial_state_indices if indexed else None, state_out, None, not indexed, False, bool(normalize_qk),
-        float(scale), None, not use_raw, indexed, None)
+    # chunk count: exact from trusted host offsets, else the bound T/64 + batch (no device read)
+    if raw_cu_seqlens is not None:
+        offs = raw_cu_seqlens.tolist() if isinstance(raw_cu_seqlens, torch.Tensor) else list(raw_cu_seqlens)
+        max_chunks = sum((int(b) - int(a) + CHUNK_SIZE - 1) // CHUNK_SIZE for a, b in zip(offs, offs[1:]))
+    else:
+        max_chunks = T // CHUNK_SIZE + batch
+    g_cum = torch.zeros((1, T, H), dtype=torch.float32, device=q.device)
+    ops.gdn_prefill_chunked(
+        q[0], k[0], v[0], gate, bet, A_log, dt_bias, o[0], g_cum[0], cu32, initial_state,
+        initial_state_indices if indexed else None, state_out, None, not indexed, bool(normalize_qk),
+        float(scale), not use_raw, indexed, int(max_chunks), 0, None)
     if indexed and output_final_state:
         final_state = initial_state[initial_state_indices.long()]
-    return None, None, o, None, final_state
+    return g_cum, None, o, None, final_state
 
 
 def gdn_prefill_packed_qkv_fwd(
