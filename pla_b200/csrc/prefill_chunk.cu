@@ -134,41 +134,47 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
     fence_mbar_init();
   }
 
-  // ---- phase A1: coalesced copy of the chunk's 64 k rows and 64 q rows (any alignment) to shared memory ----
-  constexpr int STG = 65;  // staged row pitch in 32-bit words (odd: row-per-thread reads are conflict-free)
+  // ---- phase A1: coalesced copy of the chunk's 64 k rows and 64 q rows to shared memory. A row of any
+  // 2-byte alignment is fetched as the 17 aligned 16-byte pieces that cover it (up to 14 bytes of
+  // its neighbours in the same buffer come along) and starts (address % 16) / 2 halfwords into
+  // its staged copy. ----
+  constexpr int STG = 68;  // staged row pitch in 32-bit words = 17 x 16 bytes
   static_assert(128 * STG * 4 <= sizeof(PrepSmem::L), "row staging must fit into the L buffers");
   uint32_t* stg = reinterpret_cast<uint32_t*>(sh.L);
   for (int r = warp; r < 128; r += 4) {
     const int c = r & 63;
-    if (c >= pos.n) continue;
+    if (c >= pos.n || lane >= 17) continue;
     const act_t* base = static_cast<const act_t*>(r >= 64 ? p.q : p.k);
     const act_t* row = base + (pos.tok0 + c) * (r >= 64 ? p.q_tok_stride : p.k_tok_stride) + h * D;
-    if ((reinterpret_cast<uintptr_t>(row) & 3) == 0) {
-      const uint32_t* w = reinterpret_cast<const uint32_t*>(row);
-      stg[r * STG + lane] = w[lane];
-      stg[r * STG + 32 + lane] = w[32 + lane];
-    } else {
-      const unsigned short* e = reinterpret_cast<const unsigned short*>(row);
-      unsigned short* d16 = reinterpret_cast<unsigned short*>(stg + r * STG);
-#pragma unroll
-      for (int t = 0; t < 4; ++t) d16[lane + 32 * t] = e[lane + 32 * t];
-    }
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<uintptr_t>(row) & ~uintptr_t(15));
+    reinterpret_cast<uint4*>(stg + r * STG)[lane] = src[lane];
   }
   __syncthreads();
   // ---- phase A2: one thread per row: L2 norm, tf32 rounding, operand images ----
   {
     const int c = tid & 63;
     const bool is_q = tid >= 64;
-    float4* kq4 = reinterpret_cast<float4*>(sh.kq);
-    float* knt_g = reinterpret_cast<float*>(static_cast<unsigned char*>(p.workspace) + ws_hblob(gc, h, p.H) + KQ_BYTES);
+    // restrict: the staged rows (read), the operand image and the workspace (written) never overlap;
+    // without it every load waits for the previous store
+    float4* __restrict__ kq4 = reinterpret_cast<float4*>(sh.kq);
+    float* __restrict__ knt_g =
+        reinterpret_cast<float*>(static_cast<unsigned char*>(p.workspace) + ws_hblob(gc, h, p.H) + KQ_BYTES);
     if (c < pos.n) {
-      const uint32_t* srow = stg + tid * STG;
+      const act_t* base = static_cast<const act_t*>(is_q ? p.q : p.k);
+      const act_t* row = base + (pos.tok0 + c) * (is_q ? p.q_tok_stride : p.k_tok_stride) + h * D;
+      const int sh_half = static_cast<int>((reinterpret_cast<uintptr_t>(row) & 15) >> 1);   // 0..7
+      const uint32_t* __restrict__ srow = stg + tid * STG + (sh_half >> 1);
+      const bool odd = sh_half & 1;
+      // element pair (2i, 2i+1) of the row as one 32-bit word
+      auto pair_at = [&](int i) -> uint32_t {
+        return odd ? __funnelshift_r(srow[i], srow[i + 1], 16) : srow[i];
+      };
       float r = is_q ? p.scale : 1.0f;
       if (p.normalize_qk) {
         float ss = 0.f;
 #pragma unroll 8
         for (int i = 0; i < D / 2; ++i) {
-          const uint32_t w = srow[i];
+          const uint32_t w = pair_at(i);
           const act_t* e = reinterpret_cast<const act_t*>(&w);
           const float x0 = to_f32(e[0]), x1 = to_f32(e[1]);
           ss = fmaf(x0, x0, fmaf(x1, x1, ss));
@@ -177,7 +183,7 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
       }
 #pragma unroll 4
       for (int kc = 0; kc < D / 4; ++kc) {
-        const uint32_t w0 = srow[2 * kc], w1 = srow[2 * kc + 1];
+        const uint32_t w0 = pair_at(2 * kc), w1 = pair_at(2 * kc + 1);
         const act_t* e0 = reinterpret_cast<const act_t*>(&w0);
         const act_t* e1 = reinterpret_cast<const act_t*>(&w1);
         const float4 x = make_float4(tc05::to_tf32(to_f32(e0[0]) * r), tc05::to_tf32(to_f32(e0[1]) * r),
@@ -185,7 +191,7 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
         kq4[kc * 128 + tid] = x;
         if (!is_q) {
           // transposed image (rows = feature, K = token) straight to the workspace
-          float* dst = knt_g + (c >> 2) * (D * 4) + (kc * 4) * 4 + (c & 3);
+          float* __restrict__ dst = knt_g + (c >> 2) * (D * 4) + (kc * 4) * 4 + (c & 3);
           dst[0] = x.x;
           dst[4] = x.y;
           dst[8] = x.z;
@@ -296,21 +302,22 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
     for (int s = 0; s < heads_now; ++s) {
       const int hv = h * R + r0 + s;
       const float gi = sh.G[s][i_row];
+      const float* __restrict__ Gs = sh.G[s];
       if (!p_row) {
         const float bi = sh.beta[s][i_row];
-        float* Lrow = sh.L[s] + i_row * L_STRIDE;
+        float* __restrict__ Lrow = sh.L[s] + i_row * L_STRIDE;
 #pragma unroll
         for (int j = 0; j < C; ++j)
-          Lrow[j] = (j < i_row) ? bi * d0[j] * __expf(gi - sh.G[s][j]) : 0.0f;
+          Lrow[j] = (j < i_row) ? bi * d0[j] * __expf(gi - Gs[j]) : 0.0f;
       } else {
-        float4* Pimg = reinterpret_cast<float4*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv) + TM_BYTES);
+        float4* __restrict__ Pimg = reinterpret_cast<float4*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv) + TM_BYTES);
 #pragma unroll
         for (int jc = 0; jc < C / 4; ++jc) {
           float x[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int j = jc * 4 + u;
-            x[u] = (j <= i_row && i_row < pos.n) ? tc05::to_tf32(d0[j] * __expf(gi - sh.G[s][j])) : 0.0f;
+            x[u] = (j <= i_row && i_row < pos.n) ? tc05::to_tf32(d0[j] * __expf(gi - Gs[j])) : 0.0f;
           }
           Pimg[jc * C + i_row] = make_float4(x[0], x[1], x[2], x[3]);
         }
@@ -393,11 +400,23 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
 // D1 is double-buffered across chunks so that E3 of chunk c overlaps MMA1 of chunk c+1.
 // TMEM columns: S 0..127, D1[0] 128..255, D1[1] 256..383, D2 384..447, D3 448..511.
 // Warps: 0 = bulk-copy producer, 1 = MMA issuer (and TMEM owner), 2..9 = two epilogue warpgroups that
-// split the columns of every accumulator between them (a warp may only touch TMEM lanes 32*(warp%4)..+31).
+// split the columns of every accumulator between them (a warp may only touch TMEM lanes 32*(warp%4)..+31),
+// 10 = V loader (global rows of any alignment -> shared memory, one chunk ahead), 11 = output storer
+// (bulk stores of the chunk's output rows from shared memory).
 constexpr uint32_t COL_S = 0, COL_D1 = 128, COL_D2 = 384, COL_D3 = 448;
 constexpr uint32_t kWaitLimit = 1u << 20;
-constexpr int CHAIN_THREADS = 320;
+
+// Optional phase timestamps of chain CTA 0 (development builds only: -DPLA_B200_DEBUG_CLOCKS).
+#ifdef PLA_B200_DEBUG_CLOCKS
+__device__ long long g_dbg_clock[2][16][8];
+#define DBG_CLOCK(role, c, k) \
+  do { if (blockIdx.x == 0 && (c) < 16) g_dbg_clock[role][c][k] = clock64(); } while (0)
+#else
+#define DBG_CLOCK(role, c, k) do {} while (0)
+#endif
+constexpr int CHAIN_THREADS = 384;
 constexpr int E_THREADS = 256;
+constexpr int V_PITCH = 136;  // halfwords per staged V row: 128 + room for one leading / trailing halfword, 16-byte multiple
 
 struct ChainSmem {
   alignas(1024) float kq[KQ_BYTES / 4];
@@ -405,7 +424,10 @@ struct ChainSmem {
   alignas(1024) float tm[TM_BYTES / 4];
   alignas(1024) float pm[PM_BYTES / 4];
   alignas(16) float vec[2][VEC_BYTES / 4];
+  alignas(128) unsigned short v[2][C * V_PITCH];   // raw 16-bit V rows of a chunk, double-buffered
+  alignas(128) unsigned short o[C * D];      // output rows of a chunk, 16-bit
   alignas(8) uint64_t full_kq, full_t, full_pk, full_vec[2];
+  uint64_t v_full[2], v_free[2], o_full, o_free;
   uint64_t mma1_done, mma2_done, mma34_done;
   uint64_t s_ready, a2_ready, a34_ready, e_done;
   uint32_t tmem_base;
@@ -471,6 +493,12 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
     mbar_init(&sh.a2_ready, E_THREADS);
     mbar_init(&sh.a34_ready, E_THREADS);
     mbar_init(&sh.e_done, E_THREADS);
+    mbar_init(&sh.v_full[0], 32);
+    mbar_init(&sh.v_full[1], 32);
+    mbar_init(&sh.v_free[0], E_THREADS);
+    mbar_init(&sh.v_free[1], E_THREADS);
+    mbar_init(&sh.o_full, E_THREADS);
+    mbar_init(&sh.o_free, 1);
     sh.abort = 0;
     fence_mbar_init();
   }
@@ -540,18 +568,23 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
         const uint32_t d1 = tb + COL_D1 + ph * 128;
         if (!(ok = chain_wait(sh, &sh.full_kq, ph))) break;
         tc05::fence_after_sync();
+        DBG_CLOCK(0, c, 0);
 #pragma unroll
         for (int j = 0; j < D / 8; ++j)
           tc05::mma_tf32_ts(d1, tb + COL_S + j * 8, tc05::desc_advance(kq_desc, j * 2 * 128 * 16), i128, j > 0);
         tc05::mma_commit(&sh.mma1_done);
+        DBG_CLOCK(0, c, 1);
         if (!(ok = chain_wait(sh, &sh.a2_ready, ph) && chain_wait(sh, &sh.full_t, ph))) break;
         tc05::fence_after_sync();
+        DBG_CLOCK(0, c, 2);
 #pragma unroll
         for (int j = 0; j < C / 8; ++j)
           tc05::mma_tf32_ts(tb + COL_D2, d1 + j * 8, tc05::desc_advance(t_desc, j * 2 * 64 * 16), i64, j > 0);
         tc05::mma_commit(&sh.mma2_done);
+        DBG_CLOCK(0, c, 3);
         if (!(ok = chain_wait(sh, &sh.a34_ready, ph) && chain_wait(sh, &sh.full_pk, ph))) break;
         tc05::fence_after_sync();
+        DBG_CLOCK(0, c, 4);
 #pragma unroll
         for (int j = 0; j < C / 8; ++j)
           tc05::mma_tf32_ts(tb + COL_D3, tb + COL_D2 + j * 8, tc05::desc_advance(p_desc, j * 2 * 64 * 16), i64, j > 0);
@@ -559,7 +592,61 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
         for (int j = 0; j < C / 8; ++j)
           tc05::mma_tf32_ts(tb + COL_S, d1 + j * 8, tc05::desc_advance(knt_desc, j * 2 * 128 * 16), i128, true);
         tc05::mma_commit(&sh.mma34_done);
+        DBG_CLOCK(0, c, 5);
       }
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------------ V loader
+    // Asynchronous copies (no register staging) of the chunk's 64 V rows, one chunk ahead. A row
+    // of any 2-byte alignment is fetched as the 17 aligned 16-byte pieces that cover it; it then
+    // starts (address % 16) / 2 halfwords into its staged copy (the epilogue adds the same shift).
+    // Up to 14 bytes before and after the row are read as well: they belong to neighbouring
+    // heads / tokens of the same buffer.
+    const unsigned short* vbase = reinterpret_cast<const unsigned short*>(p.v) + static_cast<int64_t>(hv) * D;
+    for (int c = 0; c < nch; ++c) {
+      const int b = c & 1;
+      if (c >= 2 && !chain_wait(sh, &sh.v_free[b], ((c >> 1) - 1) & 1)) break;
+      if (lane == 0) DBG_CLOCK(0, c, 6);
+      const int n = min(C, len - c * C);
+      unsigned short* dst = sh.v[b];
+      // lane l copies rows l and l + 32: 17 aligned 16-byte pieces that cover each 256-byte row
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int r = lane + 32 * k;
+        const unsigned short* row = vbase + (bos + static_cast<int64_t>(c) * C + r) * p.v_tok_stride;
+        const uint32_t d = smem_addr(dst + r * V_PITCH);
+        if (r >= n) {
+          uint4* z = reinterpret_cast<uint4*>(dst + r * V_PITCH);
+#pragma unroll
+          for (int i = 0; i < 17; ++i) z[i] = make_uint4(0u, 0u, 0u, 0u);
+        } else {
+          const char* src = reinterpret_cast<const char*>(reinterpret_cast<uintptr_t>(row) & ~uintptr_t(15));
+#pragma unroll
+          for (int i = 0; i < 17; ++i)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d + i * 16), "l"(src + i * 16) : "memory");
+        }
+      }
+      if (n < C) __threadfence_block();  // the zero rows above are plain stores
+      // counts as this lane's arrival once all of its copies above have landed
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(&sh.v_full[b])) : "memory");
+      if (lane == 0) DBG_CLOCK(0, c, 7);
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  } else if (warp == 11) {
+    // ------------------------------------------------------------------ output storer
+    // 256-byte output rows from shared memory, two rows per warp instruction (16 bytes per lane).
+    for (int c = 0; c < nch; ++c) {
+      if (!chain_wait(sh, &sh.o_full, c & 1)) break;
+      const int n = min(C, len - c * C);
+      act_t* orow = o_col + (bos + static_cast<int64_t>(c) * C) * p.HV * D;
+      const uint4* src = reinterpret_cast<const uint4*>(sh.o);
+#pragma unroll 8
+      for (int r2 = 0; r2 < C / 2; ++r2) {
+        const int r = r2 * 2 + (lane >> 4);
+        if (r < n) reinterpret_cast<uint4*>(orow + static_cast<int64_t>(r) * p.HV * D)[lane & 15] = src[r * 16 + (lane & 15)];
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.o_free);
     }
   } else {
     // ------------------------------------------------------------------ epilogue warpgroups (2 x 128 threads)
@@ -592,19 +679,6 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
       mbar_arrive(&sh.s_ready);
     }
 
-    // this thread's V values for its 32 tokens of one chunk (raw 16-bit; the loads stay in flight
-    // until E1 of that chunk touches them)
-    unsigned short vraw[32];
-    auto fetch_v = [&](int c) {
-      const int n = min(C, len - c * C);
-      const unsigned short* col = reinterpret_cast<const unsigned short*>(p.v) + static_cast<int64_t>(hv) * D + m +
-                                  (bos + static_cast<int64_t>(c) * C + cg) * p.v_tok_stride;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) vraw[j] = (cg + j < n) ? col[static_cast<int64_t>(j) * p.v_tok_stride] : 0;
-    };
-    auto v_at = [&](int j) -> float { return to_f32(*reinterpret_cast<const act_t*>(&vraw[j])); };
-    fetch_v(0);
-
     bool ok = true;
     for (int c = 0; c < nch && ok; ++c) {
       const uint32_t ph = c & 1;
@@ -612,8 +686,16 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
       const int n = min(C, len - c * C);
       const float* vec = sh.vec[ph];
       if (!(ok = chain_wait(sh, &sh.full_vec[ph], (c >> 1) & 1))) break;
+      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 3);
+      if (!(ok = chain_wait(sh, &sh.v_full[ph], (c >> 1) & 1))) break;
+      const act_t* vrows = reinterpret_cast<const act_t*>(sh.v[ph]);
+      // halfword shift of token (cg + j)'s staged row = (element address of the row) mod 8
+      const int64_t v_e0 = static_cast<int64_t>(reinterpret_cast<uintptr_t>(p.v) >> 1) + static_cast<int64_t>(hv) * D +
+                           (bos + static_cast<int64_t>(c) * C + cg) * p.v_tok_stride;
+      const int v_sh0 = static_cast<int>(v_e0 & 7), v_shs = static_cast<int>(p.v_tok_stride & 7);
       if (!(ok = chain_wait(sh, &sh.mma1_done, ph))) break;
       tc05::fence_after_sync();
+      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 1);
       // ---- E1: W^T over (Kn S)^T ----
       {
         float x[32];
@@ -622,14 +704,15 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int i = cg + j;
-          x[j] = tc05::to_tf32(vec[C + i] * (v_at(j) - vec[2 * C + i] * x[j]));
+          x[j] = tc05::to_tf32(vec[C + i] * (to_f32(vrows[i * V_PITCH + ((v_sh0 + j * v_shs) & 7) + m]) - vec[2 * C + i] * x[j]));
         }
         tc05::tmem_st32(tD1 + cg, x);
       }
       tc05::wait_st();
       tc05::fence_before_sync();
       mbar_arrive(&sh.a2_ready);
-      if (c + 1 < nch) fetch_v(c + 1);  // lands while the rest of this chunk runs
+      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 2);
+      mbar_arrive(&sh.v_free[ph]);
       // ---- S *= e^{G_C} (MMA1 has consumed S; MMA4 comes after a34_ready) ----
       {
         const float gC = vec[2 * C + C - 1];
@@ -645,6 +728,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
       }
       if (!(ok = chain_wait(sh, &sh.mma2_done, ph))) break;
       tc05::fence_after_sync();
+      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 4);
       // ---- E2: A3 = V'^T in place, A4 = decayed copy over W^T ----
       {
         float x[32], y[32];
@@ -661,21 +745,29 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
       tc05::wait_st();
       tc05::fence_before_sync();
       mbar_arrive(&sh.a34_ready);
+      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 5);
       if (!(ok = chain_wait(sh, &sh.mma34_done, ph))) break;
       tc05::fence_after_sync();
+      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 6);
       // ---- E3: output rows of this chunk ----
       {
-        act_t* orow = o_col + (bos + static_cast<int64_t>(c) * C + cg) * p.HV * D + m;
         float qs[32], d3[32];
         tc05::tmem_ld32(tD1 + 64 + cg, qs);
         tc05::tmem_ld32(tD3 + cg, d3);
+        if (c >= 1 && !(ok = chain_wait(sh, &sh.o_free, (c - 1) & 1))) break;  // previous rows stored
         tc05::wait_ld();
+        if (m == 0 && wg == 0) DBG_CLOCK(1, c, 0);
+        act_t* so = reinterpret_cast<act_t*>(sh.o);
+        // values first, stores second: the stores may alias `vec` as far as the compiler knows
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (cg + j < n) orow[static_cast<int64_t>(j) * p.HV * D] = from_f32<act_t>(vec[2 * C + cg + j] * qs[j] + d3[j]);
+        for (int j = 0; j < 32; ++j) qs[j] = fmaf(vec[2 * C + cg + j], qs[j], d3[j]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) so[(cg + j) * D + m] = from_f32<act_t>(qs[j]);
+        mbar_arrive(&sh.o_full);  // the storer reads with ordinary loads: no proxy fence needed
       }
       tc05::fence_before_sync();
       mbar_arrive(&sh.e_done);
+      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 7);
     }
 
     // ---- final state ----
@@ -757,7 +849,7 @@ extern "C" int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args,
   PLA_REQUIRE(a.slot_indices != nullptr || a.state_by_request, PLA_B200_E_INVALID, "slot indices are required");
   PLA_REQUIRE(!a.write_state || a.state_out != nullptr || a.state != nullptr, PLA_B200_E_INVALID,
               "a final state needs somewhere to go");
-  PLA_REQUIRE((reinterpret_cast<uintptr_t>(a.o) & 3) == 0, PLA_B200_E_ALIGN, "o must be 4-byte aligned");
+  PLA_REQUIRE(aligned16(a.o), PLA_B200_E_ALIGN, "o must be 16-byte aligned");
   auto launch_chain = [&](auto kern) -> int {
     static bool configured[64] = {};
     int dev = 0;
@@ -776,3 +868,9 @@ extern "C" int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args,
   return a.act_dtype == PLA_B200_BF16 ? launch_chain(gdn_chunk_chain_kernel<__nv_bfloat16>)
                                       : launch_chain(gdn_chunk_chain_kernel<__half>);
 }
+
+#ifdef PLA_B200_DEBUG_CLOCKS
+extern "C" int pla_b200_debug_chain_clocks(long long* out) {
+  return cudaMemcpyFromSymbol(out, pla::g_dbg_clock, sizeof(pla::g_dbg_clock)) == cudaSuccess ? 0 : -4;
+}
+#endif
