@@ -146,9 +146,13 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
     if (c >= pos.n || lane >= 17) continue;
     const act_t* base = static_cast<const act_t*>(r >= 64 ? p.q : p.k);
     const act_t* row = base + (pos.tok0 + c) * (r >= 64 ? p.q_tok_stride : p.k_tok_stride) + h * D;
-    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<uintptr_t>(row) & ~uintptr_t(15));
-    reinterpret_cast<uint4*>(stg + r * STG)[lane] = src[lane];
+    const char* src = reinterpret_cast<const char*>(reinterpret_cast<uintptr_t>(row) & ~uintptr_t(15));
+    // asynchronous 16-byte copies: all rows of the warp are in flight together
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(stg + r * STG) + lane * 16),
+                 "l"(src + lane * 16)
+                 : "memory");
   }
+  asm volatile("cp.async.wait_all;" ::: "memory");
   __syncthreads();
   // ---- phase A2: one thread per row: L2 norm, tf32 rounding, operand images ----
   {

@@ -121,3 +121,72 @@ def test_chunked_prefill_matches_oracle_and_fixture(native_built, name, with_sta
                            "state vs chunked reference fixture")
     else:
         assert torch.equal(c["pool"], pool_before)          # no state given: nothing written
+
+
+def test_chunked_prefill_long_sequences_against_token_recurrence(native_built):
+    """Many chunks per chain (barrier phases wrap, errors accumulate): the tensor-core path against the
+    CPU oracle on a 2048-token sequence and against the token-recurrent GPU kernel at 8 x ~4K tokens."""
+    from pla_b200._ops import ops
+    g = torch.Generator().manual_seed(77)
+    Hg, H = 1, 2
+    lengths = [2048, 333]
+    T = sum(lengths)
+    width = 2 * Hg * D + H * D
+    packed = torch.randn(T, width, generator=g).bfloat16()
+    gates = torch.randn(T, 2 * H, generator=g).bfloat16()
+    A_log = torch.rand(H, generator=g) * float(np.log(16.0))
+    dt_bias = torch.randn(H, generator=g) * 0.1
+    pool = torch.randn(4, H, D, D, generator=g) * 0.02
+    cu = [0, 2048, T]
+    q = packed[:, :Hg * D].reshape(T, Hg, D)
+    k = packed[:, Hg * D:2 * Hg * D].reshape(T, Hg, D)
+    v = packed[:, 2 * Hg * D:].reshape(T, H, D)
+    exp_out, exp_state, _ = odec.klast_forward(q=q, k=k, v=v, a=gates[:, :H], b=gates[:, H:], A_log=A_log,
+                                               dt_bias=dt_bias, state=pool, slot_indices=[2, 0], lengths=lengths,
+                                               scale=D ** -0.5)
+    dp = packed.cuda()
+    dq = dp.as_strided((T, Hg, D), (width, D, 1), 0)
+    dk = dp.as_strided((T, Hg, D), (width, D, 1), Hg * D)
+    dv = dp.as_strided((T, H, D), (width, D, 1), 2 * Hg * D)
+    dg = gates.cuda()
+    dpool = pool.cuda()
+    out = torch.empty(T, H, D, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.gdn_prefill_chunked(dq, dk, dv, dg[:, :H], dg[:, H:], A_log.cuda(), dt_bias.cuda(), out, None,
+                            torch.tensor(cu, dtype=torch.int32, device="cuda"), dpool,
+                            torch.tensor([2, 0], dtype=torch.int32, device="cuda"), None, None, False, True,
+                            D ** -0.5, False, True, sum((n + C - 1) // C for n in lengths), 0, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert_out_close(out, exp_out)
+    assert_state_close(dpool.cpu(), exp_state)
+
+    # config-3 sized: both GPU evaluations of the same recurrence must agree
+    Hg, H = 16, 32
+    lengths = torch.randint(512, 8193, (8,), generator=g).tolist()
+    T = sum(lengths)
+    width = 2 * Hg * D + H * D
+    dp = torch.empty(T, width, dtype=torch.bfloat16, device="cuda").normal_(generator=torch.Generator("cuda").manual_seed(3))
+    dq = dp.as_strided((T, Hg, D), (width, D, 1), 0)
+    dk = dp.as_strided((T, Hg, D), (width, D, 1), Hg * D)
+    dv = dp.as_strided((T, H, D), (width, D, 1), 2 * Hg * D)
+    dg = torch.randn(T, 2 * H, generator=g).bfloat16().cuda()
+    A_log = (torch.rand(H, generator=g) * float(np.log(16.0))).cuda()
+    dt_bias = (torch.randn(H, generator=g) * 0.1).cuda()
+    pool_a = (torch.randn(16, H, D, D, generator=g) * 0.02).cuda()
+    pool_b = pool_a.clone()
+    idx = torch.arange(1, 16, 2, dtype=torch.int32, device="cuda")
+    offs = [0]
+    for n in lengths:
+        offs.append(offs[-1] + n)
+    cu = torch.tensor(offs, dtype=torch.int32, device="cuda")
+    out_a = torch.empty(T, H, D, dtype=torch.bfloat16, device="cuda")
+    out_b = torch.empty_like(out_a)
+    ops.gdn_prefill_chunked(dq, dk, dv, dg[:, :H], dg[:, H:], A_log, dt_bias, out_a, None, cu, pool_a, idx, None, None,
+                            False, True, D ** -0.5, False, True, sum((n + C - 1) // C for n in lengths), 0, status)
+    ops.prefill_recurrent(dq, dk, dv, dg[:, :H], dg[:, H:], A_log, dt_bias, out_b, cu, pool_b, idx, None, None, False,
+                          False, True, D ** -0.5, None, False, True, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert_out_close(out_a, out_b, "chunked vs token-recurrent output")
+    assert_state_close(pool_a, pool_b, "chunked vs token-recurrent state")
