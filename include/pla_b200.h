@@ -212,7 +212,12 @@ typedef struct pla_b200_gdn_chunk_args {
   int32_t H, HV;
   float scale;
   int32_t normalize_qk;
-  int32_t stage;              /* 0: prepare + chain; 1: prepare only (tests) */
+  int32_t stage;              /* 0: prepare + chain; 1: prepare only; 2: chain only, over a workspace that a
+                                 stage-1 call with the same tokens filled */
+  int32_t prescan;            /* context parallelism: instead of outputs, store per (sequence, value head) the
+                                 segment's offset B (state reached from zero) and transition M (state reached
+                                 from the identity with V = 0) into state_out [N, HV, 2, 128, 128] fp32, so that
+                                 S_out[v, :] = S_in[v, :] M + B[v, :]; initial states and slots are not read */
   void* workspace;            /* device scratch of pla_b200_gdn_chunk_workspace_bytes() bytes, 128-byte aligned */
   int64_t workspace_bytes;
   int32_t* status;

@@ -135,9 +135,9 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
   }
 
   // ---- phase A1: coalesced copy of the chunk's 64 k rows and 64 q rows to shared memory. A row of any
-  // 2-byte alignment is fetched as the 17 aligned 16-byte pieces that cover it (up to 14 bytes of
-  // its neighbours in the same buffer come along) and starts (address % 16) / 2 halfwords into
-  // its staged copy. ----
+  // 2-byte alignment is fetched as the 16 or 17 aligned 16-byte pieces that overlap it (up to 14
+  // bytes before and after it come along, always from a 16-byte granule that the row itself
+  // occupies, hence from mapped memory) and starts (address % 16) / 2 halfwords into its staged copy. ----
   constexpr int STG = 68;  // staged row pitch in 32-bit words = 17 x 16 bytes
   static_assert(128 * STG * 4 <= sizeof(PrepSmem::L), "row staging must fit into the L buffers");
   uint32_t* stg = reinterpret_cast<uint32_t*>(sh.L);
@@ -147,6 +147,9 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
     const act_t* base = static_cast<const act_t*>(r >= 64 ? p.q : p.k);
     const act_t* row = base + (pos.tok0 + c) * (r >= 64 ? p.q_tok_stride : p.k_tok_stride) + h * D;
     const char* src = reinterpret_cast<const char*>(reinterpret_cast<uintptr_t>(row) & ~uintptr_t(15));
+    // an aligned row ends with its 16th piece: the 17th would lie wholly outside it (and, for the
+    // buffer's last row, outside the allocation)
+    if (lane == 16 && src == reinterpret_cast<const char*>(row)) continue;
     // asynchronous 16-byte copies: all rows of the warp are in flight together
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(stg + r * STG) + lane * 16),
                  "l"(src + lane * 16)
@@ -455,8 +458,13 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
   ChainSmem& sh = *reinterpret_cast<ChainSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  const unsigned chains = static_cast<unsigned>(p.N) * p.HV;
+  // Prescan mode (context parallelism): every (sequence, value head) runs two chains that store no
+  // output, kind 0 from a zero state over the real V (the segment's offset B) and kind 1 from the
+  // identity over V = 0 (the segment's transition M), so that  S_out = S_in M + B  row by row.
+  const bool prescan = p.prescan != 0;
+  const unsigned chains = static_cast<unsigned>(p.N) * p.HV * (prescan ? 2u : 1u);
   if (blockIdx.x >= chains) {
+    if (prescan) return;
     // trailing CTAs: physical token rows past the last sequence get zero output
     const int64_t first = p.cu_seqlens[p.N];
     const int64_t words = (p.T_total - first) * p.HV * (D / 2);
@@ -467,7 +475,9 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
       dst[i] = 0u;
     return;
   }
-  const int seq = blockIdx.x / p.HV, hv = blockIdx.x % p.HV;
+  const int kind = prescan ? static_cast<int>(blockIdx.x & 1u) : 0;
+  const unsigned chain = prescan ? blockIdx.x >> 1 : blockIdx.x;
+  const int seq = chain / p.HV, hv = chain % p.HV;
   const int h = hv / (p.HV / p.H);
   const int64_t bos = p.cu_seqlens[seq];
   const int len = p.cu_seqlens[seq + 1] - static_cast<int>(bos);
@@ -476,9 +486,9 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
   const int gc0 = first_chunk_of(p.cu_seqlens, seq);
 
   int slot = seq;
-  if (p.slot_indices != nullptr) slot = p.slot_indices[seq];
+  if (p.slot_indices != nullptr && !prescan) slot = p.slot_indices[seq];
   act_t* o_col = static_cast<act_t*>(p.o) + static_cast<int64_t>(hv) * D;  // + tok*HV*D + v
-  if (p.slot_indices != nullptr && (slot < 0 || (p.num_slots > 0 && slot >= p.num_slots))) {
+  if (!prescan && p.slot_indices != nullptr && (slot < 0 || (p.num_slots > 0 && slot >= p.num_slots))) {
     if (slot >= 0 && tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_BAD_SLOT);
     for (int i = tid; i < len * D; i += CHAIN_THREADS) o_col[(bos + i / D) * p.HV * D + (i % D)] = from_f32<act_t>(0.f);
     return;
@@ -602,16 +612,16 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
   } else if (warp == 10) {
     // ------------------------------------------------------------------ V loader
     // Asynchronous copies (no register staging) of the chunk's 64 V rows, one chunk ahead. A row
-    // of any 2-byte alignment is fetched as the 17 aligned 16-byte pieces that cover it; it then
-    // starts (address % 16) / 2 halfwords into its staged copy (the epilogue adds the same shift).
-    // Up to 14 bytes before and after the row are read as well: they belong to neighbouring
-    // heads / tokens of the same buffer.
+    // of any 2-byte alignment is fetched as the 16 or 17 aligned 16-byte pieces that overlap it; it
+    // then starts (address % 16) / 2 halfwords into its staged copy (the epilogue adds the same
+    // shift). Up to 14 bytes before and after the row are read as well, always from a 16-byte
+    // granule that the row itself occupies.
     const unsigned short* vbase = reinterpret_cast<const unsigned short*>(p.v) + static_cast<int64_t>(hv) * D;
     for (int c = 0; c < nch; ++c) {
       const int b = c & 1;
       if (c >= 2 && !chain_wait(sh, &sh.v_free[b], ((c >> 1) - 1) & 1)) break;
       if (lane == 0) DBG_CLOCK(0, c, 6);
-      const int n = min(C, len - c * C);
+      const int n = kind == 1 ? 0 : min(C, len - c * C);
       unsigned short* dst = sh.v[b];
       // lane l copies rows l and l + 32: 17 aligned 16-byte pieces that cover each 256-byte row
 #pragma unroll
@@ -625,9 +635,12 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
           for (int i = 0; i < 17; ++i) z[i] = make_uint4(0u, 0u, 0u, 0u);
         } else {
           const char* src = reinterpret_cast<const char*>(reinterpret_cast<uintptr_t>(row) & ~uintptr_t(15));
+          // an aligned row ends with its 16th piece; the 17th would lie wholly outside the row
+          const int pieces = src == reinterpret_cast<const char*>(row) ? 16 : 17;
 #pragma unroll
           for (int i = 0; i < 17; ++i)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d + i * 16), "l"(src + i * 16) : "memory");
+            if (i < pieces)
+              asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d + i * 16), "l"(src + i * 16) : "memory");
         }
       }
       if (n < C) __threadfence_block();  // the zero rows above are plain stores
@@ -641,7 +654,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
     // 256-byte output rows from shared memory, two rows per warp instruction (16 bytes per lane).
     for (int c = 0; c < nch; ++c) {
       if (!chain_wait(sh, &sh.o_full, c & 1)) break;
-      const int n = min(C, len - c * C);
+      const int n = prescan ? 0 : min(C, len - c * C);
       act_t* orow = o_col + (bos + static_cast<int64_t>(c) * C) * p.HV * D;
       const uint4* src = reinterpret_cast<const uint4*>(sh.o);
 #pragma unroll 8
@@ -671,8 +684,10 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int kx = q4 * 32 + j;
-          s[j] = p.state_init_zero ? 0.0f
-                                   : load_any(p.state, p.state_dtype,
+          s[j] = prescan ? (kind == 1 && kx == m ? 1.0f : 0.0f)
+                 : p.state_init_zero
+                     ? 0.0f
+                     : load_any(p.state, p.state_dtype,
                                               in_base + (p.state_transposed ? static_cast<int64_t>(kx) * D + m
                                                                             : static_cast<int64_t>(m) * D + kx));
         }
@@ -775,7 +790,20 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
     }
 
     // ---- final state ----
-    if (ok && p.write_state) {
+    if (ok && prescan) {
+      // [sequence][value head][offset, transition][v][k] fp32
+      float* dst = static_cast<float*>(p.state_out) + (static_cast<int64_t>(chain) * 2 + kind) * TILE +
+                   static_cast<int64_t>(m) * D;
+#pragma unroll 1
+      for (int q4 = 2 * wg; q4 < 2 * wg + 2; ++q4) {
+        float s[32];
+        tc05::tmem_ld32(tS + q4 * 32, s);
+        tc05::wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + q4 * 32 + j) = make_float4(s[j], s[j + 1], s[j + 2], s[j + 3]);
+      }
+    } else if (ok && p.write_state) {
       void* dst = p.state;
       int64_t base = static_cast<int64_t>(slot) * p.state_slot_stride;
       if (p.state_out != nullptr) {
@@ -846,13 +874,22 @@ extern "C" int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args,
     PLA_CUDA_OK(cudaGetLastError());
     return PLA_B200_OK;
   };
-  int rc = a.act_dtype == PLA_B200_BF16 ? launch_prepare(gdn_chunk_prepare_kernel<__nv_bfloat16>)
-                                        : launch_prepare(gdn_chunk_prepare_kernel<__half>);
+  PLA_REQUIRE(a.stage >= 0 && a.stage <= 2, PLA_B200_E_INVALID, "stage must be 0, 1 or 2");
+  int rc = PLA_B200_OK;
+  if (a.stage != 2)
+    rc = a.act_dtype == PLA_B200_BF16 ? launch_prepare(gdn_chunk_prepare_kernel<__nv_bfloat16>)
+                                      : launch_prepare(gdn_chunk_prepare_kernel<__half>);
   if (rc != PLA_B200_OK || a.stage == 1) return rc;
-  PLA_REQUIRE(a.state_init_zero || a.state != nullptr, PLA_B200_E_INVALID, "an initial state or state_init_zero is required");
-  PLA_REQUIRE(a.slot_indices != nullptr || a.state_by_request, PLA_B200_E_INVALID, "slot indices are required");
-  PLA_REQUIRE(!a.write_state || a.state_out != nullptr || a.state != nullptr, PLA_B200_E_INVALID,
-              "a final state needs somewhere to go");
+  if (a.prescan) {
+    PLA_REQUIRE(a.state_out != nullptr && aligned16(a.state_out), PLA_B200_E_INVALID,
+                "prescan needs a 16-byte aligned state_out of [N, HV, 2, 128, 128] fp32");
+  } else {
+    PLA_REQUIRE(a.state_init_zero || a.state != nullptr, PLA_B200_E_INVALID,
+                "an initial state or state_init_zero is required");
+    PLA_REQUIRE(a.slot_indices != nullptr || a.state_by_request, PLA_B200_E_INVALID, "slot indices are required");
+    PLA_REQUIRE(!a.write_state || a.state_out != nullptr || a.state != nullptr, PLA_B200_E_INVALID,
+                "a final state needs somewhere to go");
+  }
   PLA_REQUIRE(aligned16(a.o), PLA_B200_E_ALIGN, "o must be 16-byte aligned");
   auto launch_chain = [&](auto kern) -> int {
     static bool configured[64] = {};
@@ -863,7 +900,7 @@ extern "C" int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args,
                                        static_cast<int>(sizeof(ChainSmem) + 1024)));
       configured[dev] = true;
     }
-    const int64_t ctas = static_cast<int64_t>(a.N) * a.HV + 32;
+    const int64_t ctas = a.prescan ? static_cast<int64_t>(a.N) * a.HV * 2 : static_cast<int64_t>(a.N) * a.HV + 32;
     PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "N*HV exceeds the grid limit");
     kern<<<static_cast<unsigned>(ctas), CHAIN_THREADS, sizeof(ChainSmem) + 1024, s>>>(a);
     PLA_CUDA_OK(cudaGetLastError());

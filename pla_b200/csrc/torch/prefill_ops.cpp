@@ -149,12 +149,13 @@ void prefill_recurrent(const at::Tensor& q, const at::Tensor& k, const at::Tenso
 
 // Chunked (chunk 64) GDN prefill on the tensor cores. Returns the scratch workspace it allocated
 // from the caching allocator (callers normally drop it; tests inspect the operand images).
-at::Tensor gdn_prefill_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& gate,
-                               const at::Tensor& beta, const Optional& A_log, const Optional& dt_bias, at::Tensor out,
-                               const Optional& g_cum, const at::Tensor& cu_seqlens, const Optional& state_in,
-                               const Optional& in_indices, const Optional& state_out, const Optional& out_indices,
-                               bool transposed, bool normalize_qk, double scale, bool gate_activated,
-                               bool update_in_place, int64_t max_chunks, int64_t stage, const Optional& status) {
+at::Tensor run_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& gate,
+                       const at::Tensor& beta, const Optional& A_log, const Optional& dt_bias, at::Tensor out,
+                       const Optional& g_cum, const at::Tensor& cu_seqlens, const Optional& state_in,
+                       const Optional& in_indices, const Optional& state_out, const Optional& out_indices,
+                       bool transposed, bool normalize_qk, double scale, bool gate_activated, bool update_in_place,
+                       int64_t max_chunks, int64_t stage, const Optional& status, const Optional& workspace_in,
+                       bool prescan) {
   check_cuda(q, "q");
   const int64_t T = q.size(0);
   TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3, "q, k, v must be [tokens, heads, 128]");
@@ -232,7 +233,13 @@ at::Tensor gdn_prefill_chunked(const at::Tensor& q, const at::Tensor& k, const a
     g.state_by_request = 1;
     if (state_in.has_value()) TORCH_CHECK(state_in->size(0) >= N, "the initial state needs one slot per sequence");
   }
-  if (state_out.has_value()) {
+  if (prescan) {
+    TORCH_CHECK(state_out.has_value() && state_out->scalar_type() == at::kFloat && state_out->is_contiguous() &&
+                    state_out->numel() == N * H * 2 * 128 * 128 && state_out->device() == q.device(),
+                "a prescan stores contiguous fp32 [batch, H, 2, 128, 128] on q's device");
+    g.state_out = state_out->data_ptr();
+    g.prescan = 1;
+  } else if (state_out.has_value()) {
     state_ok(*state_out, H, q, "final state");
     if (state_in.has_value())
       TORCH_CHECK(state_out->scalar_type() == state_in->scalar_type(), "initial and final state dtypes must match");
@@ -261,12 +268,48 @@ at::Tensor gdn_prefill_chunked(const at::Tensor& q, const at::Tensor& k, const a
   g.normalize_qk = normalize_qk;
   g.stage = static_cast<int32_t>(stage);
   const int64_t bytes = pla_b200_gdn_chunk_workspace_bytes(g.max_chunks, g.H, g.HV);
-  at::Tensor workspace = at::empty({std::max<int64_t>(bytes, 16)}, q.options().dtype(at::kByte));
+  at::Tensor workspace;
+  if (workspace_in.has_value()) {
+    workspace = *workspace_in;
+    TORCH_CHECK(workspace.scalar_type() == at::kByte && workspace.is_contiguous() && workspace.numel() >= bytes &&
+                    workspace.device() == q.device(),
+                "the workspace must be contiguous uint8 of at least ", bytes, " bytes on q's device");
+  } else {
+    TORCH_CHECK(stage != 2, "stage 2 runs over the workspace of a stage-1 call");
+    workspace = at::empty({std::max<int64_t>(bytes, 16)}, q.options().dtype(at::kByte));
+  }
   g.workspace = workspace.data_ptr();
   g.workspace_bytes = bytes;
   g.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
   check_abi(pla_b200_gdn_prefill_chunked(&g, stream_of(q)), "gdn chunked prefill");
   return workspace;
+}
+
+at::Tensor gdn_prefill_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& gate,
+                               const at::Tensor& beta, const Optional& A_log, const Optional& dt_bias, at::Tensor out,
+                               const Optional& g_cum, const at::Tensor& cu_seqlens, const Optional& state_in,
+                               const Optional& in_indices, const Optional& state_out, const Optional& out_indices,
+                               bool transposed, bool normalize_qk, double scale, bool gate_activated,
+                               bool update_in_place, int64_t max_chunks, int64_t stage, const Optional& status) {
+  return run_chunked(q, k, v, gate, beta, A_log, dt_bias, out, g_cum, cu_seqlens, state_in, in_indices, state_out,
+                     out_indices, transposed, normalize_qk, scale, gate_activated, update_in_place, max_chunks, stage,
+                     status, c10::nullopt, false);
+}
+
+// The same kernels, one stage at a time, for context parallelism: stage 1 fills `workspace` (or a
+// fresh one) from the rank's tokens; stage 2 with prescan stores each (sequence, head)'s offset and
+// transition into `state_out` [batch, H, 2, 128, 128]; stage 2 without prescan is the ordinary
+// chain from `state_in`. Returns the workspace.
+at::Tensor gdn_prefill_chunked_stage(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                     const at::Tensor& gate, const at::Tensor& beta, const Optional& A_log,
+                                     const Optional& dt_bias, at::Tensor out, const Optional& g_cum,
+                                     const at::Tensor& cu_seqlens, const Optional& state_in, const Optional& state_out,
+                                     const Optional& workspace, bool transposed, bool normalize_qk, double scale,
+                                     bool gate_activated, int64_t max_chunks, int64_t stage, bool prescan,
+                                     const Optional& status) {
+  return run_chunked(q, k, v, gate, beta, A_log, dt_bias, out, g_cum, cu_seqlens, state_in, c10::nullopt, state_out,
+                     c10::nullopt, transposed, normalize_qk, scale, gate_activated, false, max_chunks, stage, status,
+                     workspace, prescan);
 }
 
 }  // namespace
@@ -279,6 +322,12 @@ TORCH_LIBRARY_FRAGMENT(pla_b200, m) {
       "Tensor(c!)? state_out, Tensor? out_indices, bool transposed, bool normalize_qk, float scale, "
       "bool gate_activated, bool update_in_place, int max_chunks, int stage, Tensor(d!)? status) -> Tensor",
       &pla_ops::gdn_prefill_chunked);
+  m.def(
+      "gdn_prefill_chunked_stage(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor? A_log, "
+      "Tensor? dt_bias, Tensor(a!) out, Tensor(e!)? g_cum, Tensor cu_seqlens, Tensor? state_in, Tensor(c!)? state_out, "
+      "Tensor(w!)? workspace, bool transposed, bool normalize_qk, float scale, bool gate_activated, int max_chunks, "
+      "int stage, bool prescan, Tensor(d!)? status) -> Tensor",
+      &pla_ops::gdn_prefill_chunked_stage);
   m.def(
       "prefill_recurrent(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor? A_log, Tensor? dt_bias, "
       "Tensor(a!) out, Tensor cu_seqlens, Tensor(b!)? state_in, Tensor? in_indices, Tensor(c!)? state_out, "

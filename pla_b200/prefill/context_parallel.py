@@ -1,0 +1,162 @@
+"""Context-parallel GDN prefill: one long sequence cut into contiguous token ranges, one per GPU.
+
+Over a token range the gated delta rule is an affine map of the incoming state, row by row of the
+k-last state ``S[v, k]``:  ``S_out = S_in @ M + B``  with ``M [K, K]`` the product of the per-token
+transitions ``gamma_t (I - beta_t k_t k_t^T)`` and ``B [V, K]`` the state reached from zero
+(the reference derives the same pair for its intra-card split:
+docs/prefill_flashkdapro_cp_design.md:22-46, src/prefill/flashqla/kernels/prepare_h_cute.cu:59-67).
+
+Per rank:
+  1. prepare     chunk operands of the rank's tokens (tensor-core kernel, shared by 2 and 5)
+  2. prescan     two chains per value head, no output: B from a zero state, M from the identity with V = 0
+  3. all-gather  ``[H, 2, 128, 128]`` fp32 per rank -- the only collective on the path
+  4. fold        ``S_in(r) = fold_{j<r}(M_j, B_j)(S_0)``: at most ``world-1`` batched 128^3 products,
+                 recomputed on every rank instead of a second collective
+  5. segment     the ordinary chain from ``S_in(r)``; the last rank's final state is the sequence's
+
+The last rank's (M, B) is never used, so it skips step 2 and contributes zeros to the gather.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+D = 128
+CHUNK = 64
+
+
+class CudaSegmentKernels:
+    """Steps 1, 2 and 5 on the rank's GPU (pla_b200_gdn_prefill_chunked, stages 1 and 2)."""
+
+    def __init__(self, q, k, v, gate, beta, A_log, dt_bias, scale, normalize_qk, gate_activated):
+        from .._ops import ops  # raises ImportError when the native libraries are missing
+        self._ops = ops
+        self.a = (q, k, v, gate, beta, A_log, dt_bias)
+        self.scale, self.normalize_qk, self.gate_activated = float(scale), bool(normalize_qk), bool(gate_activated)
+        T, H = v.shape[0], v.shape[1]
+        self.T, self.H = T, H
+        self.cu = torch.tensor([0, T], dtype=torch.int32, device=q.device)
+        self.max_chunks = (T + CHUNK - 1) // CHUNK
+        self.out = torch.empty(T, H, D, dtype=q.dtype, device=q.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        self.ws = None
+
+    def _stage(self, stage, prescan, state_in, state_out):
+        q, k, v, gate, beta, A_log, dt_bias = self.a
+        self.ws = self._ops.gdn_prefill_chunked_stage(
+            q, k, v, gate, beta, A_log, dt_bias, self.out, None, self.cu, state_in, state_out, self.ws, False,
+            self.normalize_qk, self.scale, self.gate_activated, self.max_chunks, stage, prescan, self.status)
+
+    def prepare(self):
+        self._stage(1, False, None, None)
+
+    def prescan(self) -> torch.Tensor:
+        mb = torch.empty(1, self.H, 2, D, D, dtype=torch.float32, device=self.out.device)
+        self._stage(2, True, None, mb)
+        return mb[0]
+
+    def segment(self, state_in: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        final = torch.empty(1, self.H, D, D, dtype=torch.float32, device=self.out.device)
+        self._stage(2, False, state_in[None].contiguous(), final)
+        return self.out, final[0]
+
+    def check(self):
+        code = int(self.status.item())
+        if code:
+            raise RuntimeError(f"chunked prefill reported device status {code:#x}")
+
+
+class SegmentPlan:
+    """State of one rank between the two halves of the algorithm."""
+
+    def __init__(self, kernels, rank, world, tokens, H, device, transfer):
+        self.kernels, self.rank, self.world, self.tokens, self.H = kernels, rank, world, tokens, H
+        self.device, self.transfer = device, transfer
+
+
+def identity_transfer(H: int, device) -> torch.Tensor:
+    """(B, M) of an empty token range: zero offset, identity transition."""
+    mb = torch.zeros(H, 2, D, D, dtype=torch.float32, device=device)
+    mb[:, 1] = torch.eye(D, dtype=torch.float32, device=device)
+    return mb
+
+
+def begin_segment(kernels, rank: int, world: int, tokens: int, H: int, device) -> SegmentPlan:
+    """Steps 1-2. ``transfer`` is what the rank contributes to the all-gather."""
+    if tokens > 0:
+        kernels.prepare()
+    if rank == world - 1:
+        transfer = torch.zeros(H, 2, D, D, dtype=torch.float32, device=device)      # never read
+    elif tokens == 0:
+        transfer = identity_transfer(H, device)
+    else:
+        transfer = kernels.prescan()
+    return SegmentPlan(kernels, rank, world, tokens, H, device, transfer)
+
+
+def fold_transfers(initial_state: Optional[torch.Tensor], gathered: torch.Tensor, rank: int) -> torch.Tensor:
+    """Step 4: the state entering rank ``rank``'s range. gathered: [world, H, 2, 128, 128] (B, M)."""
+    H = gathered.shape[1]
+    if initial_state is None:
+        state = torch.zeros(H, D, D, dtype=torch.float32, device=gathered.device)
+    else:
+        state = initial_state.to(torch.float32)
+    for j in range(rank):
+        state = torch.baddbmm(gathered[j, :, 0], state, gathered[j, :, 1])
+    return state
+
+
+def finish_segment(plan: SegmentPlan, initial_state: Optional[torch.Tensor], gathered: torch.Tensor):
+    """Steps 4-5. Returns (o [tokens, H, 128], state leaving this rank's range [H, 128, 128])."""
+    state_in = fold_transfers(initial_state, gathered, plan.rank)
+    if plan.tokens == 0:
+        return None, state_in
+    return plan.kernels.segment(state_in)
+
+
+def gdn_prefill_context_parallel(
+    q: torch.Tensor,                       # [T_rank, Hg, 128] this rank's tokens
+    k: torch.Tensor,                       # [T_rank, Hg, 128]
+    v: torch.Tensor,                       # [T_rank, H, 128]
+    gate: torch.Tensor,                    # [T_rank, H] raw gate input (or fp32 log decay when gate_activated)
+    beta: torch.Tensor,                    # [T_rank, H] raw beta input (or fp32 beta when gate_activated)
+    A_log: Optional[torch.Tensor] = None,  # [H] fp32
+    dt_bias: Optional[torch.Tensor] = None,
+    initial_state: Optional[torch.Tensor] = None,   # [H, 128(V), 128(K)] fp32, the same on every rank
+    scale: Optional[float] = None,
+    normalize_qk: bool = True,
+    gate_activated: bool = False,
+    output_final_state: bool = True,
+    group: Optional[dist.ProcessGroup] = None,
+    segment_kernels=None,
+):
+    """Rank ``r`` of ``group`` holds tokens ``[sum(T_j, j<r), sum(T_j, j<=r))`` of one sequence; ranges
+    may have different (even zero) lengths and need no alignment. Returns ``(o, final_state)``:
+    this rank's output rows and, when ``output_final_state``, the sequence's final state on every rank.
+
+    ``segment_kernels`` replaces the GPU steps (host-side tests of the exchange); by default the CUDA
+    kernels run and a missing native library is an ImportError.
+    """
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    T, H = v.shape[0], v.shape[1]
+    if scale is None:
+        scale = D ** -0.5
+    kernels = segment_kernels
+    if kernels is None:
+        kernels = CudaSegmentKernels(q, k, v, gate, beta, A_log, dt_bias, scale, normalize_qk, gate_activated)
+    plan = begin_segment(kernels, rank, world, T, H, v.device)
+    gathered = torch.empty(world, H, 2, D, D, dtype=torch.float32, device=v.device)
+    dist.all_gather_into_tensor(gathered, plan.transfer[None].contiguous(), group=group)
+    o, state_out = finish_segment(plan, initial_state, gathered)
+    if o is None:
+        o = v.new_empty((0, H, D))
+    final = None
+    if output_final_state:
+        final = state_out.contiguous()
+        dist.broadcast(final, src=dist.get_global_rank(group, world - 1) if group is not None else world - 1,
+                       group=group)
+    if hasattr(kernels, "check"):
+        kernels.check()
+    return o, final

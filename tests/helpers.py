@@ -32,3 +32,36 @@ def assert_state_close(state, ref, what="state", tol=STATE_REL_L2):
     assert torch.isfinite(state).all(), f"{what}: non-finite values"
     r = rel_l2(state, ref)
     assert r <= tol, f"{what}: rel-L2 {r:.3e} > {tol}"
+
+
+class OracleSegmentKernels:
+    """The three GPU steps restated with the oracle's token recurrence (test double)."""
+
+    def __init__(self, q, k, v, gate, beta, A_log, dt_bias, scale):
+        self.q, self.k, self.v, self.gate, self.beta = q, k, v, gate, beta
+        self.A_log, self.dt_bias, self.scale = A_log, dt_bias, scale
+        self.H = v.shape[1]
+
+    def _run(self, v, state):
+        out, new_state, _ = _odec().klast_forward(q=self.q, k=self.k, v=v, a=self.gate, b=self.beta, A_log=self.A_log,
+                                               dt_bias=self.dt_bias, state=state[None], slot_indices=[0],
+                                               lengths=[v.shape[0]], scale=self.scale)
+        return out, new_state[0]
+
+    def prepare(self):
+        pass
+
+    def prescan(self):
+        zero = torch.zeros(self.H, 128, 128)
+        eye = torch.eye(128).expand(self.H, 128, 128).contiguous()
+        _, B = self._run(self.v, zero)
+        _, M = self._run(torch.zeros_like(self.v), eye)
+        return torch.stack([B, M], dim=1)
+
+    def segment(self, state_in):
+        return self._run(self.v, state_in)
+
+
+def _odec():
+    from oracle import decode
+    return decode

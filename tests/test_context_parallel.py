@@ -1,0 +1,84 @@
+"""Host side of the context-parallel prefill on CPU: gloo ranks exchange (offset, transition) pairs
+computed by the oracle recurrence and must reproduce the serial recurrence."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from helpers import OracleSegmentKernels
+from oracle import decode as odec
+from pla_b200.prefill import context_parallel as cp
+
+D = 128
+
+
+def make_inputs(T, Hg, H, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(T, Hg, D, generator=g).bfloat16()
+    k = torch.randn(T, Hg, D, generator=g).bfloat16()
+    v = torch.randn(T, H, D, generator=g).bfloat16()
+    gate = torch.randn(T, H, generator=g).bfloat16()
+    beta = torch.randn(T, H, generator=g).bfloat16()
+    A_log = torch.rand(H, generator=g) * 2.0
+    dt_bias = torch.randn(H, generator=g) * 0.1
+    S0 = torch.randn(H, D, D, generator=g) * 0.05
+    return q, k, v, gate, beta, A_log, dt_bias, S0
+
+
+def _worker(rank, world, port, splits, with_state, result_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        T = sum(splits)
+        q, k, v, gate, beta, A_log, dt_bias, S0 = make_inputs(T, 1, 2, 5)
+        lo = sum(splits[:rank])
+        hi = lo + splits[rank]
+        sl = slice(lo, hi)
+        kern = OracleSegmentKernels(q[sl], k[sl], v[sl], gate[sl], beta[sl], A_log, dt_bias, D ** -0.5)
+        o, final = cp.gdn_prefill_context_parallel(q[sl], k[sl], v[sl], gate[sl], beta[sl], A_log, dt_bias,
+                                                   initial_state=S0 if with_state else None, segment_kernels=kern)
+        torch.save({"o": o, "final": final}, os.path.join(result_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("splits,with_state", [((37, 43), True), ((30, 0, 25), False)])
+def test_gloo_ranks_reproduce_the_serial_recurrence(tmp_path, splits, with_state):
+    world = len(splits)
+    mp.spawn(_worker, args=(world, _free_port(), splits, with_state, str(tmp_path)), nprocs=world, join=True)
+    T = sum(splits)
+    q, k, v, gate, beta, A_log, dt_bias, S0 = make_inputs(T, 1, 2, 5)
+    state = S0 if with_state else torch.zeros_like(S0)
+    exp_out, exp_state, _ = odec.klast_forward(q=q, k=k, v=v, a=gate, b=beta, A_log=A_log, dt_bias=dt_bias,
+                                               state=state[None], slot_indices=[0], lengths=[T], scale=D ** -0.5)
+    outs = []
+    for r in range(world):
+        res = torch.load(os.path.join(tmp_path, f"rank{r}.pt"))
+        assert res["o"].shape[0] == splits[r]
+        outs.append(res["o"].float())
+        torch.testing.assert_close(res["final"], exp_state[0], rtol=1e-4, atol=1e-5)   # same on every rank
+    torch.testing.assert_close(torch.cat(outs), exp_out.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_fold_is_the_composition_of_affine_maps():
+    g = torch.Generator().manual_seed(0)
+    H, W = 3, 4
+    gathered = torch.randn(W, H, 2, D, D, generator=g) * 0.1
+    S0 = torch.randn(H, D, D, generator=g)
+    s = S0.clone()
+    for r in range(W):
+        torch.testing.assert_close(cp.fold_transfers(S0, gathered, r), s)
+        s = s @ gathered[r, :, 1] + gathered[r, :, 0]
+    ident = cp.identity_transfer(H, "cpu")
+    torch.testing.assert_close(cp.fold_transfers(S0, ident[None], 1), S0)
+    assert torch.equal(cp.fold_transfers(None, gathered, 0), torch.zeros(H, D, D))

@@ -1,0 +1,79 @@
+"""Context-parallel prefill kernels on one GPU: the ranks of a group are emulated one after another
+(no kernel waits on another), so the prescan pairs, the fold and the segment pass are all checked
+against the single-pass kernel and the CPU oracle."""
+import pytest
+import torch
+
+from helpers import OracleSegmentKernels, assert_out_close, assert_state_close
+from oracle import decode as odec
+
+pytestmark = pytest.mark.gpu
+D = 128
+
+
+def make(T, Hg, H, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(T, Hg, D, generator=g).bfloat16()
+    k = torch.randn(T, Hg, D, generator=g).bfloat16()
+    v = torch.randn(T, H, D, generator=g).bfloat16()
+    gate = torch.randn(T, H, generator=g).bfloat16()
+    beta = torch.randn(T, H, generator=g).bfloat16()
+    A_log = torch.rand(H, generator=g) * 2.0
+    dt_bias = torch.randn(H, generator=g) * 0.1
+    S0 = torch.randn(H, D, D, generator=g) * 0.05
+    return q, k, v, gate, beta, A_log, dt_bias, S0
+
+
+def test_prescan_pairs_match_the_oracle(native_built):
+    from pla_b200.prefill import context_parallel as cp
+    T, Hg, H = 200, 1, 2
+    q, k, v, gate, beta, A_log, dt_bias, _ = make(T, Hg, H, 11)
+    ref = OracleSegmentKernels(q, k, v, gate, beta, A_log, dt_bias, D ** -0.5).prescan()
+    kern = cp.CudaSegmentKernels(q.cuda(), k.cuda(), v.cuda(), gate.cuda(), beta.cuda(), A_log.cuda(), dt_bias.cuda(),
+                                 D ** -0.5, True, False)
+    kern.prepare()
+    mb = kern.prescan()
+    kern.check()
+    assert_state_close(mb[:, 0].cpu(), ref[:, 0], "offset B")
+    assert_state_close(mb[:, 1].cpu(), ref[:, 1], "transition M")
+
+
+@pytest.mark.parametrize("splits", [(400, 0, 333, 767), (64, 64), (1000,)])
+def test_emulated_ranks_match_single_pass_and_oracle(native_built, splits):
+    from pla_b200._ops import ops
+    from pla_b200.prefill import context_parallel as cp
+    T, Hg, H, W = sum(splits), 2, 4, len(splits)
+    q, k, v, gate, beta, A_log, dt_bias, S0 = make(T, Hg, H, 23)
+    dev = torch.device("cuda")
+    dq, dk, dv, dg, db = (x.to(dev) for x in (q, k, v, gate, beta))
+    dA, dB, dS0 = A_log.to(dev), dt_bias.to(dev), S0.to(dev)
+    plans, lo = [], 0
+    for r, n in enumerate(splits):
+        sl = slice(lo, lo + n)
+        kern = cp.CudaSegmentKernels(dq[sl], dk[sl], dv[sl], dg[sl], db[sl], dA, dB, D ** -0.5, True, False)
+        plans.append(cp.begin_segment(kern, r, W, n, H, dev))
+        lo += n
+    gathered = torch.stack([p.transfer for p in plans])
+    outs, state = [], None
+    for p in plans:
+        o, state = cp.finish_segment(p, dS0, gathered)
+        if o is not None:
+            outs.append(o)
+        p.kernels.check()
+    out = torch.cat(outs)
+
+    # the same kernels in a single pass
+    one = torch.empty(T, H, D, dtype=torch.bfloat16, device=dev)
+    final = torch.empty(1, H, D, D, dtype=torch.float32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.gdn_prefill_chunked(dq, dk, dv, dg, db, dA, dB, one, None, torch.tensor([0, T], dtype=torch.int32, device=dev),
+                            dS0[None].contiguous(), None, final, None, False, True, D ** -0.5, False, False,
+                            (T + 63) // 64, 0, status)
+    assert status.item() == 0
+    assert_out_close(out, one, "ranks vs single pass")
+    assert_state_close(state, final[0], "ranks vs single pass")
+
+    exp_out, exp_state, _ = odec.klast_forward(q=q, k=k, v=v, a=gate, b=beta, A_log=A_log, dt_bias=dt_bias,
+                                               state=S0[None], slot_indices=[0], lengths=[T], scale=D ** -0.5)
+    assert_out_close(out, exp_out)
+    assert_state_close(state.cpu(), exp_state[0])

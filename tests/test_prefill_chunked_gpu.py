@@ -190,3 +190,31 @@ def test_chunked_prefill_long_sequences_against_token_recurrence(native_built):
     assert status.item() == 0
     assert_out_close(out_a, out_b, "chunked vs token-recurrent output")
     assert_state_close(pool_a, pool_b, "chunked vs token-recurrent state")
+
+
+def test_chunked_prefill_rows_ending_at_the_allocation_end(native_built):
+    """q, k, v that fill their allocations exactly (2 MiB each, 16-byte aligned rows): the staged row
+    copies must not touch a byte past the last row."""
+    from pla_b200._ops import ops
+    g = torch.Generator().manual_seed(9)
+    T, Hg, H = 1024, 8, 8
+    q, k, v = (torch.randn(T, n, D, generator=g).bfloat16() for n in (Hg, Hg, H))
+    gates = torch.randn(T, 2 * H, generator=g).bfloat16()
+    A_log = torch.rand(H, generator=g) * float(np.log(16.0))
+    dt_bias = torch.randn(H, generator=g) * 0.1
+    exp_out, exp_state, _ = odec.klast_forward(q=q, k=k, v=v, a=gates[:, :H], b=gates[:, H:], A_log=A_log,
+                                               dt_bias=dt_bias, state=torch.zeros(1, H, D, D), slot_indices=[0],
+                                               lengths=[T], scale=D ** -0.5)
+    dq, dk, dv = q.cuda(), k.cuda(), v.cuda()
+    assert all(x.numel() * 2 == 2 << 20 and x.data_ptr() % 16 == 0 for x in (dq, dk, dv))
+    dg = gates.cuda()
+    out = torch.empty(T, H, D, dtype=torch.bfloat16, device="cuda")
+    final = torch.empty(1, H, D, D, dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.gdn_prefill_chunked(dq, dk, dv, dg[:, :H], dg[:, H:], A_log.cuda(), dt_bias.cuda(), out, None,
+                            torch.tensor([0, T], dtype=torch.int32, device="cuda"), None, None, final, None, False,
+                            True, D ** -0.5, False, False, T // C, 0, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert_out_close(out, exp_out)
+    assert_state_close(final.cpu()[0], exp_state[0])
