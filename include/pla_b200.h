@@ -292,9 +292,62 @@ typedef struct pla_b200_kda_verify_args {
   int32_t gate;               /* pla_b200_gate */
   float scale, lower_bound, softplus_beta, softplus_threshold;
   int32_t* status;
+  /* optional fused gated output RMSNorm over the 128 value channels of each (token, head)
+   * (src/decode/kda_replayssm/kda_mtp_verify.cu:185-212):
+   *   out = o * rsqrt(mean(o^2) + eps) * weight * sigmoid(gate),  o the unrounded fp32 output.
+   * All of onorm_gate, onorm_weight and out_f32 or none. */
+  const void* onorm_gate;     /* bf16 [T, H*128] view */
+  int64_t onorm_gate_tok_stride;
+  const float* onorm_weight;  /* [128] */
+  float onorm_eps;
+  float* out_f32;             /* staging [T, H*128] fp32, overwritten */
+  int32_t win_steps;          /* step capacity of the conv-window tensors when smaller than Q; 0 = Q */
 } pla_b200_kda_verify_args;
 
 int pla_b200_kda_replay_verify(const pla_b200_kda_verify_args* args, void* stream);
+/* The same kernels under the SGLang contract (launch_verify, src/decode/kda_replayssm/kda_mtp_abi.h:127-136):
+ * requires row_by_slot = 1, i.e. records are rings addressed by state slot [slots, H, Q, 128] and
+ * conv windows are addressed by scratch_idx. */
+int pla_b200_kda_ring_verify(const pla_b200_kda_verify_args* args, void* stream);
+
+/* Exact fold of each request's accepted ring prefix into the fp32 state of every layer, in place,
+ * one launch (launch_fold, src/decode/kda_replayssm/kda_mtp_abi.h:138-145; kernel
+ * kda_mtp_fold.cu:254-529). Request b folds accept_lens[b] steps of ring row slot_idx[b] into
+ * state[layer, slot_idx[b]]; rows with slot <= null_block_id or accept_lens <= 0 are skipped.
+ * With tracking, the state after step track_step[b] (0-based) is also stored to slot track_idx[b]. */
+typedef struct pla_b200_kda_fold_args {
+  float* state;               /* [layers, slots, HV, 128(V), 128(K)] */
+  int64_t state_layer_stride, state_slot_stride;
+  const void* rawv;           /* bf16 [layers, slots, HV, L, 128] */
+  int64_t rawv_layer_stride, rawv_slot_stride;
+  const void* rawk;           /* bf16 [layers, slots, H, L, 128] */
+  int64_t rawk_layer_stride, rawk_slot_stride;
+  const float* gate;          /* [layers, slots, HV, L, 128] log-decay */
+  int64_t gate_layer_stride, gate_slot_stride;
+  const float* beta;          /* [layers, slots, HV, L] */
+  int64_t beta_layer_stride, beta_slot_stride;
+  pla_b200_index slot_idx, accept_lens;   /* [B] */
+  pla_b200_index track_idx, track_step;   /* [B]; data NULL = no tracking */
+  int32_t layers, B, H, HV, L, slots, null_block_id;
+  int32_t* status;
+} pla_b200_kda_fold_args;
+
+int pla_b200_kda_fold_layers(const pla_b200_kda_fold_args* args, void* stream);
+
+/* Conv-state rollback: dst[layer, dst_idx[n], :, :] = src[layer, n, step_idx[n], :, :], byte-exact, for
+ * every request n with step_idx[n] >= 0 and a destination in range (launch_conv_scatter,
+ * src/decode/kda_replayssm/kda_mtp_abi.h:147-150; kernel kda_mtp_fold.cu:595-640). */
+typedef struct pla_b200_kda_conv_scatter_args {
+  void* dst;                  /* [layers, slots, dim, taps], any positive strides */
+  const void* src;            /* [layers, rows, steps, dim, taps] */
+  int64_t dst_layer, dst_slot, dst_channel, dst_tap;            /* element strides */
+  int64_t src_layer, src_row, src_step, src_channel, src_tap;
+  pla_b200_index dst_idx, step_idx;   /* [reqs] */
+  int32_t elem_size;          /* 2 (bf16) or 4 (fp32) */
+  int32_t layers, reqs, dim, taps, src_rows, src_steps, dst_slots;
+} pla_b200_kda_conv_scatter_args;
+
+int pla_b200_kda_conv_scatter(const pla_b200_kda_conv_scatter_args* args, void* stream);
 
 /* Columns of the per-layer descriptor table (int64 [layers, 11], device memory)
  * (src/decode/kda_replayssm/kda_mtp_abi.h:115-118). */

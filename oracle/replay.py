@@ -181,3 +181,80 @@ def commit_apply(state, conv_ds, records, plan, source, null_block_id=0):
         new_state[final] = fold_state(old[src], *args, n).float()
         new_conv[final, :, :3] = records.conv[b, n - 1]
     return new_state, new_conv
+
+
+# ---- SGLang contract: rings addressed by state slot, conv windows by scratch row ----
+
+def ring_verify(vi: dict) -> dict:
+    """fused_kda_decode_mtp_dspark in fp64 over an input dict with the entry point's keyword names
+    (_reference.py:92-180): returns out [1,T,H,128], the four rings and the three conv-window tensors
+    as they are after the call (inputs are not modified). Requests with a slot < 0 are skipped."""
+    f = torch.float64
+    x_q = vi["x_q"][0]
+    T, H, _ = x_q.shape
+    slots = [int(s) for s in vi["ssm_state_indices"]]
+    scratch = [int(s) for s in vi["intermediate_state_indices"]]
+    cu = [int(c) for c in vi["cu_seqlens"]]
+    out = torch.zeros(1, T, H, D, dtype=f)
+    rings = {k: vi[k].to(f).clone() for k in ("replayssm_rawv", "replayssm_rawk", "replayssm_g", "replayssm_beta")}
+    wins = {k: vi[k].to(f).clone() for k in ("intermediate_conv_q", "intermediate_conv_k", "intermediate_conv_v")}
+    for n, slot in enumerate(slots):
+        if slot < 0:
+            continue
+        b, e = cu[n], cu[n + 1]
+        if e <= b:
+            continue
+        r = verify_request(vi["x_q"][0, b:e], vi["x_k"][0, b:e], vi["x_v"][0, b:e], vi["g"][0, b:e], vi["beta"][0, b:e],
+                           vi["w_q"], vi["w_k"], vi["w_v"], vi["cs_q"][slot], vi["cs_k"][slot], vi["cs_v"][slot],
+                           vi["A_log"], vi["dt_bias"], vi["recurrent_state"][slot], float(vi["scale"]),
+                           vi["lower_bound"])
+        n_tok = e - b
+        out[0, b:e] = r["out"]
+        rings["replayssm_rawv"][slot, :, :n_tok] = r["rawv"]
+        rings["replayssm_rawk"][slot, :, :n_tok] = r["rawk"]
+        rings["replayssm_g"][slot, :, :n_tok] = r["g"]
+        rings["replayssm_beta"][slot, :, :n_tok] = r["beta"]
+        wins["intermediate_conv_q"][scratch[n], :n_tok] = r["win_q"]
+        wins["intermediate_conv_k"][scratch[n], :n_tok] = r["win_k"]
+        wins["intermediate_conv_v"][scratch[n], :n_tok] = r["win_v"]
+    if vi.get("onorm_gate") is not None:
+        # gated RMSNorm over the value channels, from the unrounded output (_reference.py:170-175)
+        gate = torch.sigmoid(vi["onorm_gate"][0].to(f))
+        rms = torch.rsqrt((out[0] * out[0]).mean(-1, keepdim=True) + float(vi["onorm_eps"]))
+        out = (out[0] * rms * vi["onorm_weight"].to(f)[None, None, :] * gate)[None]
+    return dict(out=out, **rings, **wins)
+
+
+def fold_layers(temporal, rawv, rawk, gk, beta, slot_idx, accept_lens, track_idx=None, track_step=None,
+                null_block_id: int = -1):
+    """commit-time exact fold for all layers (_reference.py:183-216; tracking as in
+    src/decode/kda_replayssm/kda_mtp_fold.cu:470-485: the state after 0-based step track_step[b] also
+    goes to slot track_idx[b]). temporal [layers,slots,HV,V,K]; rawk has H <= HV heads. Returns the
+    folded copy in fp64."""
+    f = torch.float64
+    new = temporal.to(f).clone()
+    layers, _, HV = temporal.shape[:3]
+    grp = HV // rawk.shape[2]
+    for l in range(layers):
+        for b, slot in enumerate(int(s) for s in slot_idx):
+            n = int(accept_lens[b])
+            if slot <= null_block_id or n <= 0:
+                continue
+            kk = rawk[l, slot].repeat_interleave(grp, dim=0)
+            if track_idx is not None:
+                tt, ts = int(track_step[b]), int(track_idx[b])
+                if 0 <= tt < n and ts > null_block_id:
+                    new[l, ts] = fold_state(temporal[l, slot], kk, rawv[l, slot], gk[l, slot], beta[l, slot], tt + 1)
+            new[l, slot] = fold_state(temporal[l, slot], kk, rawv[l, slot], gk[l, slot], beta[l, slot], n)
+    return new
+
+
+def conv_window_scatter(dst, src, dst_idx, step_idx):
+    """dst[layer, dst_idx[n]] = src[layer, n, step_idx[n]] for requests with step >= 0 and a valid
+    destination (src/decode/kda_replayssm/kda_mtp_fold.cu:595-618). Returns the updated copy."""
+    new = dst.clone()
+    for n, (d, s) in enumerate(zip((int(x) for x in dst_idx), (int(x) for x in step_idx))):
+        if s < 0 or d < 0 or d >= dst.shape[1] or n >= src.shape[1] or s >= src.shape[2]:
+            continue
+        new[:, d] = src[:, n, s]
+    return new

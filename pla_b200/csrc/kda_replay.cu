@@ -104,6 +104,10 @@ __device__ __forceinline__ void kda_step(float* s_state, const float* sk, const 
 }
 
 // ------------------------------------------------------------------ verify
+// Longest window a request may have: the record steps, or the conv-window steps when fewer.
+__device__ __forceinline__ int window_capacity(const pla_b200_kda_verify_args& p) {
+  return p.win_steps > 0 ? min(p.Q, p.win_steps) : p.Q;
+}
 __global__ void __launch_bounds__(NT) kda_verify_kernel(const pla_b200_kda_verify_args p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   Smem& sh = *reinterpret_cast<Smem*>(smem_raw);
@@ -117,7 +121,7 @@ __global__ void __launch_bounds__(NT) kda_verify_kernel(const pla_b200_kda_verif
   const int64_t begin = idx_at(p.cu, n), end = idx_at(p.cu, n + 1);
   const int64_t slot = idx_at(p.slot_idx, n);
   // rows whose metadata is unusable are left completely alone
-  if (idx_at(p.cu, 0) != 0 || begin < 0 || end < begin || end > p.T || end - begin > p.Q || slot >= p.slots ||
+  if (idx_at(p.cu, 0) != 0 || begin < 0 || end < begin || end > p.T || end - begin > window_capacity(p) || slot >= p.slots ||
       begin == end)
     return;
   const int n_tok = static_cast<int>(end - begin);
@@ -259,8 +263,38 @@ __global__ void __launch_bounds__(NT) kda_verify_kernel(const pla_b200_kda_verif
                      lane);
     }
     __syncthreads();
-    for (int i = tid; i < nt * BV; i += NT)
-      out[(begin + t0 + i / BV) * out_stride + (i % BV)] = __float2bfloat16(sh.o[i / BV][i % BV]);
+    if (p.out_f32 != nullptr) {
+      float* of = p.out_f32 + static_cast<int64_t>(h) * D + row0;
+      for (int i = tid; i < nt * BV; i += NT) of[(begin + t0 + i / BV) * out_stride + (i % BV)] = sh.o[i / BV][i % BV];
+    } else {
+      for (int i = tid; i < nt * BV; i += NT)
+        out[(begin + t0 + i / BV) * out_stride + (i % BV)] = __float2bfloat16(sh.o[i / BV][i % BV]);
+    }
+  }
+}
+
+// Gated RMSNorm of the staged fp32 outputs: one CTA per (request, head), one warp per token,
+// four channels per lane. Rows that verify left alone (unusable metadata, padding) stay as they are.
+__global__ void __launch_bounds__(NT) kda_onorm_kernel(const pla_b200_kda_verify_args p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.x % p.H, n = blockIdx.x / p.H;
+  const int64_t begin = idx_at(p.cu, n), end = idx_at(p.cu, n + 1);
+  const int64_t slot = idx_at(p.slot_idx, n);
+  if (idx_at(p.cu, 0) != 0 || begin < 0 || end < begin || end > p.T || end - begin > window_capacity(p) || slot >= p.slots ||
+      begin == end || slot <= p.null_block_id)
+    return;
+  const __nv_bfloat16* gate = static_cast<const __nv_bfloat16*>(p.onorm_gate);
+  const float4 w = reinterpret_cast<const float4*>(p.onorm_weight)[lane];
+  const int64_t row_elems = static_cast<int64_t>(p.H) * D;
+  for (int64_t tok = begin + warp; tok < end; tok += NW) {
+    const float4 o = *reinterpret_cast<const float4*>(p.out_f32 + tok * row_elems + h * D + lane * 4);
+    const float r = rsqrtf(warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w) * (1.0f / D) + p.onorm_eps);
+    const __nv_bfloat16* gp = gate + tok * p.onorm_gate_tok_stride + h * D + lane * 4;
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + tok * row_elems + h * D + lane * 4;
+    dst[0] = __float2bfloat16(o.x * r * w.x * sigmoidf_fast(__bfloat162float(gp[0])));
+    dst[1] = __float2bfloat16(o.y * r * w.y * sigmoidf_fast(__bfloat162float(gp[1])));
+    dst[2] = __float2bfloat16(o.z * r * w.z * sigmoidf_fast(__bfloat162float(gp[2])));
+    dst[3] = __float2bfloat16(o.w * r * w.w * sigmoidf_fast(__bfloat162float(gp[3])));
   }
 }
 
@@ -487,6 +521,103 @@ __global__ void __launch_bounds__(NT) fold_scatter_kernel(const pla_b200_kda_com
     scatter_cta(p, blockIdx.x - g.fold_ctas, g.conv_tiles);
 }
 
+// SGLang contract: rings and state of all layers in single tensors, ring row = state slot.
+__global__ void __launch_bounds__(NT) fold_layers_kernel(const pla_b200_kda_fold_args p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  Smem& sh = *reinterpret_cast<Smem*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int vs = blockIdx.x % NVS;
+  const int hvl = (blockIdx.x / NVS) % (p.layers * p.HV);
+  const int b = blockIdx.x / (NVS * p.layers * p.HV);
+  const int64_t layer = hvl / p.HV;
+  const int hv = hvl % p.HV, h = hv / (p.HV / p.H);
+  const int64_t slot = idx_at(p.slot_idx, b);
+  const int64_t n_commit = idx_at(p.accept_lens, b);
+  if (slot <= p.null_block_id || n_commit <= 0) return;
+  if (slot < 0 || slot >= p.slots || n_commit > p.L) {
+    if (tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_BAD_SLOT);
+    return;
+  }
+  const bool has_track = p.track_idx.data != nullptr;
+  const int64_t t_track = has_track ? idx_at(p.track_step, b) : -1;
+  const int64_t slot_track = has_track ? idx_at(p.track_idx, b) : p.null_block_id;
+  const int row0 = vs * BV;
+  const int64_t tile_off = static_cast<int64_t>(hv) * TILE + row0 * D;
+  float* pool = p.state + layer * p.state_layer_stride;
+  const __nv_bfloat16* rawv = static_cast<const __nv_bfloat16*>(p.rawv) + layer * p.rawv_layer_stride +
+                              slot * p.rawv_slot_stride + static_cast<int64_t>(hv) * p.L * D;
+  const __nv_bfloat16* rawk = static_cast<const __nv_bfloat16*>(p.rawk) + layer * p.rawk_layer_stride +
+                              slot * p.rawk_slot_stride + static_cast<int64_t>(h) * p.L * D;
+  const float* gate = p.gate + layer * p.gate_layer_stride + slot * p.gate_slot_stride + static_cast<int64_t>(hv) * p.L * D;
+  const float* beta = p.beta + layer * p.beta_layer_stride + slot * p.beta_slot_stride + static_cast<int64_t>(hv) * p.L;
+
+  if (tid == 0) {
+    mbar_init(&sh.bar, 1);
+    fence_mbar_init();
+    mbar_expect_tx(&sh.bar, kSliceBytes);
+    bulk_load(sh.state, pool + slot * p.state_slot_stride + tile_off, kSliceBytes, &sh.bar);
+  }
+  bool loaded = false;
+  const int n = static_cast<int>(n_commit);
+  for (int t0 = 0; t0 < n; t0 += TS) {
+    const int nt = min(TS, n - t0);
+    if (t0 > 0) __syncthreads();
+    for (int s = 0; s < nt; ++s) {
+      const int64_t rec = static_cast<int64_t>(t0 + s) * D;
+      const float kf = __bfloat162float(rawk[rec + tid]);
+      sh.k[s][tid] = kf;
+      sh.gam[s][tid] = __expf(gate[rec + tid]);
+      const float sk = warp_sum(kf * kf);
+      if (lane == 0) sh.part[s][1][warp] = sk;
+      if (tid < BV) sh.v[s][tid] = __bfloat162float(rawv[rec + row0 + tid]);
+      if (tid == 0) sh.beta[s] = beta[t0 + s];
+    }
+    __syncthreads();
+    if (!loaded) {
+      const bool ok = mbar_wait(&sh.bar, 0);
+      if (__syncthreads_or(!ok)) {
+        if (tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_WAIT_TIMEOUT);
+        (void)mbar_wait(&sh.bar, 0);
+        return;
+      }
+      loaded = true;
+    }
+    for (int s = 0; s < nt; ++s) {
+      float sk = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) sk += sh.part[s][1][w];
+      const float kinv = 1.0f / sqrtf(sk + 1e-6f);  // division form, as the records are replayed
+      float* snap = nullptr;
+      if (has_track && t0 + s == t_track && slot_track > p.null_block_id && slot_track >= 0 && slot_track < p.slots)
+        snap = pool + slot_track * p.state_slot_stride + tile_off;
+      kda_step<false>(sh.state, sh.k[s], nullptr, sh.gam[s], sh.v[s], kinv, 0.f, sh.beta[s], nullptr, snap, warp,
+                      lane);
+    }
+  }
+  fence_async_smem();
+  __syncthreads();
+  if (tid == 0) {
+    bulk_store(pool + slot * p.state_slot_stride + tile_off, sh.state, kSliceBytes);
+    bulk_commit();
+    bulk_wait_read<0>();
+  }
+}
+
+template <typename T>
+__global__ void conv_scatter_kernel(const pla_b200_kda_conv_scatter_args p) {
+  const int req = blockIdx.x;
+  const int64_t layer = blockIdx.y;
+  const int64_t step = idx_at(p.step_idx, req), d = idx_at(p.dst_idx, req);
+  if (step < 0 || d < 0 || d >= p.dst_slots || req >= p.src_rows || step >= p.src_steps) return;
+  const T* src = static_cast<const T*>(p.src) + layer * p.src_layer + req * p.src_row + step * p.src_step;
+  T* dst = static_cast<T*>(p.dst) + layer * p.dst_layer + d * p.dst_slot;
+  const int total = p.dim * p.taps;
+  for (int i = blockIdx.z * blockDim.x + threadIdx.x; i < total; i += gridDim.z * blockDim.x) {
+    const int c = i / p.taps, w = i % p.taps;
+    dst[c * p.dst_channel + w * p.dst_tap] = src[c * p.src_channel + w * p.src_tap];
+  }
+}
+
 int check_commit(const pla_b200_kda_commit_args& a) {
   PLA_REQUIRE(a.null_block_id == -1 || a.null_block_id == 0, PLA_B200_E_INVALID, "null_block_id must be -1 or 0");
   PLA_REQUIRE(a.capacity >= 0 && a.N >= 0 && a.N <= a.capacity, PLA_B200_E_INVALID,
@@ -546,7 +677,69 @@ extern "C" int pla_b200_kda_replay_verify(const pla_b200_kda_verify_args* args, 
   }
   const int64_t ctas = static_cast<int64_t>(a.N) * a.H * NVS;
   PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "N*H exceeds the grid limit");
+  const bool onorm = a.onorm_gate != nullptr || a.onorm_weight != nullptr || a.out_f32 != nullptr;
+  PLA_REQUIRE(!onorm || (a.onorm_gate && a.onorm_weight && a.out_f32 && aligned16(a.out_f32) &&
+                         aligned16(a.onorm_weight) && a.onorm_eps >= 0.0f),
+              PLA_B200_E_INVALID, "the fused output norm needs gate, weight, eps >= 0 and a 16-byte aligned fp32 staging buffer");
   kda_verify_kernel<<<static_cast<unsigned>(ctas), NT, sizeof(Smem), static_cast<cudaStream_t>(stream)>>>(a);
+  PLA_CUDA_OK(cudaGetLastError());
+  if (onorm) {
+    kda_onorm_kernel<<<static_cast<unsigned>(a.N) * a.H, NT, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    PLA_CUDA_OK(cudaGetLastError());
+  }
+  return PLA_B200_OK;
+}
+
+extern "C" int pla_b200_kda_ring_verify(const pla_b200_kda_verify_args* args, void* stream) {
+  using namespace pla;
+  PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
+  PLA_REQUIRE(args->row_by_slot == 1, PLA_B200_E_INVALID, "ring verify addresses records by state slot (row_by_slot = 1)");
+  return pla_b200_kda_replay_verify(args, stream);
+}
+
+extern "C" int pla_b200_kda_fold_layers(const pla_b200_kda_fold_args* args, void* stream) {
+  using namespace pla;
+  PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
+  const pla_b200_kda_fold_args& a = *args;
+  PLA_REQUIRE(a.layers > 0 && a.B >= 0 && a.H > 0 && a.HV >= a.H && a.HV % a.H == 0 && a.L >= 1 && a.L <= 32 &&
+                  a.slots > 0,
+              PLA_B200_E_INVALID, "fold requires grouped heads, positive dimensions, and ring length 1..32");
+  if (a.B == 0) return PLA_B200_OK;
+  PLA_REQUIRE(a.state && a.rawv && a.rawk && a.gate && a.beta && a.slot_idx.data && a.accept_lens.data,
+              PLA_B200_E_INVALID, "fold: a required pointer is NULL");
+  PLA_REQUIRE((a.track_idx.data != nullptr) == (a.track_step.data != nullptr), PLA_B200_E_INVALID,
+              "tracking indices and steps must be supplied together");
+  PLA_REQUIRE(aligned16(a.state) && a.state_slot_stride % 4 == 0 && a.state_layer_stride % 4 == 0, PLA_B200_E_ALIGN,
+              "recurrent state must be 16-byte aligned");
+  static bool configured[64] = {};
+  int dev = 0;
+  PLA_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    PLA_CUDA_OK(cudaFuncSetAttribute(fold_layers_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(Smem)));
+    configured[dev] = true;
+  }
+  const int64_t ctas = static_cast<int64_t>(a.B) * a.layers * a.HV * NVS;
+  PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "fold grid too large");
+  fold_layers_kernel<<<static_cast<unsigned>(ctas), NT, sizeof(Smem), static_cast<cudaStream_t>(stream)>>>(a);
+  PLA_CUDA_OK(cudaGetLastError());
+  return PLA_B200_OK;
+}
+
+extern "C" int pla_b200_kda_conv_scatter(const pla_b200_kda_conv_scatter_args* args, void* stream) {
+  using namespace pla;
+  PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
+  const pla_b200_kda_conv_scatter_args& a = *args;
+  PLA_REQUIRE(a.layers >= 0 && a.reqs >= 0 && a.dim >= 0 && a.taps >= 1 && a.taps <= 4, PLA_B200_E_INVALID,
+              "conv scatter: unsupported conv window");
+  PLA_REQUIRE(a.elem_size == 2 || a.elem_size == 4, PLA_B200_E_INVALID, "conv scatter: unsupported dtype");
+  if (a.reqs == 0 || a.layers == 0 || a.dim == 0) return PLA_B200_OK;
+  PLA_REQUIRE(a.dst && a.src && a.dst_idx.data && a.step_idx.data, PLA_B200_E_INVALID,
+              "conv scatter: a required pointer is NULL");
+  PLA_REQUIRE(a.layers <= 65535, PLA_B200_E_TOO_LARGE, "too many layers");
+  const int tiles = min(64, (a.dim * a.taps + 255) / 256);
+  const dim3 grid(a.reqs, a.layers, tiles);
+  if (a.elem_size == 2) conv_scatter_kernel<uint16_t><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  else conv_scatter_kernel<uint32_t><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
   PLA_CUDA_OK(cudaGetLastError());
   return PLA_B200_OK;
 }

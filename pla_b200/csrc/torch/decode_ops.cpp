@@ -4,6 +4,8 @@
 //   pla.decode.gdn.v_last.fused_sigmoid_gating_delta_rule_forward      (src/decode/v-last/fused_sigmoid_gating_v_last.cpp:133-235)
 // checked with TORCH_CHECK (-> RuntimeError), then one C-ABI call on the
 // current stream of the tensors' device. No synchronisation, no D2H.
+#include <cmath>
+
 #include "ops_common.h"
 
 namespace pla_ops {
@@ -332,10 +334,50 @@ void decode_v_last(const at::Tensor& A_log, const at::Tensor& a, const at::Tenso
   check_abi(pla_b200_decode_vlast(&g, stream_of(q)), "fused_sigmoid_gating_delta_rule_forward (v-last)");
 }
 
+// vLLM-signature KDA adapter (src/decode/k-last/fused_recurrent_kda.cpp:146-314): flattens the raw
+// gate to [T, H*128], casts gate inputs to the activation dtype and index vectors to int32, narrows
+// the fp32 dt_bias to the activation dtype only when the call takes the plain decode path, and runs
+// the k-last op with is_kda. A 2-D slot table (one slot per draft token) means the per-step states
+// are the commit, so the start slot is not written again.
+void fused_recurrent_kda(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& raw_g,
+                         const at::Tensor& raw_beta, const at::Tensor& A_log, const at::Tensor& dt_bias,
+                         std::optional<double> lower_bound, const at::Tensor& initial_state,
+                         const at::Tensor& cu_seqlens, const at::Tensor& ssm_state_indices,
+                         const std::optional<at::Tensor>& num_accepted_tokens, at::Tensor out, bool is_sglang,
+                         const std::optional<at::Tensor>& status) {
+  TORCH_CHECK(q.dim() == 4 && q.size(0) == 1, "q must be packed as [1, T, H, K]");
+  const int64_t T = q.size(1), H = q.size(2), K = q.size(3);
+  const auto act = q.scalar_type();
+  const bool per_token_slots = ssm_state_indices.dim() == 2;
+  at::Tensor a = raw_g.reshape({T, H * K}).to(act).contiguous();
+  at::Tensor b = raw_beta.reshape({T, H}).to(act).contiguous();
+  at::Tensor cu32 = cu_seqlens.to(at::kInt).contiguous();
+  at::Tensor slots = ssm_state_indices.to(at::kInt).contiguous();
+  const int64_t B = cu32.numel() - 1;
+  TORCH_CHECK(B > 0, "k-last requires at least one sequence");
+  // the plain decode path (one token per request, 1-D slots) reads dt_bias at the activation dtype
+  const bool mtp = per_token_slots || T != B;
+  at::Tensor bias = dt_bias.reshape({H, K});
+  if (!mtp) bias = bias.to(act);
+  bias = bias.contiguous();
+  std::optional<at::Tensor> accepted;
+  if (num_accepted_tokens.has_value()) accepted = num_accepted_tokens->to(at::kInt).contiguous();
+  at::Tensor o = out.is_contiguous() ? out : at::empty(v.sizes(), v.options());
+  decode_k_last(A_log.reshape({-1}).contiguous(), a, bias, 1.0, 20.0, q.contiguous(), k.contiguous(), v.contiguous(), b,
+                initial_state, slots, std::pow(static_cast<double>(K), -0.5), true, cu32, true, per_token_slots,
+                std::nullopt, std::nullopt, std::nullopt, accepted, std::nullopt, lower_bound, is_sglang, o, status, 0);
+  if (!out.is_contiguous()) out.copy_(o);
+}
+
 }  // namespace
 }  // namespace pla_ops
 
 TORCH_LIBRARY_FRAGMENT(pla_b200, m) {
+  m.def(
+      "fused_recurrent_kda(Tensor q, Tensor k, Tensor v, Tensor raw_g, Tensor raw_beta, Tensor A_log, Tensor dt_bias, "
+      "float? lower_bound, Tensor(a!) initial_state, Tensor cu_seqlens, Tensor ssm_state_indices, "
+      "Tensor? num_accepted_tokens, Tensor(b!) out, bool is_sglang, Tensor(c!)? status) -> ()",
+      &pla_ops::fused_recurrent_kda);
   m.def(
       "decode_k_last(Tensor A_log, Tensor a, Tensor dt_bias, float softplus_beta, float softplus_threshold, "
       "Tensor q, Tensor k, Tensor v, Tensor b, Tensor(a!) initial_state_source, Tensor initial_state_indices, "

@@ -331,3 +331,92 @@ def kda_prefill_case(name, softplus=False, device="cpu"):
         cu.append(cu[-1] + n)
     return dict(q=q, k=k, v=v, g=g, beta=beta, A_log=A_log, dt_bias=dt_bias, init=init, cu=cu, lengths=lengths, T=T,
                 H=H, lower_bound=None if softplus else -5.0)
+
+
+# ---- SGLang ReplaySSM contract (fused_kda_decode_mtp_dspark / commit_kda_replayssm_after_verify) ----
+SGLANG_VERIFY_CASES = {"sg_dense": dict(bs=3, dtn=4, heads=2, ring=6, slots=6, onorm=False, pad=False),
+                       "sg_onorm_pad": dict(bs=4, dtn=3, heads=2, ring=4, slots=7, onorm=True, pad=True)}
+
+
+def sglang_verify_case(name, device="cpu"):
+    """Input dict with the entry point's keyword names. Slots are a non-trivial permutation, the
+    scratch rows are reversed, q/k/v/g are views with a padded token stride."""
+    c = SGLANG_VERIFY_CASES[name]
+    rs = _rs(sum(map(ord, name)))
+    bs, dtn, H, L, slots = c["bs"], c["dtn"], c["heads"], c["ring"], c["slots"]
+    T, dim = bs * dtn, c["heads"] * D
+    mixed = _t(rs, 1, T, 4 * dim + 64, scale=0.5)                       # q | k | v | g thirds of one row + padding
+    x_q, x_k, x_v, g = (mixed[..., i * dim:(i + 1) * dim].view(1, T, H, D) for i in range(4))
+    vi = dict(
+        x_q=x_q, x_k=x_k, x_v=x_v, g=g, beta=_t(rs, 1, T, H),
+        w_q=_t(rs, dim, 4, dtype=torch.float32, scale=0.3), w_k=_t(rs, dim, 4, dtype=torch.float32, scale=0.3),
+        w_v=_t(rs, dim, 4, dtype=torch.float32, scale=0.3),
+        A_log=torch.from_numpy(rs.uniform(0.5, 1.0, H).astype("float32")),
+        dt_bias=_t(rs, dim, dtype=torch.float32, scale=0.1),
+        recurrent_state=_t(rs, slots, H, D, D, dtype=torch.float32, scale=0.1),
+        lower_bound=-8.0, scale=D ** -0.5, intermediate_ssm=None,
+        replayssm_rawv=torch.full((slots, H, L, D), -3.0, dtype=torch.bfloat16),
+        replayssm_rawk=torch.full((slots, H, L, D), -3.0, dtype=torch.bfloat16),
+        replayssm_g=torch.full((slots, H, L, D), -3.0), replayssm_beta=torch.full((slots, H, L), -3.0),
+    )
+    conv = _t(rs, slots, 3, 3 * dim, scale=0.3)                          # [slots, width, 3*dim] pool, split + transposed
+    vi["cs_q"], vi["cs_k"], vi["cs_v"] = (conv[..., i * dim:(i + 1) * dim].transpose(-1, -2) for i in range(3))
+    ic = torch.full((bs + 1, dtn, 3 * dim, 3), -3.0, dtype=torch.bfloat16)
+    vi["intermediate_conv_q"], vi["intermediate_conv_k"], vi["intermediate_conv_v"] = (
+        ic[:, :, i * dim:(i + 1) * dim] for i in range(3))
+    order = rs.permutation(slots)[:bs].astype("int32")
+    if c["pad"]:
+        order[1] = -1
+    vi["ssm_state_indices"] = torch.from_numpy(order)
+    vi["intermediate_state_indices"] = torch.arange(bs - 1, -1, -1, dtype=torch.int64)
+    vi["cu_seqlens"] = torch.arange(0, T + 1, dtn, dtype=torch.int32)
+    if c["onorm"]:
+        vi["onorm_gate"] = _t(rs, 1, T, H, D, scale=0.5)
+        vi["onorm_weight"] = torch.from_numpy(rs.uniform(0.75, 1.25, D).astype("float32"))
+        vi["onorm_eps"] = 1e-6
+    if device != "cpu":
+        base = {id(mixed): mixed.to(device), id(conv): conv.to(device), id(ic): ic.to(device)}
+        dm, dc, di = base[id(mixed)], base[id(conv)], base[id(ic)]
+        moved = {k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in vi.items()}
+        for i, key in enumerate(("x_q", "x_k", "x_v", "g")):
+            moved[key] = dm[..., i * dim:(i + 1) * dim].view(1, T, H, D)
+        for i, key in enumerate(("cs_q", "cs_k", "cs_v")):
+            moved[key] = dc[..., i * dim:(i + 1) * dim].transpose(-1, -2)
+        for i, key in enumerate(("intermediate_conv_q", "intermediate_conv_k", "intermediate_conv_v")):
+            moved[key] = di[:, :, i * dim:(i + 1) * dim]
+        vi = moved
+    return vi, c
+
+
+SGLANG_COMMIT_CASES = {"sg_commit": dict(bs=4, dtn=4, heads=2, k_heads=2, ring=5, slots=7, layers=2, track=False),
+                       "sg_commit_track_gva": dict(bs=4, dtn=3, heads=4, k_heads=2, ring=4, slots=7, layers=1, track=True)}
+
+
+def sglang_commit_case(name, device="cpu"):
+    """Tensors for commit_kda_replayssm_after_verify: state, rings, one conv pool + window list."""
+    c = SGLANG_COMMIT_CASES[name]
+    rs = _rs(sum(map(ord, name)))
+    bs, dtn, HV, H, L, slots, nl = c["bs"], c["dtn"], c["heads"], c["k_heads"], c["ring"], c["slots"], c["layers"]
+    dim = 3 * HV * D
+    ci = dict(
+        temporal=_t(rs, nl, slots, HV, D, D, dtype=torch.float32, scale=0.1),
+        rawv=_t(rs, nl, slots, HV, L, D, scale=0.5), rawk=_t(rs, nl, slots, H, L, D, scale=0.5),
+        gk=-torch.from_numpy(rs.uniform(0, 0.5, (nl, slots, HV, L, D)).astype("float32")),
+        beta=torch.from_numpy(rs.uniform(0, 1, (nl, slots, HV, L)).astype("float32")),
+        conv=[_t(rs, nl, slots, dim, 3)], intermediate_conv_window=[_t(rs, nl, bs, dtn, dim, 3)],
+    )
+    order = rs.permutation(slots)[:bs].astype("int64")
+    order[bs - 1] = -1                                                      # a padding request
+    accept = np.array([(i % dtn) + 1 for i in range(bs)], dtype="int32")
+    accept[0] = 0                                                           # commits nothing
+    ci["state_batch_indices"] = torch.from_numpy(order)
+    ci["accept_lens"] = torch.from_numpy(accept)
+    ci["last_correct_step_indices"] = torch.from_numpy(accept.astype("int64") - 1)
+    if c["track"]:
+        free = [s for s in range(slots) if s not in order.tolist()]
+        # request 1 snapshots after its first step, request 2 after its last one
+        ci["mamba_track_indices"] = torch.tensor([-1, free[0], free[1], -1][:bs], dtype=torch.int64)
+        ci["mamba_steps_to_track"] = torch.tensor([0, 0, 2, 0][:bs], dtype=torch.int64)
+    if device != "cpu":
+        ci = {k: ([t.to(device) for t in v] if isinstance(v, list) else v.to(device)) for k, v in ci.items()}
+    return ci, c

@@ -103,6 +103,33 @@ def make_replay():
     print("plans", len(plans))
 
 
+def make_sglang():
+    """SGLang-contract verify and fold: the reference's fp64 oracle
+    (scripts/decode/kda_mtp_sglang/private/_reference.py:92-216) on the cases of cases.py."""
+    import importlib.util
+    from types import SimpleNamespace
+    spec = importlib.util.spec_from_file_location(
+        "ref_sglang", REF / "scripts" / "decode" / "kda_mtp_sglang" / "private" / "_reference.py")
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    for name in cases.SGLANG_VERIFY_CASES:
+        vi, c = cases.sglang_verify_case(name)
+        cfg = SimpleNamespace(heads=c["heads"], T=c["bs"] * c["dtn"], draft_token_num=c["dtn"], ring_len=c["ring"],
+                              slots=c["slots"], bs=c["bs"])
+        feed = {k: v for k, v in vi.items() if v is not None}
+        want = ref.verify_reference(feed, cfg)
+        np.savez_compressed(HERE / f"sglang_verify_{name}.npz", **{k: v.float().numpy() for k, v in want.items()})
+        print("sglang verify", name, tuple(want["out"].shape))
+    for name in cases.SGLANG_COMMIT_CASES:
+        ci, c = cases.sglang_commit_case(name)
+        want = ref.fold_reference(ci, None)
+        touched = sorted({int(s) for s, n in zip(ci["state_batch_indices"], ci["accept_lens"]) if s >= 0 and n > 0})
+        np.savez_compressed(HERE / f"sglang_fold_{name}.npz", touched=np.array(touched),
+                            state=cases.subsample(want[:, touched].float()),
+                            state_sum=np.float64(want[:, touched].sum().item()))
+        print("sglang fold", name, touched)
+
+
 def make_prefill():
     """GDN: the vendored chunked torch reference the reference's own prefill tests compare with
     (scripts/prefill/flashqla/private/ref_gdr.py, chunk 64, called per sequence as in
@@ -166,3 +193,5 @@ if __name__ == "__main__":
         make_replay()
     if which in ("all", "prefill"):
         make_prefill()
+    if which in ("all", "sglang"):
+        make_sglang()
