@@ -383,45 +383,61 @@ def run_prefill(args):
 
 
 def run_prefill_cp(args):
-    """Secondary line: the GDN part of config 4, one 64K-token sequence (Hqk=8, HV=24) cut into contiguous
-    token ranges over the ranks; prescan -> all-gather of (offset, transition) -> fold -> segment pass."""
+    """Secondary lines for config 4, one long sequence cut into contiguous token ranges over the ranks
+    (prescan -> all-gather of (offset, transition) -> fold -> segment pass):
+    prefill_cp      GDN, 64K tokens, Hqk=8, HV=24, chunk-64 tensor-core kernels;
+    prefill_cp_kda  KDA, 128K tokens, 32 heads, per-channel softplus gate with weak decay
+                    (A_log ~ U(-4, -2)), token-recurrent kernel."""
     import torch.distributed as dist
     from pla_b200._ops import ops
-    from pla_b200.prefill.context_parallel import gdn_prefill_context_parallel
+    from pla_b200.prefill.context_parallel import gdn_prefill_context_parallel, kda_prefill_context_parallel
+    kda = args.workload == "prefill_cp_kda"
     rank, world, local = (int(os.environ.get(k_, d_)) for k_, d_ in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29533")
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    T, Hg, H = 65536, 8, 24
-    gd = torch.Generator(device=dev).manual_seed(44)   # every rank draws the whole sequence and keeps its range
-    q = torch.nn.functional.normalize(torch.randn(T, Hg, D, generator=gd, device=dev), dim=-1).bfloat16()
-    k = torch.nn.functional.normalize(torch.randn(T, Hg, D, generator=gd, device=dev), dim=-1).bfloat16()
-    v = torch.randn(T, H, D, generator=gd, device=dev).bfloat16()
-    gate = torch.randn(T, H, generator=gd, device=dev).bfloat16()
-    beta = torch.randn(T, H, generator=gd, device=dev).bfloat16()
-    A_log = torch.rand(H, generator=gd, device=dev) * math.log(16.0)
-    dt_bias = torch.randn(H, generator=gd, device=dev) * 0.1
-    S0 = torch.randn(H, D, D, generator=gd, device=dev) * 0.02
+    T, Hg, H = (131072, 32, 32) if kda else (65536, 8, 24)
     per = (T // world + 63) // 64 * 64
     lo, hi = min(rank * per, T), min((rank + 1) * per, T)
-    mine = [x[lo:hi] for x in (q, k, v, gate, beta)]
+    gd = torch.Generator(device=dev).manual_seed(44)
+
+    def draw(*shape):
+        """Every rank draws the whole tensor from the same seed and keeps its token range (rank 0 keeps all
+        of it for the single-pass comparison)."""
+        full = torch.randn(*shape, generator=gd, device=dev)
+        return full if rank == 0 else full[lo:hi].clone()
+
+    q = torch.nn.functional.normalize(draw(T, Hg, D), dim=-1).bfloat16()
+    k = torch.nn.functional.normalize(draw(T, Hg, D), dim=-1).bfloat16()
+    v = draw(T, H, D).bfloat16()
+    gate = (draw(T, H, D) if kda else draw(T, H)).bfloat16()
+    beta = draw(T, H).bfloat16()
+    u = torch.rand(H, generator=gd, device=dev)
+    A_log = (-4.0 + 2.0 * u) if kda else u * math.log(16.0)
+    dt_bias = torch.randn(H, D, generator=gd, device=dev) * 0.1 if kda else torch.randn(H, generator=gd, device=dev) * 0.1
+    S0 = torch.randn(H, D, D, generator=gd, device=dev) * 0.02
+    sl = slice(lo, hi) if rank == 0 else slice(None)
+    mine = [x[sl] for x in (q, k, v, gate, beta)]
+    steps = min(args.steps, 5) if kda else args.steps
 
     def step():
+        if kda:
+            return kda_prefill_context_parallel(*mine, A_log, dt_bias, None, initial_state=S0)
         return gdn_prefill_context_parallel(*mine, A_log, dt_bias, initial_state=S0)
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(1 if kda else max(args.warmup, 3)):
         o, final = step()
     torch.cuda.synchronize()
     dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         o, final = step()
     e1.record()
     torch.cuda.synchronize()
-    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms = float(ms.item())
     if rank == 0:
@@ -429,15 +445,21 @@ def run_prefill_cp(args):
         one = torch.empty(T, H, D, dtype=torch.bfloat16, device=dev)
         fin = torch.empty(1, H, D, D, dtype=torch.float32, device=dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
-        ops.gdn_prefill_chunked(q, k, v, gate, beta, A_log, dt_bias, one, None,
-                                torch.tensor([0, T], dtype=torch.int32, device=dev), S0[None].contiguous(), None, fin,
-                                None, False, True, D ** -0.5, False, False, T // 64, 0, status)
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        if kda:
+            ops.prefill_recurrent(q, k, v, gate, beta, A_log, dt_bias, one, cu, S0[None].contiguous(), None, fin, None,
+                                  False, True, True, D ** -0.5, None, False, False, status)
+        else:
+            ops.gdn_prefill_chunked(q, k, v, gate, beta, A_log, dt_bias, one, None, cu, S0[None].contiguous(), None, fin,
+                                    None, False, True, D ** -0.5, False, False, T // 64, 0, status)
         rel = lambda a, b: float((a.float() - b.float()).norm() / b.float().norm())
-        print(json.dumps({"metric": "gdn_prefill_context_parallel_64K", "value": round(T / ms / 1e3, 3),
-                          "unit": "Mtok/s", "n_gpus": world, "steps": args.steps, "ms_per_step": round(ms, 4),
+        what = (f"config4 (KDA part): 1 sequence, T={T}, 32 heads, softplus gate, A_log~U(-4,-2), token-recurrent kernel"
+                if kda else f"config4 (GDN part): 1 sequence, T={T}, Hqk=8 HV=24, chunk 64 (tf32)")
+        print(json.dumps({"metric": "kda_prefill_context_parallel_128K" if kda else "gdn_prefill_context_parallel_64K",
+                          "value": round(T / ms / 1e3, 3),
+                          "unit": "Mtok/s", "n_gpus": world, "steps": steps, "ms_per_step": round(ms, 4),
                           "higher_is_better": True, "scaling": "strong", "dtype": "f32", "data": "synthetic",
-                          "config": {"workload": f"config4 (GDN part): 1 sequence, T={T}, Hqk=8 HV=24, "
-                                                 f"{per} tokens per rank, chunk 64 (tf32), one all-gather of "
+                          "config": {"workload": f"{what}, {per} tokens per rank, one all-gather of "
                                                  f"[{H},2,128,128] fp32 per rank",
                                      "out_rel_l2_vs_single_pass": rel(o, one[lo:hi]),
                                      "state_rel_l2_vs_single_pass": rel(final, fin[0]),
@@ -487,7 +509,7 @@ def run_replay(args):
 def main():
     global B, SLOTS, WORKLOAD
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill_cp", "replay"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill_cp", "prefill_cp_kda", "replay"],
                     help="decode = the headline metric; prefill / replay print secondary lines (1 GPU)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
@@ -502,7 +524,7 @@ def main():
     if (args.batch, args.slots) != (B, SLOTS):
         B, SLOTS = args.batch, args.slots
         WORKLOAD = f"REDUCED (not the headline): GDN decode B={B} Hqk=16 HV=32 d=128, fp32 k-last pool {SLOTS} slots"
-    if args.workload == "prefill_cp":
+    if args.workload in ("prefill_cp", "prefill_cp_kda"):
         args.steps = min(args.steps, 50)
         run_prefill_cp(args)
         return

@@ -124,6 +124,11 @@ typedef struct pla_b200_klast_args {
   int32_t state_transposed;         /* slots hold [K,V] (V contiguous) instead of [V,K] */
   int32_t gate_activated;           /* a = fp32 log-decay, b = fp32 beta, both already activated */
   int64_t o_total_rows;             /* > 0: rows [cu_seqlens[B], o_total_rows) of o are set to zero */
+  int32_t prescan;            /* prefill only, context parallelism: run every (request, head) twice without
+                                 output rows -- from a zero state (offset B) and from the identity with
+                                 V = 0 (transition M) -- and store both to state_out
+                                 [B, HV, 2, 128, 128] fp32, so that S_out[v, :] = S_in[v, :] M + B[v, :];
+                                 the state pool and its slots are not read */
 } pla_b200_klast_args;
 
 int pla_b200_decode_klast(const pla_b200_klast_args* args, void* stream);

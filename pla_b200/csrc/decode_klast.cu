@@ -132,7 +132,13 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
   } else {
     slot = n;  // state_by_request
   }
-  const bool is_pad = p.slot_indices != nullptr && ((p.pad == PLA_B200_PAD_SGLANG) ? (slot < 0) : (slot <= 0));
+  // Prescan (context parallelism): blockIdx.y = 0 runs the range from a zero state (offset B), 1 from the
+  // identity with V = 0 (transition M); no output rows, no slot pool, results to state_out
+  // [request][HV][2][V][K] fp32.
+  const bool prescan = p.prescan != 0;
+  const int kind = prescan ? static_cast<int>(blockIdx.y) : 0;
+  if (prescan) slot = 0;
+  const bool is_pad = !prescan && p.slot_indices != nullptr && ((p.pad == PLA_B200_PAD_SGLANG) ? (slot < 0) : (slot <= 0));
   const bool oob = !is_pad && p.num_slots > 0 && slot >= p.num_slots;
   act_t* o_base = static_cast<act_t*>(p.o) + hv * D + row0;
   if (is_pad || oob) {
@@ -152,7 +158,7 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
   const bool bulk_io = f32_state && !p.state_transposed;
   float* g_tile = static_cast<float*>(p.state) + in_off;  // only dereferenced when bulk_io
   constexpr uint32_t kBlockBytes = BV * D * 4;
-  const bool bulk_in = bulk_io && !p.state_init_zero;
+  const bool bulk_in = bulk_io && !p.state_init_zero && !prescan;
 
   if (bulk_in) {
     if (tid == 0) {
@@ -165,7 +171,9 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
     // zero start, 16-bit pool or transposed slots: fill shared memory by hand (once per sequence)
     for (int i = tid; i < BV * D; i += NT) {
       float x = 0.0f;
-      if (!p.state_init_zero) {
+      if (prescan) {
+        s_state[i] = (kind == 1 && row0 + i / D == i % D) ? 1.0f : 0.0f;
+      } else if (!p.state_init_zero) {
         const int r = p.state_transposed ? (i % BV) : (i / D);
         const int c = p.state_transposed ? (i / BV) : (i % D);
         const int64_t e = in_off + (p.state_transposed ? static_cast<int64_t>(c) * D + r : static_cast<int64_t>(r) * D + c);
@@ -233,7 +241,7 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
           s_gam[s] = __expf(fa[tok * p.a_tok_stride + hv]);
         }
         if (lane == 0) s_beta[s] = static_cast<const float*>(p.b)[tok * p.b_tok_stride + hv];
-        for (int i = lane; i < BV; i += 32) s_v[s * BV + i] = to_f32(gv[tok * p.v_tok_stride + i]);
+        for (int i = lane; i < BV; i += 32) s_v[s * BV + i] = kind == 1 ? 0.0f : to_f32(gv[tok * p.v_tok_stride + i]);
         continue;
       }
       if constexpr (IS_KDA) {
@@ -255,7 +263,7 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
         s_gam[s] = __expf(log_decay(x, A_log, p.gate, p.softplus_beta, p.softplus_threshold, p.lower_bound));
       }
       if (lane == 0) s_beta[s] = sigmoidf_fast(to_f32(gb[tok * p.b_tok_stride + hv]));
-      for (int i = lane; i < BV; i += 32) s_v[s * BV + i] = to_f32(gv[tok * p.v_tok_stride + i]);
+      for (int i = lane; i < BV; i += 32) s_v[s * BV + i] = kind == 1 ? 0.0f : to_f32(gv[tok * p.v_tok_stride + i]);
     }
 
     // Step parameters visible to all; also orders the mbarrier initialisation
@@ -360,10 +368,24 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
       }
     }
     __syncthreads();
-    for (int i = tid; i < nt * BV; i += NT) {
-      const int s = i / BV, r = i % BV;
-      o_base[(bos + t0 + s) * static_cast<int64_t>(HV) * D + r] = from_f32<act_t>(s_o[i]);
+    if (!prescan) {
+      for (int i = tid; i < nt * BV; i += NT) {
+        const int s = i / BV, r = i % BV;
+        o_base[(bos + t0 + s) * static_cast<int64_t>(HV) * D + r] = from_f32<act_t>(s_o[i]);
+      }
     }
+  }
+
+  if (prescan) {
+    float* dst = static_cast<float*>(p.state_out) + ((static_cast<int64_t>(n) * HV + hv) * 2 + kind) * TILE + row0 * D;
+    fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      bulk_store(dst, s_state, kBlockBytes);
+      bulk_commit();
+      bulk_wait_read<0>();
+    }
+    return;
   }
 
   if (!p.disable_state_update) {
@@ -408,9 +430,9 @@ int launch_one(const pla_b200_klast_args& a, cudaStream_t stream) {
     configured[dev] = true;
   }
   int64_t ctas = static_cast<int64_t>(a.B) * a.HV * (D / BV);
-  if (a.o_total_rows > 0) ctas += 64;  // CTAs that zero the padded output suffix
+  if (a.o_total_rows > 0 && !a.prescan) ctas += 64;  // CTAs that zero the padded output suffix
   PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "B*HV*(128/rows_per_cta) exceeds the grid limit");
-  kern<<<static_cast<unsigned>(ctas), NT, L::kBytes, stream>>>(a);
+  kern<<<dim3(static_cast<unsigned>(ctas), a.prescan ? 2 : 1), NT, L::kBytes, stream>>>(a);
   PLA_CUDA_OK(cudaGetLastError());
   return PLA_B200_OK;
 }
@@ -452,10 +474,13 @@ extern "C" int pla_b200_decode_klast(const pla_b200_klast_args* args, void* stre
   if (a.B == 0 || a.t_max == 0) return PLA_B200_OK;
   PLA_REQUIRE(a.H > 0 && a.HV >= a.H && a.HV % a.H == 0, PLA_B200_E_INVALID,
               "HV must be a positive multiple of H, got H=%d, HV=%d", a.H, a.HV);
-  PLA_REQUIRE(a.q && a.k && a.v && a.a && a.b && a.o && a.A_log && a.dt_bias, PLA_B200_E_INVALID,
+  PLA_REQUIRE(a.q && a.k && a.v && a.a && a.b && (a.o || a.prescan) && a.A_log && a.dt_bias, PLA_B200_E_INVALID,
               "q, k, v, a, b, o, A_log and dt_bias are required");
-  PLA_REQUIRE((a.state != nullptr || a.state_init_zero) && (a.slot_indices != nullptr || a.state_by_request),
+  PLA_REQUIRE(a.prescan || ((a.state != nullptr || a.state_init_zero) && (a.slot_indices != nullptr || a.state_by_request)),
               PLA_B200_E_INVALID, "the state pool and its slot indices are required");
+  PLA_REQUIRE(!a.prescan || (a.state_out != nullptr && a.cu_seqlens != nullptr && a.slot_row_stride == 0 &&
+                             a.cache == nullptr),
+              PLA_B200_E_INVALID, "a prescan needs cu_seqlens and state_out [B, HV, 2, 128, 128] fp32, and no cache or slot table");
   PLA_REQUIRE(a.state != nullptr || a.state_out != nullptr || a.disable_state_update, PLA_B200_E_INVALID,
               "a final state needs somewhere to go");
   PLA_REQUIRE(a.act_dtype == PLA_B200_BF16 || a.act_dtype == PLA_B200_F16, PLA_B200_E_INVALID,
@@ -466,8 +491,8 @@ extern "C" int pla_b200_decode_klast(const pla_b200_klast_args* args, void* stre
               "state slot pitch must cover HV*128*128 elements");
   PLA_REQUIRE(a.state == nullptr || (aligned16(a.state) && a.state_slot_stride % 4 == 0), PLA_B200_E_ALIGN,
               "state pool base and slot pitch must be 16-byte aligned");
-  PLA_REQUIRE(a.state_out == nullptr || (aligned16(a.state_out) && a.state_out_slot_stride % 4 == 0 &&
-                                         a.state_out_slot_stride >= static_cast<int64_t>(a.HV) * 16384),
+  PLA_REQUIRE(a.state_out == nullptr || (aligned16(a.state_out) && (a.prescan || (a.state_out_slot_stride % 4 == 0 &&
+                                         a.state_out_slot_stride >= static_cast<int64_t>(a.HV) * 16384))),
               PLA_B200_E_ALIGN, "final-state base and slot pitch must be 16-byte aligned and cover HV*128*128");
   PLA_REQUIRE(a.cache == nullptr || aligned16(a.cache), PLA_B200_E_ALIGN, "snapshot cache must be 16-byte aligned");
   PLA_REQUIRE(a.o_total_rows == 0 || (reinterpret_cast<uintptr_t>(a.o) & 3) == 0, PLA_B200_E_ALIGN,

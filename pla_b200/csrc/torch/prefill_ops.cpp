@@ -23,12 +23,12 @@ void state_ok(const at::Tensor& t, int64_t H, const at::Tensor& ref, const char*
               ": the [H,128,128] block of a slot must be contiguous");
 }
 
-void prefill_recurrent(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& gate,
-                       const at::Tensor& beta, const Optional& A_log, const Optional& dt_bias, at::Tensor out,
-                       const at::Tensor& cu_seqlens, const Optional& state_in, const Optional& in_indices,
-                       const Optional& state_out, const Optional& out_indices, bool transposed, bool is_kda,
-                       bool normalize_qk, double scale, std::optional<double> lower_bound, bool gate_activated,
-                       bool update_in_place, const Optional& status) {
+void run_recurrent(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& gate,
+                   const at::Tensor& beta, const Optional& A_log, const Optional& dt_bias, at::Tensor out,
+                   const at::Tensor& cu_seqlens, const Optional& state_in, const Optional& in_indices,
+                   const Optional& state_out, const Optional& out_indices, bool transposed, bool is_kda,
+                   bool normalize_qk, double scale, std::optional<double> lower_bound, bool gate_activated,
+                   bool update_in_place, const Optional& status, const Optional& prescan_out) {
   check_cuda(q, "q");
   const int64_t T = q.size(0);
   TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3, "q, k, v must be [tokens, heads, 128]");
@@ -144,7 +144,43 @@ void prefill_recurrent(const at::Tensor& q, const at::Tensor& k, const at::Tenso
   g.pad = PLA_B200_PAD_SGLANG;
   g.o_total_rows = T;
   g.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
+  if (prescan_out.has_value()) {
+    TORCH_CHECK(prescan_out->scalar_type() == at::kFloat && prescan_out->is_contiguous() &&
+                    prescan_out->numel() == N * H * 2 * 128 * 128 && prescan_out->device() == q.device(),
+                "a prescan stores contiguous fp32 [batch, H, 2, 128, 128] on q's device");
+    g.prescan = 1;
+    g.state = nullptr;
+    g.state_out = prescan_out->data_ptr();
+    g.state_out_indices = nullptr;
+    g.slot_indices = nullptr;
+    g.state_dtype = PLA_B200_F32;
+    g.state_transposed = 0;
+    g.o_total_rows = 0;
+  }
   check_abi(pla_b200_prefill_recurrent(&g, stream_of(q)), "prefill");
+}
+
+void prefill_recurrent(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& gate,
+                       const at::Tensor& beta, const Optional& A_log, const Optional& dt_bias, at::Tensor out,
+                       const at::Tensor& cu_seqlens, const Optional& state_in, const Optional& in_indices,
+                       const Optional& state_out, const Optional& out_indices, bool transposed, bool is_kda,
+                       bool normalize_qk, double scale, std::optional<double> lower_bound, bool gate_activated,
+                       bool update_in_place, const Optional& status) {
+  run_recurrent(q, k, v, gate, beta, A_log, dt_bias, out, cu_seqlens, state_in, in_indices, state_out, out_indices,
+                transposed, is_kda, normalize_qk, scale, lower_bound, gate_activated, update_in_place, status,
+                c10::nullopt);
+}
+
+// Context-parallel prescan with the token recurrence (GDN or KDA): per (sequence, head) the offset B and
+// the transition M of the token range, stored to `pairs` [batch, H, 2, 128, 128] fp32; no output rows.
+void prefill_recurrent_prescan(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& gate,
+                               const at::Tensor& beta, const Optional& A_log, const Optional& dt_bias,
+                               const at::Tensor& cu_seqlens, at::Tensor pairs, bool is_kda, bool normalize_qk,
+                               double scale, std::optional<double> lower_bound, bool gate_activated,
+                               const Optional& status) {
+  at::Tensor no_out = at::empty({v.size(0), v.size(1), 128}, v.options().dtype(q.scalar_type()).memory_format(at::MemoryFormat::Contiguous));
+  run_recurrent(q, k, v, gate, beta, A_log, dt_bias, no_out, cu_seqlens, c10::nullopt, c10::nullopt, c10::nullopt,
+                c10::nullopt, false, is_kda, normalize_qk, scale, lower_bound, gate_activated, false, status, pairs);
 }
 
 // Chunked (chunk 64) GDN prefill on the tensor cores. Returns the scratch workspace it allocated
@@ -328,6 +364,11 @@ TORCH_LIBRARY_FRAGMENT(pla_b200, m) {
       "Tensor(w!)? workspace, bool transposed, bool normalize_qk, float scale, bool gate_activated, int max_chunks, "
       "int stage, bool prescan, Tensor(d!)? status) -> Tensor",
       &pla_ops::gdn_prefill_chunked_stage);
+  m.def(
+      "prefill_recurrent_prescan(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor? A_log, "
+      "Tensor? dt_bias, Tensor cu_seqlens, Tensor(a!) pairs, bool is_kda, bool normalize_qk, float scale, "
+      "float? lower_bound, bool gate_activated, Tensor(b!)? status) -> ()",
+      &pla_ops::prefill_recurrent_prescan);
   m.def(
       "prefill_recurrent(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor? A_log, Tensor? dt_bias, "
       "Tensor(a!) out, Tensor cu_seqlens, Tensor(b!)? state_in, Tensor? in_indices, Tensor(c!)? state_out, "

@@ -1,4 +1,4 @@
-"""Context-parallel GDN prefill: one long sequence cut into contiguous token ranges, one per GPU.
+"""Context-parallel GDN / KDA prefill: one long sequence cut into contiguous token ranges, one per GPU.
 
 Over a token range the gated delta rule is an affine map of the incoming state, row by row of the
 k-last state ``S[v, k]``:  ``S_out = S_in @ M + B``  with ``M [K, K]`` the product of the per-token
@@ -15,6 +15,8 @@ Per rank:
   5. segment     the ordinary chain from ``S_in(r)``; the last rank's final state is the sequence's
 
 The last rank's (M, B) is never used, so it skips step 2 and contributes zeros to the gather.
+GDN runs the chunk-64 tensor-core kernels; KDA (per-channel decay: M = prod diag(gamma_t)(I - beta_t k_t k_t^T),
+the same row-wise affine form) runs the token-recurrent kernel in its prescan mode.
 """
 from __future__ import annotations
 
@@ -66,6 +68,45 @@ class CudaSegmentKernels:
         code = int(self.status.item())
         if code:
             raise RuntimeError(f"chunked prefill reported device status {code:#x}")
+
+
+class RecurrentSegmentKernels:
+    """Steps 2 and 5 with the token-recurrent kernel (pla_b200_prefill_recurrent; KDA or GDN)."""
+
+    def __init__(self, q, k, v, gate, beta, A_log, dt_bias, scale, normalize_qk, gate_activated, is_kda, lower_bound):
+        from .._ops import ops  # raises ImportError when the native libraries are missing
+        self._ops = ops
+        self.a = (q, k, v, gate, beta, A_log, dt_bias)
+        self.scale, self.normalize_qk, self.gate_activated = float(scale), bool(normalize_qk), bool(gate_activated)
+        self.is_kda = bool(is_kda)
+        self.lower_bound = None if lower_bound is None else float(lower_bound)
+        T, H = v.shape[0], v.shape[1]
+        self.T, self.H = T, H
+        self.cu = torch.tensor([0, T], dtype=torch.int32, device=q.device)
+        self.out = torch.empty(T, H, D, dtype=q.dtype, device=q.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=q.device)
+
+    def prepare(self):
+        pass
+
+    def prescan(self) -> torch.Tensor:
+        q, k, v, gate, beta, A_log, dt_bias = self.a
+        pairs = torch.empty(1, self.H, 2, D, D, dtype=torch.float32, device=self.out.device)
+        self._ops.prefill_recurrent_prescan(q, k, v, gate, beta, A_log, dt_bias, self.cu, pairs, self.is_kda,
+                                            self.normalize_qk, self.scale, self.lower_bound, self.gate_activated,
+                                            self.status)
+        return pairs[0]
+
+    def segment(self, state_in: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        q, k, v, gate, beta, A_log, dt_bias = self.a
+        final = torch.empty(1, self.H, D, D, dtype=torch.float32, device=self.out.device)
+        self._ops.prefill_recurrent(q, k, v, gate, beta, A_log, dt_bias, self.out, self.cu,
+                                    state_in[None].contiguous(), None, final, None, False, self.is_kda,
+                                    self.normalize_qk, self.scale, self.lower_bound, self.gate_activated, False,
+                                    self.status)
+        return self.out, final[0]
+
+    check = CudaSegmentKernels.check
 
 
 class SegmentPlan:
@@ -139,13 +180,45 @@ def gdn_prefill_context_parallel(
     ``segment_kernels`` replaces the GPU steps (host-side tests of the exchange); by default the CUDA
     kernels run and a missing native library is an ImportError.
     """
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
-    T, H = v.shape[0], v.shape[1]
     if scale is None:
         scale = D ** -0.5
     kernels = segment_kernels
     if kernels is None:
         kernels = CudaSegmentKernels(q, k, v, gate, beta, A_log, dt_bias, scale, normalize_qk, gate_activated)
+    return run_context_parallel(kernels, v, initial_state, output_final_state, group)
+
+
+def kda_prefill_context_parallel(
+    q: torch.Tensor,                       # [T_rank, H, 128]
+    k: torch.Tensor,                       # [T_rank, H, 128]
+    v: torch.Tensor,                       # [T_rank, H, 128]
+    g: torch.Tensor,                       # [T_rank, H, 128] raw per-channel gate input
+    beta: torch.Tensor,                    # [T_rank, H] raw beta input
+    A_log: torch.Tensor,                   # [H] fp32
+    dt_bias: torch.Tensor,                 # [H, 128] fp32
+    lower_bound: Optional[float],          # safe-gate bound, None = softplus gate
+    initial_state: Optional[torch.Tensor] = None,   # [H, 128(V), 128(K)] fp32, the same on every rank
+    scale: Optional[float] = None,
+    normalize_qk: bool = True,
+    output_final_state: bool = True,
+    group: Optional[dist.ProcessGroup] = None,
+    segment_kernels=None,
+):
+    """KDA counterpart of :func:`gdn_prefill_context_parallel` (same ranges, same exchange), evaluated
+    with the token-recurrent kernel."""
+    if scale is None:
+        scale = D ** -0.5
+    kernels = segment_kernels
+    if kernels is None:
+        kernels = RecurrentSegmentKernels(q, k, v, g, beta, A_log, dt_bias, scale, normalize_qk, False, True,
+                                          lower_bound)
+    return run_context_parallel(kernels, v, initial_state, output_final_state, group)
+
+
+def run_context_parallel(kernels, v, initial_state, output_final_state, group):
+    """Steps 1-5 over ``group`` with the given kernel set; ``v`` only supplies shapes, dtype and device."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    T, H = v.shape[0], v.shape[1]
     plan = begin_segment(kernels, rank, world, T, H, v.device)
     gathered = torch.empty(world, H, 2, D, D, dtype=torch.float32, device=v.device)
     dist.all_gather_into_tensor(gathered, plan.transfer[None].contiguous(), group=group)

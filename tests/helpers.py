@@ -37,15 +37,16 @@ def assert_state_close(state, ref, what="state", tol=STATE_REL_L2):
 class OracleSegmentKernels:
     """The three GPU steps restated with the oracle's token recurrence (test double)."""
 
-    def __init__(self, q, k, v, gate, beta, A_log, dt_bias, scale):
+    def __init__(self, q, k, v, gate, beta, A_log, dt_bias, scale, **oracle_kw):
         self.q, self.k, self.v, self.gate, self.beta = q, k, v, gate, beta
         self.A_log, self.dt_bias, self.scale = A_log, dt_bias, scale
         self.H = v.shape[1]
+        self.oracle_kw = oracle_kw          # e.g. is_kda=True, lower_bound=-5.0
 
     def _run(self, v, state):
         out, new_state, _ = _odec().klast_forward(q=self.q, k=self.k, v=v, a=self.gate, b=self.beta, A_log=self.A_log,
                                                dt_bias=self.dt_bias, state=state[None], slot_indices=[0],
-                                               lengths=[v.shape[0]], scale=self.scale)
+                                               lengths=[v.shape[0]], scale=self.scale, **self.oracle_kw)
         return out, new_state[0]
 
     def prepare(self):

@@ -77,3 +77,53 @@ def test_emulated_ranks_match_single_pass_and_oracle(native_built, splits):
                                                state=S0[None], slot_indices=[0], lengths=[T], scale=D ** -0.5)
     assert_out_close(out, exp_out)
     assert_state_close(state.cpu(), exp_state[0])
+
+
+def make_kda(T, H, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(T, H, D, generator=g).bfloat16()
+    k = torch.randn(T, H, D, generator=g).bfloat16()
+    v = torch.randn(T, H, D, generator=g).bfloat16()
+    gate = torch.randn(T, H, D, generator=g).bfloat16()
+    beta = torch.randn(T, H, generator=g).bfloat16()
+    A_log = -4.0 + 2.0 * torch.rand(H, generator=g)            # weak decay, as the long-sequence config states
+    dt_bias = torch.randn(H, D, generator=g) * 0.1
+    S0 = torch.randn(H, D, D, generator=g) * 0.05
+    return q, k, v, gate, beta, A_log, dt_bias, S0
+
+
+@pytest.mark.parametrize("lower_bound", [-5.0, None])
+def test_kda_emulated_ranks_match_oracle(native_built, lower_bound):
+    """KDA: prescan pairs of the token-recurrent kernel against the oracle, then ranks emulated one after
+    another against the serial oracle recurrence."""
+    from pla_b200.prefill import context_parallel as cp
+    splits = (90, 37, 0, 61)
+    T, H, W = sum(splits), 2, len(splits)
+    q, k, v, gate, beta, A_log, dt_bias, S0 = make_kda(T, H, 31)
+    dev = torch.device("cuda")
+    dq, dk, dv, dg, db = (x.to(dev) for x in (q, k, v, gate, beta))
+    dA, dB, dS0 = A_log.to(dev), dt_bias.to(dev), S0.to(dev)
+    plans, lo = [], 0
+    for r, n in enumerate(splits):
+        sl = slice(lo, lo + n)
+        kern = cp.RecurrentSegmentKernels(dq[sl], dk[sl], dv[sl], dg[sl], db[sl], dA, dB, D ** -0.5, True, False, True,
+                                          lower_bound)
+        plans.append(cp.begin_segment(kern, r, W, n, H, dev))
+        if r == 0:
+            ref = OracleSegmentKernels(q[sl], k[sl], v[sl], gate[sl], beta[sl], A_log, dt_bias, D ** -0.5, is_kda=True,
+                                       lower_bound=lower_bound).prescan()
+            assert_state_close(plans[0].transfer[:, 0].cpu(), ref[:, 0], "offset B")
+            assert_state_close(plans[0].transfer[:, 1].cpu(), ref[:, 1], "transition M")
+        lo += n
+    gathered = torch.stack([p.transfer for p in plans])
+    outs, state = [], None
+    for p in plans:
+        o, state = cp.finish_segment(p, dS0, gathered)
+        if o is not None:
+            outs.append(o)
+        p.kernels.check()
+    exp_out, exp_state, _ = odec.klast_forward(q=q, k=k, v=v, a=gate, b=beta, A_log=A_log, dt_bias=dt_bias,
+                                               state=S0[None], slot_indices=[0], lengths=[T], scale=D ** -0.5,
+                                               is_kda=True, lower_bound=lower_bound)
+    assert_out_close(torch.cat(outs), exp_out)
+    assert_state_close(state.cpu(), exp_state[0])
