@@ -42,6 +42,8 @@ extern "C" {
 #define PLA_B200_DEV_BAD_PARENT 2   /* tree parent index >= its own step      */
 #define PLA_B200_DEV_WAIT_TIMEOUT 4 /* a bounded wait on a bulk copy ran out  */
 #define PLA_B200_DEV_BAD_SLOT 8     /* slot index outside the pool            */
+#define PLA_B200_DEV_DECAY_RANGE 16 /* chunked KDA prefill: a key channel decayed by more than 80 nats inside 16
+                                       tokens (unbounded softplus gate); results of that call are not valid */
 
 /* ---- enums ---------------------------------------------------------------- */
 enum pla_b200_dtype { PLA_B200_BF16 = 0, PLA_B200_F16 = 1, PLA_B200_F32 = 2 };
@@ -226,10 +228,23 @@ typedef struct pla_b200_gdn_chunk_args {
   void* workspace;            /* device scratch of pla_b200_gdn_chunk_workspace_bytes() bytes, 128-byte aligned */
   int64_t workspace_bytes;
   int32_t* status;
+  /* KDA only (pla_b200_kda_prefill_chunked): gate is the raw per-channel input [T, H*128] in the activation
+   * dtype, dt_bias [H*128], H == HV, gate_activated = 0 */
+  int32_t is_kda;             /* set by the KDA entry */
+  int32_t gate_kind;          /* pla_b200_gate */
+  float lower_bound;
 } pla_b200_gdn_chunk_args;
 
 int64_t pla_b200_gdn_chunk_workspace_bytes(int32_t max_chunks, int32_t H, int32_t HV);
 int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args, void* stream);
+
+/* Chunked KDA prefill (chunk 64, decay references every 16 tokens) on the tensor cores: replaces the launch
+ * chain behind flashkda_fwd (src/prefill/flashkdapro/host/torch_extension_cute.cc:1686; its tc01 backend also
+ * works on 64-token chunks with 16-token sub-chunks, src/prefill/flashkdapro/tc01/kernel_bt64_prefill_tc01.cu:82-96).
+ * Same args struct, stages and prescan mode as the GDN entry. Safe gate with lower_bound >= -5, or a softplus
+ * gate whose decay stays within 80 nats per 16 tokens (else PLA_B200_DEV_DECAY_RANGE is set). */
+int64_t pla_b200_kda_chunk_workspace_bytes(int32_t max_chunks, int32_t H);
+int pla_b200_kda_prefill_chunked(const pla_b200_gdn_chunk_args* args, void* stream);
 
 /* ======================================================================== *
  * KDA ReplaySSM: verify (read-only checkpoint, replay records out) and commit

@@ -82,6 +82,39 @@ __device__ __forceinline__ int first_chunk_of(const int32_t* cu, int seq) {
 // ================================================================================================
 constexpr int L_STRIDE = 68;  // padded row of the fp32 L matrix (floats); rows stay 16-byte aligned
 
+// T = (I + L)^-1, one column per thread, rows by forward substitution, all in registers.
+// Columns are dealt to threads in 16-wide blocks; a column of block cb is zero above row 16*cb and
+// only needs rows / terms from its own block on. Blocks {0,3} share one warp and {1,2} the other,
+// which evens out the two warps' work. L: strictly lower triangle, fp32, row pitch L_STRIDE.
+__device__ __forceinline__ int inverse_column_block(int t6) {
+  return (t6 < 32) ? ((t6 & 16) ? 3 : 0) : ((t6 & 16) ? 2 : 1);
+}
+__device__ __forceinline__ void invert_column(const float* __restrict__ L, int cb, int col, float (&Tcol)[C]) {
+#pragma unroll
+  for (int i = 0; i < C; ++i) Tcol[i] = 0.0f;
+#pragma unroll
+  for (int i = 0; i < C; ++i) {
+    if (cb <= (i >> 4)) {
+      const float4* Lrow = reinterpret_cast<const float4*>(L + i * L_STRIDE);
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+      for (int jb = 0; jb <= (i >> 4); ++jb) {
+        if (cb <= jb) {
+#pragma unroll
+          for (int j4 = jb * 4; j4 < jb * 4 + 4 && j4 < (i + 3) / 4; ++j4) {
+            const float4 l = Lrow[j4];  // entries at j >= i are zero
+            a0 = fmaf(l.x, Tcol[4 * j4 + 0], a0);
+            a1 = fmaf(l.y, Tcol[4 * j4 + 1], a1);
+            a2 = fmaf(l.z, Tcol[4 * j4 + 2], a2);
+            a3 = fmaf(l.w, Tcol[4 * j4 + 3], a3);
+          }
+        }
+      }
+      Tcol[i] = ((i == col) ? 1.0f : 0.0f) - ((a0 + a1) + (a2 + a3));
+    }
+  }
+}
+
 struct PrepSmem {
   alignas(1024) float kq[KQ_BYTES / 4];
   alignas(16) float L[2][C * L_STRIDE];  // phase A reuses this space to stage the raw rows
@@ -338,34 +371,12 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
       // 16*cb and only needs rows/terms from its own block on. Blocks {0,3} share one warp and
       // {1,2} the other, which evens out the two warps' work.
       const int s = tid >> 6, t6 = tid & 63;
-      const int cb = (t6 < 32) ? ((t6 & 16) ? 3 : 0) : ((t6 & 16) ? 2 : 1);
+      const int cb = inverse_column_block(t6);
       const int col = cb * 16 + (t6 & 15);
       if (s < heads_now) {
         const int hv = h * R + r0 + s;
         float Tcol[C];
-#pragma unroll
-        for (int i = 0; i < C; ++i) Tcol[i] = 0.0f;
-#pragma unroll
-        for (int i = 0; i < C; ++i) {
-          if (cb <= (i >> 4)) {
-            const float4* Lrow = reinterpret_cast<const float4*>(sh.L[s] + i * L_STRIDE);
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-            for (int jb = 0; jb <= (i >> 4); ++jb) {
-              if (cb <= jb) {
-#pragma unroll
-                for (int j4 = jb * 4; j4 < jb * 4 + 4 && j4 < (i + 3) / 4; ++j4) {
-                  const float4 l = Lrow[j4];  // entries at j >= i are zero
-                  a0 = fmaf(l.x, Tcol[4 * j4 + 0], a0);
-                  a1 = fmaf(l.y, Tcol[4 * j4 + 1], a1);
-                  a2 = fmaf(l.z, Tcol[4 * j4 + 2], a2);
-                  a3 = fmaf(l.w, Tcol[4 * j4 + 3], a3);
-                }
-              }
-            }
-            Tcol[i] = ((i == col) ? 1.0f : 0.0f) - ((a0 + a1) + (a2 + a3));
-          }
-        }
+        invert_column(sh.L[s], cb, col, Tcol);
         float* Timg = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv));
 #pragma unroll
         for (int i = 0; i < C; ++i) Timg[(col >> 2) * (C * 4) + i * 4 + (col & 3)] = tc05::to_tf32(Tcol[i]);
@@ -389,6 +400,326 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
   tc05::fence_before_sync();
   __syncthreads();
   if (warp == 0) tc05::tmem_dealloc(tbase, 64);
+}
+
+// ================================================================================================
+// KDA (per-channel decay): prepare in two launches
+// ================================================================================================
+// With a decay per key channel the factor e^{G_i[c] - G_j[c]} sits inside the contraction over c, so
+// it is folded into the operands. To keep every factor representable the chunk is cut into four
+// sub-blocks of 16 tokens with reference points R_a = cumulative log decay before sub-block a:
+//     L[i, j] = beta_i sum_c (k_i e^{G_i - R_a})[c] (k_j e^{R_a - G_j})[c],   i in sub-block a, j < i
+// The first factor is <= 1; the second is <= 1 for j in an earlier sub-block and at most the inverse
+// decay of one sub-block for j in the same one (bounded by 16 |lower_bound| <= 80 nats for the safe
+// gate; an unbounded softplus gate that decays by more than 80 nats inside 16 tokens sets
+// PLA_B200_DEV_DECAY_RANGE). One B image per reference a (rows j < 16 (a + 1)), one A image
+// [K e^{G-R}; Q e^{G-R}], four MMA chains; row block a of chain a is the wanted block row.
+// The chain kernel gets  [K e^{G}; Q e^{G}]  (decay from the chunk start folded in),
+// (K e^{G_C - G})^T  for the state update, beta and e^{G_C} per channel.
+// Launch 1 (`kda_chunk_prepare_kernel`, 256 threads, one CTA per SM) builds everything except T and
+// leaves L (fp32) in the workspace; launch 2 (`kda_chunk_inverse_kernel`, light, many CTAs per SM)
+// turns L into the T image.
+constexpr int DM_PITCH = 132;  // floats per row of the decay-factor matrix: float4 rows, conflict-free per quarter warp
+constexpr int KM_BYTES = 81920;  // four B images of 16, 32, 48, 64 rows x 512 bytes, back to back
+constexpr int L_BYTES = C * C * 4;
+__host__ __device__ constexpr int km_offset(int a) { return a * (a + 1) / 2 * 8192; }
+__host__ __device__ inline int64_t ws_lmat(int64_t max_chunks, int H, int64_t gc, int h) {
+  return max_chunks * H * static_cast<int64_t>(HBLOB + VBLOB) + (gc * H + h) * static_cast<int64_t>(L_BYTES);
+}
+
+struct KdaPrepSmem {
+  alignas(1024) float kq[KQ_BYTES / 4];
+  alignas(1024) unsigned char km[KM_BYTES];  // first the staged gate rows, then the four B images
+  alignas(16) float dm[C * DM_PITCH];        // e^{G - R_block} per (token, channel)
+  alignas(16) uint32_t stg[128 * 68];        // staged raw k rows (0..63) and q rows (64..127)
+  alignas(16) float rv[4][D];                // R_a
+  alignas(16) float erb[4][D];               // e^{R_a}
+  alignas(16) float egc[4][D];               // e^{G_C - R_a}
+  alignas(16) float fab[6][D];               // e^{R_a - R_b}, a > b, at index a (a - 1) / 2 + b
+  float gc[D];
+  float beta[C];
+  float rnorm[128];
+  alignas(8) uint64_t bar;
+  uint32_t tmem_base;
+};
+
+template <typename act_t>
+__global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const pla_b200_gdn_chunk_args p) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem_raw = smem_dyn + ((1024u - (smem_addr(smem_dyn) & 1023u)) & 1023u);
+  KdaPrepSmem& sh = *reinterpret_cast<KdaPrepSmem*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.x % p.H;
+  const int gc = blockIdx.x / p.H;
+  ChunkPos pos;
+  if (!locate_chunk(p.cu_seqlens, p.N, gc, pos)) return;
+
+  if (warp == 0) tc05::tmem_alloc(&sh.tmem_base, 256);
+  if (tid == 0) {
+    mbar_init(&sh.bar, 1);
+    fence_mbar_init();
+  }
+  constexpr int STG = 68;  // staged row pitch in 32-bit words = 17 x 16 bytes
+  uint32_t* gstg = reinterpret_cast<uint32_t*>(sh.km);
+
+  // ---- stage the chunk's k, q and gate rows (16 or 17 aligned 16-byte pieces per 256-byte row) ----
+  for (int r = warp; r < 192; r += 8) {
+    const int c = r & 63, which = r >> 6;
+    if (c >= pos.n || lane >= 17) continue;
+    const act_t* base = static_cast<const act_t*>(which == 0 ? p.k : which == 1 ? p.q : p.gate);
+    const int64_t stride = which == 0 ? p.k_tok_stride : which == 1 ? p.q_tok_stride : p.gate_tok_stride;
+    const act_t* row = base + (pos.tok0 + c) * stride + h * D;
+    const char* src = reinterpret_cast<const char*>(reinterpret_cast<uintptr_t>(row) & ~uintptr_t(15));
+    if (lane == 16 && src == reinterpret_cast<const char*>(row)) continue;
+    uint32_t* dst = which < 2 ? sh.stg + r * STG : gstg + c * STG;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst) + lane * 16), "l"(src + lane * 16)
+                 : "memory");
+  }
+  asm volatile("cp.async.wait_all;" ::: "memory");
+  __syncthreads();
+
+  if (tid < 128) {
+    // ---- one thread per channel: log decay, running sum, sub-block references, decay factors ----
+    const int c = tid;
+    const float A_log = p.A_log[h];
+    const float dtb = p.dt_bias[h * D + c];
+    const unsigned short* gs = reinterpret_cast<const unsigned short*>(gstg);
+    const int64_t e0 = static_cast<int64_t>(reinterpret_cast<uintptr_t>(p.gate) >> 1) + pos.tok0 * p.gate_tok_stride + h * D;
+    float G = 0.f, R = 0.f;
+    bool range_ok = true;
+    for (int t = 0; t < C; ++t) {
+      if ((t & 15) == 0) {
+        range_ok &= (R - G) <= 80.0f;
+        R = G;
+        sh.rv[t >> 4][c] = R;
+      }
+      if (t < pos.n) {
+        const int shf = static_cast<int>((e0 + t * p.gate_tok_stride) & 7);
+        act_t raw;
+        *reinterpret_cast<unsigned short*>(&raw) = gs[t * (STG * 2) + shf + c];
+        G += log_decay(to_f32(raw) + dtb, A_log, p.gate_kind, 1.0f, 20.0f, p.lower_bound);
+      }
+      sh.dm[t * DM_PITCH + c] = __expf(G - R);
+    }
+    range_ok &= (R - G) <= 80.0f;
+    sh.gc[c] = G;
+    if (!range_ok && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_DECAY_RANGE);
+  } else {
+    // ---- meanwhile one thread per k / q row: L2 norm; k-row threads also activate beta ----
+    const int r = tid - 128, c = r & 63;
+    const bool is_q = r >= 64;
+    float rn = 0.f;
+    if (c < pos.n) {
+      const act_t* base = static_cast<const act_t*>(is_q ? p.q : p.k);
+      const act_t* row = base + (pos.tok0 + c) * (is_q ? p.q_tok_stride : p.k_tok_stride) + h * D;
+      const int sh_half = static_cast<int>((reinterpret_cast<uintptr_t>(row) & 15) >> 1);
+      const uint32_t* srow = sh.stg + r * STG + (sh_half >> 1);
+      const bool odd = sh_half & 1;
+      rn = is_q ? p.scale : 1.0f;
+      if (p.normalize_qk) {
+        float ss = 0.f;
+        const int rot = lane >> 3;  // rows of a warp are 4 banks apart: start each group of 8 lanes one word later
+#pragma unroll 8
+        for (int i0 = 0; i0 < D / 2; ++i0) {
+          const int i = (i0 + rot) & 63;
+          const uint32_t w = odd ? __funnelshift_r(srow[i], srow[i + 1], 16) : srow[i];
+          const act_t* e = reinterpret_cast<const act_t*>(&w);
+          const float x0 = to_f32(e[0]), x1 = to_f32(e[1]);
+          ss = fmaf(x0, x0, fmaf(x1, x1, ss));
+        }
+        rn *= rsqrtf(ss + 1e-6f);
+      }
+      if (!is_q) sh.beta[c] = sigmoidf_fast(to_f32(static_cast<const act_t*>(p.beta)[(pos.tok0 + c) * p.beta_tok_stride + h]));
+    } else if (!is_q) {
+      sh.beta[c] = 0.f;
+    }
+    sh.rnorm[r] = rn;
+  }
+  __syncthreads();
+  // ---- per-channel tables ----
+  for (int i = tid; i < 14 * D; i += 256) {
+    const int which = i / D, c = i % D;
+    if (which < 4) sh.erb[which][c] = __expf(sh.rv[which][c]);
+    else if (which < 8) sh.egc[which - 4][c] = __expf(sh.gc[c] - sh.rv[which - 4][c]);
+    else {
+      const int f = which - 8;                       // (a, b): (1,0) (2,0) (2,1) (3,0) (3,1) (3,2)
+      const int a = f < 1 ? 1 : f < 3 ? 2 : 3, b = f - a * (a - 1) / 2;
+      sh.fab[f][c] = __expf(sh.rv[a][c] - sh.rv[b][c]);
+    }
+  }
+  __syncthreads();  // also: the staged gate rows (aliased with the B images) are fully consumed
+
+  // ---- operand images: thread = (row, half of the channels) ----
+  unsigned char* ws = static_cast<unsigned char*>(p.workspace);
+  {
+    const int r = tid & 127, hh = tid >> 7, c = r & 63, blk = c >> 4;
+    const bool is_q = r >= 64;
+    const float rn = sh.rnorm[r];
+    const act_t* base = static_cast<const act_t*>(is_q ? p.q : p.k);
+    const act_t* row = base + (pos.tok0 + c) * (is_q ? p.q_tok_stride : p.k_tok_stride) + h * D;
+    const int sh_half = static_cast<int>((reinterpret_cast<uintptr_t>(row) & 15) >> 1);
+    const uint32_t* __restrict__ srow = sh.stg + r * STG + (sh_half >> 1);
+    const bool odd = sh_half & 1;
+    const bool live = c < pos.n;
+    auto pair_at = [&](int i) -> uint32_t { return odd ? __funnelshift_r(srow[i], srow[i + 1], 16) : srow[i]; };
+    float4* __restrict__ kq4 = reinterpret_cast<float4*>(sh.kq);
+    float4* __restrict__ kqs_g = reinterpret_cast<float4*>(ws + ws_hblob(gc, h, p.H));
+    float* __restrict__ ke_g = reinterpret_cast<float*>(ws + ws_hblob(gc, h, p.H) + KQ_BYTES);
+    const float4* __restrict__ dmrow = reinterpret_cast<const float4*>(sh.dm + c * DM_PITCH);
+#pragma unroll 2
+    for (int kc = hh * 16; kc < hh * 16 + 16; ++kc) {
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (live) {
+        const uint32_t w0 = pair_at(2 * kc), w1 = pair_at(2 * kc + 1);
+        const act_t* e0 = reinterpret_cast<const act_t*>(&w0);
+        const act_t* e1 = reinterpret_cast<const act_t*>(&w1);
+        x = make_float4(to_f32(e0[0]) * rn, to_f32(e0[1]) * rn, to_f32(e1[0]) * rn, to_f32(e1[1]) * rn);
+      }
+      const float4 dv = dmrow[kc];
+      const float4 xp = make_float4(x.x * dv.x, x.y * dv.y, x.z * dv.z, x.w * dv.w);
+      kq4[kc * 128 + r] = make_float4(tc05::to_tf32(xp.x), tc05::to_tf32(xp.y), tc05::to_tf32(xp.z), tc05::to_tf32(xp.w));
+      const float4 er = reinterpret_cast<const float4*>(sh.erb[blk])[kc];
+      kqs_g[kc * 128 + r] = make_float4(tc05::to_tf32(xp.x * er.x), tc05::to_tf32(xp.y * er.y),
+                                        tc05::to_tf32(xp.z * er.z), tc05::to_tf32(xp.w * er.w));
+      if (!is_q) {
+        const float4 bs = make_float4(__fdividef(x.x, fmaxf(dv.x, 1e-37f)), __fdividef(x.y, fmaxf(dv.y, 1e-37f)),
+                                      __fdividef(x.z, fmaxf(dv.z, 1e-37f)), __fdividef(x.w, fmaxf(dv.w, 1e-37f)));
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          if (a < blk) continue;
+          float4 f = make_float4(1.f, 1.f, 1.f, 1.f);
+          if (a > blk) f = reinterpret_cast<const float4*>(sh.fab[a * (a - 1) / 2 + blk])[kc];
+          float4* img = reinterpret_cast<float4*>(sh.km + km_offset(a));
+          img[kc * (16 * (a + 1)) + c] = make_float4(tc05::to_tf32(bs.x * f.x), tc05::to_tf32(bs.y * f.y),
+                                                     tc05::to_tf32(bs.z * f.z), tc05::to_tf32(bs.w * f.w));
+        }
+        const float4 eg = reinterpret_cast<const float4*>(sh.egc[blk])[kc];
+        float* __restrict__ dst = ke_g + (c >> 2) * (D * 4) + (kc * 4) * 4 + (c & 3);
+        dst[0] = tc05::to_tf32(bs.x * eg.x);
+        dst[4] = tc05::to_tf32(bs.y * eg.y);
+        dst[8] = tc05::to_tf32(bs.z * eg.z);
+        dst[12] = tc05::to_tf32(bs.w * eg.w);
+      }
+    }
+  }
+  fence_async_smem();
+  tc05::fence_before_sync();
+  __syncthreads();
+  tc05::fence_after_sync();
+  const uint32_t tbase = sh.tmem_base;
+
+  // ---- four MMA chains: D_a[128 x 16(a+1)] = [K+; Q+] (128 x 128) * (K-(a))^T ----
+  if (tid == 0) {
+    const uint64_t a_desc = tc05::smem_desc(sh.kq, 128 * 16, 128);
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const int rows = 16 * (a + 1);
+      const uint64_t b_desc = tc05::smem_desc(sh.km + km_offset(a), rows * 16, 128);
+      const uint32_t idesc = tc05::idesc_tf32(128, rows);
+      const uint32_t col = 8 * a * (a + 1);   // 0, 16, 48, 96
+#pragma unroll
+      for (int j = 0; j < D / 8; ++j)
+        tc05::mma_tf32_ss(tbase + col, tc05::desc_advance(a_desc, j * 2 * 128 * 16),
+                          tc05::desc_advance(b_desc, j * 2 * rows * 16), idesc, j > 0);
+    }
+    tc05::mma_commit(&sh.bar);
+  }
+  {
+    const bool ok = mbar_wait(&sh.bar, 0, 1u << 20);
+    if (__syncthreads_or(!ok)) {
+      if (tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_WAIT_TIMEOUT);
+      __syncthreads();
+      if (warp == 0) tc05::tmem_dealloc(tbase, 256);
+      return;
+    }
+  }
+  tc05::fence_after_sync();
+
+  if (tid < 128) {
+    // this thread's row: i = tid % 64 of K+ K-^T (tid < 64) or of Q+ K-^T; lanes 0-15 of a warp sit in
+    // sub-block a0 = 2 (warp % 2), lanes 16-31 in a0 + 1
+    const int i_row = tid & 63;
+    const bool p_row = tid >= 64;
+    const int a0 = 2 * (warp & 1);
+    float d0[C];
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const int a = a0 + pass;
+      float t0[32], t1[32];
+      tc05::tmem_ld32(tc05::taddr(tbase, warp * 32, 8 * a * (a + 1)), t0);
+      tc05::tmem_ld32(tc05::taddr(tbase, warp * 32, 8 * a * (a + 1) + 32), t1);
+      tc05::wait_ld();
+      if ((lane >> 4) == pass) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          d0[j] = t0[j];
+          d0[32 + j] = t1[j];
+        }
+      }
+    }
+    if (!p_row) {
+      const float bi = sh.beta[i_row];
+      float4* __restrict__ Lg = reinterpret_cast<float4*>(ws + ws_lmat(p.max_chunks, p.H, gc, h)) + i_row * (C / 4);
+#pragma unroll
+      for (int jc = 0; jc < C / 4; ++jc) {
+        float x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) x[u] = (jc * 4 + u < i_row) ? bi * d0[jc * 4 + u] : 0.0f;
+        Lg[jc] = make_float4(x[0], x[1], x[2], x[3]);
+      }
+    } else {
+      float4* __restrict__ Pimg = reinterpret_cast<float4*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, h) + TM_BYTES);
+#pragma unroll
+      for (int jc = 0; jc < C / 4; ++jc) {
+        float x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = jc * 4 + u;
+          x[u] = (j <= i_row && i_row < pos.n) ? tc05::to_tf32(d0[j]) : 0.0f;
+        }
+        Pimg[jc * C + i_row] = make_float4(x[0], x[1], x[2], x[3]);
+      }
+    }
+  } else {
+    // vectors for the chain: beta per token, e^{G_C} per channel
+    float* vec = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, h) + TM_BYTES + PM_BYTES);
+    const int c = tid - 128;
+    vec[2 * C + c] = __expf(sh.gc[c]);
+    if (c < C) {
+      vec[c] = 0.f;
+      vec[C + c] = sh.beta[c];
+    }
+  }
+  tc05::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc05::tmem_dealloc(tbase, 256);
+}
+
+// L (fp32, strictly lower) -> T = (I + L)^-1 as a tf32 operand image. Two (chunk, head) items per CTA.
+__global__ void __launch_bounds__(128) kda_chunk_inverse_kernel(const pla_b200_gdn_chunk_args p, int items) {
+  __shared__ __align__(16) float Ls[2][C * L_STRIDE];
+  const int tid = threadIdx.x, s = tid >> 6, t6 = tid & 63;
+  const int item = blockIdx.x * 2 + s;
+  const bool live = item < items;
+  unsigned char* ws = static_cast<unsigned char*>(p.workspace);
+  const int h = live ? item % p.H : 0;
+  const int gc = live ? item / p.H : 0;
+  ChunkPos pos;
+  const bool found = live && locate_chunk(p.cu_seqlens, p.N, gc, pos);
+  if (found) {
+    const float4* Lg = reinterpret_cast<const float4*>(ws + ws_lmat(p.max_chunks, p.H, gc, h));
+    for (int i = t6; i < C * C / 4; i += 64)
+      *reinterpret_cast<float4*>(&Ls[s][(i >> 4) * L_STRIDE + (i & 15) * 4]) = Lg[i];
+  }
+  __syncthreads();
+  if (!found) return;
+  const int cb = inverse_column_block(t6);
+  const int col = cb * 16 + (t6 & 15);
+  float Tcol[C];
+  invert_column(Ls[s], cb, col, Tcol);
+  float* Timg = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, h));
+#pragma unroll
+  for (int i = 0; i < C; ++i) Timg[(col >> 2) * (C * 4) + i * 4 + (col & 3)] = tc05::to_tf32(Tcol[i]);
 }
 
 // ================================================================================================
@@ -674,6 +1005,9 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t tS = tb + lane_base + COL_S, tD2 = tb + lane_base + COL_D2, tD3 = tb + lane_base + COL_D3;
     const bool f32_state = p.state_dtype == PLA_B200_F32;
+    // KDA: the decay factors are folded into the operand images, so E1 / E2 / E3 apply none and the
+    // state is rescaled per key channel (vec[128 + k] = e^{G_C}[k]).
+    const bool kda = p.is_kda != 0;
 
     // initial state row v = m -> TMEM (fp32)
     {
@@ -723,7 +1057,8 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int i = cg + j;
-          x[j] = tc05::to_tf32(vec[C + i] * (to_f32(vrows[i * V_PITCH + ((v_sh0 + j * v_shs) & 7) + m]) - vec[2 * C + i] * x[j]));
+          const float eg = kda ? 1.0f : vec[2 * C + i];
+          x[j] = tc05::to_tf32(vec[C + i] * (to_f32(vrows[i * V_PITCH + ((v_sh0 + j * v_shs) & 7) + m]) - eg * x[j]));
         }
         tc05::tmem_st32(tD1 + cg, x);
       }
@@ -741,7 +1076,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
           tc05::tmem_ld32(tS + q4 * 32, s);
           tc05::wait_ld();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) s[j] *= gC;
+          for (int j = 0; j < 32; ++j) s[j] *= kda ? vec[2 * C + q4 * 32 + j] : gC;
           tc05::tmem_st32(tS + q4 * 32, s);
         }
       }
@@ -755,7 +1090,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
         tc05::wait_ld();
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          y[j] = tc05::to_tf32(vec[3 * C + cg + j] * x[j]);
+          y[j] = tc05::to_tf32((kda ? 1.0f : vec[3 * C + cg + j]) * x[j]);
           x[j] = tc05::to_tf32(x[j]);
         }
         tc05::tmem_st32(tD2 + cg, x);
@@ -779,7 +1114,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
         act_t* so = reinterpret_cast<act_t*>(sh.o);
         // values first, stores second: the stores may alias `vec` as far as the compiler knows
 #pragma unroll
-        for (int j = 0; j < 32; ++j) qs[j] = fmaf(vec[2 * C + cg + j], qs[j], d3[j]);
+        for (int j = 0; j < 32; ++j) qs[j] = fmaf(kda ? 1.0f : vec[2 * C + cg + j], qs[j], d3[j]);
 #pragma unroll
         for (int j = 0; j < 32; ++j) so[(cg + j) * D + m] = from_f32<act_t>(qs[j]);
         mbar_arrive(&sh.o_full);  // the storer reads with ordinary loads: no proxy fence needed
@@ -842,10 +1177,10 @@ extern "C" int64_t pla_b200_gdn_chunk_workspace_bytes(int32_t max_chunks, int32_
   return static_cast<int64_t>(max_chunks) * (static_cast<int64_t>(H) * pla::HBLOB + static_cast<int64_t>(HV) * pla::VBLOB);
 }
 
-extern "C" int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args, void* stream) {
-  using namespace pla;
-  PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
-  const pla_b200_gdn_chunk_args& a = *args;
+namespace pla {
+namespace {
+
+int check_chunk_args(const pla_b200_gdn_chunk_args& a, int64_t need_bytes) {
   PLA_REQUIRE(a.N > 0 && a.T_total >= 0 && a.max_chunks >= 0, PLA_B200_E_INVALID, "N, T_total, max_chunks out of range");
   PLA_REQUIRE(a.H > 0 && a.HV >= a.H && a.HV % a.H == 0, PLA_B200_E_INVALID,
               "HV must be a positive multiple of H, got H=%d, HV=%d", a.H, a.HV);
@@ -855,31 +1190,14 @@ extern "C" int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args,
   PLA_REQUIRE(a.act_dtype == PLA_B200_BF16 || a.act_dtype == PLA_B200_F16, PLA_B200_E_INVALID,
               "activation dtype must be bf16 or fp16");
   PLA_REQUIRE(a.workspace != nullptr && (reinterpret_cast<uintptr_t>(a.workspace) & 127) == 0 &&
-                  a.workspace_bytes >= pla_b200_gdn_chunk_workspace_bytes(a.max_chunks, a.H, a.HV),
+                  a.workspace_bytes >= need_bytes,
               PLA_B200_E_INVALID, "workspace missing, not 128-byte aligned or too small");
-  if (a.max_chunks == 0) return PLA_B200_OK;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int64_t items = static_cast<int64_t>(a.max_chunks) * a.H;
-  PLA_REQUIRE(items < (1ll << 31), PLA_B200_E_TOO_LARGE, "too many chunks");
-  auto launch_prepare = [&](auto kern) -> int {
-    static bool configured[64] = {};
-    int dev = 0;
-    PLA_CUDA_OK(cudaGetDevice(&dev));
-    if (dev < 64 && !configured[dev]) {
-      PLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(sizeof(PrepSmem) + 1024)));
-      configured[dev] = true;
-    }
-    kern<<<static_cast<unsigned>(items), 128, sizeof(PrepSmem) + 1024, s>>>(a);
-    PLA_CUDA_OK(cudaGetLastError());
-    return PLA_B200_OK;
-  };
   PLA_REQUIRE(a.stage >= 0 && a.stage <= 2, PLA_B200_E_INVALID, "stage must be 0, 1 or 2");
-  int rc = PLA_B200_OK;
-  if (a.stage != 2)
-    rc = a.act_dtype == PLA_B200_BF16 ? launch_prepare(gdn_chunk_prepare_kernel<__nv_bfloat16>)
-                                      : launch_prepare(gdn_chunk_prepare_kernel<__half>);
-  if (rc != PLA_B200_OK || a.stage == 1) return rc;
+  PLA_REQUIRE(static_cast<int64_t>(a.max_chunks) * a.H < (1ll << 31), PLA_B200_E_TOO_LARGE, "too many chunks");
+  return PLA_B200_OK;
+}
+
+int launch_chain_stage(const pla_b200_gdn_chunk_args& a, cudaStream_t s) {
   if (a.prescan) {
     PLA_REQUIRE(a.state_out != nullptr && aligned16(a.state_out), PLA_B200_E_INVALID,
                 "prescan needs a 16-byte aligned state_out of [N, HV, 2, 128, 128] fp32");
@@ -908,6 +1226,83 @@ extern "C" int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args,
   };
   return a.act_dtype == PLA_B200_BF16 ? launch_chain(gdn_chunk_chain_kernel<__nv_bfloat16>)
                                       : launch_chain(gdn_chunk_chain_kernel<__half>);
+}
+
+}  // namespace
+}  // namespace pla
+
+extern "C" int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args, void* stream) {
+  using namespace pla;
+  PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
+  pla_b200_gdn_chunk_args a = *args;
+  a.is_kda = 0;
+  const int rc0 = check_chunk_args(a, pla_b200_gdn_chunk_workspace_bytes(a.max_chunks, a.H, a.HV));
+  if (rc0 != PLA_B200_OK) return rc0;
+  if (a.max_chunks == 0) return PLA_B200_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t items = static_cast<int64_t>(a.max_chunks) * a.H;
+  auto launch_prepare = [&](auto kern) -> int {
+    static bool configured[64] = {};
+    int dev = 0;
+    PLA_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 64 && !configured[dev]) {
+      PLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(sizeof(PrepSmem) + 1024)));
+      configured[dev] = true;
+    }
+    kern<<<static_cast<unsigned>(items), 128, sizeof(PrepSmem) + 1024, s>>>(a);
+    PLA_CUDA_OK(cudaGetLastError());
+    return PLA_B200_OK;
+  };
+  int rc = PLA_B200_OK;
+  if (a.stage != 2)
+    rc = a.act_dtype == PLA_B200_BF16 ? launch_prepare(gdn_chunk_prepare_kernel<__nv_bfloat16>)
+                                      : launch_prepare(gdn_chunk_prepare_kernel<__half>);
+  if (rc != PLA_B200_OK || a.stage == 1) return rc;
+  return launch_chain_stage(a, s);
+}
+
+extern "C" int64_t pla_b200_kda_chunk_workspace_bytes(int32_t max_chunks, int32_t H) {
+  if (max_chunks < 0 || H <= 0) return 0;
+  return static_cast<int64_t>(max_chunks) * H * (pla::HBLOB + pla::VBLOB + pla::L_BYTES);
+}
+
+extern "C" int pla_b200_kda_prefill_chunked(const pla_b200_gdn_chunk_args* args, void* stream) {
+  using namespace pla;
+  PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
+  pla_b200_gdn_chunk_args a = *args;
+  a.is_kda = 1;
+  const int rc0 = check_chunk_args(a, pla_b200_kda_chunk_workspace_bytes(a.max_chunks, a.H));
+  if (rc0 != PLA_B200_OK) return rc0;
+  PLA_REQUIRE(a.H == a.HV, PLA_B200_E_INVALID, "KDA prefill needs as many q/k heads as value heads");
+  PLA_REQUIRE(!a.gate_activated, PLA_B200_E_INVALID, "chunked KDA prefill takes the raw gate input");
+  PLA_REQUIRE(a.gate_kind == PLA_B200_GATE_SOFTPLUS || (a.gate_kind == PLA_B200_GATE_SAFE && a.lower_bound < 0.0f &&
+                                                        a.lower_bound >= -5.0f),
+              PLA_B200_E_INVALID, "the safe gate needs -5 <= lower_bound < 0");
+  if (a.max_chunks == 0) return PLA_B200_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t items = static_cast<int64_t>(a.max_chunks) * a.H;
+  auto launch_prepare = [&](auto kern) -> int {
+    static bool configured[64] = {};
+    int dev = 0;
+    PLA_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 64 && !configured[dev]) {
+      PLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(sizeof(KdaPrepSmem) + 1024)));
+      configured[dev] = true;
+    }
+    kern<<<static_cast<unsigned>(items), 256, sizeof(KdaPrepSmem) + 1024, s>>>(a);
+    PLA_CUDA_OK(cudaGetLastError());
+    kda_chunk_inverse_kernel<<<static_cast<unsigned>((items + 1) / 2), 128, 0, s>>>(a, static_cast<int>(items));
+    PLA_CUDA_OK(cudaGetLastError());
+    return PLA_B200_OK;
+  };
+  int rc = PLA_B200_OK;
+  if (a.stage != 2)
+    rc = a.act_dtype == PLA_B200_BF16 ? launch_prepare(kda_chunk_prepare_kernel<__nv_bfloat16>)
+                                      : launch_prepare(kda_chunk_prepare_kernel<__half>);
+  if (rc != PLA_B200_OK || a.stage == 1) return rc;
+  return launch_chain_stage(a, s);
 }
 
 #ifdef PLA_B200_DEBUG_CLOCKS

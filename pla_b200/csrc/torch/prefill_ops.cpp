@@ -191,7 +191,7 @@ at::Tensor run_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tenso
                        const Optional& in_indices, const Optional& state_out, const Optional& out_indices,
                        bool transposed, bool normalize_qk, double scale, bool gate_activated, bool update_in_place,
                        int64_t max_chunks, int64_t stage, const Optional& status, const Optional& workspace_in,
-                       bool prescan) {
+                       bool prescan, bool is_kda = false, std::optional<double> lower_bound = std::nullopt) {
   check_cuda(q, "q");
   const int64_t T = q.size(0);
   TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3, "q, k, v must be [tokens, heads, 128]");
@@ -222,8 +222,16 @@ at::Tensor run_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tenso
   g.k_tok_stride = k.stride(0);
   g.v_tok_stride = v.stride(0);
   g.act_dtype = dtype_tag(q, "q");
-  TORCH_CHECK(gate.dim() == 2 && gate.size(0) == T && gate.size(1) == H && gate.stride(1) == 1,
-              "gate must be [tokens, H] with contiguous heads");
+  if (is_kda) {
+    TORCH_CHECK(Hg == H, "KDA prefill needs as many q/k heads as value heads");
+    TORCH_CHECK(!gate_activated, "chunked KDA prefill takes the raw gate input");
+    TORCH_CHECK(gate.size(0) == T && gate.numel() == T * H * 128 && gate.stride(-1) == 1 &&
+                    (gate.dim() == 2 || (gate.dim() == 3 && gate.stride(1) == 128)),
+                "the KDA gate must be [tokens, H, 128] or [tokens, H*128] with contiguous rows");
+  } else {
+    TORCH_CHECK(gate.dim() == 2 && gate.size(0) == T && gate.size(1) == H && gate.stride(1) == 1,
+                "gate must be [tokens, H] with contiguous heads");
+  }
   TORCH_CHECK(beta.dim() == 2 && beta.size(0) == T && beta.size(1) == H && beta.stride(1) == 1,
               "beta must be [tokens, H] with contiguous heads");
   if (gate_activated) {
@@ -234,8 +242,8 @@ at::Tensor run_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tenso
                 "raw gate inputs must share q's dtype");
     TORCH_CHECK(A_log.has_value() && dt_bias.has_value(), "raw gating needs A_log and dt_bias");
     TORCH_CHECK(A_log->scalar_type() == at::kFloat && dt_bias->scalar_type() == at::kFloat && A_log->is_contiguous() &&
-                    dt_bias->is_contiguous() && A_log->numel() == H && dt_bias->numel() == H,
-                "A_log [H] and dt_bias [H] must be contiguous fp32");
+                    dt_bias->is_contiguous() && A_log->numel() == H && dt_bias->numel() == (is_kda ? H * 128 : H),
+                "A_log [H] and dt_bias [H] (KDA: [H, 128]) must be contiguous fp32");
     g.A_log = A_log->data_ptr<float>();
     g.dt_bias = dt_bias->data_ptr<float>();
   }
@@ -303,7 +311,11 @@ at::Tensor run_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tenso
   g.scale = static_cast<float>(scale);
   g.normalize_qk = normalize_qk;
   g.stage = static_cast<int32_t>(stage);
-  const int64_t bytes = pla_b200_gdn_chunk_workspace_bytes(g.max_chunks, g.H, g.HV);
+  g.gate_kind = lower_bound.has_value() ? PLA_B200_GATE_SAFE : PLA_B200_GATE_SOFTPLUS;
+  g.lower_bound = static_cast<float>(lower_bound.value_or(0.0));
+  TORCH_CHECK(is_kda || !lower_bound.has_value(), "lower_bound is only supported for KDA");
+  const int64_t bytes = is_kda ? pla_b200_kda_chunk_workspace_bytes(g.max_chunks, g.H)
+                               : pla_b200_gdn_chunk_workspace_bytes(g.max_chunks, g.H, g.HV);
   at::Tensor workspace;
   if (workspace_in.has_value()) {
     workspace = *workspace_in;
@@ -317,7 +329,8 @@ at::Tensor run_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tenso
   g.workspace = workspace.data_ptr();
   g.workspace_bytes = bytes;
   g.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
-  check_abi(pla_b200_gdn_prefill_chunked(&g, stream_of(q)), "gdn chunked prefill");
+  check_abi(is_kda ? pla_b200_kda_prefill_chunked(&g, stream_of(q)) : pla_b200_gdn_prefill_chunked(&g, stream_of(q)),
+            is_kda ? "kda chunked prefill" : "gdn chunked prefill");
   return workspace;
 }
 
@@ -348,10 +361,30 @@ at::Tensor gdn_prefill_chunked_stage(const at::Tensor& q, const at::Tensor& k, c
                      workspace, prescan);
 }
 
+// Chunked KDA prefill; all the modes of the GDN ops in one signature (stage 0 = both halves with a fresh
+// workspace; stage 1 / 2 and prescan for context parallelism).
+at::Tensor kda_prefill_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& gate,
+                               const at::Tensor& beta, const at::Tensor& A_log, const at::Tensor& dt_bias,
+                               at::Tensor out, const at::Tensor& cu_seqlens, const Optional& state_in,
+                               const Optional& in_indices, const Optional& state_out, const Optional& out_indices,
+                               const Optional& workspace, bool transposed, bool normalize_qk, double scale,
+                               std::optional<double> lower_bound, bool update_in_place, int64_t max_chunks,
+                               int64_t stage, bool prescan, const Optional& status) {
+  return run_chunked(q, k, v, gate, beta, A_log, dt_bias, out, c10::nullopt, cu_seqlens, state_in, in_indices,
+                     state_out, out_indices, transposed, normalize_qk, scale, false, update_in_place, max_chunks, stage,
+                     status, workspace, prescan, true, lower_bound);
+}
+
 }  // namespace
 }  // namespace pla_ops
 
 TORCH_LIBRARY_FRAGMENT(pla_b200, m) {
+  m.def(
+      "kda_prefill_chunked(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor A_log, Tensor dt_bias, "
+      "Tensor(a!) out, Tensor cu_seqlens, Tensor(b!)? state_in, Tensor? in_indices, Tensor(c!)? state_out, "
+      "Tensor? out_indices, Tensor(w!)? workspace, bool transposed, bool normalize_qk, float scale, "
+      "float? lower_bound, bool update_in_place, int max_chunks, int stage, bool prescan, Tensor(d!)? status) -> Tensor",
+      &pla_ops::kda_prefill_chunked);
   m.def(
       "gdn_prefill_chunked(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor? A_log, Tensor? dt_bias, "
       "Tensor(a!) out, Tensor(e!)? g_cum, Tensor cu_seqlens, Tensor(b!)? state_in, Tensor? in_indices, "

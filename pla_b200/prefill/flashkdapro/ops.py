@@ -33,12 +33,23 @@ def flashkda_fwd(
     state_pool: Optional[torch.Tensor] = None,      # [slots, H, DV, DK] (in place)
     state_indices: Optional[torch.Tensor] = None,
     raw_cu_seqlens: Optional[Tuple[int, ...]] = None,
+    *,
+    backend: str = "auto",
+    status: Optional[torch.Tensor] = None,
 ) -> None:
     """KDA prefill over packed varlen tokens; writes ``out`` in full (rows past ``cu_seqlens[-1]``
     zero) and ``final_state`` or the pool slots. The gate is the safe gate
     ``lower_bound * sigmoid(exp(A_log) * (g + dt_bias))``; ``lower_bound=None`` (an extension)
     selects ``-exp(A_log) * softplus(g + dt_bias)``. ``None`` initial state starts from zero.
+
+    ``backend`` (keyword-only, not in the reference): ``"chunked"`` = chunk-64 tensor-core kernels (decay
+    references every 16 tokens; needs the decay of every key channel to stay within 80 nats per 16 tokens,
+    which the safe gate with ``lower_bound >= -5`` guarantees; a violation sets bit 16 of ``status``),
+    ``"recurrent"`` = exact fp32 token recurrence, ``"auto"`` = chunked for the safe gate with
+    ``-5 <= lower_bound < 0``, recurrent otherwise.
     """
+    if backend not in ("auto", "chunked", "recurrent"):
+        raise ValueError("backend must be auto, chunked or recurrent")
     if not q.is_cuda:
         raise ValueError("q must be a CUDA tensor")
     for name, t in (("k", k), ("v", v), ("g", g), ("beta", beta), ("A_log", A_log), ("dt_bias", dt_bias),
@@ -82,8 +93,18 @@ def flashkda_fwd(
         raise ValueError("out must be contiguous [total_tokens, H, DV]")
     bet = beta if beta.stride(-1) == 1 else beta.contiguous()
     gg = g if (g.stride(2) == 1 and g.stride(1) == 128) else g.contiguous()
+    lb = None if lower_bound is None else float(lower_bound)
+    if backend == "auto":
+        backend = "chunked" if (lb is not None and -5.0 <= lb < 0.0) else "recurrent"
+    if backend == "chunked":
+        max_chunks = T // 64 + (cu32.numel() - 1)
+        ops.kda_prefill_chunked(
+            _rows(q), _rows(k), _rows(v), gg, bet, A_log.contiguous(), dt_bias.contiguous(), out, cu32,
+            initial_state, in_idx, None if in_place else final_state, out_idx, None, False, True, float(scale), lb,
+            in_place, max_chunks, 0, False, status)
+        return None
     ops.prefill_recurrent(
         _rows(q), _rows(k), _rows(v), gg, bet, A_log.contiguous(), dt_bias.contiguous(), out, cu32,
         initial_state, in_idx, None if in_place else final_state, out_idx, False, True, True, float(scale),
-        None if lower_bound is None else float(lower_bound), False, in_place, None)
+        lb, False, in_place, status)
     return None

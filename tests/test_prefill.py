@@ -108,9 +108,10 @@ def test_gdn_legacy_state_and_activated_gates(native_built, with_state, state_dt
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("backend", ["recurrent", "chunked"])
 @pytest.mark.parametrize("softplus", [False, True])
 @pytest.mark.parametrize("name", sorted(cases.KDA_PREFILL_CASES))
-def test_kda_prefill(native_built, name, softplus):
+def test_kda_prefill(native_built, name, softplus, backend):
     from pla_b200.prefill.flashkdapro import flashkda_fwd
     cpu = cases.kda_prefill_case(name, softplus=softplus)
     c = cases.kda_prefill_case(name, softplus=softplus, device="cuda")
@@ -118,10 +119,12 @@ def test_kda_prefill(native_built, name, softplus):
     out = torch.full((c["T"], c["H"], D), 3.0, dtype=torch.bfloat16, device="cuda")
     final = torch.empty_like(c["init"])
     init_before = c["init"].clone()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
     flashkda_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"], c["A_log"], c["dt_bias"], out,
                  lower_bound=c["lower_bound"], initial_state=c["init"], final_state=final,
-                 cu_seqlens=torch.tensor(c["cu"], dtype=torch.int64, device="cuda"))
+                 cu_seqlens=torch.tensor(c["cu"], dtype=torch.int64, device="cuda"), backend=backend, status=status)
     torch.cuda.synchronize()
+    assert status.item() == 0
     n_real = c["cu"][-1]
     assert_out_close(out[:n_real], exp_out[:n_real])
     assert torch.count_nonzero(out[n_real:]) == 0
@@ -136,10 +139,62 @@ def test_kda_prefill(native_built, name, softplus):
     out2 = torch.empty_like(out)
     flashkda_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"], c["A_log"], c["dt_bias"], out2,
                  lower_bound=c["lower_bound"], cu_seqlens=torch.tensor(c["cu"], dtype=torch.int32, device="cuda"),
-                 state_pool=pool, state_indices=slots)
+                 state_pool=pool, state_indices=slots, backend=backend)
     torch.cuda.synchronize()
     assert torch.equal(out2, out)
     assert torch.equal(pool[slots.long()], final)
     with pytest.raises(ValueError, match="mutually exclusive"):
         flashkda_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"], c["A_log"], c["dt_bias"], out2, state_pool=pool,
                      state_indices=slots, final_state=final)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("lower_bound,a_lo,a_hi", [(-5.0, 0.0, 2.5), (-1.0, -1.0, 1.0), (None, -4.0, -2.0)])
+def test_kda_chunked_long_unaligned(native_built, lower_bound, a_lo, a_hi):
+    """Chunked KDA on many chunks per chain with rows 2 bytes off 16-byte alignment, strong decay (safe gate
+    down to -5 per token) and the weak softplus decay of the long-sequence config, against the oracle."""
+    from pla_b200.prefill.flashkdapro import flashkda_fwd
+    g = torch.Generator().manual_seed(123)
+    H, lengths = 2, [1100, 77]
+    T = sum(lengths)
+    width = 4 * H * D
+    packed = torch.randn(T, width + 8, generator=g).bfloat16()
+    gates = torch.randn(T, H, generator=g).bfloat16()
+    A_log = a_lo + (a_hi - a_lo) * torch.rand(H, generator=g)
+    dt_bias = torch.randn(H, D, generator=g) * 0.1
+    init = torch.randn(2, H, D, D, generator=g) * 0.05
+    views = lambda t: [t[:, 1 + i * H * D:1 + (i + 1) * H * D].unflatten(1, (H, D)) for i in range(4)]
+    q, k, v, gg = views(packed)
+    exp_out, exp_state, _ = odec.klast_forward(q=q, k=k, v=v, a=gg, b=gates, A_log=A_log, dt_bias=dt_bias.reshape(-1),
+                                               state=init, slot_indices=[0, 1], lengths=lengths, scale=D ** -0.5,
+                                               is_kda=True, lower_bound=lower_bound)
+    dq, dk, dv, dg = views(packed.cuda())
+    assert dq.data_ptr() % 16 == 2
+    out = torch.empty(T, H, D, dtype=torch.bfloat16, device="cuda")
+    final = torch.empty(2, H, D, D, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    flashkda_fwd(dq, dk, dv, dg, gates.cuda(), A_log.cuda(), dt_bias.cuda(), out, lower_bound=lower_bound,
+                 initial_state=init.cuda(), final_state=final, raw_cu_seqlens=(0, lengths[0], T), backend="chunked",
+                 status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert_out_close(out, exp_out)
+    assert_state_close(final.cpu(), exp_state)
+
+
+@pytest.mark.gpu
+def test_kda_chunked_reports_decay_out_of_range(native_built):
+    """An unbounded softplus gate that decays a channel by more than 80 nats inside 16 tokens cannot be
+    represented by the sub-block references: the call flags it instead of returning silently wrong numbers."""
+    from pla_b200.prefill.flashkdapro import flashkda_fwd
+    g = torch.Generator().manual_seed(5)
+    H, T = 1, 64
+    q, k, v = (torch.randn(T, H, D, generator=g).bfloat16().cuda() for _ in range(3))
+    gate = (torch.randn(T, H, D, generator=g) + 3.0).bfloat16().cuda()
+    beta = torch.randn(T, H, generator=g).bfloat16().cuda()
+    out = torch.empty(T, H, D, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    flashkda_fwd(q, k, v, gate, beta, torch.full((H,), 2.5).cuda(), torch.zeros(H, D).cuda(), out, lower_bound=None,
+                 backend="chunked", status=status)
+    torch.cuda.synchronize()
+    assert status.item() & 16
