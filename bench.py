@@ -420,14 +420,14 @@ def run_prefill_cp(args):
     S0 = torch.randn(H, D, D, generator=gd, device=dev) * 0.02
     sl = slice(lo, hi) if rank == 0 else slice(None)
     mine = [x[sl] for x in (q, k, v, gate, beta)]
-    steps = min(args.steps, 5) if kda else args.steps
+    steps = min(args.steps, 5) if (kda and args.kda_backend == "recurrent") else args.steps
 
     def step():
         if kda:
-            return kda_prefill_context_parallel(*mine, A_log, dt_bias, None, initial_state=S0)
+            return kda_prefill_context_parallel(*mine, A_log, dt_bias, None, initial_state=S0, backend=args.kda_backend)
         return gdn_prefill_context_parallel(*mine, A_log, dt_bias, initial_state=S0)
 
-    for _ in range(1 if kda else max(args.warmup, 3)):
+    for _ in range(1 if (kda and args.kda_backend == "recurrent") else max(args.warmup, 3)):
         o, final = step()
     torch.cuda.synchronize()
     dist.barrier()
@@ -446,14 +446,18 @@ def run_prefill_cp(args):
         fin = torch.empty(1, H, D, D, dtype=torch.float32, device=dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
         cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
-        if kda:
+        if kda and args.kda_backend == "chunked":
+            ops.kda_prefill_chunked(q, k, v, gate, beta, A_log, dt_bias, one, cu, S0[None].contiguous(), None, fin, None,
+                                    None, False, True, D ** -0.5, None, False, T // 64, 0, False, status)
+        elif kda:
             ops.prefill_recurrent(q, k, v, gate, beta, A_log, dt_bias, one, cu, S0[None].contiguous(), None, fin, None,
                                   False, True, True, D ** -0.5, None, False, False, status)
         else:
             ops.gdn_prefill_chunked(q, k, v, gate, beta, A_log, dt_bias, one, None, cu, S0[None].contiguous(), None, fin,
                                     None, False, True, D ** -0.5, False, False, T // 64, 0, status)
         rel = lambda a, b: float((a.float() - b.float()).norm() / b.float().norm())
-        what = (f"config4 (KDA part): 1 sequence, T={T}, 32 heads, softplus gate, A_log~U(-4,-2), token-recurrent kernel"
+        what = (f"config4 (KDA part): 1 sequence, T={T}, 32 heads, softplus gate, A_log~U(-4,-2), "
+                + ("chunk 64 (tf32) tensor-core kernels" if args.kda_backend == "chunked" else "token-recurrent kernel")
                 if kda else f"config4 (GDN part): 1 sequence, T={T}, Hqk=8 HV=24, chunk 64 (tf32)")
         print(json.dumps({"metric": "kda_prefill_context_parallel_128K" if kda else "gdn_prefill_context_parallel_64K",
                           "value": round(T / ms / 1e3, 3),
@@ -515,6 +519,8 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kda-backend", default="chunked", choices=["chunked", "recurrent"],
+                    help="prefill_cp_kda: chunk-64 tensor-core kernels or the exact token recurrence")
     ap.add_argument("--rows", type=int, default=0, help="state rows per CTA (0 = library default)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample (tuning runs)")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of a CUDA graph")

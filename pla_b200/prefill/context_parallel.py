@@ -70,6 +70,35 @@ class CudaSegmentKernels:
             raise RuntimeError(f"chunked prefill reported device status {code:#x}")
 
 
+class KdaChunkedSegmentKernels:
+    """Steps 1, 2 and 5 for KDA with the chunk-64 tensor-core kernels (pla_b200_kda_prefill_chunked)."""
+
+    def __init__(self, q, k, v, gate, beta, A_log, dt_bias, scale, normalize_qk, lower_bound):
+        from .._ops import ops  # raises ImportError when the native libraries are missing
+        self._ops = ops
+        self.a = (q, k, v, gate, beta, A_log, dt_bias)
+        self.scale, self.normalize_qk = float(scale), bool(normalize_qk)
+        self.lower_bound = None if lower_bound is None else float(lower_bound)
+        T, H = v.shape[0], v.shape[1]
+        self.T, self.H = T, H
+        self.cu = torch.tensor([0, T], dtype=torch.int32, device=q.device)
+        self.max_chunks = (T + CHUNK - 1) // CHUNK
+        self.out = torch.empty(T, H, D, dtype=q.dtype, device=q.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        self.ws = None
+
+    def _stage(self, stage, prescan, state_in, state_out):
+        q, k, v, gate, beta, A_log, dt_bias = self.a
+        self.ws = self._ops.kda_prefill_chunked(
+            q, k, v, gate, beta, A_log, dt_bias, self.out, self.cu, state_in, None, state_out, None, self.ws, False,
+            self.normalize_qk, self.scale, self.lower_bound, False, self.max_chunks, stage, prescan, self.status)
+
+    prepare = CudaSegmentKernels.prepare
+    prescan = CudaSegmentKernels.prescan
+    segment = CudaSegmentKernels.segment
+    check = CudaSegmentKernels.check
+
+
 class RecurrentSegmentKernels:
     """Steps 2 and 5 with the token-recurrent kernel (pla_b200_prefill_recurrent; KDA or GDN)."""
 
@@ -203,15 +232,23 @@ def kda_prefill_context_parallel(
     output_final_state: bool = True,
     group: Optional[dist.ProcessGroup] = None,
     segment_kernels=None,
+    backend: str = "auto",
 ):
-    """KDA counterpart of :func:`gdn_prefill_context_parallel` (same ranges, same exchange), evaluated
-    with the token-recurrent kernel."""
+    """KDA counterpart of :func:`gdn_prefill_context_parallel` (same ranges, same exchange).
+    ``backend``: ``"chunked"`` (tensor-core kernels; decay bounded as ``flashkda_fwd`` documents),
+    ``"recurrent"`` (exact token recurrence), ``"auto"`` = chunked for the safe gate with
+    ``-5 <= lower_bound < 0``."""
     if scale is None:
         scale = D ** -0.5
     kernels = segment_kernels
     if kernels is None:
-        kernels = RecurrentSegmentKernels(q, k, v, g, beta, A_log, dt_bias, scale, normalize_qk, False, True,
-                                          lower_bound)
+        if backend == "auto":
+            backend = "chunked" if (lower_bound is not None and -5.0 <= lower_bound < 0.0) else "recurrent"
+        if backend == "chunked":
+            kernels = KdaChunkedSegmentKernels(q, k, v, g, beta, A_log, dt_bias, scale, normalize_qk, lower_bound)
+        else:
+            kernels = RecurrentSegmentKernels(q, k, v, g, beta, A_log, dt_bias, scale, normalize_qk, False, True,
+                                              lower_bound)
     return run_context_parallel(kernels, v, initial_state, output_final_state, group)
 
 

@@ -92,8 +92,9 @@ def make_kda(T, H, seed):
     return q, k, v, gate, beta, A_log, dt_bias, S0
 
 
+@pytest.mark.parametrize("chunked", [False, True])
 @pytest.mark.parametrize("lower_bound", [-5.0, None])
-def test_kda_emulated_ranks_match_oracle(native_built, lower_bound):
+def test_kda_emulated_ranks_match_oracle(native_built, lower_bound, chunked):
     """KDA: prescan pairs of the token-recurrent kernel against the oracle, then ranks emulated one after
     another against the serial oracle recurrence."""
     from pla_b200.prefill import context_parallel as cp
@@ -106,8 +107,12 @@ def test_kda_emulated_ranks_match_oracle(native_built, lower_bound):
     plans, lo = [], 0
     for r, n in enumerate(splits):
         sl = slice(lo, lo + n)
-        kern = cp.RecurrentSegmentKernels(dq[sl], dk[sl], dv[sl], dg[sl], db[sl], dA, dB, D ** -0.5, True, False, True,
-                                          lower_bound)
+        if chunked:
+            kern = cp.KdaChunkedSegmentKernels(dq[sl], dk[sl], dv[sl], dg[sl], db[sl], dA, dB, D ** -0.5, True,
+                                               lower_bound)
+        else:
+            kern = cp.RecurrentSegmentKernels(dq[sl], dk[sl], dv[sl], dg[sl], db[sl], dA, dB, D ** -0.5, True, False,
+                                              True, lower_bound)
         plans.append(cp.begin_segment(kern, r, W, n, H, dev))
         if r == 0:
             ref = OracleSegmentKernels(q[sl], k[sl], v[sl], gate[sl], beta[sl], A_log, dt_bias, D ** -0.5, is_kda=True,
