@@ -399,6 +399,8 @@ def run_prefill_cp(args):
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     T, Hg, H = (131072, 32, 32) if kda else (65536, 8, 24)
+    if args.tokens:
+        T = args.tokens          # profiling aid; the workload string then says so
     per = (T // world + 63) // 64 * 64
     lo, hi = min(rank * per, T), min((rank + 1) * per, T)
     gd = torch.Generator(device=dev).manual_seed(44)
@@ -459,6 +461,8 @@ def run_prefill_cp(args):
         what = (f"config4 (KDA part): 1 sequence, T={T}, 32 heads, softplus gate, A_log~U(-4,-2), "
                 + ("chunk 64 (tf32) tensor-core kernels" if args.kda_backend == "chunked" else "token-recurrent kernel")
                 if kda else f"config4 (GDN part): 1 sequence, T={T}, Hqk=8 HV=24, chunk 64 (tf32)")
+        if args.tokens:
+            what = "REDUCED (profiling aid) " + what
         print(json.dumps({"metric": "kda_prefill_context_parallel_128K" if kda else "gdn_prefill_context_parallel_64K",
                           "value": round(T / ms / 1e3, 3),
                           "unit": "Mtok/s", "n_gpus": world, "steps": steps, "ms_per_step": round(ms, 4),
@@ -519,6 +523,8 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="prefill_cp / prefill_cp_kda: sequence length override (profiling aid, multiple of 64)")
     ap.add_argument("--kda-backend", default="chunked", choices=["chunked", "recurrent"],
                     help="prefill_cp_kda: chunk-64 tensor-core kernels or the exact token recurrence")
     ap.add_argument("--rows", type=int, default=0, help="state rows per CTA (0 = library default)")

@@ -416,7 +416,7 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
 // [K e^{G-R}; Q e^{G-R}], four MMA chains; row block a of chain a is the wanted block row.
 // The chain kernel gets  [K e^{G}; Q e^{G}]  (decay from the chunk start folded in),
 // (K e^{G_C - G})^T  for the state update, beta and e^{G_C} per channel.
-// Launch 1 (`kda_chunk_prepare_kernel`, 256 threads, one CTA per SM) builds everything except T and
+// Launch 1 (`kda_chunk_prepare_kernel`, 512 threads, one CTA per SM) builds everything except T and
 // leaves L (fp32) in the workspace; launch 2 (`kda_chunk_inverse_kernel`, light, many CTAs per SM)
 // turns L into the T image.
 constexpr int DM_PITCH = 132;  // floats per row of the decay-factor matrix: float4 rows, conflict-free per quarter warp
@@ -427,12 +427,15 @@ __host__ __device__ inline int64_t ws_lmat(int64_t max_chunks, int H, int64_t gc
   return max_chunks * H * static_cast<int64_t>(HBLOB + VBLOB) + (gc * H + h) * static_cast<int64_t>(L_BYTES);
 }
 
+constexpr int KDA_PREP_THREADS = 512;
+constexpr int SB = 16;  // tokens per sub-block (decay reference points)
+
 struct KdaPrepSmem {
   alignas(1024) float kq[KQ_BYTES / 4];
   alignas(1024) unsigned char km[KM_BYTES];  // first the staged gate rows, then the four B images
   alignas(16) float dm[C * DM_PITCH];        // e^{G - R_block} per (token, channel)
   alignas(16) uint32_t stg[128 * 68];        // staged raw k rows (0..63) and q rows (64..127)
-  alignas(16) float rv[4][D];                // R_a
+  alignas(16) float part[4][D];              // log decay of each sub-block, per channel
   alignas(16) float erb[4][D];               // e^{R_a}
   alignas(16) float egc[4][D];               // e^{G_C - R_a}
   alignas(16) float fab[6][D];               // e^{R_a - R_b}, a > b, at index a (a - 1) / 2 + b
@@ -444,7 +447,7 @@ struct KdaPrepSmem {
 };
 
 template <typename act_t>
-__global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const pla_b200_gdn_chunk_args p) {
+__global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(const pla_b200_gdn_chunk_args p) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem_raw = smem_dyn + ((1024u - (smem_addr(smem_dyn) & 1023u)) & 1023u);
   KdaPrepSmem& sh = *reinterpret_cast<KdaPrepSmem*>(smem_raw);
@@ -461,14 +464,16 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const pla_b20
   }
   constexpr int STG = 68;  // staged row pitch in 32-bit words = 17 x 16 bytes
   uint32_t* gstg = reinterpret_cast<uint32_t*>(sh.km);
+  const act_t* kbase = static_cast<const act_t*>(p.k) + pos.tok0 * p.k_tok_stride + h * D;
+  const act_t* qbase = static_cast<const act_t*>(p.q) + pos.tok0 * p.q_tok_stride + h * D;
 
   // ---- stage the chunk's k, q and gate rows (16 or 17 aligned 16-byte pieces per 256-byte row) ----
-  for (int r = warp; r < 192; r += 8) {
+  for (int r = warp; r < 192; r += KDA_PREP_THREADS / 32) {
     const int c = r & 63, which = r >> 6;
     if (c >= pos.n || lane >= 17) continue;
-    const act_t* base = static_cast<const act_t*>(which == 0 ? p.k : which == 1 ? p.q : p.gate);
-    const int64_t stride = which == 0 ? p.k_tok_stride : which == 1 ? p.q_tok_stride : p.gate_tok_stride;
-    const act_t* row = base + (pos.tok0 + c) * stride + h * D;
+    const act_t* row = which == 0   ? kbase + c * p.k_tok_stride
+                       : which == 1 ? qbase + c * p.q_tok_stride
+                                    : static_cast<const act_t*>(p.gate) + (pos.tok0 + c) * p.gate_tok_stride + h * D;
     const char* src = reinterpret_cast<const char*>(reinterpret_cast<uintptr_t>(row) & ~uintptr_t(15));
     if (lane == 16 && src == reinterpret_cast<const char*>(row)) continue;
     uint32_t* dst = which < 2 ? sh.stg + r * STG : gstg + c * STG;
@@ -478,128 +483,140 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const pla_b20
   asm volatile("cp.async.wait_all;" ::: "memory");
   __syncthreads();
 
-  if (tid < 128) {
-    // ---- one thread per channel: log decay, running sum, sub-block references, decay factors ----
-    const int c = tid;
+  // ---- L2 norms: four threads per row (adjacent lanes), 16 words each ----
+  {
+    const int r = tid >> 2, qt = tid & 3, c = r & 63;
+    const bool is_q = r >= 64;
+    const bool live = c < pos.n;
+    float ss = 0.f;
+    if (live && p.normalize_qk) {
+      const act_t* row = is_q ? qbase + c * p.q_tok_stride : kbase + c * p.k_tok_stride;
+      const int sh_half = static_cast<int>((reinterpret_cast<uintptr_t>(row) & 15) >> 1);
+      const uint32_t* srow = sh.stg + r * STG + (sh_half >> 1) + 16 * qt;
+      const bool odd = sh_half & 1;
+      // the eight rows of a warp start 4 banks apart and the quarters 16: a per-lane rotation of the
+      // word order gives every lane its own bank
+      const int rot = (qt & 2) | ((lane >> 4) & 1);
+#pragma unroll 8
+      for (int i0 = 0; i0 < 16; ++i0) {
+        const int i = (i0 + rot) & 15;
+        const uint32_t w = odd ? __funnelshift_r(srow[i], srow[i + 1], 16) : srow[i];
+        const act_t* e = reinterpret_cast<const act_t*>(&w);
+        const float x0 = to_f32(e[0]), x1 = to_f32(e[1]);
+        ss = fmaf(x0, x0, fmaf(x1, x1, ss));
+      }
+    }
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);   // outside every branch: all lanes take part
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    float rn = 0.f;
+    if (live) rn = (is_q ? p.scale : 1.0f) * (p.normalize_qk ? rsqrtf(ss + 1e-6f) : 1.0f);
+    if (qt == 0) sh.rnorm[r] = rn;
+    if (qt == 1 && !is_q)
+      sh.beta[c] = live ? sigmoidf_fast(to_f32(static_cast<const act_t*>(p.beta)[(pos.tok0 + c) * p.beta_tok_stride + h]))
+                        : 0.f;
+  }
+
+  // ---- one thread per (channel, sub-block): log decay, its running sum inside the sub-block, decay
+  // factors e^{G - R}; the sub-blocks are independent because R is the sum up to the sub-block start ----
+  {
+    const int c = tid & 127, blk = tid >> 7;
     const float A_log = p.A_log[h];
     const float dtb = p.dt_bias[h * D + c];
     const unsigned short* gs = reinterpret_cast<const unsigned short*>(gstg);
     const int64_t e0 = static_cast<int64_t>(reinterpret_cast<uintptr_t>(p.gate) >> 1) + pos.tok0 * p.gate_tok_stride + h * D;
-    float G = 0.f, R = 0.f;
-    bool range_ok = true;
-    for (int t = 0; t < C; ++t) {
-      if ((t & 15) == 0) {
-        range_ok &= (R - G) <= 80.0f;
-        R = G;
-        sh.rv[t >> 4][c] = R;
-      }
+    float G = 0.f;
+#pragma unroll 4
+    for (int tt = 0; tt < SB; ++tt) {
+      const int t = blk * SB + tt;
       if (t < pos.n) {
         const int shf = static_cast<int>((e0 + t * p.gate_tok_stride) & 7);
         act_t raw;
         *reinterpret_cast<unsigned short*>(&raw) = gs[t * (STG * 2) + shf + c];
         G += log_decay(to_f32(raw) + dtb, A_log, p.gate_kind, 1.0f, 20.0f, p.lower_bound);
       }
-      sh.dm[t * DM_PITCH + c] = __expf(G - R);
+      sh.dm[t * DM_PITCH + c] = __expf(G);
     }
-    range_ok &= (R - G) <= 80.0f;
-    sh.gc[c] = G;
-    if (!range_ok && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_DECAY_RANGE);
-  } else {
-    // ---- meanwhile one thread per k / q row: L2 norm; k-row threads also activate beta ----
-    const int r = tid - 128, c = r & 63;
-    const bool is_q = r >= 64;
-    float rn = 0.f;
-    if (c < pos.n) {
-      const act_t* base = static_cast<const act_t*>(is_q ? p.q : p.k);
-      const act_t* row = base + (pos.tok0 + c) * (is_q ? p.q_tok_stride : p.k_tok_stride) + h * D;
-      const int sh_half = static_cast<int>((reinterpret_cast<uintptr_t>(row) & 15) >> 1);
-      const uint32_t* srow = sh.stg + r * STG + (sh_half >> 1);
-      const bool odd = sh_half & 1;
-      rn = is_q ? p.scale : 1.0f;
-      if (p.normalize_qk) {
-        float ss = 0.f;
-        const int rot = lane >> 3;  // rows of a warp are 4 banks apart: start each group of 8 lanes one word later
-#pragma unroll 8
-        for (int i0 = 0; i0 < D / 2; ++i0) {
-          const int i = (i0 + rot) & 63;
-          const uint32_t w = odd ? __funnelshift_r(srow[i], srow[i + 1], 16) : srow[i];
-          const act_t* e = reinterpret_cast<const act_t*>(&w);
-          const float x0 = to_f32(e[0]), x1 = to_f32(e[1]);
-          ss = fmaf(x0, x0, fmaf(x1, x1, ss));
-        }
-        rn *= rsqrtf(ss + 1e-6f);
-      }
-      if (!is_q) sh.beta[c] = sigmoidf_fast(to_f32(static_cast<const act_t*>(p.beta)[(pos.tok0 + c) * p.beta_tok_stride + h]));
-    } else if (!is_q) {
-      sh.beta[c] = 0.f;
-    }
-    sh.rnorm[r] = rn;
+    sh.part[blk][c] = G;
+    if (G < -80.0f && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_DECAY_RANGE);
   }
   __syncthreads();
-  // ---- per-channel tables ----
-  for (int i = tid; i < 14 * D; i += 256) {
+  // ---- per-channel tables from the sub-block sums ----
+  for (int i = tid; i < 14 * D; i += KDA_PREP_THREADS) {
     const int which = i / D, c = i % D;
-    if (which < 4) sh.erb[which][c] = __expf(sh.rv[which][c]);
-    else if (which < 8) sh.egc[which - 4][c] = __expf(sh.gc[c] - sh.rv[which - 4][c]);
-    else {
+    const float b0 = sh.part[0][c], b1 = sh.part[1][c], b2 = sh.part[2][c], b3 = sh.part[3][c];
+    // R_a = log decay before sub-block a
+    auto ref = [&](int a) { return (a > 0 ? b0 : 0.f) + (a > 1 ? b1 : 0.f) + (a > 2 ? b2 : 0.f); };
+    const float total = b0 + b1 + b2 + b3;
+    if (which < 4) {
+      sh.erb[which][c] = __expf(ref(which));
+      if (which == 0) sh.gc[c] = total;
+    } else if (which < 8) {
+      sh.egc[which - 4][c] = __expf(total - ref(which - 4));
+    } else {
       const int f = which - 8;                       // (a, b): (1,0) (2,0) (2,1) (3,0) (3,1) (3,2)
       const int a = f < 1 ? 1 : f < 3 ? 2 : 3, b = f - a * (a - 1) / 2;
-      sh.fab[f][c] = __expf(sh.rv[a][c] - sh.rv[b][c]);
+      sh.fab[f][c] = __expf(ref(a) - ref(b));
     }
   }
   __syncthreads();  // also: the staged gate rows (aliased with the B images) are fully consumed
 
-  // ---- operand images: thread = (row, half of the channels) ----
+  // ---- operand images: thread = (token c, eighth of the channels), for the k row AND the q row of the
+  // token (same decay factors, same work for every thread) ----
   unsigned char* ws = static_cast<unsigned char*>(p.workspace);
   {
-    const int r = tid & 127, hh = tid >> 7, c = r & 63, blk = c >> 4;
-    const bool is_q = r >= 64;
-    const float rn = sh.rnorm[r];
-    const act_t* base = static_cast<const act_t*>(is_q ? p.q : p.k);
-    const act_t* row = base + (pos.tok0 + c) * (is_q ? p.q_tok_stride : p.k_tok_stride) + h * D;
-    const int sh_half = static_cast<int>((reinterpret_cast<uintptr_t>(row) & 15) >> 1);
-    const uint32_t* __restrict__ srow = sh.stg + r * STG + (sh_half >> 1);
-    const bool odd = sh_half & 1;
+    const int c = tid & 63, e8 = tid >> 6, blk = c >> 4;
     const bool live = c < pos.n;
-    auto pair_at = [&](int i) -> uint32_t { return odd ? __funnelshift_r(srow[i], srow[i + 1], 16) : srow[i]; };
+    const float rnk = sh.rnorm[c], rnq = sh.rnorm[64 + c];
+    const int shk = static_cast<int>((reinterpret_cast<uintptr_t>(kbase + c * p.k_tok_stride) & 15) >> 1);
+    const int shq = static_cast<int>((reinterpret_cast<uintptr_t>(qbase + c * p.q_tok_stride) & 15) >> 1);
+    const uint32_t* __restrict__ krow = sh.stg + c * STG + (shk >> 1);
+    const uint32_t* __restrict__ qrow = sh.stg + (64 + c) * STG + (shq >> 1);
+    const bool oddk = shk & 1, oddq = shq & 1;
     float4* __restrict__ kq4 = reinterpret_cast<float4*>(sh.kq);
     float4* __restrict__ kqs_g = reinterpret_cast<float4*>(ws + ws_hblob(gc, h, p.H));
     float* __restrict__ ke_g = reinterpret_cast<float*>(ws + ws_hblob(gc, h, p.H) + KQ_BYTES);
     const float4* __restrict__ dmrow = reinterpret_cast<const float4*>(sh.dm + c * DM_PITCH);
-#pragma unroll 2
-    for (int kc = hh * 16; kc < hh * 16 + 16; ++kc) {
-      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    auto tf4 = [](float4 v) {
+      return make_float4(tc05::to_tf32(v.x), tc05::to_tf32(v.y), tc05::to_tf32(v.z), tc05::to_tf32(v.w));
+    };
+    auto mul4 = [](float4 a, float4 b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); };
+#pragma unroll
+    for (int kc = e8 * 4; kc < e8 * 4 + 4; ++kc) {
+      float4 xk = make_float4(0.f, 0.f, 0.f, 0.f), xq = xk;
       if (live) {
-        const uint32_t w0 = pair_at(2 * kc), w1 = pair_at(2 * kc + 1);
-        const act_t* e0 = reinterpret_cast<const act_t*>(&w0);
-        const act_t* e1 = reinterpret_cast<const act_t*>(&w1);
-        x = make_float4(to_f32(e0[0]) * rn, to_f32(e0[1]) * rn, to_f32(e1[0]) * rn, to_f32(e1[1]) * rn);
+        const uint32_t k0 = oddk ? __funnelshift_r(krow[2 * kc], krow[2 * kc + 1], 16) : krow[2 * kc];
+        const uint32_t k1 = oddk ? __funnelshift_r(krow[2 * kc + 1], krow[2 * kc + 2], 16) : krow[2 * kc + 1];
+        const uint32_t q0 = oddq ? __funnelshift_r(qrow[2 * kc], qrow[2 * kc + 1], 16) : qrow[2 * kc];
+        const uint32_t q1 = oddq ? __funnelshift_r(qrow[2 * kc + 1], qrow[2 * kc + 2], 16) : qrow[2 * kc + 1];
+        const act_t* a0 = reinterpret_cast<const act_t*>(&k0);
+        const act_t* a1 = reinterpret_cast<const act_t*>(&k1);
+        const act_t* b0 = reinterpret_cast<const act_t*>(&q0);
+        const act_t* b1 = reinterpret_cast<const act_t*>(&q1);
+        xk = make_float4(to_f32(a0[0]) * rnk, to_f32(a0[1]) * rnk, to_f32(a1[0]) * rnk, to_f32(a1[1]) * rnk);
+        xq = make_float4(to_f32(b0[0]) * rnq, to_f32(b0[1]) * rnq, to_f32(b1[0]) * rnq, to_f32(b1[1]) * rnq);
       }
       const float4 dv = dmrow[kc];
-      const float4 xp = make_float4(x.x * dv.x, x.y * dv.y, x.z * dv.z, x.w * dv.w);
-      kq4[kc * 128 + r] = make_float4(tc05::to_tf32(xp.x), tc05::to_tf32(xp.y), tc05::to_tf32(xp.z), tc05::to_tf32(xp.w));
       const float4 er = reinterpret_cast<const float4*>(sh.erb[blk])[kc];
-      kqs_g[kc * 128 + r] = make_float4(tc05::to_tf32(xp.x * er.x), tc05::to_tf32(xp.y * er.y),
-                                        tc05::to_tf32(xp.z * er.z), tc05::to_tf32(xp.w * er.w));
-      if (!is_q) {
-        const float4 bs = make_float4(__fdividef(x.x, fmaxf(dv.x, 1e-37f)), __fdividef(x.y, fmaxf(dv.y, 1e-37f)),
-                                      __fdividef(x.z, fmaxf(dv.z, 1e-37f)), __fdividef(x.w, fmaxf(dv.w, 1e-37f)));
+      const float4 kp = mul4(xk, dv), qp = mul4(xq, dv);
+      kq4[kc * 128 + c] = tf4(kp);
+      kq4[kc * 128 + 64 + c] = tf4(qp);
+      kqs_g[kc * 128 + c] = tf4(mul4(kp, er));
+      kqs_g[kc * 128 + 64 + c] = tf4(mul4(qp, er));
+      const float4 bs = make_float4(__fdividef(xk.x, fmaxf(dv.x, 1e-37f)), __fdividef(xk.y, fmaxf(dv.y, 1e-37f)),
+                                    __fdividef(xk.z, fmaxf(dv.z, 1e-37f)), __fdividef(xk.w, fmaxf(dv.w, 1e-37f)));
 #pragma unroll
-        for (int a = 0; a < 4; ++a) {
-          if (a < blk) continue;
-          float4 f = make_float4(1.f, 1.f, 1.f, 1.f);
-          if (a > blk) f = reinterpret_cast<const float4*>(sh.fab[a * (a - 1) / 2 + blk])[kc];
-          float4* img = reinterpret_cast<float4*>(sh.km + km_offset(a));
-          img[kc * (16 * (a + 1)) + c] = make_float4(tc05::to_tf32(bs.x * f.x), tc05::to_tf32(bs.y * f.y),
-                                                     tc05::to_tf32(bs.z * f.z), tc05::to_tf32(bs.w * f.w));
-        }
-        const float4 eg = reinterpret_cast<const float4*>(sh.egc[blk])[kc];
-        float* __restrict__ dst = ke_g + (c >> 2) * (D * 4) + (kc * 4) * 4 + (c & 3);
-        dst[0] = tc05::to_tf32(bs.x * eg.x);
-        dst[4] = tc05::to_tf32(bs.y * eg.y);
-        dst[8] = tc05::to_tf32(bs.z * eg.z);
-        dst[12] = tc05::to_tf32(bs.w * eg.w);
+      for (int a = 0; a < 4; ++a) {
+        if (a < blk) continue;
+        float4 f = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (a > blk) f = reinterpret_cast<const float4*>(sh.fab[a * (a - 1) / 2 + blk])[kc];
+        reinterpret_cast<float4*>(sh.km + km_offset(a))[kc * (16 * (a + 1)) + c] = tf4(mul4(bs, f));
       }
+      const float4 ke = tf4(mul4(bs, reinterpret_cast<const float4*>(sh.egc[blk])[kc]));
+      float* __restrict__ dst = ke_g + (c >> 2) * (D * 4) + (kc * 4) * 4 + (c & 3);
+      dst[0] = ke.x;
+      dst[4] = ke.y;
+      dst[8] = ke.z;
+      dst[12] = ke.w;
     }
   }
   fence_async_smem();
@@ -624,6 +641,16 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const pla_b20
     }
     tc05::mma_commit(&sh.bar);
   }
+  // vectors for the chain while the tensor core works: beta per token, e^{G_C} per channel
+  if (tid >= 128 && tid < 256) {
+    float* vec = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, h) + TM_BYTES + PM_BYTES);
+    const int c = tid - 128;
+    vec[2 * C + c] = __expf(sh.gc[c]);
+    if (c < C) {
+      vec[c] = 0.f;
+      vec[C + c] = sh.beta[c];
+    }
+  }
   {
     const bool ok = mbar_wait(&sh.bar, 0, 1u << 20);
     if (__syncthreads_or(!ok)) {
@@ -635,59 +662,50 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_prepare_kernel(const pla_b20
   }
   tc05::fence_after_sync();
 
-  if (tid < 128) {
-    // this thread's row: i = tid % 64 of K+ K-^T (tid < 64) or of Q+ K-^T; lanes 0-15 of a warp sit in
-    // sub-block a0 = 2 (warp % 2), lanes 16-31 in a0 + 1
-    const int i_row = tid & 63;
-    const bool p_row = tid >= 64;
-    const int a0 = 2 * (warp & 1);
-    float d0[C];
+  // ---- rows of L and P: TMEM lane = row (0..63 K+ rows, 64..127 Q+ rows); the four warps that may touch a
+  // lane quadrant split the 64 columns; lanes 0-15 of a warp sit in sub-block a0 = 2 (quadrant % 2),
+  // lanes 16-31 in a0 + 1 ----
+  {
+    const int quad = warp & 3, cs = warp >> 2;        // column slice: j in [16 cs, 16 cs + 16)
+    const int row = quad * 32 + lane;                 // TMEM lane
+    const int i_row = row & 63;
+    const bool p_row = row >= 64;
+    const int a0 = 2 * (quad & 1);
+    float d0[16];
 #pragma unroll
     for (int pass = 0; pass < 2; ++pass) {
       const int a = a0 + pass;
-      float t0[32], t1[32];
-      tc05::tmem_ld32(tc05::taddr(tbase, warp * 32, 8 * a * (a + 1)), t0);
-      tc05::tmem_ld32(tc05::taddr(tbase, warp * 32, 8 * a * (a + 1) + 32), t1);
+      float t0[32];
+      tc05::tmem_ld32(tc05::taddr(tbase, quad * 32, 8 * a * (a + 1) + 16 * cs), t0);   // 16 of the 32 are used
       tc05::wait_ld();
       if ((lane >> 4) == pass) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          d0[j] = t0[j];
-          d0[32 + j] = t1[j];
-        }
+        for (int j = 0; j < 16; ++j) d0[j] = t0[j];
       }
     }
+    // columns at or beyond 16 (a + 1) of chain a hold other chains' data: never selected below (j <= i_row)
     if (!p_row) {
       const float bi = sh.beta[i_row];
-      float4* __restrict__ Lg = reinterpret_cast<float4*>(ws + ws_lmat(p.max_chunks, p.H, gc, h)) + i_row * (C / 4);
+      float4* __restrict__ Lg = reinterpret_cast<float4*>(ws + ws_lmat(p.max_chunks, p.H, gc, h)) + i_row * (C / 4) + cs * 4;
 #pragma unroll
-      for (int jc = 0; jc < C / 4; ++jc) {
+      for (int jc = 0; jc < 4; ++jc) {
         float x[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) x[u] = (jc * 4 + u < i_row) ? bi * d0[jc * 4 + u] : 0.0f;
+        for (int u = 0; u < 4; ++u) x[u] = (cs * 16 + jc * 4 + u < i_row) ? bi * d0[jc * 4 + u] : 0.0f;
         Lg[jc] = make_float4(x[0], x[1], x[2], x[3]);
       }
     } else {
       float4* __restrict__ Pimg = reinterpret_cast<float4*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, h) + TM_BYTES);
 #pragma unroll
-      for (int jc = 0; jc < C / 4; ++jc) {
+      for (int jc = 0; jc < 4; ++jc) {
         float x[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const int j = jc * 4 + u;
-          x[u] = (j <= i_row && i_row < pos.n) ? tc05::to_tf32(d0[j]) : 0.0f;
+          const int j = cs * 16 + jc * 4 + u;
+          x[u] = (j <= i_row && i_row < pos.n) ? tc05::to_tf32(d0[jc * 4 + u]) : 0.0f;
         }
-        Pimg[jc * C + i_row] = make_float4(x[0], x[1], x[2], x[3]);
+        Pimg[(cs * 4 + jc) * C + i_row] = make_float4(x[0], x[1], x[2], x[3]);
       }
-    }
-  } else {
-    // vectors for the chain: beta per token, e^{G_C} per channel
-    float* vec = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, h) + TM_BYTES + PM_BYTES);
-    const int c = tid - 128;
-    vec[2 * C + c] = __expf(sh.gc[c]);
-    if (c < C) {
-      vec[c] = 0.f;
-      vec[C + c] = sh.beta[c];
     }
   }
   tc05::fence_before_sync();
@@ -1291,7 +1309,7 @@ extern "C" int pla_b200_kda_prefill_chunked(const pla_b200_gdn_chunk_args* args,
                                        static_cast<int>(sizeof(KdaPrepSmem) + 1024)));
       configured[dev] = true;
     }
-    kern<<<static_cast<unsigned>(items), 256, sizeof(KdaPrepSmem) + 1024, s>>>(a);
+    kern<<<static_cast<unsigned>(items), KDA_PREP_THREADS, sizeof(KdaPrepSmem) + 1024, s>>>(a);
     PLA_CUDA_OK(cudaGetLastError());
     kda_chunk_inverse_kernel<<<static_cast<unsigned>((items + 1) / 2), 128, 0, s>>>(a, static_cast<int>(items));
     PLA_CUDA_OK(cudaGetLastError());

@@ -117,11 +117,11 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
                : "memory");
 }
 
-// fp32 -> tf32 with round-to-nearest (the tensor core itself only truncates).
+// fp32 -> tf32 with round-to-nearest, ties away from zero (what cvt.rna.tf32.f32 computes; the tensor
+// core itself only truncates). Done on the integer pipe: the conversion instruction shares the
+// transcendental unit, which the operand builders already keep busy.
 __device__ __forceinline__ float to_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
+  return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
 }
 
 }  // namespace tc05
