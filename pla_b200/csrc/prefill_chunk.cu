@@ -11,12 +11,14 @@
 // Launch 1, `prepare` (one CTA per chunk and q/k head): L2-normalises the chunk's k and q rows,
 // rounds them to tf32 into the tensor-core operand layout, forms Kn Kn^T and Qn Kn^T with ONE
 // 128x64x128 tcgen05 MMA chain ([Kn; Qn] against Kn), and per value head of that q/k head builds
-// the gate cumsum, P = tril(Qn Kn^T .* Gamma) and T by fp32 forward substitution (one thread per
-// column, the reference found low-precision inverses unstable: docs/prefill_readme.md:162-166).
+// the gate cumsum, L (fp32) and P = tril(Qn Kn^T .* Gamma).
+// Launch 2, `inverse` (64 threads per chunk and value head): T = (I + L)^-1 by fp32 forward
+// substitution, one thread per column (the reference found low-precision inverses unstable:
+// docs/prefill_readme.md:162-166).
 // Everything the chain needs is written to the workspace as ready-made operand images, so the
 // chain fetches them with plain 1-D bulk copies.
 //
-// Launch 2, `chain` (one CTA per sequence and value head): see the second half of this file.
+// Launch 3, `chain` (one CTA per sequence and value head): see the second half of this file.
 //
 // Precision: all contractions run as kind::tf32 with fp32 accumulation. The operands written by
 // this code are rounded to nearest; a bf16 pipeline misses the 1e-3 state bar (measured on a CPU
@@ -115,41 +117,29 @@ __device__ __forceinline__ void invert_column(const float* __restrict__ L, int c
   }
 }
 
+constexpr int PREP_THREADS = 256;
+constexpr int PREP_HEADS = 8;   // value heads of one q/k head handled per pass
+constexpr int L_BYTES = C * C * 4;
+// fp32 L matrices [chunk][value head][64][64] behind the operand images
+__host__ __device__ inline int64_t ws_lmat(int64_t max_chunks, int H, int HV, int64_t gc, int hv) {
+  return max_chunks * (H * static_cast<int64_t>(HBLOB) + HV * static_cast<int64_t>(VBLOB)) +
+         (gc * HV + hv) * static_cast<int64_t>(L_BYTES);
+}
+
 struct PrepSmem {
   alignas(1024) float kq[KQ_BYTES / 4];
-  alignas(16) float L[2][C * L_STRIDE];  // phase A reuses this space to stage the raw rows
-  float G[2][C];
-  float beta[2][C];
+  alignas(16) uint32_t stg[128 * 68];    // staged raw k rows (0..63) and q rows (64..127)
+  float G[PREP_HEADS][C];
+  float beta[PREP_HEADS][C];
+  float rnorm[128];
   alignas(8) uint64_t bar;
   uint32_t tmem_base;
 };
 
+// Launch 1 of the GDN prepare: operand images, Kn Kn^T | Qn Kn^T on the tensor core, gates, L (fp32, to the
+// workspace) and the P image. 256 threads, two CTAs per SM. Launch 2 (`chunk_inverse_kernel`) inverts I + L.
 template <typename act_t>
-__device__ __forceinline__ float row_sumsq(const act_t* row, bool vec) {
-  float ss = 0.f;
-  if (vec) {
-#pragma unroll 4
-    for (int i = 0; i < D / 8; ++i) {
-      const uint4 raw = reinterpret_cast<const uint4*>(row)[i];
-      const act_t* e = reinterpret_cast<const act_t*>(&raw);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float x = to_f32(e[j]);
-        ss += x * x;
-      }
-    }
-  } else {
-#pragma unroll 8
-    for (int i = 0; i < D; ++i) {
-      const float x = to_f32(row[i]);
-      ss += x * x;
-    }
-  }
-  return ss;
-}
-
-template <typename act_t>
-__global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_gdn_chunk_args p) {
+__global__ void __launch_bounds__(PREP_THREADS, 2) gdn_chunk_prepare_kernel(const pla_b200_gdn_chunk_args p) {
   extern __shared__ unsigned char smem_dyn[];
   // the launch reserves 1 KiB of slack so that the operand images can be aligned by hand
   unsigned char* smem_raw = smem_dyn + ((1024u - (smem_addr(smem_dyn) & 1023u)) & 1023u);
@@ -166,92 +156,107 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
     mbar_init(&sh.bar, 1);
     fence_mbar_init();
   }
-
-  // ---- phase A1: coalesced copy of the chunk's 64 k rows and 64 q rows to shared memory. A row of any
-  // 2-byte alignment is fetched as the 16 or 17 aligned 16-byte pieces that overlap it (up to 14
-  // bytes before and after it come along, always from a 16-byte granule that the row itself
-  // occupies, hence from mapped memory) and starts (address % 16) / 2 halfwords into its staged copy. ----
   constexpr int STG = 68;  // staged row pitch in 32-bit words = 17 x 16 bytes
-  static_assert(128 * STG * 4 <= sizeof(PrepSmem::L), "row staging must fit into the L buffers");
-  uint32_t* stg = reinterpret_cast<uint32_t*>(sh.L);
-  for (int r = warp; r < 128; r += 4) {
+  const act_t* kbase = static_cast<const act_t*>(p.k) + pos.tok0 * p.k_tok_stride + h * D;
+  const act_t* qbase = static_cast<const act_t*>(p.q) + pos.tok0 * p.q_tok_stride + h * D;
+
+  // ---- stage the chunk's 64 k rows and 64 q rows. A row of any 2-byte alignment is fetched as the 16 or
+  // 17 aligned 16-byte pieces that overlap it (up to 14 bytes before and after it come along, always
+  // from a 16-byte granule that the row itself occupies, hence from mapped memory) and starts
+  // (address % 16) / 2 halfwords into its staged copy. ----
+  for (int r = warp; r < 128; r += PREP_THREADS / 32) {
     const int c = r & 63;
     if (c >= pos.n || lane >= 17) continue;
-    const act_t* base = static_cast<const act_t*>(r >= 64 ? p.q : p.k);
-    const act_t* row = base + (pos.tok0 + c) * (r >= 64 ? p.q_tok_stride : p.k_tok_stride) + h * D;
+    const act_t* row = r >= 64 ? qbase + c * p.q_tok_stride : kbase + c * p.k_tok_stride;
     const char* src = reinterpret_cast<const char*>(reinterpret_cast<uintptr_t>(row) & ~uintptr_t(15));
     // an aligned row ends with its 16th piece: the 17th would lie wholly outside it (and, for the
     // buffer's last row, outside the allocation)
     if (lane == 16 && src == reinterpret_cast<const char*>(row)) continue;
-    // asynchronous 16-byte copies: all rows of the warp are in flight together
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(stg + r * STG) + lane * 16),
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(sh.stg + r * STG) + lane * 16),
                  "l"(src + lane * 16)
                  : "memory");
   }
   asm volatile("cp.async.wait_all;" ::: "memory");
   __syncthreads();
-  // ---- phase A2: one thread per row: L2 norm, tf32 rounding, operand images ----
+
+  // ---- L2 norms: two threads per row (adjacent lanes), 32 words each ----
   {
-    const int c = tid & 63;
-    const bool is_q = tid >= 64;
+    const int r = tid >> 1, half = tid & 1, c = r & 63;
+    const bool is_q = r >= 64, live = c < pos.n;
+    float ss = 0.f;
+    if (live && p.normalize_qk) {
+      const act_t* row = is_q ? qbase + c * p.q_tok_stride : kbase + c * p.k_tok_stride;
+      const int sh_half = static_cast<int>((reinterpret_cast<uintptr_t>(row) & 15) >> 1);
+      const uint32_t* srow = sh.stg + r * STG + (sh_half >> 1) + 32 * half;
+      const bool odd = sh_half & 1;
+      // rows 8 apart and the two halves of a row start on the same bank: rotate the word order per lane
+      const int rot = half | ((lane >> 4) << 1);
+#pragma unroll 8
+      for (int i0 = 0; i0 < 32; ++i0) {
+        const int i = (i0 + rot) & 31;
+        const uint32_t w = odd ? __funnelshift_r(srow[i], srow[i + 1], 16) : srow[i];
+        const act_t* e = reinterpret_cast<const act_t*>(&w);
+        const float x0 = to_f32(e[0]), x1 = to_f32(e[1]);
+        ss = fmaf(x0, x0, fmaf(x1, x1, ss));
+      }
+    }
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);   // outside every branch: all lanes take part
+    float rn = 0.f;
+    if (live) rn = (is_q ? p.scale : 1.0f) * (p.normalize_qk ? rsqrtf(ss + 1e-6f) : 1.0f);
+    if (half == 0) sh.rnorm[r] = rn;
+  }
+  __syncthreads();
+
+  // ---- operand images: thread = (token c, quarter of the features) for the k row AND the q row ----
+  unsigned char* ws = static_cast<unsigned char*>(p.workspace);
+  {
+    const int c = tid & 63, qq = tid >> 6;
+    const bool live = c < pos.n;
+    const float rnk = sh.rnorm[c], rnq = sh.rnorm[64 + c];
+    const int shk = static_cast<int>((reinterpret_cast<uintptr_t>(kbase + c * p.k_tok_stride) & 15) >> 1);
+    const int shq = static_cast<int>((reinterpret_cast<uintptr_t>(qbase + c * p.q_tok_stride) & 15) >> 1);
+    const uint32_t* __restrict__ krow = sh.stg + c * STG + (shk >> 1);
+    const uint32_t* __restrict__ qrow = sh.stg + (64 + c) * STG + (shq >> 1);
+    const bool oddk = shk & 1, oddq = shq & 1;
     // restrict: the staged rows (read), the operand image and the workspace (written) never overlap;
     // without it every load waits for the previous store
     float4* __restrict__ kq4 = reinterpret_cast<float4*>(sh.kq);
-    float* __restrict__ knt_g =
-        reinterpret_cast<float*>(static_cast<unsigned char*>(p.workspace) + ws_hblob(gc, h, p.H) + KQ_BYTES);
-    if (c < pos.n) {
-      const act_t* base = static_cast<const act_t*>(is_q ? p.q : p.k);
-      const act_t* row = base + (pos.tok0 + c) * (is_q ? p.q_tok_stride : p.k_tok_stride) + h * D;
-      const int sh_half = static_cast<int>((reinterpret_cast<uintptr_t>(row) & 15) >> 1);   // 0..7
-      const uint32_t* __restrict__ srow = stg + tid * STG + (sh_half >> 1);
-      const bool odd = sh_half & 1;
-      // element pair (2i, 2i+1) of the row as one 32-bit word
-      auto pair_at = [&](int i) -> uint32_t {
-        return odd ? __funnelshift_r(srow[i], srow[i + 1], 16) : srow[i];
-      };
-      float r = is_q ? p.scale : 1.0f;
-      if (p.normalize_qk) {
-        float ss = 0.f;
-#pragma unroll 8
-        for (int i = 0; i < D / 2; ++i) {
-          const uint32_t w = pair_at(i);
-          const act_t* e = reinterpret_cast<const act_t*>(&w);
-          const float x0 = to_f32(e[0]), x1 = to_f32(e[1]);
-          ss = fmaf(x0, x0, fmaf(x1, x1, ss));
-        }
-        r *= rsqrtf(ss + 1e-6f);
-      }
+    float* __restrict__ knt_g = reinterpret_cast<float*>(ws + ws_hblob(gc, h, p.H) + KQ_BYTES);
 #pragma unroll 4
-      for (int kc = 0; kc < D / 4; ++kc) {
-        const uint32_t w0 = pair_at(2 * kc), w1 = pair_at(2 * kc + 1);
-        const act_t* e0 = reinterpret_cast<const act_t*>(&w0);
-        const act_t* e1 = reinterpret_cast<const act_t*>(&w1);
-        const float4 x = make_float4(tc05::to_tf32(to_f32(e0[0]) * r), tc05::to_tf32(to_f32(e0[1]) * r),
-                                     tc05::to_tf32(to_f32(e1[0]) * r), tc05::to_tf32(to_f32(e1[1]) * r));
-        kq4[kc * 128 + tid] = x;
-        if (!is_q) {
-          // transposed image (rows = feature, K = token) straight to the workspace
-          float* __restrict__ dst = knt_g + (c >> 2) * (D * 4) + (kc * 4) * 4 + (c & 3);
-          dst[0] = x.x;
-          dst[4] = x.y;
-          dst[8] = x.z;
-          dst[12] = x.w;
-        }
+    for (int kc = qq * 8; kc < qq * 8 + 8; ++kc) {
+      float4 xk = make_float4(0.f, 0.f, 0.f, 0.f), xq = xk;
+      if (live) {
+        const uint32_t k0 = oddk ? __funnelshift_r(krow[2 * kc], krow[2 * kc + 1], 16) : krow[2 * kc];
+        const uint32_t k1 = oddk ? __funnelshift_r(krow[2 * kc + 1], krow[2 * kc + 2], 16) : krow[2 * kc + 1];
+        const uint32_t q0 = oddq ? __funnelshift_r(qrow[2 * kc], qrow[2 * kc + 1], 16) : qrow[2 * kc];
+        const uint32_t q1 = oddq ? __funnelshift_r(qrow[2 * kc + 1], qrow[2 * kc + 2], 16) : qrow[2 * kc + 1];
+        const act_t* a0 = reinterpret_cast<const act_t*>(&k0);
+        const act_t* a1 = reinterpret_cast<const act_t*>(&k1);
+        const act_t* b0 = reinterpret_cast<const act_t*>(&q0);
+        const act_t* b1 = reinterpret_cast<const act_t*>(&q1);
+        xk = make_float4(tc05::to_tf32(to_f32(a0[0]) * rnk), tc05::to_tf32(to_f32(a0[1]) * rnk),
+                         tc05::to_tf32(to_f32(a1[0]) * rnk), tc05::to_tf32(to_f32(a1[1]) * rnk));
+        xq = make_float4(tc05::to_tf32(to_f32(b0[0]) * rnq), tc05::to_tf32(to_f32(b0[1]) * rnq),
+                         tc05::to_tf32(to_f32(b1[0]) * rnq), tc05::to_tf32(to_f32(b1[1]) * rnq));
       }
-    } else {
-      for (int i = 0; i < D / 4; ++i) kq4[i * 128 + tid] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (!is_q)
-        for (int kk = 0; kk < D; ++kk) knt_g[(c >> 2) * (D * 4) + kk * 4 + (c & 3)] = 0.f;
+      kq4[kc * 128 + c] = xk;
+      kq4[kc * 128 + 64 + c] = xq;
+      // transposed image (rows = feature, K = token) straight to the workspace
+      float* __restrict__ dst = knt_g + (c >> 2) * (D * 4) + (kc * 4) * 4 + (c & 3);
+      dst[0] = xk.x;
+      dst[4] = xk.y;
+      dst[8] = xk.z;
+      dst[12] = xk.w;
     }
   }
-  __syncthreads();  // staging (aliased with L) fully consumed
-  fence_async_smem();   // the images are read by the tensor core and by bulk stores (async proxy)
+  fence_async_smem();   // the images are read by the tensor core and by a bulk store (async proxy)
   tc05::fence_before_sync();
   __syncthreads();
   tc05::fence_after_sync();
   const uint32_t tbase = sh.tmem_base;
 
-  // ---- phase B: one MMA chain  D0[128 x 64] = [Kn; Qn] (128 x 128) * Kn^T ----
+  // ---- one MMA chain  D0[128 x 64] = [Kn; Qn] (128 x 128) * Kn^T; the finished image goes to the
+  // workspace with one bulk store meanwhile ----
   if (tid == 0) {
     const uint64_t a_desc = tc05::smem_desc(sh.kq, 128 * 16, 128);
     constexpr uint32_t idesc = tc05::idesc_tf32(128, 64);
@@ -261,39 +266,19 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
       tc05::mma_tf32_ss(tbase, d, d, idesc, j > 0);  // B = the first 64 rows of the same image
     }
     tc05::mma_commit(&sh.bar);
-  }
-  {
-    const bool ok = mbar_wait(&sh.bar, 0, 1u << 20);
-    if (__syncthreads_or(!ok)) {
-      if (tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_WAIT_TIMEOUT);
-      __syncthreads();
-      if (warp == 0) tc05::tmem_dealloc(tbase, 64);
-      return;
-    }
-  }
-  tc05::fence_after_sync();
-
-  // this thread's row of D0: row i = tid % 64 of Kn Kn^T (tid < 64) or of Qn Kn^T (tid >= 64)
-  float d0[C];
-  {
-    float t0[32], t1[32];
-    tc05::tmem_ld32(tc05::taddr(tbase, warp * 32, 0), t0);
-    tc05::tmem_ld32(tc05::taddr(tbase, warp * 32, 32), t1);
-    tc05::wait_ld();
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      d0[j] = t0[j];
-      d0[32 + j] = t1[j];
-    }
+    bulk_store(ws + ws_hblob(gc, h, p.H), sh.kq, KQ_BYTES);
+    bulk_commit();
   }
 
-  unsigned char* ws = static_cast<unsigned char*>(p.workspace);
-  const int i_row = tid & 63;
-  const bool p_row = tid >= 64;
-
-  for (int r0 = 0; r0 < R; r0 += 2) {
-    const int heads_now = min(2, R - r0);
-    // ---- gates of up to two value heads: warp s computes head s ----
+  const int quad = warp & 3, ch = warp >> 2;   // TMEM lane quadrant, column half
+  const int i_row = (quad * 32 + lane) & 63;
+  const bool p_row = quad >= 2;
+  float d0[32];
+  bool have_d0 = false;
+  for (int r0 = 0; r0 < R; r0 += PREP_HEADS) {
+    const int heads_now = min(PREP_HEADS, R - r0);
+    if (r0 > 0) __syncthreads();  // G / beta of the previous pass fully consumed
+    // ---- gates of up to eight value heads: warp s computes head s (while the tensor core works) ----
     if (warp < heads_now) {
       const int hv = h * R + r0 + warp;
       float g2[2], b2[2];
@@ -335,71 +320,104 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
         if (lane < pos.n) p.g_cum[(pos.tok0 + lane) * p.HV + hv] = s0;
         if (lane + 32 < pos.n) p.g_cum[(pos.tok0 + lane + 32) * p.HV + hv] = s1;
       }
+      // vectors for the chain
+      float* vec = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv) + TM_BYTES + PM_BYTES);
+      const float g_last = __shfl_sync(0xffffffffu, s1, 31);
+      vec[lane] = s0;
+      vec[lane + 32] = s1;
+      vec[C + lane] = b2[0];
+      vec[C + lane + 32] = b2[1];
+      vec[2 * C + lane] = __expf(s0);
+      vec[2 * C + lane + 32] = __expf(s1);
+      vec[3 * C + lane] = __expf(g_last - s0);
+      vec[3 * C + lane + 32] = __expf(g_last - s1);
     }
-    __syncthreads();
+    if (!have_d0) {
+      const bool ok = mbar_wait(&sh.bar, 0, 1u << 20);
+      if (__syncthreads_or(!ok)) {
+        if (tid == 0) {
+          if (p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_WAIT_TIMEOUT);
+          bulk_wait_read<0>();
+        }
+        __syncthreads();
+        if (warp == 0) tc05::tmem_dealloc(tbase, 64);
+        return;
+      }
+      tc05::fence_after_sync();
+      // this thread's half row of D0: row i of Kn Kn^T (lane quadrants 0, 1) or of Qn Kn^T (2, 3)
+      tc05::tmem_ld32(tc05::taddr(tbase, quad * 32, 32 * ch), d0);
+      tc05::wait_ld();
+      have_d0 = true;
+    } else {
+      __syncthreads();
+    }
 
-    // ---- L (strictly lower, fp32, shared) and P (lower incl. diagonal, tf32 image, global) ----
+    // ---- L (strictly lower, fp32) and P (lower incl. diagonal, tf32 image), both to the workspace ----
     for (int s = 0; s < heads_now; ++s) {
       const int hv = h * R + r0 + s;
       const float gi = sh.G[s][i_row];
-      const float* __restrict__ Gs = sh.G[s];
+      const float* __restrict__ Gs = sh.G[s] + 32 * ch;
       if (!p_row) {
         const float bi = sh.beta[s][i_row];
-        float* __restrict__ Lrow = sh.L[s] + i_row * L_STRIDE;
+        float4* __restrict__ Lg =
+            reinterpret_cast<float4*>(ws + ws_lmat(p.max_chunks, p.H, p.HV, gc, hv)) + i_row * (C / 4) + ch * 8;
 #pragma unroll
-        for (int j = 0; j < C; ++j)
-          Lrow[j] = (j < i_row) ? bi * d0[j] * __expf(gi - Gs[j]) : 0.0f;
-      } else {
-        float4* __restrict__ Pimg = reinterpret_cast<float4*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv) + TM_BYTES);
-#pragma unroll
-        for (int jc = 0; jc < C / 4; ++jc) {
+        for (int jc = 0; jc < 8; ++jc) {
           float x[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int j = jc * 4 + u;
-            x[u] = (j <= i_row && i_row < pos.n) ? tc05::to_tf32(d0[j] * __expf(gi - Gs[j])) : 0.0f;
+            x[u] = (32 * ch + j < i_row) ? bi * d0[j] * __expf(gi - Gs[j]) : 0.0f;
           }
-          Pimg[jc * C + i_row] = make_float4(x[0], x[1], x[2], x[3]);
+          Lg[jc] = make_float4(x[0], x[1], x[2], x[3]);
+        }
+      } else {
+        float4* __restrict__ Pimg = reinterpret_cast<float4*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv) + TM_BYTES);
+#pragma unroll
+        for (int jc = 0; jc < 8; ++jc) {
+          float x[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int j = jc * 4 + u;
+            x[u] = (32 * ch + j <= i_row && i_row < pos.n) ? tc05::to_tf32(d0[j] * __expf(gi - Gs[j])) : 0.0f;
+          }
+          Pimg[(ch * 8 + jc) * C + i_row] = make_float4(x[0], x[1], x[2], x[3]);
         }
       }
     }
-    __syncthreads();
-
-    // ---- T = (I + L)^-1: thread = one column, rows by forward substitution, all in registers ----
-    {
-      // Columns are dealt to threads in 16-wide blocks; a column of block cb is zero above row
-      // 16*cb and only needs rows/terms from its own block on. Blocks {0,3} share one warp and
-      // {1,2} the other, which evens out the two warps' work.
-      const int s = tid >> 6, t6 = tid & 63;
-      const int cb = inverse_column_block(t6);
-      const int col = cb * 16 + (t6 & 15);
-      if (s < heads_now) {
-        const int hv = h * R + r0 + s;
-        float Tcol[C];
-        invert_column(sh.L[s], cb, col, Tcol);
-        float* Timg = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv));
-#pragma unroll
-        for (int i = 0; i < C; ++i) Timg[(col >> 2) * (C * 4) + i * 4 + (col & 3)] = tc05::to_tf32(Tcol[i]);
-        float* vec = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv) + TM_BYTES + PM_BYTES);
-        vec[col] = sh.G[s][col];
-        vec[C + col] = sh.beta[s][col];
-        vec[2 * C + col] = __expf(sh.G[s][col]);
-        vec[3 * C + col] = __expf(sh.G[s][C - 1] - sh.G[s][col]);
-      }
-    }
-    __syncthreads();  // L / G / beta are rewritten by the next pair of heads
   }
 
-  // ---- Kn|Qn image -> workspace (bulk store straight from shared memory) ----
-  if (tid == 0) {
-    unsigned char* dst = ws + ws_hblob(gc, h, p.H);
-    bulk_store(dst, sh.kq, KQ_BYTES);
-    bulk_commit();
-    bulk_wait_read<0>();
-  }
+  if (tid == 0) bulk_wait_read<0>();   // the image store must have read shared memory before the CTA leaves
   tc05::fence_before_sync();
   __syncthreads();
   if (warp == 0) tc05::tmem_dealloc(tbase, 64);
+}
+
+// L (fp32, strictly lower) -> T = (I + L)^-1 as a tf32 operand image. Two (chunk, value head) items per CTA.
+__global__ void __launch_bounds__(128) chunk_inverse_kernel(const pla_b200_gdn_chunk_args p, int items) {
+  __shared__ __align__(16) float Ls[2][C * L_STRIDE];
+  const int tid = threadIdx.x, s = tid >> 6, t6 = tid & 63;
+  const int item = blockIdx.x * 2 + s;
+  const bool live = item < items;
+  unsigned char* ws = static_cast<unsigned char*>(p.workspace);
+  const int hv = live ? item % p.HV : 0;
+  const int gc = live ? item / p.HV : 0;
+  ChunkPos pos;
+  const bool found = live && locate_chunk(p.cu_seqlens, p.N, gc, pos);
+  if (found) {
+    const float4* Lg = reinterpret_cast<const float4*>(ws + ws_lmat(p.max_chunks, p.H, p.HV, gc, hv));
+    for (int i = t6; i < C * C / 4; i += 64)
+      *reinterpret_cast<float4*>(&Ls[s][(i >> 4) * L_STRIDE + (i & 15) * 4]) = Lg[i];
+  }
+  __syncthreads();
+  if (!found) return;
+  const int cb = inverse_column_block(t6);
+  const int col = cb * 16 + (t6 & 15);
+  float Tcol[C];
+  invert_column(Ls[s], cb, col, Tcol);
+  float* Timg = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv));
+#pragma unroll
+  for (int i = 0; i < C; ++i) Timg[(col >> 2) * (C * 4) + i * 4 + (col & 3)] = tc05::to_tf32(Tcol[i]);
 }
 
 // ================================================================================================
@@ -417,15 +435,11 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const pla_b200_g
 // The chain kernel gets  [K e^{G}; Q e^{G}]  (decay from the chunk start folded in),
 // (K e^{G_C - G})^T  for the state update, beta and e^{G_C} per channel.
 // Launch 1 (`kda_chunk_prepare_kernel`, 512 threads, one CTA per SM) builds everything except T and
-// leaves L (fp32) in the workspace; launch 2 (`kda_chunk_inverse_kernel`, light, many CTAs per SM)
+// leaves L (fp32) in the workspace; launch 2 (`chunk_inverse_kernel`, light, many CTAs per SM)
 // turns L into the T image.
 constexpr int DM_PITCH = 132;  // floats per row of the decay-factor matrix: float4 rows, conflict-free per quarter warp
 constexpr int KM_BYTES = 81920;  // four B images of 16, 32, 48, 64 rows x 512 bytes, back to back
-constexpr int L_BYTES = C * C * 4;
 __host__ __device__ constexpr int km_offset(int a) { return a * (a + 1) / 2 * 8192; }
-__host__ __device__ inline int64_t ws_lmat(int64_t max_chunks, int H, int64_t gc, int h) {
-  return max_chunks * H * static_cast<int64_t>(HBLOB + VBLOB) + (gc * H + h) * static_cast<int64_t>(L_BYTES);
-}
 
 constexpr int KDA_PREP_THREADS = 512;
 constexpr int SB = 16;  // tokens per sub-block (decay reference points)
@@ -686,7 +700,7 @@ __global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(
     // columns at or beyond 16 (a + 1) of chain a hold other chains' data: never selected below (j <= i_row)
     if (!p_row) {
       const float bi = sh.beta[i_row];
-      float4* __restrict__ Lg = reinterpret_cast<float4*>(ws + ws_lmat(p.max_chunks, p.H, gc, h)) + i_row * (C / 4) + cs * 4;
+      float4* __restrict__ Lg = reinterpret_cast<float4*>(ws + ws_lmat(p.max_chunks, p.H, p.HV, gc, h)) + i_row * (C / 4) + cs * 4;
 #pragma unroll
       for (int jc = 0; jc < 4; ++jc) {
         float x[4];
@@ -711,33 +725,6 @@ __global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(
   tc05::fence_before_sync();
   __syncthreads();
   if (warp == 0) tc05::tmem_dealloc(tbase, 256);
-}
-
-// L (fp32, strictly lower) -> T = (I + L)^-1 as a tf32 operand image. Two (chunk, head) items per CTA.
-__global__ void __launch_bounds__(128) kda_chunk_inverse_kernel(const pla_b200_gdn_chunk_args p, int items) {
-  __shared__ __align__(16) float Ls[2][C * L_STRIDE];
-  const int tid = threadIdx.x, s = tid >> 6, t6 = tid & 63;
-  const int item = blockIdx.x * 2 + s;
-  const bool live = item < items;
-  unsigned char* ws = static_cast<unsigned char*>(p.workspace);
-  const int h = live ? item % p.H : 0;
-  const int gc = live ? item / p.H : 0;
-  ChunkPos pos;
-  const bool found = live && locate_chunk(p.cu_seqlens, p.N, gc, pos);
-  if (found) {
-    const float4* Lg = reinterpret_cast<const float4*>(ws + ws_lmat(p.max_chunks, p.H, gc, h));
-    for (int i = t6; i < C * C / 4; i += 64)
-      *reinterpret_cast<float4*>(&Ls[s][(i >> 4) * L_STRIDE + (i & 15) * 4]) = Lg[i];
-  }
-  __syncthreads();
-  if (!found) return;
-  const int cb = inverse_column_block(t6);
-  const int col = cb * 16 + (t6 & 15);
-  float Tcol[C];
-  invert_column(Ls[s], cb, col, Tcol);
-  float* Timg = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, h));
-#pragma unroll
-  for (int i = 0; i < C; ++i) Timg[(col >> 2) * (C * 4) + i * 4 + (col & 3)] = tc05::to_tf32(Tcol[i]);
 }
 
 // ================================================================================================
@@ -826,7 +813,25 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
   }
   const int kind = prescan ? static_cast<int>(blockIdx.x & 1u) : 0;
   const unsigned chain = prescan ? blockIdx.x >> 1 : blockIdx.x;
-  const int seq = chain / p.HV, hv = chain % p.HV;
+  int seq = chain / p.HV;
+  const int hv = chain % p.HV;
+  // Longest sequences first: CTAs start roughly in block order and a chain's run time is its chunk
+  // count, so the block index is mapped through the sequences sorted by descending length (for
+  // batches small enough to rank in place).
+  if (p.N > 1 && p.N <= CHAIN_THREADS) {
+    __shared__ int picked;
+    if (tid < p.N) {
+      const int mine = max(p.cu_seqlens[tid + 1] - p.cu_seqlens[tid], 0);
+      int rank = 0;
+      for (int s = 0; s < p.N; ++s) {
+        const int other = max(p.cu_seqlens[s + 1] - p.cu_seqlens[s], 0);
+        rank += (other > mine) || (other == mine && s < tid);
+      }
+      if (rank == seq) picked = tid;
+    }
+    __syncthreads();
+    seq = picked;
+  }
   const int h = hv / (p.HV / p.H);
   const int64_t bos = p.cu_seqlens[seq];
   const int len = p.cu_seqlens[seq + 1] - static_cast<int>(bos);
@@ -1145,7 +1150,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
     // ---- final state ----
     if (ok && prescan) {
       // [sequence][value head][offset, transition][v][k] fp32
-      float* dst = static_cast<float*>(p.state_out) + (static_cast<int64_t>(chain) * 2 + kind) * TILE +
+      float* dst = static_cast<float*>(p.state_out) + ((static_cast<int64_t>(seq) * p.HV + hv) * 2 + kind) * TILE +
                    static_cast<int64_t>(m) * D;
 #pragma unroll 1
       for (int q4 = 2 * wg; q4 < 2 * wg + 2; ++q4) {
@@ -1192,7 +1197,8 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
 
 extern "C" int64_t pla_b200_gdn_chunk_workspace_bytes(int32_t max_chunks, int32_t H, int32_t HV) {
   if (max_chunks < 0 || H <= 0 || HV <= 0) return 0;
-  return static_cast<int64_t>(max_chunks) * (static_cast<int64_t>(H) * pla::HBLOB + static_cast<int64_t>(HV) * pla::VBLOB);
+  return static_cast<int64_t>(max_chunks) *
+         (static_cast<int64_t>(H) * pla::HBLOB + static_cast<int64_t>(HV) * (pla::VBLOB + pla::L_BYTES));
 }
 
 namespace pla {
@@ -1268,7 +1274,11 @@ extern "C" int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args,
                                        static_cast<int>(sizeof(PrepSmem) + 1024)));
       configured[dev] = true;
     }
-    kern<<<static_cast<unsigned>(items), 128, sizeof(PrepSmem) + 1024, s>>>(a);
+    kern<<<static_cast<unsigned>(items), PREP_THREADS, sizeof(PrepSmem) + 1024, s>>>(a);
+    PLA_CUDA_OK(cudaGetLastError());
+    const int64_t inv_items = static_cast<int64_t>(a.max_chunks) * a.HV;
+    PLA_REQUIRE(inv_items < (1ll << 31), PLA_B200_E_TOO_LARGE, "too many chunks");
+    chunk_inverse_kernel<<<static_cast<unsigned>((inv_items + 1) / 2), 128, 0, s>>>(a, static_cast<int>(inv_items));
     PLA_CUDA_OK(cudaGetLastError());
     return PLA_B200_OK;
   };
@@ -1311,7 +1321,7 @@ extern "C" int pla_b200_kda_prefill_chunked(const pla_b200_gdn_chunk_args* args,
     }
     kern<<<static_cast<unsigned>(items), KDA_PREP_THREADS, sizeof(KdaPrepSmem) + 1024, s>>>(a);
     PLA_CUDA_OK(cudaGetLastError());
-    kda_chunk_inverse_kernel<<<static_cast<unsigned>((items + 1) / 2), 128, 0, s>>>(a, static_cast<int>(items));
+    chunk_inverse_kernel<<<static_cast<unsigned>((items + 1) / 2), 128, 0, s>>>(a, static_cast<int>(items));
     PLA_CUDA_OK(cudaGetLastError());
     return PLA_B200_OK;
   };
