@@ -247,6 +247,22 @@ int64_t pla_b200_kda_chunk_workspace_bytes(int32_t max_chunks, int32_t H);
 int pla_b200_kda_prefill_chunked(const pla_b200_gdn_chunk_args* args, void* stream);
 
 /* ======================================================================== *
+ * Context parallelism for one long sequence cut into token ranges (one per GPU). The prescan is the
+ * `prescan` mode of the three prefill entries above; the fold below turns the gathered pairs into the state
+ * entering a rank's range (the composition the reference applies to its intra-card segments,
+ * src/prefill/flashqla/kernels/prepare_h_cute.cu:59-67, docs/prefill_flashkdapro_cp_design.md:22-46).
+ * ======================================================================== */
+typedef struct pla_b200_cp_fold_args {
+  const float* pairs;          /* [world, HV, 2, 128, 128]: offset B, then transition M, per rank and head */
+  const float* initial_state;  /* [HV, 128(V), 128(K)] state entering rank 0's range; NULL = zero */
+  float* state_out;            /* [HV, 128, 128]: fold over ranks 0 .. rank-1 of S <- S M_j + B_j */
+  int32_t HV, rank, world;
+  int32_t* status;
+} pla_b200_cp_fold_args;
+
+int pla_b200_cp_fold_prefix(const pla_b200_cp_fold_args* args, void* stream);
+
+/* ======================================================================== *
  * KDA ReplaySSM: verify (read-only checkpoint, replay records out) and commit
  * (integer plan, exact fold of the accepted prefix, conv-window scatter).
  * Replaces launch_verify_native / launch_commit_plan / launch_fold_native /

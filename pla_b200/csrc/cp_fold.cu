@@ -1,0 +1,95 @@
+// Context parallelism, fold step: the state entering a rank's token range from the (offset, transition)
+// pairs of the ranks before it,  S <- S M_j + B_j  for j = 0 .. rank-1, row by row of the k-last state
+// S[v, k] (the composition the reference applies to its intra-card segments,
+// src/prefill/flashqla/kernels/prepare_h_cute.cu:59-67). Exact fp32 FMAs: the products are tiny
+// (rank-1 steps of 128^3 per head) and the result seeds a whole token range.
+#include "common.cuh"
+
+namespace pla {
+namespace {
+
+constexpr int D = 128;
+constexpr int TILE = D * D;
+constexpr int ROWS = 16;                   // state rows per CTA
+constexpr int FOLD_THREADS = 256;
+constexpr uint32_t kTileBytes = TILE * 4;
+
+struct FoldSmem {
+  alignas(128) float m[TILE];              // transition of the current step, [k][k']
+  alignas(16) float s[ROWS * D];           // this CTA's rows of the state
+  alignas(8) uint64_t bar;
+};
+
+__global__ void __launch_bounds__(FOLD_THREADS) cp_fold_kernel(const pla_b200_cp_fold_args p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  FoldSmem& sh = *reinterpret_cast<FoldSmem*>(smem_raw);
+  const int tid = threadIdx.x;
+  const int rs = blockIdx.x % (D / ROWS), hv = blockIdx.x / (D / ROWS);
+  const int row0 = rs * ROWS;
+  const int col = tid & 127, rg = tid >> 7;   // this thread: column `col` of rows rg*8 .. rg*8+7
+
+  for (int i = tid; i < ROWS * D; i += FOLD_THREADS)
+    sh.s[i] = p.initial_state != nullptr ? p.initial_state[static_cast<int64_t>(hv) * TILE + row0 * D + i] : 0.0f;
+  if (tid == 0) {
+    mbar_init(&sh.bar, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  for (int j = 0; j < p.rank; ++j) {
+    const float* pair = p.pairs + (static_cast<int64_t>(j) * p.HV + hv) * 2 * TILE;   // [offset B | transition M]
+    if (tid == 0) {
+      mbar_expect_tx(&sh.bar, kTileBytes);
+      bulk_load(sh.m, pair + TILE, kTileBytes, &sh.bar);
+    }
+    float acc[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) acc[r] = pair[(row0 + rg * 8 + r) * D + col];   // B rows
+    const bool ok = mbar_wait(&sh.bar, j & 1);
+    if (__syncthreads_or(!ok)) {
+      if (tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_WAIT_TIMEOUT);
+      (void)mbar_wait(&sh.bar, j & 1);
+      return;
+    }
+#pragma unroll 4
+    for (int k4 = 0; k4 < D / 4; ++k4) {
+      const float m0 = sh.m[(4 * k4 + 0) * D + col], m1 = sh.m[(4 * k4 + 1) * D + col];
+      const float m2 = sh.m[(4 * k4 + 2) * D + col], m3 = sh.m[(4 * k4 + 3) * D + col];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float4 sv = *reinterpret_cast<const float4*>(&sh.s[(rg * 8 + r) * D + 4 * k4]);   // broadcast
+        acc[r] = fmaf(sv.x, m0, fmaf(sv.y, m1, fmaf(sv.z, m2, fmaf(sv.w, m3, acc[r]))));
+      }
+    }
+    __syncthreads();   // every thread has read the old rows and the transition
+#pragma unroll
+    for (int r = 0; r < 8; ++r) sh.s[(rg * 8 + r) * D + col] = acc[r];
+    __syncthreads();
+  }
+  for (int i = tid; i < ROWS * D; i += FOLD_THREADS) p.state_out[static_cast<int64_t>(hv) * TILE + row0 * D + i] = sh.s[i];
+}
+
+}  // namespace
+}  // namespace pla
+
+extern "C" int pla_b200_cp_fold_prefix(const pla_b200_cp_fold_args* args, void* stream) {
+  using namespace pla;
+  PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
+  const pla_b200_cp_fold_args& a = *args;
+  PLA_REQUIRE(a.HV > 0 && a.rank >= 0 && a.world > 0 && a.rank < a.world, PLA_B200_E_INVALID,
+              "fold needs HV > 0 and 0 <= rank < world");
+  PLA_REQUIRE(a.state_out != nullptr && (a.rank == 0 || a.pairs != nullptr), PLA_B200_E_INVALID,
+              "pairs and state_out are required");
+  PLA_REQUIRE(a.rank == 0 || aligned16(a.pairs), PLA_B200_E_ALIGN, "pairs must be 16-byte aligned");
+  static bool configured[64] = {};
+  int dev = 0;
+  PLA_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    PLA_CUDA_OK(cudaFuncSetAttribute(cp_fold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(FoldSmem)));
+    configured[dev] = true;
+  }
+  cp_fold_kernel<<<static_cast<unsigned>(a.HV) * (D / ROWS), FOLD_THREADS, sizeof(FoldSmem),
+                   static_cast<cudaStream_t>(stream)>>>(a);
+  PLA_CUDA_OK(cudaGetLastError());
+  return PLA_B200_OK;
+}

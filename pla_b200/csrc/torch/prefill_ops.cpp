@@ -361,6 +361,32 @@ at::Tensor gdn_prefill_chunked_stage(const at::Tensor& q, const at::Tensor& k, c
                      workspace, prescan);
 }
 
+// Fold of the gathered (offset, transition) pairs of the ranks before `rank` into the state entering its range.
+at::Tensor cp_fold_prefix(const at::Tensor& pairs, const Optional& initial_state, int64_t rank, const Optional& status) {
+  check_cuda(pairs, "pairs");
+  TORCH_CHECK(pairs.scalar_type() == at::kFloat && pairs.is_contiguous() && pairs.dim() == 5 && pairs.size(2) == 2 &&
+                  pairs.size(3) == 128 && pairs.size(4) == 128,
+              "pairs must be contiguous fp32 [world, H, 2, 128, 128]");
+  const int64_t world = pairs.size(0), H = pairs.size(1);
+  TORCH_CHECK(rank >= 0 && rank < world, "rank out of range");
+  if (initial_state.has_value())
+    TORCH_CHECK(initial_state->scalar_type() == at::kFloat && initial_state->is_contiguous() &&
+                    initial_state->numel() == H * 128 * 128 && initial_state->device() == pairs.device(),
+                "the initial state must be contiguous fp32 [H, 128, 128] on the pairs' device");
+  c10::cuda::CUDAGuard guard(pairs.device());
+  at::Tensor out = at::empty({H, 128, 128}, pairs.options());
+  pla_b200_cp_fold_args f{};
+  f.pairs = pairs.data_ptr<float>();
+  f.initial_state = initial_state.has_value() ? initial_state->data_ptr<float>() : nullptr;
+  f.state_out = out.data_ptr<float>();
+  f.HV = static_cast<int32_t>(H);
+  f.rank = static_cast<int32_t>(rank);
+  f.world = static_cast<int32_t>(world);
+  f.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
+  check_abi(pla_b200_cp_fold_prefix(&f, stream_of(pairs)), "cp fold");
+  return out;
+}
+
 // Chunked KDA prefill; all the modes of the GDN ops in one signature (stage 0 = both halves with a fresh
 // workspace; stage 1 / 2 and prescan for context parallelism).
 at::Tensor kda_prefill_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& gate,
@@ -379,6 +405,8 @@ at::Tensor kda_prefill_chunked(const at::Tensor& q, const at::Tensor& k, const a
 }  // namespace pla_ops
 
 TORCH_LIBRARY_FRAGMENT(pla_b200, m) {
+  m.def("cp_fold_prefix(Tensor pairs, Tensor? initial_state, int rank, Tensor(a!)? status) -> Tensor",
+        &pla_ops::cp_fold_prefix);
   m.def(
       "kda_prefill_chunked(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor A_log, Tensor dt_bias, "
       "Tensor(a!) out, Tensor cu_seqlens, Tensor(b!)? state_in, Tensor? in_indices, Tensor(c!)? state_out, "

@@ -180,7 +180,13 @@ def fold_transfers(initial_state: Optional[torch.Tensor], gathered: torch.Tensor
 
 def finish_segment(plan: SegmentPlan, initial_state: Optional[torch.Tensor], gathered: torch.Tensor):
     """Steps 4-5. Returns (o [tokens, H, 128], state leaving this rank's range [H, 128, 128])."""
-    state_in = fold_transfers(initial_state, gathered, plan.rank)
+    ops = getattr(plan.kernels, "_ops", None)
+    if ops is not None and gathered.is_cuda:
+        # the library's fold kernel (pla_b200_cp_fold_prefix); fold_transfers is the same algebra in torch
+        init = None if initial_state is None else initial_state.to(torch.float32).contiguous()
+        state_in = ops.cp_fold_prefix(gathered.contiguous(), init, plan.rank, plan.kernels.status)
+    else:
+        state_in = fold_transfers(initial_state, gathered, plan.rank)
     if plan.tokens == 0:
         return None, state_in
     return plan.kernels.segment(state_in)

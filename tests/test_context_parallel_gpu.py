@@ -132,3 +132,20 @@ def test_kda_emulated_ranks_match_oracle(native_built, lower_bound, chunked):
                                                is_kda=True, lower_bound=lower_bound)
     assert_out_close(torch.cat(outs), exp_out)
     assert_state_close(state.cpu(), exp_state[0])
+
+
+def test_fold_kernel_matches_torch_fold(native_built):
+    from pla_b200._ops import ops
+    from pla_b200.prefill import context_parallel as cp
+    g = torch.Generator().manual_seed(2)
+    W, H = 5, 3
+    pairs = torch.randn(W, H, 2, D, D, generator=g) * 0.09
+    S0 = torch.randn(H, D, D, generator=g)
+    dp, dS = pairs.cuda(), S0.cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for rank in range(W):
+        for init, dinit in ((S0, dS), (None, None)):
+            got = ops.cp_fold_prefix(dp, dinit, rank, status)
+            want = cp.fold_transfers(init, pairs, rank)
+            torch.testing.assert_close(got.cpu(), want, rtol=1e-4, atol=1e-5)
+    assert status.item() == 0
