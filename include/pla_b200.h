@@ -126,6 +126,8 @@ typedef struct pla_b200_klast_args {
   int32_t state_transposed;         /* slots hold [K,V] (V contiguous) instead of [V,K] */
   int32_t gate_activated;           /* a = fp32 log-decay, b = fp32 beta, both already activated */
   int64_t o_total_rows;             /* > 0: rows [cu_seqlens[B], o_total_rows) of o are set to zero */
+  float* o_f32;               /* single-token streaming decode only: when set, the unrounded fp32 outputs go
+                                 here ([tokens, HV, 128]) instead of o; padding rows still get zeros in o */
   int32_t prescan;            /* prefill only, context parallelism: run every (request, head) twice without
                                  output rows -- from a zero state (offset B) and from the identity with
                                  V = 0 (transition M) -- and store both to state_out
@@ -434,6 +436,46 @@ int pla_b200_kda_replay_commit(const pla_b200_kda_commit_args* args, void* strea
  *     stream capture starts;
  *   - it never calls cudaMalloc / cudaFree or any allocating routine. */
 int pla_b200_kda_replay_plan_static(const pla_b200_kda_commit_args* args, void* stream);
+
+/* ======================================================================== *
+ * Fused KDA decode step (Kimi K3): causal conv (width 4) + SiLU over the packed q|k|v projections with
+ * the 3-tap conv state shifted in place, L2 norms, per-channel gate, single-token recurrence on the fp32
+ * k-last state in place, optional gated output RMSNorm. Replaces the launchers behind
+ * fused_kda_decode_mega_forward (src/decode/k-last/fused_kda_decode_mega.cu; device contract
+ * src/decode/k-last/fused_kda_decode_mega_kernel.cuh:36-79). A slot < 0 is padding: zero output row,
+ * nothing else read or written; slot 0 is an ordinary slot.
+ * ======================================================================== */
+typedef struct pla_b200_kda_mega_args {
+  const void* x;               /* [B, 3*H*128] activation dtype, channels contiguous */
+  int64_t x_row_stride;
+  const float* weight;         /* [3, 4, H*128]: segment (q, k, v), tap (3 = current token), channel */
+  const float* bias;           /* [3*H*128] or NULL */
+  void* conv_state;            /* activation dtype, addressed [slot, channel, tap] with the strides below */
+  pla_b200_conv_strides conv_strides;
+  const void* raw_g;           /* [B, H*128] activation dtype, contiguous */
+  const void* raw_beta;        /* [B, H] activation dtype */
+  int64_t beta_row_stride;
+  const float* A_log;          /* [H] */
+  const float* dt_bias;        /* [H*128] */
+  const int32_t* state_indices; /* [B] */
+  float* state;                /* [slots, H, 128(V), 128(K)] fp32 */
+  int64_t state_slot_stride;
+  int32_t slots;
+  void* out;                   /* [B, H*128] activation dtype, contiguous */
+  const void* output_gate;     /* [B, H*128] activation dtype view or NULL (then no output norm) */
+  int64_t gate_row_stride;
+  const float* norm_weight;    /* [128], with output_gate */
+  float norm_eps;
+  void* mixed;                 /* scratch [B, 3*H*128] activation dtype, 16-byte aligned: conv outputs */
+  float* out_f32;              /* scratch [B, H*128] fp32, 16-byte aligned; required with output_gate */
+  int32_t B, H;
+  int32_t act_dtype;           /* pla_b200_dtype: BF16 or F16 */
+  int32_t gate;                /* pla_b200_gate */
+  float lower_bound, scale;
+  int32_t* status;
+} pla_b200_kda_mega_args;
+
+int pla_b200_kda_decode_mega(const pla_b200_kda_mega_args* args, void* stream);
 
 #ifdef __cplusplus
 }

@@ -129,3 +129,47 @@ def vlast_forward(*, q, k, v, a, b, A_log, dt_bias, state, slot_indices, scale: 
         keep = torch.as_tensor(slot_indices)[:B] < 0
         out[keep] = out_init[keep]
     return out, st.transpose(-1, -2).contiguous()
+
+
+def kda_mega_forward(*, x, weight, bias, conv_state, raw_g, raw_beta, A_log, dt_bias, state_indices, state,
+                     lower_bound: Optional[float], output_gate=None, norm_weight=None, norm_eps: float = 1e-5):
+    """Fused KDA decode step in fp32 (scripts/decode/kda_fusion/compare_kda_decode_fusion.py:252-308):
+    width-4 causal conv + SiLU over the packed q|k|v row with the 3-tap history shifted, L2 norms
+    (q scaled by 128^-0.5), per-channel decay (safe gate when ``lower_bound`` is given, softplus otherwise),
+    one delta-rule step per head on the k-last state, optional gated RMSNorm of the output.
+
+    x [B, 3*H*128]; weight [3, 4, H*128]; conv_state [slots, 3*H*128, 3]; raw_g [1, B, H, 128];
+    raw_beta [1, B, H]; state [slots, H, 128(V), 128(K)]; output_gate [B, H, 128].
+    Rows with a negative slot give zeros and change nothing.
+    Returns (out [B, H, 128] fp32, new_state, new_conv_state in conv_state's dtype)."""
+    B, dim3 = x.shape
+    dim = dim3 // 3
+    H = dim // 128
+    new_state = state.clone().float()
+    new_conv = conv_state.clone()
+    out = torch.zeros(B, H, 128)
+    w = weight.float()                                       # [3, 4, dim]
+    for b in range(B):
+        slot = int(state_indices[b])
+        if slot < 0:
+            continue
+        taps = new_conv[slot].float()                        # [3*dim, 3]
+        xn = x[b].float()
+        window = torch.cat([taps, xn[:, None]], dim=1)       # [3*dim, 4]
+        wflat = w.permute(0, 2, 1).reshape(3 * dim, 4)       # [3*dim, 4]
+        acc = (window * wflat).sum(-1)
+        if bias is not None:
+            acc = acc + bias.float()
+        mixed = acc * torch.sigmoid(acc)
+        new_conv[slot] = torch.cat([new_conv[slot][:, 1:], x[b][:, None].to(new_conv.dtype)], dim=1)
+        q, k, v = (mixed[i * dim:(i + 1) * dim].view(H, 128) for i in range(3))
+        q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * 128 ** -0.5
+        k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+        g = log_decay(raw_g[0, b].float() + dt_bias.float().view(H, 128), A_log.float().view(H, 1), lower_bound)
+        S, o = step(new_state[slot], q, k, v, g.exp(), torch.sigmoid(raw_beta[0, b].float()))
+        new_state[slot] = S
+        if output_gate is not None:
+            rstd = torch.rsqrt((o * o).mean(-1, keepdim=True) + norm_eps)
+            o = o * rstd * norm_weight.float()[None, :] * torch.sigmoid(output_gate.reshape(B, H, 128)[b].float())
+        out[b] = o
+    return out, new_state, new_conv

@@ -259,8 +259,13 @@ __global__ void __launch_bounds__(NWARP * 32, 1) klast_stream_kernel(const pla_b
           ov[pp] = group8_sum(oacc);
         }
         if (j == 0) {
-          act_t packed[2] = {from_f32<act_t>(ov[0]), from_f32<act_t>(ov[1])};
-          *reinterpret_cast<uint32_t*>(orow + sub * RU) = *reinterpret_cast<const uint32_t*>(packed);
+          if (p.o_f32 != nullptr) {
+            *reinterpret_cast<float2*>(p.o_f32 + (cur.tok * p.HV + cur.hv) * D + cur.row0 + r * 2 + sub * RU) =
+                make_float2(ov[0], ov[1]);
+          } else {
+            act_t packed[2] = {from_f32<act_t>(ov[0]), from_f32<act_t>(ov[1])};
+            *reinterpret_cast<uint32_t*>(orow + sub * RU) = *reinterpret_cast<const uint32_t*>(packed);
+          }
         }
         fence_async_smem();  // in-place updates -> visible to the bulk-copy engine
         __syncwarp();

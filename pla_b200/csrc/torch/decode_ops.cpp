@@ -369,10 +369,107 @@ void fused_recurrent_kda(const at::Tensor& q, const at::Tensor& k, const at::Ten
   if (!out.is_contiguous()) out.copy_(o);
 }
 
+// Fused KDA decode step; tensor contract of fused_kda_decode_mega_forward
+// (src/decode/k-last/fused_sigmoid_gating.cpp:136-144, docs/readme.md:232-267). Writes conv_state, state and
+// out in place. Scratch (conv outputs, fp32 outputs for the norm) comes from the caching allocator.
+void kda_decode_mega(const at::Tensor& x, const at::Tensor& weight, const std::optional<at::Tensor>& bias,
+                     at::Tensor conv_state, const at::Tensor& raw_g, const at::Tensor& raw_beta,
+                     const at::Tensor& a_log, const at::Tensor& dt_bias, const at::Tensor& state_indices,
+                     at::Tensor state, at::Tensor out, std::optional<double> lower_bound,
+                     const std::optional<at::Tensor>& output_gate, const std::optional<at::Tensor>& norm_weight,
+                     double norm_eps, const std::optional<at::Tensor>& status) {
+  check_cuda(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.size(1) % (3 * 128) == 0 && x.stride(1) == 1,
+              "x must be [B, 3*H*128] with contiguous channels");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf, "x must be fp16 or bf16");
+  const int64_t B = x.size(0), dim = x.size(1) / 3, H = dim / 128;
+  TORCH_CHECK(weight.scalar_type() == at::kFloat && weight.is_contiguous() && weight.dim() == 3 &&
+                  weight.size(0) == 3 && weight.size(1) == 4 && weight.size(2) == dim,
+              "weight must be contiguous fp32 [3, 4, H*128]");
+  if (bias.has_value())
+    TORCH_CHECK(bias->scalar_type() == at::kFloat && bias->is_contiguous() && bias->numel() == 3 * dim,
+                "bias must be contiguous fp32 [3*H*128]");
+  TORCH_CHECK(conv_state.scalar_type() == x.scalar_type() && conv_state.dim() == 3 && conv_state.size(1) == 3 * dim &&
+                  conv_state.size(2) == 3,
+              "conv_state must be [slots, 3*H*128, 3] in the activation dtype");
+  TORCH_CHECK(raw_g.scalar_type() == x.scalar_type() && raw_g.is_contiguous() && raw_g.numel() == B * dim,
+              "raw_g must be contiguous [1, B, H, 128] in the activation dtype");
+  TORCH_CHECK(raw_beta.scalar_type() == x.scalar_type() && raw_beta.numel() == B * H && raw_beta.dim() == 3 &&
+                  raw_beta.size(0) == 1 && raw_beta.stride(2) == 1,
+              "raw_beta must be [1, B, H] with contiguous heads in the activation dtype");
+  TORCH_CHECK(a_log.scalar_type() == at::kFloat && a_log.is_contiguous() && a_log.numel() == H,
+              "a_log must be contiguous fp32 [H]");
+  TORCH_CHECK(dt_bias.scalar_type() == at::kFloat && dt_bias.is_contiguous() && dt_bias.numel() == dim,
+              "dt_bias must be contiguous fp32 [H, 128]");
+  TORCH_CHECK(state_indices.scalar_type() == at::kInt && state_indices.is_contiguous() && state_indices.numel() == B,
+              "state_indices must be contiguous int32 [B]");
+  TORCH_CHECK(state.scalar_type() == at::kFloat && state.dim() == 4 && state.size(1) == H && state.size(2) == 128 &&
+                  state.size(3) == 128 && state.stride(3) == 1 && state.stride(2) == 128 && state.stride(1) == 16384,
+              "state must be fp32 [slots, H, 128, 128] with contiguous slot contents");
+  TORCH_CHECK(conv_state.size(0) == state.size(0), "conv_state and state must have the same slots");
+  TORCH_CHECK(out.scalar_type() == x.scalar_type() && out.is_contiguous() && out.numel() == B * dim,
+              "out must be contiguous [1, B, H, 128] in the activation dtype");
+  TORCH_CHECK(output_gate.has_value() == norm_weight.has_value(), "output_gate and norm_weight are supplied together");
+  for (const at::Tensor* t : std::initializer_list<const at::Tensor*>{&weight, &conv_state, &raw_g, &raw_beta, &a_log,
+                                                                     &dt_bias, &state_indices, &state, &out})
+    TORCH_CHECK(t->device() == x.device(), "all tensors must be on x's device");
+  c10::cuda::CUDAGuard guard(x.device());
+
+  pla_b200_kda_mega_args g{};
+  g.x = x.data_ptr();
+  g.x_row_stride = x.stride(0);
+  g.weight = weight.data_ptr<float>();
+  g.bias = bias.has_value() ? bias->data_ptr<float>() : nullptr;
+  g.conv_state = conv_state.data_ptr();
+  g.conv_strides = {conv_state.stride(0), conv_state.stride(1), conv_state.stride(2)};
+  g.raw_g = raw_g.data_ptr();
+  g.raw_beta = raw_beta.data_ptr();
+  g.beta_row_stride = raw_beta.stride(1);
+  g.A_log = a_log.data_ptr<float>();
+  g.dt_bias = dt_bias.data_ptr<float>();
+  g.state_indices = state_indices.data_ptr<int32_t>();
+  g.state = state.data_ptr<float>();
+  g.state_slot_stride = state.stride(0);
+  g.slots = static_cast<int32_t>(state.size(0));
+  g.out = out.data_ptr();
+  at::Tensor mixed = at::empty({B, 3 * dim}, x.options());
+  g.mixed = mixed.data_ptr();
+  at::Tensor staging;
+  if (output_gate.has_value()) {
+    const at::Tensor& gate = *output_gate;
+    TORCH_CHECK(gate.scalar_type() == x.scalar_type() && gate.numel() == B * dim && gate.stride(-1) == 1 &&
+                    gate.stride(-2) == 128 && gate.device() == x.device(),
+                "output_gate must be [B, H, 128] or [1, B, H, 128] in the activation dtype with contiguous heads");
+    TORCH_CHECK(norm_weight->scalar_type() == at::kFloat && norm_weight->is_contiguous() && norm_weight->numel() == 128 &&
+                    norm_weight->device() == x.device(),
+                "norm_weight must be contiguous fp32 [128]");
+    TORCH_CHECK(std::isfinite(norm_eps) && norm_eps >= 0.0, "norm_eps must be finite and non-negative");
+    staging = at::empty({B, dim}, x.options().dtype(at::kFloat));
+    g.output_gate = gate.data_ptr();
+    g.gate_row_stride = gate.stride(gate.dim() - 3);
+    g.norm_weight = norm_weight->data_ptr<float>();
+    g.norm_eps = static_cast<float>(norm_eps);
+    g.out_f32 = staging.data_ptr<float>();
+  }
+  g.B = static_cast<int32_t>(B);
+  g.H = static_cast<int32_t>(H);
+  g.act_dtype = dtype_tag(x, "x");
+  g.gate = lower_bound.has_value() ? PLA_B200_GATE_SAFE : PLA_B200_GATE_SOFTPLUS;
+  g.lower_bound = static_cast<float>(lower_bound.value_or(0.0));
+  g.scale = 1.0f / std::sqrt(128.0f);
+  g.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
+  check_abi(pla_b200_kda_decode_mega(&g, stream_of(x)), "fused_kda_decode_mega_forward");
+}
+
 }  // namespace
 }  // namespace pla_ops
 
 TORCH_LIBRARY_FRAGMENT(pla_b200, m) {
+  m.def(
+      "kda_decode_mega(Tensor x, Tensor weight, Tensor? bias, Tensor(a!) conv_state, Tensor raw_g, Tensor raw_beta, "
+      "Tensor a_log, Tensor dt_bias, Tensor state_indices, Tensor(b!) state, Tensor(c!) out, float? lower_bound, "
+      "Tensor? output_gate, Tensor? norm_weight, float norm_eps, Tensor(d!)? status) -> ()",
+      &pla_ops::kda_decode_mega);
   m.def(
       "fused_recurrent_kda(Tensor q, Tensor k, Tensor v, Tensor raw_g, Tensor raw_beta, Tensor A_log, Tensor dt_bias, "
       "float? lower_bound, Tensor(a!) initial_state, Tensor cu_seqlens, Tensor ssm_state_indices, "

@@ -12,7 +12,7 @@ import torch
 
 from ..._ops import ops
 
-__all__ = ["fused_recurrent_kda"]
+__all__ = ["fused_recurrent_kda", "fused_kda_decode_mega_forward"]
 
 
 def fused_recurrent_kda(
@@ -69,3 +69,36 @@ def fused_recurrent_kda(
                             None if lower_bound is None else float(lower_bound), initial_state, cu_seqlens,
                             ssm_state_indices, num_accepted_tokens, out, bool(is_sglang), status)
     return out, initial_state
+
+
+def fused_kda_decode_mega_forward(
+    x: torch.Tensor,                        # [B, 3*H*128] fp16/bf16, channel-contiguous packed q|k|v projections
+    weight: torch.Tensor,                   # fp32 [3, 4, H*128]: segment, tap (3 = current token), channel
+    bias: Optional[torch.Tensor] = None,    # fp32 [3*H*128]
+    conv_state: torch.Tensor = None,        # activation dtype [slots, 3*H*128, 3], shifted in place
+    raw_g: torch.Tensor = None,             # [1, B, H, 128]
+    raw_beta: torch.Tensor = None,          # [1, B, H]
+    a_log: torch.Tensor = None,             # fp32 [H]
+    dt_bias: torch.Tensor = None,           # fp32 [H, 128]
+    state_indices: torch.Tensor = None,     # int32 [B]; < 0 = padding row
+    state: torch.Tensor = None,             # fp32 [slots, H, 128, 128], updated in place
+    out: torch.Tensor = None,               # activation dtype [1, B, H, 128], written
+    lower_bound: Optional[float] = None,    # safe gate when given, softplus gate otherwise
+    output_gate: Optional[torch.Tensor] = None,   # [B, H, 128] or [1, B, H, 128]
+    norm_weight: Optional[torch.Tensor] = None,   # fp32 [128]
+    norm_eps: float = 1e-5,
+    *,
+    status: Optional[torch.Tensor] = None,
+) -> None:
+    """Kimi K3 fused decode step (docs/readme.md:232-267 of the reference): causal conv + SiLU, gating,
+    single-token KDA recurrence and optional gated output RMSNorm; writes ``conv_state``, ``state`` and
+    ``out`` in place and returns ``None``. ``output_gate`` and ``norm_weight`` come together. Rows whose
+    slot is negative produce a zero output row and touch nothing; slot 0 is an ordinary slot."""
+    for name, t in (("conv_state", conv_state), ("raw_g", raw_g), ("raw_beta", raw_beta), ("a_log", a_log),
+                    ("dt_bias", dt_bias), ("state_indices", state_indices), ("state", state), ("out", out)):
+        if t is None:
+            raise TypeError(f"fused_kda_decode_mega_forward() missing required argument: '{name}'")
+    ops.kda_decode_mega(x, weight, bias, conv_state, raw_g, raw_beta, a_log, dt_bias, state_indices, state, out,
+                        None if lower_bound is None else float(lower_bound), output_gate, norm_weight,
+                        float(norm_eps), status)
+    return None

@@ -420,3 +420,50 @@ def sglang_commit_case(name, device="cpu"):
     if device != "cpu":
         ci = {k: ([t.to(device) for t in v] if isinstance(v, list) else v.to(device)) for k, v in ci.items()}
     return ci, c
+
+
+# ---- fused KDA decode step (fused_kda_decode_mega_forward) ----
+MEGA_CASES = {"mega_h4_norm": dict(H=4, B=3, lower_bound=-5.0, norm=True, dtype="bf16"),
+              "mega_h6_softplus": dict(H=6, B=2, lower_bound=None, norm=False, dtype="bf16"),
+              "mega_h4_fp16_bias": dict(H=4, B=2, lower_bound=-5.0, norm=True, dtype="fp16")}
+
+
+def mega_case(name, device="cpu", pad_rows=()):
+    """Inputs shaped like the reference's own builder (compare_kda_decode_fusion.py:128-186): padded rows of
+    x / raw_beta / output_gate, conv state stored [slots, 3, 3*dim] and viewed [slots, 3*dim, 3], slots in
+    descending order (slot 0 included)."""
+    c = MEGA_CASES[name]
+    rs = _rs(sum(map(ord, name)))
+    H, B = c["H"], c["B"]
+    dt = torch.bfloat16 if c["dtype"] == "bf16" else torch.float16
+    dim, slots = H * D, B + 2
+    x = _t(rs, B, 3 * dim + 17, dtype=dt)[:, :3 * dim]
+    weight = _t(rs, 3, 4, dim, dtype=torch.float32, scale=0.1)
+    bias = _t(rs, 3 * dim, dtype=torch.float32, scale=0.05) if "bias" in name else None
+    conv_state = _t(rs, slots, 3, 3 * dim, dtype=dt, scale=0.1).transpose(1, 2)
+    raw_g = _t(rs, 1, B, H, D, dtype=dt)
+    raw_beta = _t(rs, 1, B, H + 1, dtype=dt)[:, :, :H]
+    output_gate = _t(rs, B, dim + 8, dtype=dt)[:, :dim].view(B, H, D)
+    norm_weight = _t(rs, D, dtype=torch.float32)
+    A_log = _t(rs, H, dtype=torch.float32, scale=0.5)
+    dt_bias = _t(rs, dim, dtype=torch.float32, scale=0.1)
+    idx = torch.arange(B - 1, -1, -1, dtype=torch.int32)
+    for r in pad_rows:
+        idx[r] = -1
+    state = _t(rs, slots, H, D, D, dtype=torch.float32, scale=0.01)
+    kw = dict(x=x, weight=weight, bias=bias, conv_state=conv_state, raw_g=raw_g, raw_beta=raw_beta, a_log=A_log,
+              dt_bias=dt_bias, state_indices=idx, state=state, lower_bound=c["lower_bound"],
+              output_gate=output_gate if c["norm"] else None, norm_weight=norm_weight if c["norm"] else None,
+              norm_eps=1e-5)
+    if device != "cpu":
+        moved = {}
+        for k_, v_ in kw.items():
+            if not isinstance(v_, torch.Tensor):
+                moved[k_] = v_
+            elif k_ in ("x", "raw_beta", "output_gate", "conv_state"):      # keep the padded / transposed views
+                base = v_._base if v_._base is not None else v_
+                moved[k_] = torch.as_strided(base.to(device), v_.shape, v_.stride(), v_.storage_offset())
+            else:
+                moved[k_] = v_.to(device)
+        kw = moved
+    return kw, c

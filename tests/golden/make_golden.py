@@ -130,6 +130,34 @@ def make_sglang():
         print("sglang fold", name, touched)
 
 
+def make_mega():
+    """Fused KDA decode step: the reference's step-by-step fp32 recurrence
+    (scripts/decode/kda_fusion/compare_kda_decode_fusion.py:252-308, extracted by name because the module
+    imports GPU-only code at its top) on the cases of cases.py. Its result dtype is fp16 by construction."""
+    import math
+    path = REF / "scripts" / "decode" / "kda_fusion" / "compare_kda_decode_fusion.py"
+    ns = {"torch": torch, "math": math, "D": 128, "W": 4, "NORM_EPS": 1e-5, "DEVICE": "cpu",
+          "SCALE": 1.0 / math.sqrt(128)}
+    load_function(path, "_silu", ns)
+    ref = load_function(path, "torch_reference_fp16", ns)
+    for name in cases.MEGA_CASES:
+        kw, c = cases.mega_case(name)
+        assert kw["bias"] is None or name.endswith("bias")
+        inp = {"num_seqs": c["B"], "num_heads": c["H"], "packed_x": kw["x"], "fused_weight": kw["weight"],
+               "conv_seed": kw["conv_state"], "raw_g": kw["raw_g"], "raw_beta": kw["raw_beta"], "A_log": kw["a_log"],
+               "dt_bias": kw["dt_bias"], "state_seed": kw["state"], "state_indices": kw["state_indices"],
+               "output_gate": kw["output_gate"] if c["norm"] else torch.zeros(c["B"], c["H"], 128),
+               "norm_weight": kw["norm_weight"] if c["norm"] else torch.ones(128)}
+        if kw["bias"] is not None:
+            continue    # the reference recurrence has no bias term: that case is checked against the oracle only
+        out, state, conv = ref(inp, c["lower_bound"], c["norm"])
+        touched = sorted(int(s) for s in kw["state_indices"])
+        np.savez_compressed(HERE / f"mega_{name}.npz", out=out.float().numpy(),
+                            state=cases.subsample(state[touched]), conv=conv[touched].float().numpy(),
+                            touched=np.array(touched))
+        print("mega", name, tuple(out.shape))
+
+
 def make_prefill():
     """GDN: the vendored chunked torch reference the reference's own prefill tests compare with
     (scripts/prefill/flashqla/private/ref_gdr.py, chunk 64, called per sequence as in
@@ -195,3 +223,5 @@ if __name__ == "__main__":
         make_prefill()
     if which in ("all", "sglang"):
         make_sglang()
+    if which in ("all", "mega"):
+        make_mega()
