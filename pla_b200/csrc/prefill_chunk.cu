@@ -1234,7 +1234,9 @@ int launch_chain_stage(const pla_b200_gdn_chunk_args& a, cudaStream_t s) {
   }
   PLA_REQUIRE(aligned16(a.o), PLA_B200_E_ALIGN, "o must be 16-byte aligned");
   auto launch_chain = [&](auto kern) -> int {
-    static bool configured[64] = {};
+    // one flag per kernel instantiation: both dtypes share this lambda's body (same function-pointer type)
+    static bool configured_by_dtype[2][64] = {};
+    bool* configured = configured_by_dtype[a.act_dtype == PLA_B200_BF16 ? 0 : 1];
     int dev = 0;
     PLA_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 64 && !configured[dev]) {
@@ -1266,7 +1268,9 @@ extern "C" int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t items = static_cast<int64_t>(a.max_chunks) * a.H;
   auto launch_prepare = [&](auto kern) -> int {
-    static bool configured[64] = {};
+    // one flag per kernel instantiation: both dtypes share this lambda's body (same function-pointer type)
+    static bool configured_by_dtype[2][64] = {};
+    bool* configured = configured_by_dtype[a.act_dtype == PLA_B200_BF16 ? 0 : 1];
     int dev = 0;
     PLA_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 64 && !configured[dev]) {
@@ -1311,7 +1315,9 @@ extern "C" int pla_b200_kda_prefill_chunked(const pla_b200_gdn_chunk_args* args,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t items = static_cast<int64_t>(a.max_chunks) * a.H;
   auto launch_prepare = [&](auto kern) -> int {
-    static bool configured[64] = {};
+    // one flag per kernel instantiation: both dtypes share this lambda's body (same function-pointer type)
+    static bool configured_by_dtype[2][64] = {};
+    bool* configured = configured_by_dtype[a.act_dtype == PLA_B200_BF16 ? 0 : 1];
     int dev = 0;
     PLA_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 64 && !configured[dev]) {

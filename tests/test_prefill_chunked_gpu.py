@@ -218,3 +218,35 @@ def test_chunked_prefill_rows_ending_at_the_allocation_end(native_built):
     assert status.item() == 0
     assert_out_close(out, exp_out)
     assert_state_close(final.cpu()[0], exp_state[0])
+
+
+@pytest.mark.parametrize("dtype,Hg,H", [(torch.float16, 1, 2), (torch.bfloat16, 1, 12), (torch.bfloat16, 2, 6)])
+def test_chunked_prefill_head_groups_and_fp16(native_built, dtype, Hg, H):
+    """fp16 activations, and value-head groups of 2, 3 and 12 per q/k head (more than one pass of eight heads
+    inside the prepare kernel), against the oracle."""
+    from pla_b200._ops import ops
+    g = torch.Generator().manual_seed(41)
+    lengths = [130, 64, 1]
+    T = sum(lengths)
+    q, k, v = (torch.randn(T, n, D, generator=g).to(dtype) for n in (Hg, Hg, H))
+    gates = torch.randn(T, 2 * H, generator=g).to(dtype)
+    A_log = torch.rand(H, generator=g) * float(np.log(16.0))
+    dt_bias = torch.randn(H, generator=g) * 0.1
+    pool = torch.randn(5, H, D, D, generator=g) * 0.05
+    slots = [3, 0, 4]
+    exp_out, exp_state, _ = odec.klast_forward(q=q, k=k, v=v, a=gates[:, :H], b=gates[:, H:], A_log=A_log,
+                                               dt_bias=dt_bias, state=pool, slot_indices=slots, lengths=lengths,
+                                               scale=D ** -0.5)
+    dg, dpool = gates.cuda(), pool.cuda()
+    out = torch.empty(T, H, D, dtype=dtype, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cu = torch.tensor([0, 130, 194, 195], dtype=torch.int32, device="cuda")
+    ops.gdn_prefill_chunked(q.cuda(), k.cuda(), v.cuda(), dg[:, :H], dg[:, H:], A_log.cuda(), dt_bias.cuda(), out, None,
+                            cu, dpool, torch.tensor(slots, dtype=torch.int32, device="cuda"), None, None, False, True,
+                            D ** -0.5, False, True, T // C + 3, 0, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert_out_close(out, exp_out)
+    assert_state_close(dpool.cpu(), exp_state)
+    untouched = [s for s in range(5) if s not in slots]
+    assert torch.equal(dpool[untouched].cpu(), pool[untouched])
