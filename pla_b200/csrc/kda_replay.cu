@@ -49,56 +49,57 @@ __device__ __forceinline__ int64_t idx_at(const pla_b200_index& a, int64_t i) {
 
 __device__ __forceinline__ float silu(float x) { return x * sigmoidf_fast(x); }
 
-// One delta-rule step on the CTA's 32 rows held in shared memory. 8 lanes per row.
+// One delta-rule step on 8 * NPASS state rows (row_base ..) held in shared memory, one warp, 8 lanes per
+// row. The norm factors stay scalars: d = kr (S k), S += (vn kr) k, o = qr (S q) with k, q as staged.
 // WITH_OUT: also form o = S q. `snap` (optional) receives the updated rows.
-template <bool WITH_OUT>
+template <bool WITH_OUT, int NPASS = 1>
 __device__ __forceinline__ void kda_step(float* s_state, const float* sk, const float* sq, const float* sgam,
                                          const float* sv, float kr, float qr, float beta, float* so,
-                                         float* snap, int warp, int lane) {
-  const int row = warp * 8 + (lane >> 3) * 2;  // two consecutive rows per lane group
+                                         float* snap, int row_base, int lane) {
   const int j = lane & 7;
   float4 kk[4], qq[4], gg[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     kk[i] = reinterpret_cast<const float4*>(sk)[i * 8 + j];
-    kk[i].x *= kr; kk[i].y *= kr; kk[i].z *= kr; kk[i].w *= kr;
     gg[i] = reinterpret_cast<const float4*>(sgam)[i * 8 + j];
-    if constexpr (WITH_OUT) {
-      qq[i] = reinterpret_cast<const float4*>(sq)[i * 8 + j];
-      qq[i].x *= qr; qq[i].y *= qr; qq[i].z *= qr; qq[i].w *= qr;
-    }
+    if constexpr (WITH_OUT) qq[i] = reinterpret_cast<const float4*>(sq)[i * 8 + j];
   }
+  const float bk = beta * kr;
 #pragma unroll
-  for (int pp = 0; pp < 2; ++pp) {
-    float4* srow = reinterpret_cast<float4*>(s_state + (row + pp) * D);
-    float4 st[4];
-    float d = 0.0f;
+  for (int ps = 0; ps < NPASS; ++ps) {
+    const int row = row_base + ps * 8 + (lane >> 3) * 2;  // two consecutive rows per lane group
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      st[i] = srow[i * 8 + j];
-      st[i].x *= gg[i].x; st[i].y *= gg[i].y; st[i].z *= gg[i].z; st[i].w *= gg[i].w;
-      d += dot4(st[i], kk[i]);
-    }
-    d += __shfl_xor_sync(0xffffffffu, d, 1);
-    d += __shfl_xor_sync(0xffffffffu, d, 2);
-    d += __shfl_xor_sync(0xffffffffu, d, 4);
-    const float vn = (sv[row + pp] - d) * beta;
-    float oacc = 0.0f;
+    for (int pp = 0; pp < 2; ++pp) {
+      float4* srow = reinterpret_cast<float4*>(s_state + (row + pp) * D);
+      float4 st[4];
+      float d = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      st[i].x = fmaf(vn, kk[i].x, st[i].x);
-      st[i].y = fmaf(vn, kk[i].y, st[i].y);
-      st[i].z = fmaf(vn, kk[i].z, st[i].z);
-      st[i].w = fmaf(vn, kk[i].w, st[i].w);
-      if constexpr (WITH_OUT) oacc += dot4(st[i], qq[i]);
-      srow[i * 8 + j] = st[i];
-      if (snap != nullptr) *reinterpret_cast<float4*>(snap + (row + pp) * D + (i * 8 + j) * 4) = st[i];
-    }
-    if constexpr (WITH_OUT) {
-      oacc += __shfl_xor_sync(0xffffffffu, oacc, 1);
-      oacc += __shfl_xor_sync(0xffffffffu, oacc, 2);
-      oacc += __shfl_xor_sync(0xffffffffu, oacc, 4);
-      if (j == 0) so[row + pp] = oacc;
+      for (int i = 0; i < 4; ++i) {
+        st[i] = srow[i * 8 + j];
+        st[i].x *= gg[i].x; st[i].y *= gg[i].y; st[i].z *= gg[i].z; st[i].w *= gg[i].w;
+        d += dot4(st[i], kk[i]);
+      }
+      d += __shfl_xor_sync(0xffffffffu, d, 1);
+      d += __shfl_xor_sync(0xffffffffu, d, 2);
+      d += __shfl_xor_sync(0xffffffffu, d, 4);
+      const float vn = (sv[row + pp] * beta - d * bk) * kr;   // (v - kr d) beta, times kr for the update
+      float oacc = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        st[i].x = fmaf(vn, kk[i].x, st[i].x);
+        st[i].y = fmaf(vn, kk[i].y, st[i].y);
+        st[i].z = fmaf(vn, kk[i].z, st[i].z);
+        st[i].w = fmaf(vn, kk[i].w, st[i].w);
+        if constexpr (WITH_OUT) oacc += dot4(st[i], qq[i]);
+        srow[i * 8 + j] = st[i];
+        if (snap != nullptr) *reinterpret_cast<float4*>(snap + (row + pp) * D + (i * 8 + j) * 4) = st[i];
+      }
+      if constexpr (WITH_OUT) {
+        oacc += __shfl_xor_sync(0xffffffffu, oacc, 1);
+        oacc += __shfl_xor_sync(0xffffffffu, oacc, 2);
+        oacc += __shfl_xor_sync(0xffffffffu, oacc, 4);
+        if (j == 0) so[row + pp] = oacc * qr;
+      }
     }
   }
 }
@@ -108,15 +109,30 @@ __device__ __forceinline__ void kda_step(float* s_state, const float* sk, const 
 __device__ __forceinline__ int window_capacity(const pla_b200_kda_verify_args& p) {
   return p.win_steps > 0 ? min(p.Q, p.win_steps) : p.Q;
 }
-__global__ void __launch_bounds__(NT) kda_verify_kernel(const pla_b200_kda_verify_args p) {
+// One CTA per (request, head), 256 threads, the whole 128 x 128 state in shared memory (read once,
+// never written back). Threads 0..127 own a q / k / gate channel, threads 128..255 a v channel; conv +
+// SiLU, gate and records are formed once per (token, channel); the recurrence runs over the staged
+// tokens with warp w on state rows 16w .. 16w + 15.
+constexpr int VNT = 256;
+constexpr int VTS = 4;             // tokens staged per pass of the verify kernel
+struct VerifySmem {
+  alignas(128) float state[D * D];
+  float q[VTS][D];
+  float k[VTS][D];
+  float gam[VTS][D];
+  float v[VTS][D];
+  float o[VTS][D];
+  float part[VTS][2][4];
+  float beta[VTS];
+  alignas(8) uint64_t bar;
+};
+
+__global__ void __launch_bounds__(VNT, 2) kda_verify_kernel(const pla_b200_kda_verify_args p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  Smem& sh = *reinterpret_cast<Smem*>(smem_raw);
+  VerifySmem& sh = *reinterpret_cast<VerifySmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int vs = blockIdx.x % NVS;
-  const int h = (blockIdx.x / NVS) % p.H;
-  const int n = blockIdx.x / (NVS * p.H);
-  const int row0 = vs * BV;
-  const bool writer = vs == 0;  // q/k/gate/beta records are written once per (row, head)
+  const int h = blockIdx.x % p.H;
+  const int n = blockIdx.x / p.H;
 
   const int64_t begin = idx_at(p.cu, n), end = idx_at(p.cu, n + 1);
   const int64_t slot = idx_at(p.slot_idx, n);
@@ -125,120 +141,131 @@ __global__ void __launch_bounds__(NT) kda_verify_kernel(const pla_b200_kda_verif
       begin == end)
     return;
   const int n_tok = static_cast<int>(end - begin);
-  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(h) * D + row0;
   const int64_t out_stride = static_cast<int64_t>(p.H) * D;
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(h) * D;
   if (slot <= p.null_block_id) {  // padding row: zero its output interval, touch nothing else
-    for (int i = tid; i < n_tok * BV; i += NT)
-      out[(begin + i / BV) * out_stride + (i % BV)] = __float2bfloat16(0.0f);
+    for (int i = tid; i < n_tok * D; i += VNT) out[(begin + i / D) * out_stride + (i % D)] = __float2bfloat16(0.0f);
     return;
   }
 
   if (tid == 0) {
     mbar_init(&sh.bar, 1);
     fence_mbar_init();
-    mbar_expect_tx(&sh.bar, kSliceBytes);
-    bulk_load(sh.state, p.state + slot * p.state_slot_stride + static_cast<int64_t>(h) * TILE + row0 * D,
-              kSliceBytes, &sh.bar);
+    mbar_expect_tx(&sh.bar, D * D * 4);
+    const float* src = p.state + slot * p.state_slot_stride + static_cast<int64_t>(h) * TILE;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) bulk_load(sh.state + i * (TILE / 4), src + i * (TILE / 4), TILE, &sh.bar);
   }
 
   const int64_t rec_row = p.row_by_slot ? slot : n;
   const int64_t win_row = (p.row_by_slot && p.scratch_idx.data != nullptr) ? idx_at(p.scratch_idx, n) : n;
-  const int ch = h * D + tid;          // q/k/gate channel of this thread
-  const int chv = h * D + row0 + tid;  // v channel (threads < BV)
-  const __nv_bfloat16* xq = static_cast<const __nv_bfloat16*>(p.x_q);
-  const __nv_bfloat16* xk = static_cast<const __nv_bfloat16*>(p.x_k);
-  const __nv_bfloat16* xv = static_cast<const __nv_bfloat16*>(p.x_v);
-  const __nv_bfloat16* gin = static_cast<const __nv_bfloat16*>(p.raw_g);
-  const __nv_bfloat16* bin = static_cast<const __nv_bfloat16*>(p.raw_beta);
+  const bool is_v = tid >= D;
+  const int c = tid & (D - 1);
+  const int ch = h * D + c;             // channel of this thread inside its q / k / gate or v tensor
+  const __nv_bfloat16* gin = static_cast<const __nv_bfloat16*>(p.raw_g) + begin * p.g_tok_stride + ch;
+  const __nv_bfloat16* bin = static_cast<const __nv_bfloat16*>(p.raw_beta) + begin * p.beta_tok_stride + h;
 
-  // conv taps and the sliding 3-tap history, all in registers
-  float wq[4], wk[4], wv[4], hq[3], hk[3], hv3[3];
-#pragma unroll
-  for (int w = 0; w < 4; ++w) {
-    wq[w] = p.w_q[ch * 4 + w];
-    wk[w] = p.w_k[ch * 4 + w];
-    wv[w] = (tid < BV) ? p.w_v[chv * 4 + w] : 0.0f;
-  }
+  // conv taps and the sliding 3-tap history in registers: (q, k) for the first half, v for the second
+  float wa[4], wb[4], ha[3], hb[3];
+  const __nv_bfloat16 *xa, *xb = nullptr;
+  int64_t xa_stride, xb_stride = 0;
+  __nv_bfloat16 *wina, *winb = nullptr;
+  int64_t wina_step, wina_tap, winb_step = 0, winb_tap = 0;
   {
-    const __nv_bfloat16* cq = static_cast<const __nv_bfloat16*>(p.cs_q);
-    const __nv_bfloat16* ck = static_cast<const __nv_bfloat16*>(p.cs_k);
-    const __nv_bfloat16* cv = static_cast<const __nv_bfloat16*>(p.cs_v);
+    const float* w0 = is_v ? p.w_v : p.w_q;
+    const __nv_bfloat16* cs0 = static_cast<const __nv_bfloat16*>(is_v ? p.cs_v : p.cs_q);
+    const pla_b200_conv_strides& st0 = is_v ? p.cs_v_strides : p.cs_q_strides;
+    const pla_b200_window_strides& ws0 = is_v ? p.win_v_strides : p.win_q_strides;
 #pragma unroll
-    for (int w = 0; w < 3; ++w) {
-      hq[w] = __bfloat162float(cq[slot * p.cs_q_strides.slot + ch * p.cs_q_strides.channel + w * p.cs_q_strides.tap]);
-      hk[w] = __bfloat162float(ck[slot * p.cs_k_strides.slot + ch * p.cs_k_strides.channel + w * p.cs_k_strides.tap]);
-      hv3[w] = (tid < BV) ? __bfloat162float(cv[slot * p.cs_v_strides.slot + chv * p.cs_v_strides.channel +
-                                                w * p.cs_v_strides.tap])
-                          : 0.0f;
+    for (int w = 0; w < 4; ++w) wa[w] = w0[ch * 4 + w];
+#pragma unroll
+    for (int w = 0; w < 3; ++w) ha[w] = __bfloat162float(cs0[slot * st0.slot + ch * st0.channel + w * st0.tap]);
+    xa = static_cast<const __nv_bfloat16*>(is_v ? p.x_v : p.x_q) + begin * (is_v ? p.xv_tok_stride : p.xq_tok_stride) + ch;
+    xa_stride = is_v ? p.xv_tok_stride : p.xq_tok_stride;
+    wina = static_cast<__nv_bfloat16*>(is_v ? p.win_v : p.win_q) + win_row * ws0.row + ch * ws0.channel;
+    wina_step = ws0.step;
+    wina_tap = ws0.tap;
+    if (!is_v) {
+      const __nv_bfloat16* cs1 = static_cast<const __nv_bfloat16*>(p.cs_k);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) wb[w] = p.w_k[ch * 4 + w];
+#pragma unroll
+      for (int w = 0; w < 3; ++w)
+        hb[w] = __bfloat162float(cs1[slot * p.cs_k_strides.slot + ch * p.cs_k_strides.channel + w * p.cs_k_strides.tap]);
+      xb = static_cast<const __nv_bfloat16*>(p.x_k) + begin * p.xk_tok_stride + ch;
+      xb_stride = p.xk_tok_stride;
+      winb = static_cast<__nv_bfloat16*>(p.win_k) + win_row * p.win_k_strides.row + ch * p.win_k_strides.channel;
+      winb_step = p.win_k_strides.step;
+      winb_tap = p.win_k_strides.tap;
     }
   }
   const float A_log = p.A_log[h];
-  const float dtb = p.dt_bias[ch];
-  __nv_bfloat16* wqo = static_cast<__nv_bfloat16*>(p.win_q);
-  __nv_bfloat16* wko = static_cast<__nv_bfloat16*>(p.win_k);
-  __nv_bfloat16* wvo = static_cast<__nv_bfloat16*>(p.win_v);
-  __nv_bfloat16* rrk = static_cast<__nv_bfloat16*>(p.rec_rawk);
-  __nv_bfloat16* rrv = static_cast<__nv_bfloat16*>(p.rec_rawv);
+  const float dtb = is_v ? 0.f : p.dt_bias[ch];
+  const int64_t rec0 = (rec_row * p.H + h) * p.Q;       // record row of step 0, in 128-element rows
+  __nv_bfloat16* rra = static_cast<__nv_bfloat16*>(is_v ? p.rec_rawv : p.rec_rawk) + rec0 * D + c;
+  float* rg = p.rec_g + rec0 * D + c;
 
   bool loaded = false;
-  for (int t0 = 0; t0 < n_tok; t0 += TS) {
-    const int nt = min(TS, n_tok - t0);
+  for (int t0 = 0; t0 < n_tok; t0 += VTS) {
+    const int nt = min(VTS, n_tok - t0);
     if (t0 > 0) __syncthreads();
-    for (int s = 0; s < nt; ++s) {
-      const int t = t0 + s;
-      const int64_t tok = begin + t;
-      const int64_t rec = ((rec_row * p.H + h) * p.Q + t) * D;
-      const __nv_bfloat16 bq = xq[tok * p.xq_tok_stride + ch], bk = xk[tok * p.xk_tok_stride + ch];
-      const float fq = __bfloat162float(bq), fk = __bfloat162float(bk);
-      float cq = fq * wq[3], ck = fk * wk[3];
+    // all of this pass's inputs first: the record / window stores below would otherwise keep each
+    // token's loads behind the previous token's stores
+    float in_a[VTS], in_b[VTS], in_g[VTS], in_beta[VTS];
 #pragma unroll
-      for (int w = 0; w < 3; ++w) {
-        cq += hq[w] * wq[w];
-        ck += hk[w] * wk[w];
-      }
-      cq = silu(cq);
-      ck = silu(ck);
-      const float x = __bfloat162float(gin[tok * p.g_tok_stride + ch]) + dtb;
-      const float gk = log_decay(x, A_log, p.gate, p.softplus_beta, p.softplus_threshold, p.lower_bound);
-      hq[0] = hq[1]; hq[1] = hq[2]; hq[2] = fq;
-      hk[0] = hk[1]; hk[1] = hk[2]; hk[2] = fk;
-      if (writer) {
-        rrk[rec + tid] = __float2bfloat16(ck);
-        p.rec_g[rec + tid] = gk;
-        const int64_t iq = win_row * p.win_q_strides.row + t * p.win_q_strides.step + ch * p.win_q_strides.channel;
-        const int64_t ik = win_row * p.win_k_strides.row + t * p.win_k_strides.step + ch * p.win_k_strides.channel;
-#pragma unroll
-        for (int w = 0; w < 3; ++w) {
-          wqo[iq + w * p.win_q_strides.tap] = __float2bfloat16(hq[w]);  // exact: the values came from bf16
-          wko[ik + w * p.win_k_strides.tap] = __float2bfloat16(hk[w]);
+    for (int s = 0; s < VTS; ++s) {
+      in_a[s] = in_b[s] = in_g[s] = in_beta[s] = 0.f;
+      if (s < nt) {
+        const int t = t0 + s;
+        in_a[s] = __bfloat162float(xa[t * xa_stride]);
+        if (!is_v) {
+          in_b[s] = __bfloat162float(xb[t * xb_stride]);
+          in_g[s] = __bfloat162float(gin[t * p.g_tok_stride]);
+        } else if (c == 0) {
+          in_beta[s] = __bfloat162float(bin[t * p.beta_tok_stride]);
         }
       }
-      sh.q[s][tid] = cq;
-      sh.k[s][tid] = ck;
-      sh.gam[s][tid] = __expf(gk);
-      const float sq = warp_sum(cq * cq), sk = warp_sum(ck * ck);
-      if (lane == 0) {
-        sh.part[s][0][warp] = sq;
-        sh.part[s][1][warp] = sk;
-      }
-      if (tid < BV) {
-        const __nv_bfloat16 bvv = xv[tok * p.xv_tok_stride + chv];
-        const float fv = __bfloat162float(bvv);
-        float cv = fv * wv[3];
+    }
 #pragma unroll
-        for (int w = 0; w < 3; ++w) cv += hv3[w] * wv[w];
-        cv = silu(cv);
-        hv3[0] = hv3[1]; hv3[1] = hv3[2]; hv3[2] = fv;
-        sh.v[s][tid] = cv;
-        rrv[rec + row0 + tid] = __float2bfloat16(cv);
-        const int64_t iv = win_row * p.win_v_strides.row + t * p.win_v_strides.step + chv * p.win_v_strides.channel;
+    for (int s = 0; s < VTS; ++s) {
+      if (s >= nt) break;
+      const int t = t0 + s;
+      const float fa = in_a[s];
+      float ca = fa * wa[3];
 #pragma unroll
-        for (int w = 0; w < 3; ++w) wvo[iv + w * p.win_v_strides.tap] = __float2bfloat16(hv3[w]);
-      }
-      if (tid == 0) {
-        const float beta = sigmoidf_fast(__bfloat162float(bin[tok * p.beta_tok_stride + h]));
-        sh.beta[s] = beta;
-        if (writer) p.rec_beta[(rec_row * p.H + h) * p.Q + t] = beta;
+      for (int w = 0; w < 3; ++w) ca += ha[w] * wa[w];
+      ca = silu(ca);
+      ha[0] = ha[1]; ha[1] = ha[2]; ha[2] = fa;
+#pragma unroll
+      for (int w = 0; w < 3; ++w) wina[t * wina_step + w * wina_tap] = __float2bfloat16(ha[w]);  // exact: values came from bf16
+      if (is_v) {
+        sh.v[s][c] = ca;
+        rra[static_cast<int64_t>(t) * D] = __float2bfloat16(ca);
+        if (c == 0) {
+          const float beta = sigmoidf_fast(in_beta[s]);
+          sh.beta[s] = beta;
+          p.rec_beta[rec0 + t] = beta;
+        }
+      } else {
+        const float fb = in_b[s];
+        float cb = fb * wb[3];
+#pragma unroll
+        for (int w = 0; w < 3; ++w) cb += hb[w] * wb[w];
+        cb = silu(cb);
+        hb[0] = hb[1]; hb[1] = hb[2]; hb[2] = fb;
+#pragma unroll
+        for (int w = 0; w < 3; ++w) winb[t * winb_step + w * winb_tap] = __float2bfloat16(hb[w]);
+        const float gk = log_decay(in_g[s] + dtb, A_log, p.gate, p.softplus_beta, p.softplus_threshold, p.lower_bound);
+        rra[static_cast<int64_t>(t) * D] = __float2bfloat16(cb);
+        rg[static_cast<int64_t>(t) * D] = gk;
+        sh.q[s][c] = ca;
+        sh.k[s][c] = cb;
+        sh.gam[s][c] = __expf(gk);
+        const float sq = warp_sum(ca * ca), sk = warp_sum(cb * cb);
+        if (lane == 0) {
+          sh.part[s][0][warp] = sq;
+          sh.part[s][1][warp] = sk;
+        }
       }
     }
     __syncthreads();
@@ -252,23 +279,19 @@ __global__ void __launch_bounds__(NT) kda_verify_kernel(const pla_b200_kda_verif
       loaded = true;
     }
     for (int s = 0; s < nt; ++s) {
-      float sq = 0.f, sk = 0.f;
-#pragma unroll
-      for (int w = 0; w < NW; ++w) {
-        sq += sh.part[s][0][w];
-        sk += sh.part[s][1][w];
-      }
+      const float sq = (sh.part[s][0][0] + sh.part[s][0][1]) + (sh.part[s][0][2] + sh.part[s][0][3]);
+      const float sk = (sh.part[s][1][0] + sh.part[s][1][1]) + (sh.part[s][1][2] + sh.part[s][1][3]);
       const float qr = rsqrtf(sq + 1e-6f) * p.scale, kr = rsqrtf(sk + 1e-6f);
-      kda_step<true>(sh.state, sh.k[s], sh.q[s], sh.gam[s], sh.v[s], kr, qr, sh.beta[s], sh.o[s], nullptr, warp,
-                     lane);
+      kda_step<true, 2>(sh.state, sh.k[s], sh.q[s], sh.gam[s], sh.v[s], kr, qr, sh.beta[s], sh.o[s], nullptr,
+                        warp * 16, lane);
     }
     __syncthreads();
     if (p.out_f32 != nullptr) {
-      float* of = p.out_f32 + static_cast<int64_t>(h) * D + row0;
-      for (int i = tid; i < nt * BV; i += NT) of[(begin + t0 + i / BV) * out_stride + (i % BV)] = sh.o[i / BV][i % BV];
+      float* of = p.out_f32 + static_cast<int64_t>(h) * D;
+      for (int i = tid; i < nt * D; i += VNT) of[(begin + t0 + i / D) * out_stride + (i % D)] = sh.o[i / D][i % D];
     } else {
-      for (int i = tid; i < nt * BV; i += NT)
-        out[(begin + t0 + i / BV) * out_stride + (i % BV)] = __float2bfloat16(sh.o[i / BV][i % BV]);
+      for (int i = tid; i < nt * D; i += VNT)
+        out[(begin + t0 + i / D) * out_stride + (i % D)] = __float2bfloat16(sh.o[i / D][i % D]);
     }
   }
 }
@@ -473,7 +496,7 @@ __device__ void fold_cta(const pla_b200_kda_commit_args& p, int cta, Smem& sh) {
       float* snap = nullptr;
       if (bc > 0 && t0 + s == bc - 1 && boundary > p.null_block_id && boundary < p.slots)
         snap = pool + static_cast<int64_t>(boundary) * slot_stride + tile_off;
-      kda_step<false>(sh.state, sh.k[s], nullptr, sh.gam[s], sh.v[s], kinv, 0.f, sh.beta[s], nullptr, snap, warp,
+      kda_step<false>(sh.state, sh.k[s], nullptr, sh.gam[s], sh.v[s], kinv, 0.f, sh.beta[s], nullptr, snap, warp * 8,
                       lane);
     }
   }
@@ -590,7 +613,7 @@ __global__ void __launch_bounds__(NT) fold_layers_kernel(const pla_b200_kda_fold
       float* snap = nullptr;
       if (has_track && t0 + s == t_track && slot_track > p.null_block_id && slot_track >= 0 && slot_track < p.slots)
         snap = pool + slot_track * p.state_slot_stride + tile_off;
-      kda_step<false>(sh.state, sh.k[s], nullptr, sh.gam[s], sh.v[s], kinv, 0.f, sh.beta[s], nullptr, snap, warp,
+      kda_step<false>(sh.state, sh.k[s], nullptr, sh.gam[s], sh.v[s], kinv, 0.f, sh.beta[s], nullptr, snap, warp * 8,
                       lane);
     }
   }
@@ -672,16 +695,16 @@ extern "C" int pla_b200_kda_replay_verify(const pla_b200_kda_verify_args* args, 
   int dev = 0;
   PLA_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
-    PLA_CUDA_OK(cudaFuncSetAttribute(kda_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(Smem)));
+    PLA_CUDA_OK(cudaFuncSetAttribute(kda_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(VerifySmem)));
     configured[dev] = true;
   }
-  const int64_t ctas = static_cast<int64_t>(a.N) * a.H * NVS;
+  const int64_t ctas = static_cast<int64_t>(a.N) * a.H;
   PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "N*H exceeds the grid limit");
   const bool onorm = a.onorm_gate != nullptr || a.onorm_weight != nullptr || a.out_f32 != nullptr;
   PLA_REQUIRE(!onorm || (a.onorm_gate && a.onorm_weight && a.out_f32 && aligned16(a.out_f32) &&
                          aligned16(a.onorm_weight) && a.onorm_eps >= 0.0f),
               PLA_B200_E_INVALID, "the fused output norm needs gate, weight, eps >= 0 and a 16-byte aligned fp32 staging buffer");
-  kda_verify_kernel<<<static_cast<unsigned>(ctas), NT, sizeof(Smem), static_cast<cudaStream_t>(stream)>>>(a);
+  kda_verify_kernel<<<static_cast<unsigned>(ctas), VNT, sizeof(VerifySmem), static_cast<cudaStream_t>(stream)>>>(a);
   PLA_CUDA_OK(cudaGetLastError());
   if (onorm) {
     kda_onorm_kernel<<<static_cast<unsigned>(a.N) * a.H, NT, 0, static_cast<cudaStream_t>(stream)>>>(a);
