@@ -121,8 +121,8 @@ def make_inputs(hv_lo: int, hv_hi: int, device):
     b = torch.randn(B, HV, generator=g)
     A_log = torch.rand(HV, generator=g) * math.log(16.0)
     dt_bias = torch.randn(HV, generator=g) * 0.1
-    perm = torch.randperm(SLOTS - 1, generator=g) + 1          # slot 0 left out (padding under the vLLM rule)
-    slot_sets = [perm[i * B:(i + 1) * B].to(torch.int32) for i in range((SLOTS - 1) // B)]
+    perm = torch.randperm(SLOTS, generator=g)                  # SGLang padding rule: slot 0 is an ordinary slot
+    slot_sets = [perm[i * B:(i + 1) * B].to(torch.int32) for i in range(SLOTS // B)]   # disjoint sets (4 at B=256)
     hl = h_hi - h_lo
     hvl = hv_hi - hv_lo
     mixed = torch.cat([q[:, h_lo:h_hi].reshape(B, hl * D), k[:, h_lo:h_hi].reshape(B, hl * D),
@@ -176,7 +176,7 @@ def run_ours(args):
     # ~25 us of kernel time and per-call host overhead would otherwise be what is measured.
     for i in range(args.warmup):
         step(i, dev_in)
-    G = max(g_ for g_ in range(1, 31) if args.steps % g_ == 0)
+    G = max(g_ for g_ in range(1, 41) if args.steps % g_ == 0)     # 40 steps per graph at the default 2000
     graph = None
     if not args.no_graph:
         side = torch.cuda.Stream()
@@ -406,7 +406,8 @@ def run_prefill(args):
                       "n_gpus": 1, "steps": args.steps, "ms_per_step": round(ms, 4), "higher_is_better": True,
                       "dtype": "f32", "data": "synthetic",
                       "config": {"workload": f"config3: 8 sequences {lengths}, T={T}, Hqk=16 HV=32, chunk 64 on the tensor cores (tf32)",
-                                 "chunk_equivalent_tflops": round(flops / ms / 1e9, 2)}}), flush=True)
+                                 "chunk_equivalent_tflops": round(flops / ms / 1e9, 2),
+                                 "algorithmic_GBps": round(T * 24.7e3 / ms / 1e6, 1)}}), flush=True)
 
 
 def run_prefill_cp(args):
@@ -503,6 +504,43 @@ def run_prefill_cp(args):
     dist.destroy_process_group()
 
 
+def run_vlast(args):
+    """Secondary line: config 1 in the v-last layout ([slots, HV, K, V] pool) through
+    pla_b200.decode.gdn.v_last, one GPU, device-resident steps."""
+    from pla_b200.decode.gdn.v_last import fused_sigmoid_gating_delta_rule
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(SEED)
+    q = torch.nn.functional.normalize(torch.randn(B, 1, HQK, D, generator=g), dim=-1).bfloat16().to(dev)
+    k = torch.nn.functional.normalize(torch.randn(B, 1, HQK, D, generator=g), dim=-1).bfloat16().to(dev)
+    v = torch.randn(B, 1, HV, D, generator=g).bfloat16().to(dev)
+    a = torch.randn(B, HV, generator=g).bfloat16().to(dev)
+    b = torch.randn(B, HV, generator=g).bfloat16().to(dev)
+    A_log = (torch.rand(HV, generator=g) * math.log(16.0)).to(dev)
+    dt_bias = (torch.randn(HV, generator=g) * 0.1).bfloat16().to(dev)
+    perm = torch.randperm(SLOTS, generator=g)
+    sets = [perm[i * B:(i + 1) * B].to(torch.int32).to(dev) for i in range(SLOTS // B)]
+    pool = torch.empty(SLOTS, HV, D, D, device=dev).normal_(0.0, 0.02, generator=torch.Generator(device=dev).manual_seed(1))
+    o = torch.empty(B, 1, HV, D, dtype=torch.bfloat16, device=dev)
+    i_ = [0]
+
+    def step():
+        fused_sigmoid_gating_delta_rule(A_log, a, dt_bias, q, k, v, b, o, pool, sets[i_[0] % len(sets)], None, 1.0, 20.0,
+                                        D ** -0.5, 1, B, HQK, HV, D, D, True, True, False)
+        i_[0] += 1
+
+    ms = _time_steps(step, args.steps, max(args.warmup, 3))
+    gbs = 2 * B * HV * TILE_BYTES / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": "gdn_decode_state_bandwidth_B256_vlast", "value": round(gbs, 1), "unit": "GB/s",
+                      "n_gpus": 1, "steps": args.steps, "ms_per_step": round(ms, 5), "higher_is_better": True,
+                      "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "config1 (v-last half): GDN decode B=256 Hqk=16 HV=32 d=128, fp32 v-last pool "
+                                             "1024 slots, 4 disjoint slot sets rotated", "launch": "host call per step"},
+                      "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": measured_peaks()[0], "unit": "GB/s",
+                                   "frac": round(gbs / measured_peaks()[0], 4),
+                                   "peak_source": "of " + measured_peaks()[1]}}),
+          flush=True)
+
+
 def run_replay(args):
     """Secondary line: config 2, KDA ReplaySSM verify + commit, 32 heads, 64 rows x 4 tokens, 512 pages."""
     import numpy as np
@@ -544,7 +582,7 @@ def run_replay(args):
 def main():
     global B, SLOTS, WORKLOAD
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill_cp", "prefill_cp_kda", "replay"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "decode_vlast", "prefill", "prefill_cp", "prefill_cp_kda", "replay"],
                     help="decode = the headline metric; prefill / replay print secondary lines (1 GPU)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
@@ -570,7 +608,7 @@ def main():
     if args.workload != "decode":
         if int(os.environ.get("RANK", 0)) == 0:
             args.steps = min(args.steps, 50)
-            (run_prefill if args.workload == "prefill" else run_replay)(args)
+            {"prefill": run_prefill, "replay": run_replay, "decode_vlast": run_vlast}[args.workload](args)
         return
     if args.impl == "reference":
         run_reference(args)

@@ -459,7 +459,7 @@ int launch_shape(const pla_b200_klast_args& a, cudaStream_t stream) {
       case 128: return launch_one<act_t, 128, 256, 1, IS_KDA>(a, stream);
     }
   }
-  PLA_REQUIRE(false, PLA_B200_E_INVALID, "rows_per_cta must be 0, 16, 32, 64 or 128 (got %d)", rows);
+  PLA_REQUIRE(false, PLA_B200_E_INVALID, "rows_per_cta must be 0, 1, 16, 32, 64 or 128 (got %d)", rows);
 }
 
 }  // namespace
@@ -507,9 +507,10 @@ extern "C" int pla_b200_decode_klast(const pla_b200_klast_args* args, void* stre
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // rows_per_cta: 0 = pick (streaming kernel when the call qualifies), 16 = streaming kernel or error,
   // 32/64/128 = the one-block-per-CTA kernel.
-  if (a.rows_per_cta == 16)
+  if (a.rows_per_cta == 16 || a.rows_per_cta == 1)
     PLA_REQUIRE(klast_stream_eligible(a), PLA_B200_E_INVALID,
-                "rows_per_cta=16 selects the streaming decode kernel, which needs a plain single-token call");
+                "rows_per_cta=16 / 1 select the single-token decode kernels, which need a plain single-token call");
+  if (a.rows_per_cta == 1) return launch_klast_rows(a, s);
   if ((a.rows_per_cta == 0 || a.rows_per_cta == 16) && klast_stream_eligible(a)) return launch_klast_stream(a, s);
   if (a.act_dtype == PLA_B200_BF16)
     return a.is_kda ? launch_shape<__nv_bfloat16, true>(a, s) : launch_shape<__nv_bfloat16, false>(a, s);

@@ -29,15 +29,15 @@ def to_cuda(args, backing):
     return out, backing_d
 
 
-@pytest.mark.parametrize("rows", [0, 16, 32, 64, 128])
+@pytest.mark.parametrize("rows", [0, 1, 16, 32, 64, 128])
 @pytest.mark.parametrize("name", sorted(cases.KLAST_CASES))
 def test_klast_matches_oracle_and_fixture(native_built, name, rows):
     from pla_b200.decode import fused_sigmoid_gating_delta_rule_forward_k_last as forward
     args, backing, lengths, state_ids, cache_ids = cases.klast_case(name)
-    if rows == 16 and cases.KLAST_CASES[name]["mode"] != "decode":
+    if rows in (1, 16) and cases.KLAST_CASES[name]["mode"] != "decode":
         dargs, _ = to_cuda(args, backing)
-        with pytest.raises(RuntimeError, match="streaming decode kernel"):
-            forward(**dargs, rows_per_cta=16)   # the streaming kernel only takes plain single-token calls
+        with pytest.raises(RuntimeError, match="single-token decode kernels"):
+            forward(**dargs, rows_per_cta=rows)   # these kernels only take plain single-token calls
         return
     exp_out, exp_state, exp_cache = odec.klast_forward(**cases.oracle_kwargs(args, lengths, state_ids, cache_ids))
     dargs, dbacking = to_cuda(args, backing)
