@@ -1,7 +1,8 @@
 // Host layer of the prefill ops: tensor contracts of
 //   pla.prefill.flashqla.chunk_gated_delta_rule_fwd / gdn_prefill_packed_qkv_fwd (pla/prefill/flashqla/ops.py:225-738)
 //   pla.prefill.flashkdapro.flashkda_fwd                                          (pla/prefill/flashkdapro/ops.py:66-219)
-// mapped onto the token-recurrent prefill entry of the C ABI. No sync, no D2H.
+// mapped onto the chunked (tensor-core) and token-recurrent prefill entries of the C ABI, plus the staged /
+// prescan forms used by context parallelism. No sync, no D2H.
 #include "ops_common.h"
 
 namespace pla_ops {

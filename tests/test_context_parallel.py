@@ -82,3 +82,60 @@ def test_fold_is_the_composition_of_affine_maps():
     ident = cp.identity_transfer(H, "cpu")
     torch.testing.assert_close(cp.fold_transfers(S0, ident[None], 1), S0)
     assert torch.equal(cp.fold_transfers(None, gathered, 0), torch.zeros(H, D, D))
+
+
+def _decode_shard_worker(rank, world, port, result_dir):
+    """Rank r of the decode bench: value heads [r*HV/world, (r+1)*HV/world) of every request, its pool shard, no
+    data-path collective; the oracle stands in for the kernel."""
+    import sys
+    from pathlib import Path
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import bench
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        bench.B, bench.SLOTS = 6, 12
+        hv_lo, hv_hi = rank * bench.HV // world, (rank + 1) * bench.HV // world
+        host, const, slot_sets, hl, hvl = bench.make_inputs(hv_lo, hv_hi, "cpu")
+        g = torch.Generator().manual_seed(99)
+        pool = (torch.randn(bench.SLOTS, bench.HV, D, D, generator=g) * 0.02)[:, hv_lo:hv_hi].contiguous()
+        mixed = host["mixed"]
+        q = mixed[:, :hl * D].view(bench.B, hl, D)
+        k = mixed[:, hl * D:2 * hl * D].view(bench.B, hl, D)
+        v = mixed[:, 2 * hl * D:].view(bench.B, hvl, D)
+        out, state, _ = odec.klast_forward(q=q, k=k, v=v, a=host["a"], b=host["b"], A_log=const["A_log"],
+                                           dt_bias=const["dt_bias"], state=pool, slot_indices=slot_sets[0].tolist(),
+                                           lengths=[1] * bench.B, scale=D ** -0.5)
+        dist.barrier()                      # the only collective of the sharded decode: the timing barrier
+        torch.save({"out": out, "state": state, "slots": slot_sets[0]}, os.path.join(result_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_decode_head_shards_reassemble_to_the_unsharded_step(tmp_path):
+    import sys
+    from pathlib import Path
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import bench
+    world = 2
+    mp.spawn(_decode_shard_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    saved = (bench.B, bench.SLOTS)
+    try:
+        bench.B, bench.SLOTS = 6, 12
+        host, const, slot_sets, hl, hvl = bench.make_inputs(0, bench.HV, "cpu")
+        g = torch.Generator().manual_seed(99)
+        pool = torch.randn(bench.SLOTS, bench.HV, D, D, generator=g) * 0.02
+        mixed = host["mixed"]
+        q = mixed[:, :hl * D].view(bench.B, hl, D)
+        k = mixed[:, hl * D:2 * hl * D].view(bench.B, hl, D)
+        v = mixed[:, 2 * hl * D:].view(bench.B, hvl, D)
+        out, state, _ = odec.klast_forward(q=q, k=k, v=v, a=host["a"], b=host["b"], A_log=const["A_log"],
+                                           dt_bias=const["dt_bias"], state=pool, slot_indices=slot_sets[0].tolist(),
+                                           lengths=[1] * bench.B, scale=D ** -0.5)
+    finally:
+        bench.B, bench.SLOTS = saved
+    parts = [torch.load(os.path.join(tmp_path, f"rank{r}.pt")) for r in range(world)]
+    assert all(torch.equal(p["slots"], parts[0]["slots"]) for p in parts)      # every rank draws the same slot map
+    torch.testing.assert_close(torch.cat([p["out"] for p in parts], dim=1).float(), out.float(), rtol=0, atol=0)
+    torch.testing.assert_close(torch.cat([p["state"] for p in parts], dim=1), state, rtol=0, atol=0)
