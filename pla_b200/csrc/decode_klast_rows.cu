@@ -28,8 +28,7 @@ struct RowsSmem {
   alignas(16) float q[D];
   alignas(16) float k[D];
   alignas(16) float gam[D];
-  alignas(16) float red[8][D];          // [column strip][row] partial row sums
-  float part[2][4];
+  alignas(16) float red[D][8];          // [row][column strip] partial row sums
   alignas(8) uint64_t bar[QUARTERS];
 };
 
@@ -76,24 +75,28 @@ __global__ void __launch_bounds__(NT, 2) klast_rows_kernel(const pla_b200_klast_
     }
   }
 
-  // ---- the token's vectors: thread c < 128 forms channel c of q, k and the decay ----
-  float qf = 0.f, kf = 0.f, g = 1.0f;
-  if (tid < D) {
-    qf = to_f32(static_cast<const act_t*>(p.q)[tok * p.q_tok_stride + h * D + tid]);
-    kf = to_f32(static_cast<const act_t*>(p.k)[tok * p.k_tok_stride + h * D + tid]);
-    if (p.use_qk_l2norm) {
-      const float qs = warp_sum(qf * qf), ks = warp_sum(kf * kf);
-      if (lane == 0) {
-        sh.part[0][warp] = qs;
-        sh.part[1][warp] = ks;
-      }
-    }
-    if constexpr (IS_KDA) {
-      const float x = to_f32(static_cast<const act_t*>(p.a)[tok * p.a_tok_stride + hv * D + tid]) +
-                      load_any(p.dt_bias, p.dt_bias_dtype, static_cast<int64_t>(hv) * D + tid);
-      g = __expf(log_decay(x, load_any(p.A_log, p.A_log_dtype, hv), p.gate, p.softplus_beta, p.softplus_threshold,
-                           p.lower_bound));
-    }
+  // ---- the token's vectors: warp 0 forms q, warp 1 k, warp 2 the per-channel decay; four channels per lane ----
+  if (warp < 2) {
+    const act_t* src = static_cast<const act_t*>(warp == 0 ? p.q : p.k) + tok * (warp == 0 ? p.q_tok_stride : p.k_tok_stride) +
+                       h * D + lane * 4;
+    const float4 x = load4(src);
+    float r = warp == 0 ? p.scale : 1.0f;
+    if (p.use_qk_l2norm) r *= rsqrtf(warp_sum(dot4(x, x)) + 1e-6f);
+    reinterpret_cast<float4*>(warp == 0 ? sh.q : sh.k)[lane] = make_float4(x.x * r, x.y * r, x.z * r, x.w * r);
+  } else if (IS_KDA && warp == 2) {
+    const float4 x = load4(static_cast<const act_t*>(p.a) + tok * p.a_tok_stride + hv * D + lane * 4);
+    const float A_log = load_any(p.A_log, p.A_log_dtype, hv);
+    const int64_t c = static_cast<int64_t>(hv) * D + lane * 4;
+    float4 g;
+    g.x = __expf(log_decay(x.x + load_any(p.dt_bias, p.dt_bias_dtype, c + 0), A_log, p.gate, p.softplus_beta,
+                           p.softplus_threshold, p.lower_bound));
+    g.y = __expf(log_decay(x.y + load_any(p.dt_bias, p.dt_bias_dtype, c + 1), A_log, p.gate, p.softplus_beta,
+                           p.softplus_threshold, p.lower_bound));
+    g.z = __expf(log_decay(x.z + load_any(p.dt_bias, p.dt_bias_dtype, c + 2), A_log, p.gate, p.softplus_beta,
+                           p.softplus_threshold, p.lower_bound));
+    g.w = __expf(log_decay(x.w + load_any(p.dt_bias, p.dt_bias_dtype, c + 3), A_log, p.gate, p.softplus_beta,
+                           p.softplus_threshold, p.lower_bound));
+    reinterpret_cast<float4*>(sh.gam)[lane] = g;
   }
   float gs = 1.0f;
   if constexpr (!IS_KDA) {
@@ -103,18 +106,7 @@ __global__ void __launch_bounds__(NT, 2) klast_rows_kernel(const pla_b200_klast_
                           p.lower_bound));
   }
   const float beta = sigmoidf_fast(to_f32(static_cast<const act_t*>(p.b)[tok * p.b_tok_stride + hv]));
-  __syncthreads();  // norm partial sums (and the mbarrier initialisation) visible
-  if (tid < D) {
-    float qr = p.scale, kr = 1.0f;
-    if (p.use_qk_l2norm) {
-      qr *= rsqrtf((sh.part[0][0] + sh.part[0][1]) + (sh.part[0][2] + sh.part[0][3]) + 1e-6f);
-      kr = rsqrtf((sh.part[1][0] + sh.part[1][1]) + (sh.part[1][2] + sh.part[1][3]) + 1e-6f);
-    }
-    sh.q[tid] = qf * qr;
-    sh.k[tid] = kf * kr;
-    if constexpr (IS_KDA) sh.gam[tid] = g;
-  }
-  __syncthreads();  // q / k / decay vectors complete
+  __syncthreads();  // q / k / decay vectors complete, mbarriers initialised for everyone
 
   // ---- this thread's strip: rows row0 .. row0+3, channels 16 b .. 16 b + 15 ----
   const int b = lane & 7;
@@ -153,20 +145,23 @@ __global__ void __launch_bounds__(NT, 2) klast_rows_kernel(const pla_b200_klast_
       st[r][j] = s;
     }
   }
-  *reinterpret_cast<float4*>(&sh.red[b][row0]) = make_float4(pr[0], pr[1], pr[2], pr[3]);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) sh.red[row0 + r][b] = pr[r];
   if (__syncthreads_or(!landed)) {
     if (tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_WAIT_TIMEOUT);
     // let every copy land (bounded) before shared memory is released; nothing is stored
     for (int i = 0; i < QUARTERS; ++i) (void)mbar_wait(&sh.bar[i], 0);
     return;
   }
-  float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+  float dsum[4];
 #pragma unroll
-  for (int s8 = 0; s8 < 8; ++s8) {
-    const float4 x = *reinterpret_cast<const float4*>(&sh.red[s8][row0]);
-    d.x += x.x; d.y += x.y; d.z += x.z; d.w += x.w;
+  for (int r = 0; r < 4; ++r) {
+    const float4 x0 = *reinterpret_cast<const float4*>(&sh.red[row0 + r][0]);
+    const float4 x1 = *reinterpret_cast<const float4*>(&sh.red[row0 + r][4]);
+    dsum[r] = ((x0.x + x0.y) + (x0.z + x0.w)) + ((x1.x + x1.y) + (x1.z + x1.w));
   }
-  const float vn[4] = {(v4.x - d.x) * beta, (v4.y - d.y) * beta, (v4.z - d.z) * beta, (v4.w - d.w) * beta};
+  const float vn[4] = {(v4.x - dsum[0]) * beta, (v4.y - dsum[1]) * beta, (v4.z - dsum[2]) * beta,
+                       (v4.w - dsum[3]) * beta};
   __syncthreads();  // red is reused below
 
   // ---- pass 2: rank-1 update, partial sums of S q, the strip back to shared memory ----
@@ -185,7 +180,8 @@ __global__ void __launch_bounds__(NT, 2) klast_rows_kernel(const pla_b200_klast_
       reinterpret_cast<float4*>(sh.tile + (row0 + r) * D)[gj] = s;
     }
   }
-  *reinterpret_cast<float4*>(&sh.red[b][row0]) = make_float4(pr[0], pr[1], pr[2], pr[3]);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) sh.red[row0 + r][b] = pr[r];
   fence_async_smem();   // in-place updates -> visible to the bulk-copy engine
   __syncthreads();
   if (tid == 0) {
@@ -195,9 +191,9 @@ __global__ void __launch_bounds__(NT, 2) klast_rows_kernel(const pla_b200_klast_
     bulk_commit();
   }
   if (tid < D) {
-    float o = 0.0f;
-#pragma unroll
-    for (int s8 = 0; s8 < 8; ++s8) o += sh.red[s8][tid];
+    const float4 x0 = *reinterpret_cast<const float4*>(&sh.red[tid][0]);
+    const float4 x1 = *reinterpret_cast<const float4*>(&sh.red[tid][4]);
+    const float o = ((x0.x + x0.y) + (x0.z + x0.w)) + ((x1.x + x1.y) + (x1.z + x1.w));
     if (p.o_f32 != nullptr) p.o_f32[(tok * p.HV + hv) * D + tid] = o;
     else orow[tid] = from_f32<act_t>(o);
   }

@@ -173,6 +173,11 @@ void decode_k_last(const at::Tensor& A_log, const at::Tensor& a, const at::Tenso
     g.parents_tok_stride = parents->stride(1);
   }
 
+  if (sanity_check()) {
+    std::string bad = cu_seqlens.has_value() ? sanity_offsets(*cu_seqlens, tokens, t_max) : std::string();
+    if (bad.empty()) bad = sanity_slots(state_indices, sv.slots);
+    TORCH_CHECK(bad.empty(), "fused_sigmoid_gating_delta_rule_forward_k_last: sanity check: ", bad);
+  }
   const bool mtp = t_max > 1 || disable_state_update || target_verify;
   // dt_bias: activation dtype for plain decode; fp32 for KDA verify
   // (src/decode/k-last/fused_sigmoid_gating_cuda_k_last.cpp:201-217).
@@ -199,7 +204,7 @@ void decode_k_last(const at::Tensor& A_log, const at::Tensor& a, const at::Tenso
   g.pad = is_sglang ? PLA_B200_PAD_SGLANG : PLA_B200_PAD_VLLM;
   g.rows_per_cta = static_cast<int32_t>(rows_per_cta);
   g.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
-  check_abi(pla_b200_decode_klast(&g, stream_of(q)), "fused_sigmoid_gating_delta_rule_forward_k_last");
+  if (!bypass_exec()) check_abi(pla_b200_decode_klast(&g, stream_of(q)), "fused_sigmoid_gating_delta_rule_forward_k_last");
 }
 
 void decode_k_last_packed(const at::Tensor& mixed_qkv, const at::Tensor& a, const at::Tensor& b,
@@ -264,7 +269,7 @@ void decode_k_last_packed(const at::Tensor& mixed_qkv, const at::Tensor& a, cons
   g.pad = is_sglang ? PLA_B200_PAD_SGLANG : PLA_B200_PAD_VLLM;
   g.rows_per_cta = static_cast<int32_t>(rows_per_cta);
   g.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
-  check_abi(pla_b200_decode_klast(&g, stream_of(mixed_qkv)), "fused_sigmoid_gating_delta_rule_forward_k_last_packed");
+  if (!bypass_exec()) check_abi(pla_b200_decode_klast(&g, stream_of(mixed_qkv)), "fused_sigmoid_gating_delta_rule_forward_k_last_packed");
 }
 
 void decode_v_last(const at::Tensor& A_log, const at::Tensor& a, const at::Tensor& dt_bias, double softplus_beta,
@@ -331,7 +336,7 @@ void decode_v_last(const at::Tensor& A_log, const at::Tensor& a, const at::Tenso
   g.softplus_threshold = static_cast<float>(softplus_threshold);
   g.use_qk_l2norm = use_qk_l2norm;
   g.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
-  check_abi(pla_b200_decode_vlast(&g, stream_of(q)), "fused_sigmoid_gating_delta_rule_forward (v-last)");
+  if (!bypass_exec()) check_abi(pla_b200_decode_vlast(&g, stream_of(q)), "fused_sigmoid_gating_delta_rule_forward (v-last)");
 }
 
 // vLLM-signature KDA adapter (src/decode/k-last/fused_recurrent_kda.cpp:146-314): flattens the raw
@@ -458,7 +463,7 @@ void kda_decode_mega(const at::Tensor& x, const at::Tensor& weight, const std::o
   g.lower_bound = static_cast<float>(lower_bound.value_or(0.0));
   g.scale = 1.0f / std::sqrt(128.0f);
   g.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
-  check_abi(pla_b200_kda_decode_mega(&g, stream_of(x)), "fused_kda_decode_mega_forward");
+  if (!bypass_exec()) check_abi(pla_b200_kda_decode_mega(&g, stream_of(x)), "fused_kda_decode_mega_forward");
 }
 
 }  // namespace

@@ -7,7 +7,9 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
 
+#include <cstdlib>
 #include <optional>
+#include <string>
 
 #include "pla_b200.h"
 
@@ -28,6 +30,51 @@ inline void* stream_of(const at::Tensor& t) {
 
 inline void check_abi(int rc, const char* op) {
   TORCH_CHECK(rc == PLA_B200_OK, op, ": ", pla_b200_last_error());
+}
+
+// PLA_BYPASS_EXEC=1 (read once): every op validates its arguments and returns without launching, to
+// measure a serving stack's host overhead (src/bypass_exec.h of the reference).
+inline bool bypass_exec() {
+  static const bool on = [] {
+    const char* v = std::getenv("PLA_BYPASS_EXEC");
+    return v != nullptr && v[0] != '\0' && !(v[0] == '0' && v[1] == '\0');
+  }();
+  return on;
+}
+
+// PLA_SANITY_CHECK=1 (read at every call, as in the reference: src/sanity_check.h): value-level checks of
+// the index metadata on the host. They synchronise the stream and copy to the host: a debugging aid.
+inline bool sanity_check() {
+  const char* v = std::getenv("PLA_SANITY_CHECK");
+  return v != nullptr && v[0] != '\0' && !(v[0] == '0' && v[1] == '\0');
+}
+
+// Value checks on host copies of the index metadata. They return a message (empty = fine) and the op raises
+// it from its own frame.
+// Offsets must start at 0, never decrease, and end within `tokens`; intervals longer than `t_max` (> 0) fail.
+inline std::string sanity_offsets(const at::Tensor& cu, int64_t tokens, int64_t t_max) {
+  const at::Tensor h = cu.to(at::kCPU).to(at::kLong).contiguous();
+  const int64_t* p = h.data_ptr<int64_t>();
+  const int64_t n = h.numel();
+  if (n < 1 || p[0] != 0) return "offsets must start at 0";
+  for (int64_t i = 1; i < n; ++i) {
+    if (p[i] < p[i - 1]) return "offsets decrease at entry " + std::to_string(i);
+    if (t_max > 0 && p[i] - p[i - 1] > t_max)
+      return "interval " + std::to_string(i - 1) + " is longer than " + std::to_string(t_max);
+  }
+  if (p[n - 1] > tokens) return "offsets run past the " + std::to_string(tokens) + " token rows";
+  return std::string();
+}
+
+// Slot indices must be below `slots` (negative values are padding).
+inline std::string sanity_slots(const at::Tensor& idx, int64_t slots) {
+  const at::Tensor h = idx.to(at::kCPU).to(at::kLong).contiguous();
+  const int64_t* p = h.data_ptr<int64_t>();
+  for (int64_t i = 0; i < h.numel(); ++i)
+    if (p[i] >= slots)
+      return "slot index " + std::to_string(p[i]) + " at entry " + std::to_string(i) + " is outside the pool of " +
+             std::to_string(slots);
+  return std::string();
 }
 
 inline void check_cuda(const at::Tensor& t, const char* name) {

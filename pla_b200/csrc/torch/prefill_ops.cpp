@@ -158,7 +158,7 @@ void run_recurrent(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v
     g.state_transposed = 0;
     g.o_total_rows = 0;
   }
-  check_abi(pla_b200_prefill_recurrent(&g, stream_of(q)), "prefill");
+  if (!bypass_exec()) check_abi(pla_b200_prefill_recurrent(&g, stream_of(q)), "prefill");
 }
 
 void prefill_recurrent(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& gate,
@@ -212,6 +212,11 @@ at::Tensor run_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tenso
               "cu_seqlens must be contiguous int32 [batch+1] on q's device");
   const int64_t N = cu_seqlens.numel() - 1;
   TORCH_CHECK(max_chunks >= 0 && max_chunks <= T / 64 + N, "max_chunks out of range");
+  if (sanity_check()) {
+    std::string bad = sanity_offsets(cu_seqlens, T, 0);
+    if (bad.empty() && in_indices.has_value() && state_in.has_value()) bad = sanity_slots(*in_indices, state_in->size(0));
+    TORCH_CHECK(bad.empty(), "chunked prefill: sanity check: ", bad);
+  }
   c10::cuda::CUDAGuard guard(q.device());
 
   pla_b200_gdn_chunk_args g{};
@@ -330,7 +335,7 @@ at::Tensor run_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tenso
   g.workspace = workspace.data_ptr();
   g.workspace_bytes = bytes;
   g.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
-  check_abi(is_kda ? pla_b200_kda_prefill_chunked(&g, stream_of(q)) : pla_b200_gdn_prefill_chunked(&g, stream_of(q)),
+  if (!bypass_exec()) check_abi(is_kda ? pla_b200_kda_prefill_chunked(&g, stream_of(q)) : pla_b200_gdn_prefill_chunked(&g, stream_of(q)),
             is_kda ? "kda chunked prefill" : "gdn chunked prefill");
   return workspace;
 }
@@ -384,7 +389,7 @@ at::Tensor cp_fold_prefix(const at::Tensor& pairs, const Optional& initial_state
   f.rank = static_cast<int32_t>(rank);
   f.world = static_cast<int32_t>(world);
   f.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
-  check_abi(pla_b200_cp_fold_prefix(&f, stream_of(pairs)), "cp fold");
+  if (!bypass_exec()) check_abi(pla_b200_cp_fold_prefix(&f, stream_of(pairs)), "cp fold");
   return out;
 }
 

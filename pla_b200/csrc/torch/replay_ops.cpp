@@ -194,7 +194,7 @@ void verify(const at::Tensor& x, const at::Tensor& g, const at::Tensor& beta, co
   v.softplus_beta = 1.0f;
   v.softplus_threshold = 20.0f;
   v.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
-  check_abi(pla_b200_kda_replay_verify(&v, stream_of(state)), "kda_replay_verify");
+  if (!bypass_exec()) check_abi(pla_b200_kda_replay_verify(&v, stream_of(state)), "kda_replay_verify");
 }
 
 void commit(const at::Tensor& table, at::Tensor candidate, at::Tensor plan, const at::Tensor& sampled,
@@ -263,7 +263,7 @@ void commit(const at::Tensor& table, at::Tensor candidate, at::Tensor plan, cons
   c.token_capacity = token_capacity;
   c.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
   void* stream = static_cast<void*>(c10::cuda::getCurrentCUDAStream(table.device().index()).stream());
-  check_abi(plan_only ? pla_b200_kda_replay_plan(&c, stream) : pla_b200_kda_replay_commit(&c, stream),
+  if (!bypass_exec()) check_abi(plan_only ? pla_b200_kda_replay_plan(&c, stream) : pla_b200_kda_replay_commit(&c, stream),
             "kda_replay_commit");
 }
 
@@ -420,7 +420,7 @@ void ring_verify(const at::Tensor& x_q, const at::Tensor& x_k, const at::Tensor&
     v.onorm_eps = static_cast<float>(*onorm_eps);
     v.out_f32 = staging.data_ptr<float>();
   }
-  check_abi(pla_b200_kda_ring_verify(&v, stream_of(x_q)), "verify_dspark");
+  if (!bypass_exec()) check_abi(pla_b200_kda_ring_verify(&v, stream_of(x_q)), "verify_dspark");
 }
 
 void fold_all_layers(at::Tensor h0, const at::Tensor& rawv, const at::Tensor& rawk, const at::Tensor& gk,
@@ -494,7 +494,7 @@ void fold_all_layers(at::Tensor h0, const at::Tensor& rawv, const at::Tensor& ra
   f.slots = static_cast<int32_t>(slots);
   f.null_block_id = static_cast<int32_t>(null_block_id);
   f.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
-  check_abi(pla_b200_kda_fold_layers(&f, stream_of(h0)), "fold_all_layers");
+  if (!bypass_exec()) check_abi(pla_b200_kda_fold_layers(&f, stream_of(h0)), "fold_all_layers");
 }
 
 void conv_window_scatter(at::Tensor dst, const at::Tensor& src, const at::Tensor& dst_idx, const at::Tensor& step_idx) {
@@ -538,7 +538,7 @@ void conv_window_scatter(at::Tensor dst, const at::Tensor& src, const at::Tensor
   c.src_rows = static_cast<int32_t>(src.size(1));
   c.src_steps = static_cast<int32_t>(src.size(2));
   c.dst_slots = static_cast<int32_t>(dst.size(1));
-  check_abi(pla_b200_kda_conv_scatter(&c, stream_of(dst)), "conv_window_scatter");
+  if (!bypass_exec()) check_abi(pla_b200_kda_conv_scatter(&c, stream_of(dst)), "conv_window_scatter");
 }
 
 }  // namespace
