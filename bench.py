@@ -452,7 +452,21 @@ def run_prefill_cp(args):
     mine = [x[sl] for x in (q, k, v, gate, beta)]
     steps = min(args.steps, 5) if (kda and args.kda_backend == "recurrent") else args.steps
 
+    ranges_on_one_gpu = world == 1 and not kda
+    if ranges_on_one_gpu:
+        # one GPU: the same prescan / fold / segment scheme over token ranges inside the GPU, through the facade
+        from pla_b200.prefill.flashqla import ops as fq
+        pool1 = S0[None].clone()
+        slot0 = torch.zeros(1, dtype=torch.int32, device=dev)
+        cu1 = torch.tensor([0, T], dtype=torch.int32, device=dev)
+
     def step():
+        if ranges_on_one_gpu:
+            res = fq.chunk_gated_delta_rule_fwd(q[None], k[None], v[None], None, None, initial_state=pool1,
+                                                initial_state_indices=slot0, cu_seqlens=cu1, output_final_state=False,
+                                                auto_cp=True, normalize_qk=True, raw_cu_seqlens=(0, T), raw_gate_a=gate,
+                                                raw_beta_b=beta, A_log=A_log, dt_bias=dt_bias)
+            return res[2][0], pool1[0]
         if kda:
             return kda_prefill_context_parallel(*mine, A_log, dt_bias, None, initial_state=S0, backend=args.kda_backend)
         return gdn_prefill_context_parallel(*mine, A_log, dt_bias, initial_state=S0)
@@ -470,6 +484,9 @@ def run_prefill_cp(args):
     ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms = float(ms.item())
+    if ranges_on_one_gpu:
+        pool1.copy_(S0[None])             # the pool is updated in place: restart from S0 for the comparison
+        o, final = step()
     if rank == 0:
         # the same kernels in a single pass over the whole sequence, for comparison
         one = torch.empty(T, H, D, dtype=torch.bfloat16, device=dev)
@@ -495,8 +512,10 @@ def run_prefill_cp(args):
                           "value": round(T / ms / 1e3, 3),
                           "unit": "Mtok/s", "n_gpus": world, "steps": steps, "ms_per_step": round(ms, 4),
                           "higher_is_better": True, "scaling": "strong", "dtype": "f32", "data": "synthetic",
-                          "config": {"workload": f"{what}, {per} tokens per rank, one all-gather of "
-                                                 f"[{H},2,128,128] fp32 per rank",
+                          "config": {"workload": (f"{what}, {len(fq.plan_token_ranges([0, T], H, 148)[2])} token ranges "
+                                                  "inside the GPU (prescan, fold, segment pass)") if ranges_on_one_gpu else
+                                                 (f"{what}, {per} tokens per rank, one all-gather of "
+                                                  f"[{H},2,128,128] fp32 per rank"),
                                      "out_rel_l2_vs_single_pass": rel(o, one[lo:hi]),
                                      "state_rel_l2_vs_single_pass": rel(final, fin[0]),
                                      "status": int(status.item())}}), flush=True)

@@ -210,7 +210,8 @@ typedef struct pla_b200_gdn_chunk_args {
   int64_t state_slot_stride;
   int64_t num_slots;
   const int32_t* slot_indices;
-  void* state_out;            /* NULL: final state goes back into `state` (when write_state) */
+  void* state_out;            /* NULL: final state goes back into `state` (when write_state); with
+                                 state_out_indices, a negative index skips that sequence's final state */
   int64_t state_out_slot_stride;
   const int32_t* state_out_indices;
   int32_t write_state;
@@ -263,6 +264,23 @@ typedef struct pla_b200_cp_fold_args {
 } pla_b200_cp_fold_args;
 
 int pla_b200_cp_fold_prefix(const pla_b200_cp_fold_args* args, void* stream);
+
+/* The same fold inside one GPU: long sequences cut into consecutive token ranges that run as independent
+ * chains (the reference's intra-card split, pla/prefill/flashqla/private/cp_preprocess.py). Range j of
+ * sequence s (ranges seg_first[s] .. seg_first[s+1]-1, in token order) starts from
+ *   state_in[seg_first[s]] = the sequence's pool state (or zero),  state_in[j+1] = state_in[j] M_j + B_j. */
+typedef struct pla_b200_cp_fold_segments_args {
+  const float* pairs;          /* [ranges, HV, 2, 128, 128] from a prescan over the ranges (last range of a sequence unused) */
+  const int32_t* seg_first;    /* device [sequences + 1] */
+  const float* pool;           /* fp32 k-last pool [slots, HV, 128, 128] or NULL (zero initial states) */
+  int64_t pool_slot_stride;
+  const int32_t* slot_indices; /* device [sequences] or NULL (= sequence index); a negative slot starts from zero */
+  float* state_in;             /* out: [ranges, HV, 128, 128] */
+  int32_t HV, sequences, slots;
+  int32_t* status;
+} pla_b200_cp_fold_segments_args;
+
+int pla_b200_cp_fold_segments(const pla_b200_cp_fold_segments_args* args, void* stream);
 
 /* ======================================================================== *
  * KDA ReplaySSM: verify (read-only checkpoint, replay records out) and commit

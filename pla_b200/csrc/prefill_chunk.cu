@@ -841,6 +841,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
 
   int slot = seq;
   if (p.slot_indices != nullptr && !prescan) slot = p.slot_indices[seq];
+  if (prescan && p.slot_indices != nullptr && p.slot_indices[seq] < 0) return;   // pair of this range not wanted
   act_t* o_col = static_cast<act_t*>(p.o) + static_cast<int64_t>(hv) * D;  // + tok*HV*D + v
   if (!prescan && p.slot_indices != nullptr && (slot < 0 || (p.num_slots > 0 && slot >= p.num_slots))) {
     if (slot >= 0 && tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_BAD_SLOT);
@@ -1164,14 +1165,16 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
     } else if (ok && p.write_state) {
       void* dst = p.state;
       int64_t base = static_cast<int64_t>(slot) * p.state_slot_stride;
+      bool store = true;
       if (p.state_out != nullptr) {
         const int64_t oslot = p.state_out_indices != nullptr ? p.state_out_indices[seq] : seq;
+        store = oslot >= 0;                  // a negative destination: this chain's final state is not wanted
         dst = p.state_out;
         base = oslot * p.state_out_slot_stride;
       }
       base += static_cast<int64_t>(hv) * TILE;
 #pragma unroll 1
-      for (int q4 = 2 * wg; q4 < 2 * wg + 2; ++q4) {
+      for (int q4 = 2 * wg; store && q4 < 2 * wg + 2; ++q4) {
         float s[32];
         tc05::tmem_ld32(tS + q4 * 32, s);
         tc05::wait_ld();

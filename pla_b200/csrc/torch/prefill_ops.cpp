@@ -192,7 +192,8 @@ at::Tensor run_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tenso
                        const Optional& in_indices, const Optional& state_out, const Optional& out_indices,
                        bool transposed, bool normalize_qk, double scale, bool gate_activated, bool update_in_place,
                        int64_t max_chunks, int64_t stage, const Optional& status, const Optional& workspace_in,
-                       bool prescan, bool is_kda = false, std::optional<double> lower_bound = std::nullopt) {
+                       bool prescan, bool is_kda = false, std::optional<double> lower_bound = std::nullopt,
+                       const Optional& range_mask = std::nullopt) {
   check_cuda(q, "q");
   const int64_t T = q.size(0);
   TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3, "q, k, v must be [tokens, heads, 128]");
@@ -289,6 +290,12 @@ at::Tensor run_chunked(const at::Tensor& q, const at::Tensor& k, const at::Tenso
                 "a prescan stores contiguous fp32 [batch, H, 2, 128, 128] on q's device");
     g.state_out = state_out->data_ptr();
     g.prescan = 1;
+    if (range_mask.has_value()) {   // ranges with a negative entry are skipped by the prescan
+      TORCH_CHECK(range_mask->scalar_type() == at::kInt && range_mask->is_contiguous() && range_mask->numel() == N &&
+                      range_mask->device() == q.device(),
+                  "the range mask must be contiguous int32 [batch] on q's device");
+      g.slot_indices = range_mask->data_ptr<int32_t>();
+    }
   } else if (state_out.has_value()) {
     state_ok(*state_out, H, q, "final state");
     if (state_in.has_value())
@@ -361,10 +368,48 @@ at::Tensor gdn_prefill_chunked_stage(const at::Tensor& q, const at::Tensor& k, c
                                      const at::Tensor& cu_seqlens, const Optional& state_in, const Optional& state_out,
                                      const Optional& workspace, bool transposed, bool normalize_qk, double scale,
                                      bool gate_activated, int64_t max_chunks, int64_t stage, bool prescan,
-                                     const Optional& status) {
+                                     const Optional& status, const Optional& range_mask, const Optional& out_indices) {
   return run_chunked(q, k, v, gate, beta, A_log, dt_bias, out, g_cum, cu_seqlens, state_in, c10::nullopt, state_out,
-                     c10::nullopt, transposed, normalize_qk, scale, gate_activated, false, max_chunks, stage, status,
-                     workspace, prescan);
+                     out_indices, transposed, normalize_qk, scale, gate_activated, false, max_chunks, stage, status,
+                     workspace, prescan, false, std::nullopt, range_mask);
+}
+
+// Incoming state of every token range of every sequence from the prescan pairs (intra-GPU split).
+at::Tensor cp_fold_segments(const at::Tensor& pairs, const at::Tensor& seg_first, const Optional& pool,
+                            const Optional& slot_indices, const Optional& status) {
+  check_cuda(pairs, "pairs");
+  TORCH_CHECK(pairs.scalar_type() == at::kFloat && pairs.is_contiguous() && pairs.dim() == 5 && pairs.size(2) == 2 &&
+                  pairs.size(3) == 128 && pairs.size(4) == 128,
+              "pairs must be contiguous fp32 [ranges, H, 2, 128, 128]");
+  const int64_t ranges = pairs.size(0), H = pairs.size(1);
+  TORCH_CHECK(seg_first.scalar_type() == at::kInt && seg_first.is_contiguous() && seg_first.dim() == 1 &&
+                  seg_first.numel() >= 1 && seg_first.device() == pairs.device(),
+              "seg_first must be contiguous int32 [sequences + 1] on the pairs' device");
+  const int64_t sequences = seg_first.numel() - 1;
+  c10::cuda::CUDAGuard guard(pairs.device());
+  at::Tensor out = at::empty({ranges, H, 128, 128}, pairs.options());
+  pla_b200_cp_fold_segments_args f{};
+  f.pairs = pairs.data_ptr<float>();
+  f.seg_first = seg_first.data_ptr<int32_t>();
+  if (pool.has_value()) {
+    state_ok(*pool, H, pairs, "state pool");
+    TORCH_CHECK(pool->scalar_type() == at::kFloat, "the intra-GPU split reads an fp32 pool");
+    f.pool = pool->data_ptr<float>();
+    f.pool_slot_stride = pool->stride(0);
+    f.slots = static_cast<int32_t>(pool->size(0));
+  }
+  if (slot_indices.has_value()) {
+    TORCH_CHECK(slot_indices->scalar_type() == at::kInt && slot_indices->is_contiguous() &&
+                    slot_indices->numel() == sequences && slot_indices->device() == pairs.device(),
+                "slot indices must be contiguous int32 [sequences] on the pairs' device");
+    f.slot_indices = slot_indices->data_ptr<int32_t>();
+  }
+  f.state_in = out.data_ptr<float>();
+  f.HV = static_cast<int32_t>(H);
+  f.sequences = static_cast<int32_t>(sequences);
+  f.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
+  if (!bypass_exec()) check_abi(pla_b200_cp_fold_segments(&f, stream_of(pairs)), "cp fold segments");
+  return out;
 }
 
 // Fold of the gathered (offset, transition) pairs of the ranks before `rank` into the state entering its range.
@@ -429,8 +474,10 @@ TORCH_LIBRARY_FRAGMENT(pla_b200, m) {
       "gdn_prefill_chunked_stage(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor? A_log, "
       "Tensor? dt_bias, Tensor(a!) out, Tensor(e!)? g_cum, Tensor cu_seqlens, Tensor? state_in, Tensor(c!)? state_out, "
       "Tensor(w!)? workspace, bool transposed, bool normalize_qk, float scale, bool gate_activated, int max_chunks, "
-      "int stage, bool prescan, Tensor(d!)? status) -> Tensor",
+      "int stage, bool prescan, Tensor(d!)? status, Tensor? range_mask, Tensor? out_indices) -> Tensor",
       &pla_ops::gdn_prefill_chunked_stage);
+  m.def("cp_fold_segments(Tensor pairs, Tensor seg_first, Tensor? pool, Tensor? slot_indices, Tensor(a!)? status) -> Tensor",
+        &pla_ops::cp_fold_segments);
   m.def(
       "prefill_recurrent_prescan(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor? A_log, "
       "Tensor? dt_bias, Tensor cu_seqlens, Tensor(a!) pairs, bool is_kda, bool normalize_qk, float scale, "

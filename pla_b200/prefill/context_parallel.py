@@ -49,7 +49,7 @@ class CudaSegmentKernels:
         q, k, v, gate, beta, A_log, dt_bias = self.a
         self.ws = self._ops.gdn_prefill_chunked_stage(
             q, k, v, gate, beta, A_log, dt_bias, self.out, None, self.cu, state_in, state_out, self.ws, False,
-            self.normalize_qk, self.scale, self.gate_activated, self.max_chunks, stage, prescan, self.status)
+            self.normalize_qk, self.scale, self.gate_activated, self.max_chunks, stage, prescan, self.status, None, None)
 
     def prepare(self):
         self._stage(1, False, None, None)

@@ -42,6 +42,75 @@ def _offsets(cu_seqlens, num_tokens, raw_cu_seqlens, device):
     return cu32
 
 
+_plan_cache: "OrderedDict" = None  # type: ignore[assignment]
+
+
+def plan_token_ranges(offsets: Sequence[int], heads: int, n_sm: int, min_chunks: int = 16):
+    """Intra-GPU split of long sequences into consecutive token ranges that run as independent chains
+    (the job of the reference's planner, pla/prefill/flashqla/private/cp_preprocess.py). Pure host code.
+
+    A (sequence, value head) chain is serial, so a batch with fewer chains than SMs leaves SMs idle. Cutting
+    every sequence into ``p`` ranges costs a prescan of the first ``p - 1`` ranges (two chains each) plus the
+    ranges themselves, i.e. ``(waves(2 (p-1) n) + waves(p n)) / p`` of the unsplit time per wave, ``n`` = chains
+    of the batch, ``waves(x) = ceil(x / n_sm)``; ``p`` grows while that lowers the cost by 10 % or more, and the split is used when
+    it saves at least 20 %. Ranges are cut on chunk boundaries counted from the sequence start and are at least
+    ``min_chunks`` chunks long. Returns ``(range_offsets, seg_first, last_flags, seq_of_range)`` or ``None``
+    when nothing is split."""
+    lens = [int(b) - int(a) for a, b in zip(offsets, offsets[1:])]
+    live = sum(1 for n in lens if n > 0)
+    if live == 0:
+        return None
+    n = live * heads
+    waves = lambda x: -(-x // n_sm)
+    most = max((m + CHUNK_SIZE - 1) // CHUNK_SIZE for m in lens) // min_chunks
+    best, target = float(waves(n)), 1
+    for p in range(2, max(2, min(most, 64)) + 1):
+        cost = (waves(2 * (p - 1) * n) + waves(p * n)) / p
+        if cost < 0.9 * best:                     # more ranges only for a clear gain: each adds a fold and a prologue
+            best, target = cost, p
+    if best > 0.8 * waves(n):
+        return None
+    range_offsets, seg_first, last, seq_of = [int(offsets[0])], [0], [], []
+    split = False
+    for s, n in enumerate(lens):
+        chunks = (n + CHUNK_SIZE - 1) // CHUNK_SIZE
+        parts = max(1, min(target, chunks // min_chunks))
+        split |= parts > 1
+        start = int(offsets[s])
+        for part in range(parts):
+            end_chunk = chunks * (part + 1) // parts
+            end = start + n if part == parts - 1 else start + end_chunk * CHUNK_SIZE
+            range_offsets.append(end)
+            last.append(part == parts - 1)
+            seq_of.append(s)
+        seg_first.append(len(last))
+    return (range_offsets, seg_first, last, seq_of) if split else None
+
+
+def _range_tensors(offsets, heads, device):
+    """Device copies of the plan, cached for the most recent offset tuples (serving repeats them)."""
+    global _plan_cache
+    from collections import OrderedDict
+    if _plan_cache is None:
+        _plan_cache = OrderedDict()
+    key = (tuple(int(x) for x in offsets), heads, str(device))
+    hit = _plan_cache.get(key)
+    if hit is not None:
+        _plan_cache.move_to_end(key)
+        return hit
+    n_sm = torch.cuda.get_device_properties(device).multi_processor_count
+    plan = plan_token_ranges(key[0], heads, n_sm)
+    if plan is not None:
+        range_offsets, seg_first, last, seq_of = plan
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
+        plan = (i32(range_offsets), i32(seg_first), i32([-1 if f else 0 for f in last]),
+                torch.tensor(last, dtype=torch.bool, device=device), torch.tensor(seq_of, dtype=torch.long, device=device))
+    _plan_cache[key] = plan
+    while len(_plan_cache) > 8:
+        _plan_cache.popitem(last=False)
+    return plan
+
+
 def chunk_gated_delta_rule_fwd(
     q: torch.Tensor,                       # [1, T, Hg, DK]
     k: torch.Tensor,                       # [1, T, Hg, DK]
@@ -72,9 +141,12 @@ def chunk_gated_delta_rule_fwd(
     Evaluated chunk-wise (chunk 64, WY/UT transform) on the tensor cores. ``g_cum`` is the
     chunk-local cumulative log decay ``[1, T, H]`` fp32 at chunk size 64 (the reference uses 32);
     the reference's ``A`` by-product is not materialised in its layout and is returned as
-    ``None`` (nothing downstream of inference reads it); ``auto_cp``,
-    ``overlap_warmup_threshold`` and ``force_tc01_cp_candidate`` tune the reference's intra-card
-    planner and are accepted and ignored.
+    ``None`` (nothing downstream of inference reads it). ``auto_cp`` (default on): with host offsets
+    (``raw_cu_seqlens``) and an indexed fp32 pool, batches with fewer (sequence, head) chains than SMs have
+    their long sequences cut into token ranges that run as independent chains (prescan of every range,
+    fold of the (offset, transition) pairs, then the ranges in parallel from their incoming states); a
+    negative slot index then means "start from zero, drop the final state". ``overlap_warmup_threshold`` and
+    ``force_tc01_cp_candidate`` tune the reference's planner and are accepted and ignored.
     """
     if not q.is_cuda:
         raise ValueError("q must be a CUDA tensor")
@@ -136,6 +208,25 @@ def chunk_gated_delta_rule_fwd(
     else:
         max_chunks = T // CHUNK_SIZE + batch
     g_cum = torch.zeros((1, T, H), dtype=torch.float32, device=q.device)
+    plan = None
+    if auto_cp and raw_cu_seqlens is not None and indexed and initial_state.dtype == torch.float32:
+        plan = _range_tensors(offs, H, q.device)
+    if plan is not None:
+        cu_ranges, seg_first, prescan_mask, last_mask, seq_of = plan
+        n_ranges = prescan_mask.numel()
+        stage_args = (q[0], k[0], v[0], gate, bet, A_log, dt_bias, o[0])
+        tail = (False, bool(normalize_qk), float(scale), not use_raw, int(max_chunks))
+        ws = ops.gdn_prefill_chunked_stage(*stage_args, g_cum[0], cu_ranges, None, None, None, *tail, 1, False, None,
+                                           None, None)
+        pairs = torch.empty((n_ranges, H, 2, DV, DK), dtype=torch.float32, device=q.device)
+        ops.gdn_prefill_chunked_stage(*stage_args, None, cu_ranges, None, pairs, ws, *tail, 2, True, None,
+                                      prescan_mask, None)
+        state_in = ops.cp_fold_segments(pairs, seg_first, initial_state, initial_state_indices, None)
+        out_idx = torch.where(last_mask, initial_state_indices[seq_of], torch.full_like(prescan_mask, -1))
+        ops.gdn_prefill_chunked_stage(*stage_args, None, cu_ranges, state_in, initial_state, ws, *tail, 2, False, None,
+                                      None, out_idx)
+        final_state = initial_state[initial_state_indices.long()] if output_final_state else None
+        return g_cum, None, o, None, final_state
     ops.gdn_prefill_chunked(
         q[0], k[0], v[0], gate, bet, A_log, dt_bias, o[0], g_cum[0], cu32, initial_state,
         initial_state_indices if indexed else None, state_out, None, not indexed, bool(normalize_qk),

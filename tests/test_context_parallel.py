@@ -139,3 +139,24 @@ def test_decode_head_shards_reassemble_to_the_unsharded_step(tmp_path):
     assert all(torch.equal(p["slots"], parts[0]["slots"]) for p in parts)      # every rank draws the same slot map
     torch.testing.assert_close(torch.cat([p["out"] for p in parts], dim=1).float(), out.float(), rtol=0, atol=0)
     torch.testing.assert_close(torch.cat([p["state"] for p in parts], dim=1), state, rtol=0, atol=0)
+
+
+def test_token_range_plan_properties():
+    """The host planner: ranges tile every sequence in order, cut on 64-token chunk boundaries counted from the
+    sequence start, at least 16 chunks long, never more chains than SMs, nothing split when SMs are busy."""
+    import importlib
+    fq = importlib.import_module("pla_b200.prefill.flashqla.ops")
+    assert fq.plan_token_ranges([0, 4000, 8000], 32, 148) is None           # 64 chains: two ranges each would not pay
+    offs = [0, 65536]
+    ranges, seg_first, last, seq_of = fq.plan_token_ranges(offs, 24, 148)   # 24 chains: four ranges halve the time
+    assert seg_first == [0, 4] and last == [False] * 3 + [True] and ranges[0] == 0 and ranges[-1] == 65536
+    assert all((b - a) % 64 == 0 and b - a >= 16 * 64 for a, b in zip(ranges, ranges[1:]))
+    offs = [0, 3000, 3000, 9001, 9100]
+    ranges, seg_first, last, seq_of = fq.plan_token_ranges(offs, 4, 148)
+    assert len(seg_first) == len(offs) and seg_first[-1] == len(last) == len(seq_of)
+    for s in range(len(offs) - 1):
+        mine = ranges[seg_first[s]:seg_first[s + 1] + 1]
+        assert mine[0] == offs[s] and mine[-1] == offs[s + 1] and mine == sorted(mine)
+        assert all((x - offs[s]) % 64 == 0 for x in mine[1:-1])
+        assert last[seg_first[s]:seg_first[s + 1]] == [False] * (seg_first[s + 1] - seg_first[s] - 1) + [True]
+    assert len(last) * 4 <= 2 * 148

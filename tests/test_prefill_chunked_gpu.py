@@ -250,3 +250,52 @@ def test_chunked_prefill_head_groups_and_fp16(native_built, dtype, Hg, H):
     assert_state_close(dpool.cpu(), exp_state)
     untouched = [s for s in range(5) if s not in slots]
     assert torch.equal(dpool[untouched].cpu(), pool[untouched])
+
+
+@pytest.mark.parametrize("weak_decay", [False, True])
+def test_intra_gpu_token_ranges_match_single_chains(native_built, weak_decay):
+    """auto_cp: long sequences cut into token ranges (prescan, fold, parallel ranges) against the same
+    sequences run as single chains and against the oracle; pool updated in place either way. With weak decay
+    and small beta the transition of a 1088-token range stays of order one, so the incoming state of the later
+    ranges depends on the folded transitions and not only on the offsets."""
+    from pla_b200.prefill.flashqla import ops as fq
+    g = torch.Generator().manual_seed(17)
+    Hg, H = 1, 2
+    lengths = [3300, 0, 1300, 70]
+    T = sum(lengths)
+    offs = [0]
+    for n in lengths:
+        offs.append(offs[-1] + n)
+    plan = fq.plan_token_ranges(offs, H, 148)
+    assert plan is not None and plan[1][1] > 1 and plan[1][-1] == len(plan[2])   # the 3300-token sequence becomes three ranges
+    q, k, v = (torch.randn(1, T, n, D, generator=g).bfloat16() for n in (Hg, Hg, H))
+    gates = torch.randn(T, 2 * H, generator=g)
+    A_log = torch.rand(H, generator=g) * float(np.log(16.0))
+    if weak_decay:
+        gates[:, H:] -= 4.0
+        A_log = -8.0 + torch.rand(H, generator=g)
+    gates = gates.bfloat16()
+    dt_bias = torch.randn(H, generator=g) * 0.1
+    pool = torch.randn(6, H, D, D, generator=g) * (0.5 if weak_decay else 0.05)
+    slots = [4, 0, 2, 5]
+    exp_out, exp_state, _ = odec.klast_forward(q=q[0], k=k[0], v=v[0], a=gates[:, :H], b=gates[:, H:], A_log=A_log,
+                                               dt_bias=dt_bias, state=pool, slot_indices=slots, lengths=lengths,
+                                               scale=D ** -0.5)
+    dev = "cuda"
+    results = {}
+    for auto_cp in (False, True):
+        dpool = pool.to(dev)
+        dg = gates.to(dev)
+        res = fq.chunk_gated_delta_rule_fwd(
+            q.to(dev), k.to(dev), v.to(dev), None, None, initial_state=dpool,
+            initial_state_indices=torch.tensor(slots, dtype=torch.int32, device=dev),
+            cu_seqlens=torch.tensor(offs, dtype=torch.int32, device=dev), output_final_state=True, auto_cp=auto_cp,
+            normalize_qk=True, raw_cu_seqlens=tuple(offs), raw_gate_a=dg[:, :H], raw_beta_b=dg[:, H:],
+            A_log=A_log.to(dev), dt_bias=dt_bias.to(dev))
+        torch.cuda.synchronize()
+        results[auto_cp] = (res[2][0].cpu(), dpool.cpu(), res[4].cpu(), res[0].cpu())
+        assert_out_close(res[2][0], exp_out, f"auto_cp={auto_cp}")
+        assert_state_close(dpool.cpu(), exp_state, f"auto_cp={auto_cp}")
+        assert torch.equal(res[4].cpu(), dpool.cpu()[slots])
+    assert torch.equal(results[True][3], results[False][3])                  # g_cum is the same by-product
+    assert_out_close(results[True][0], results[False][0], "ranges vs single chains")
