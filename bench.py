@@ -560,6 +560,39 @@ def run_vlast(args):
           flush=True)
 
 
+def run_conv(args):
+    """Secondary line: the causal conv in front of config 3's prefill (8 sequences, ~32K token rows of the packed
+    q|k|v width 8192, bf16), history pool of 64 slots; algorithmic bytes = one read and one write of every row."""
+    from pla_b200.prefill.causal_conv import causal_conv1d_fn
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(SEED + 3)
+    lengths = torch.randint(512, 8193, (8,), generator=g).tolist()
+    T, C = sum(lengths), 8192
+    offs = [0]
+    for n in lengths:
+        offs.append(offs[-1] + n)
+    x = torch.randn(T, C, generator=g).bfloat16().to(dev)
+    w = (torch.randn(C, 4, generator=g) * 0.2).to(dev)
+    state = torch.zeros(64, 3, C, dtype=torch.bfloat16, device=dev).transpose(1, 2)
+    idx = torch.randperm(64, generator=g)[:8].to(torch.int32).to(dev)
+    cu = torch.tensor(offs, dtype=torch.int32, device=dev)
+    y = torch.empty_like(x)
+
+    def step():
+        causal_conv1d_fn(x, w, None, state, cu, idx, None, "silu", out=y)
+
+    ms = _time_steps(step, args.steps, max(args.warmup, 3))
+    gbs = 2 * T * C * 2 / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": "causal_conv_prefill_bandwidth", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": 1,
+                      "steps": args.steps, "ms_per_step": round(ms, 5), "higher_is_better": True, "dtype": "f32",
+                      "data": "synthetic",
+                      "config": {"workload": f"causal conv (width 4, SiLU) in front of config3: 8 sequences {lengths}, "
+                                             f"T={T}, {C} channels bf16, 1.3 GB touched per step (> L2)"},
+                      "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": measured_peaks()[0], "unit": "GB/s",
+                                   "frac": round(gbs / measured_peaks()[0], 4),
+                                   "peak_source": "of " + measured_peaks()[1]}}), flush=True)
+
+
 def run_replay(args):
     """Secondary line: config 2, KDA ReplaySSM verify + commit, 32 heads, 64 rows x 4 tokens, 512 pages."""
     import numpy as np
@@ -601,7 +634,7 @@ def run_replay(args):
 def main():
     global B, SLOTS, WORKLOAD
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="decode", choices=["decode", "decode_vlast", "prefill", "prefill_cp", "prefill_cp_kda", "replay"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "decode_vlast", "prefill", "prefill_cp", "prefill_cp_kda", "replay", "conv"],
                     help="decode = the headline metric; prefill / replay print secondary lines (1 GPU)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
@@ -627,7 +660,7 @@ def main():
     if args.workload != "decode":
         if int(os.environ.get("RANK", 0)) == 0:
             args.steps = min(args.steps, 50)
-            {"prefill": run_prefill, "replay": run_replay, "decode_vlast": run_vlast}[args.workload](args)
+            {"prefill": run_prefill, "replay": run_replay, "decode_vlast": run_vlast, "conv": run_conv}[args.workload](args)
         return
     if args.impl == "reference":
         run_reference(args)

@@ -495,6 +495,37 @@ typedef struct pla_b200_kda_mega_args {
 
 int pla_b200_kda_decode_mega(const pla_b200_kda_mega_args* args, void* stream);
 
+/* ======================================================================== *
+ * Width-4 causal conv (+ SiLU) over packed varlen token rows with a 3-tap history per request: the
+ * caller-side step that produces the packed q|k|v rows of the prefill ops (in the serving stacks a
+ * separate kernel in front of the reference's prefill; the same arithmetic as the conv inside its fused decode
+ * step, src/decode/k-last/fused_kda_decode_mega_kernel.cuh:36-79, and its verify kernels,
+ * src/decode/kda_replayssm/kda_mtp_verify.cu:356-402). y_t = act(bias + h0 w0 + h1 w1 + h2 w2 + x_t w3),
+ * (h0,h1,h2) <- (h1,h2,x_t). Rows at or past cu_seqlens[N] are written as zeros. Two launches: the conv, then
+ * the history update (last three inputs of every non-empty sequence with a writable slot).
+ * ======================================================================== */
+typedef struct pla_b200_conv_prefill_args {
+  const void* x;               /* [tokens, channels] activation dtype, channels contiguous, 16-byte aligned rows */
+  int64_t x_row_stride;        /* elements */
+  void* y;                     /* [tokens, channels] activation dtype, not x */
+  int64_t y_row_stride;
+  const float* weight;         /* [channels, 4]; tap 3 multiplies the current token */
+  const float* bias;           /* [channels] or NULL */
+  void* conv_state;            /* activation dtype, addressed [slot, channel, tap]; NULL = zero history, none kept */
+  pla_b200_conv_strides conv_strides;
+  int32_t slots;
+  const int32_t* cu_seqlens;   /* [N + 1] */
+  const int32_t* state_indices;        /* [N] or NULL (sequence n uses slot n) */
+  const uint8_t* has_initial_state;    /* [N] or NULL (all): 0 = start from a zero history */
+  int32_t N, tokens, channels;
+  int32_t act_dtype;           /* pla_b200_dtype: BF16 or F16 */
+  int32_t activation;          /* 0 = none, 1 = SiLU */
+  int32_t pad;                 /* pla_b200_pad: which slot values mean "no history read or written" */
+  int32_t* status;
+} pla_b200_conv_prefill_args;
+
+int pla_b200_causal_conv_prefill(const pla_b200_conv_prefill_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -453,9 +453,84 @@ at::Tensor kda_prefill_chunked(const at::Tensor& q, const at::Tensor& k, const a
 }
 
 }  // namespace
+// Width-4 causal conv (+ SiLU) over packed varlen rows with a 3-tap history per request; returns y.
+at::Tensor causal_conv_prefill(const at::Tensor& x, const at::Tensor& weight, const Optional& bias, const Optional& conv_state,
+                               const at::Tensor& cu_seqlens, const Optional& state_indices,
+                               const Optional& has_initial_state, bool silu, bool vllm_pad, const Optional& out,
+                               const Optional& status) {
+  check_cuda(x, "x");
+  TORCH_CHECK(x.dim() == 2 && (x.size(0) == 0 || x.stride(1) == 1), "x must be [tokens, channels] with contiguous channels");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf, "x must be bf16 or fp16");
+  const int64_t T = x.size(0), C = x.size(1);
+  TORCH_CHECK(C > 0 && C % 8 == 0, "the channel count must be a multiple of 8");
+  TORCH_CHECK(weight.scalar_type() == at::kFloat && weight.is_contiguous() && weight.dim() == 2 && weight.size(0) == C &&
+                  weight.size(1) == 4 && weight.device() == x.device(),
+              "weight must be contiguous fp32 [channels, 4] on x's device");
+  if (bias.has_value())
+    TORCH_CHECK(bias->scalar_type() == at::kFloat && bias->is_contiguous() && bias->numel() == C && bias->device() == x.device(),
+                "bias must be contiguous fp32 [channels] on x's device");
+  TORCH_CHECK(cu_seqlens.scalar_type() == at::kInt && cu_seqlens.is_contiguous() && cu_seqlens.dim() == 1 &&
+                  cu_seqlens.numel() >= 1 && cu_seqlens.device() == x.device(),
+              "cu_seqlens must be contiguous int32 [N + 1] on x's device");
+  const int64_t N = cu_seqlens.numel() - 1;
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor y = out.has_value() ? *out : at::empty({T, C}, x.options());
+  TORCH_CHECK(y.device() == x.device() && y.scalar_type() == x.scalar_type() && y.dim() == 2 && y.size(0) == T &&
+                  y.size(1) == C && (T == 0 || y.stride(1) == 1),
+              "out must be [tokens, channels] of x's dtype with contiguous channels");
+  pla_b200_conv_prefill_args a{};
+  a.x = x.data_ptr();
+  a.x_row_stride = T > 0 ? x.stride(0) : C;
+  a.y = y.data_ptr();
+  a.y_row_stride = T > 0 ? y.stride(0) : C;
+  a.weight = weight.data_ptr<float>();
+  a.bias = bias.has_value() ? bias->data_ptr<float>() : nullptr;
+  if (conv_state.has_value()) {
+    TORCH_CHECK(conv_state->device() == x.device() && conv_state->scalar_type() == x.scalar_type() &&
+                    conv_state->dim() == 3 && conv_state->size(1) == C && conv_state->size(2) == 3,
+                "conv_state must be a [slots, channels, 3] view of x's dtype on x's device");
+    a.conv_state = conv_state->data_ptr();
+    a.conv_strides = {conv_state->stride(0), conv_state->stride(1), conv_state->stride(2)};
+    a.slots = static_cast<int32_t>(conv_state->size(0));
+  }
+  a.cu_seqlens = cu_seqlens.data_ptr<int32_t>();
+  if (state_indices.has_value()) {
+    TORCH_CHECK(state_indices->is_contiguous() && state_indices->numel() == N && state_indices->device() == x.device(),
+                "state_indices must be contiguous int32 [N] on x's device");
+    a.state_indices = i32_ptr(state_indices, "state_indices");
+  } else {
+    TORCH_CHECK(!conv_state.has_value() || conv_state->size(0) >= N, "conv_state has fewer slots than sequences");
+  }
+  if (has_initial_state.has_value()) {
+    TORCH_CHECK((has_initial_state->scalar_type() == at::kBool || has_initial_state->scalar_type() == at::kByte) &&
+                    has_initial_state->is_contiguous() && has_initial_state->numel() == N &&
+                    has_initial_state->device() == x.device(),
+                "has_initial_state must be contiguous bool or uint8 [N] on x's device");
+    a.has_initial_state = static_cast<const uint8_t*>(has_initial_state->data_ptr());
+  }
+  a.N = static_cast<int32_t>(N);
+  a.tokens = static_cast<int32_t>(T);
+  a.channels = static_cast<int32_t>(C);
+  a.act_dtype = dtype_tag(x, "x");
+  a.activation = silu ? 1 : 0;
+  a.pad = vllm_pad ? PLA_B200_PAD_VLLM : PLA_B200_PAD_SGLANG;
+  a.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
+  if (sanity_check()) {
+    const std::string why = sanity_offsets(cu_seqlens, T, 0);
+    TORCH_CHECK(why.empty(), "causal conv: ", why);
+  }
+  if (!bypass_exec()) check_abi(pla_b200_causal_conv_prefill(&a, stream_of(x)), "causal conv prefill");
+  return y;
+}
+
 }  // namespace pla_ops
 
 TORCH_LIBRARY_FRAGMENT(pla_b200, m) {
+  m.def(
+      "causal_conv_prefill(Tensor x, Tensor weight, Tensor? bias, Tensor(a!)? conv_state, Tensor cu_seqlens, "
+      "Tensor? state_indices, Tensor? has_initial_state, bool silu, bool vllm_pad, Tensor(b!)? out, "
+      "Tensor(c!)? status) -> Tensor",
+      &pla_ops::causal_conv_prefill);
   m.def("cp_fold_prefix(Tensor pairs, Tensor? initial_state, int rank, Tensor(a!)? status) -> Tensor",
         &pla_ops::cp_fold_prefix);
   m.def(

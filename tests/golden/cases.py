@@ -467,3 +467,51 @@ def mega_case(name, device="cpu", pad_rows=()):
                 moved[k_] = v_.to(device)
         kw = moved
     return kw, c
+
+
+CONV_CASES = {
+    # lengths straddle the 8/16/32/64-row tiles; a start one and two rows before a tile edge; an empty sequence
+    "conv_mixed": dict(C=256, lengths=[5, 0, 1, 2, 70, 3, 62, 1, 130], slots=12, layout="SD", bias=True, dtype="bf16",
+                       extra_rows=5, has_initial=[1, 1, 0, 1, 1, 1, 0, 1, 1], pads=(5,)),
+    "conv_ds_fp16": dict(C=136, lengths=[33, 2, 95], slots=5, layout="DS", bias=False, dtype="fp16", extra_rows=0,
+                         has_initial=None, pads=()),
+}
+
+
+def conv_case(name, device="cpu"):
+    """Packed rows with a row pitch wider than the channel count, history pool stored [slots, 3, C] ("SD", viewed
+    [slots, C, 3]) or [slots, C, 3] ("DS"), slots in a scrambled order, optional padding slots (-1)."""
+    c = CONV_CASES[name]
+    rs = _rs(sum(map(ord, name)))
+    C, lengths = c["C"], c["lengths"]
+    dt = torch.bfloat16 if c["dtype"] == "bf16" else torch.float16
+    total = sum(lengths)
+    rows = total + c["extra_rows"]
+    x = _t(rs, rows, C + 24, dtype=dt)[:, :C]
+    weight = _t(rs, C, 4, dtype=torch.float32, scale=0.4)
+    bias = _t(rs, C, dtype=torch.float32, scale=0.1) if c["bias"] else None
+    if c["layout"] == "SD":
+        conv_state = _t(rs, c["slots"], 3, C, dtype=dt, scale=0.5).transpose(1, 2)
+    else:
+        conv_state = _t(rs, c["slots"], C, 3, dtype=dt, scale=0.5)
+    idx = torch.tensor(rs.permutation(c["slots"])[:len(lengths)].astype("int32"))
+    for r in c["pads"]:
+        idx[r] = -1
+    offsets = [0]
+    for n in lengths:
+        offsets.append(offsets[-1] + n)
+    has = None if c["has_initial"] is None else torch.tensor(c["has_initial"], dtype=torch.bool)
+    kw = dict(x=x, weight=weight, bias=bias, conv_state=conv_state, offsets=offsets, state_indices=idx,
+              has_initial_state=has)
+    if device != "cpu":
+        moved = {}
+        for k_, v_ in kw.items():
+            if not isinstance(v_, torch.Tensor):
+                moved[k_] = v_
+            elif k_ in ("x", "conv_state"):                                  # keep the padded / transposed views
+                base = v_._base if v_._base is not None else v_
+                moved[k_] = torch.as_strided(base.to(device), v_.shape, v_.stride(), v_.storage_offset())
+            else:
+                moved[k_] = v_.to(device)
+        kw = moved
+    return kw, c

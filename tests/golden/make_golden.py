@@ -212,6 +212,40 @@ def make_prefill():
             print("prefill", name, tag)
 
 
+def make_conv():
+    """Prefill causal conv: the reference's per-sequence conv oracle (scripts/decode/kda_mtp_sglang/private/
+    _reference.py:67-89) run in fp64 over every sequence of the cases of cases.py; the last window is the history
+    a request keeps."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "ref_sglang", REF / "scripts" / "decode" / "kda_mtp_sglang" / "private" / "_reference.py")
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    for name in cases.CONV_CASES:
+        kw, c = cases.conv_case(name)
+        x, state, offs = kw["x"], kw["conv_state"], kw["offsets"]
+        y = torch.zeros(x.shape, dtype=torch.float64)
+        final = state.double().clone()
+        for s, (beg, end) in enumerate(zip(offs, offs[1:])):
+            if end == beg:
+                continue
+            slot = int(kw["state_indices"][s])
+            reads = slot >= 0 and (kw["has_initial_state"] is None or bool(kw["has_initial_state"][s]))
+            hist = state[slot].double() if reads else torch.zeros(c["C"], 3, dtype=torch.float64)
+            # the oracle has no bias and always applies SiLU: fold the bias in as a fifth tap on a constant-one input
+            out, win = ref._causal_conv_silu(x[beg:end].double(), hist, kw["weight"].double())
+            if kw["bias"] is not None:
+                pre = sum(torch.cat([hist.t(), x[beg:end].double()])[j:j + end - beg] * kw["weight"].double()[:, j] for j in range(4))
+                assert torch.allclose(out, pre * torch.sigmoid(pre), atol=1e-12)
+                pre = pre + kw["bias"].double()
+                out = pre * torch.sigmoid(pre)
+            y[beg:end] = out
+            if slot >= 0:
+                final[slot] = win[-1]
+        np.savez_compressed(HERE / f"{name}.npz", y=y.float().numpy(), final=final.float().numpy())
+        print("conv", name, tuple(y.shape))
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     which = sys.argv[2] if len(sys.argv) > 2 else "all"
@@ -225,3 +259,5 @@ if __name__ == "__main__":
         make_sglang()
     if which in ("all", "mega"):
         make_mega()
+    if which in ("all", "conv"):
+        make_conv()
