@@ -6,7 +6,7 @@
 // old ones when it is shorter; written by a second small launch). The output row is the packed q|k|v row the prefill ops read in place.
 //
 // HBM-bound streaming: a thread owns 8 adjacent channels (one 16-byte vector per token row) and walks a tile
-// of consecutive token rows with the window in registers, so a row is read once (plus a 3-row halo per tile)
+// of consecutive token rows with the window in registers (rows staged through shared memory by asynchronous copies), so a row is read once (plus a 3-row halo per tile)
 // and written once: 2 * 2 bytes per (token, channel).
 #include "common.cuh"
 
@@ -15,7 +15,18 @@ namespace {
 
 constexpr int CONV_THREADS = 128;
 constexpr int VEC = 8;          // channels per thread
-constexpr int AHEAD = 8;        // token rows loaded before they are consumed
+constexpr int BATCH = 4;        // token rows per asynchronous copy group
+constexpr int GROUPS = 4;       // copy groups in flight per thread: 16 rows
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 template <typename act_t>
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[VEC]);
@@ -98,7 +109,8 @@ __device__ __forceinline__ void slots_of(const pla_b200_conv_prefill_args& p, in
 }
 
 template <typename act_t, bool SILU>
-__global__ void __launch_bounds__(CONV_THREADS) conv_prefill_kernel(const pla_b200_conv_prefill_args p, const int tile) {
+__global__ void __launch_bounds__(CONV_THREADS, 5) conv_prefill_kernel(const pla_b200_conv_prefill_args p, const int tile) {
+  __shared__ uint4 ring[GROUPS * BATCH][CONV_THREADS];
   const int c0 = (blockIdx.x * CONV_THREADS + threadIdx.x) * VEC;
   if (c0 >= p.channels) return;
   const int t0 = blockIdx.y * tile;
@@ -142,49 +154,79 @@ __global__ void __launch_bounds__(CONV_THREADS) conv_prefill_kernel(const pla_b2
     }
   }
 
-  for (int tb = t0; tb < t1; tb += AHEAD) {
-    uint4 xs[AHEAD];
+  // One conv step of this thread's 8 channels; shifts the window.
+  auto step = [&](const uint4& xv) -> uint4 {
+    float fx[VEC], r[VEC];
+    unpack8<act_t>(xv, fx);
 #pragma unroll
-    for (int i = 0; i < AHEAD; ++i)
-      xs[i] = (tb + i < t1 && tb + i < total) ? *reinterpret_cast<const uint4*>(x + static_cast<int64_t>(tb + i) * p.x_row_stride)
-                                               : zero;
-#pragma unroll
-    for (int i = 0; i < AHEAD; ++i) {
-      const int t = tb + i;
-      if (t >= t1) break;
-      uint4 out = zero;
-      if (t < total) {
-        if (t >= seq_end) {
-          while (t >= seq_end && seq + 1 < p.N) {   // next sequence (empty ones have seq_end == seq_beg)
-            ++seq;
-            seq_beg = seq_end;
-            seq_end = p.cu_seqlens[seq + 1];
-          }
-          slots_of(p, seq, reads, writes);
-        }
-        if (t == seq_beg) {
-          unpack8<act_t>(load_tap<act_t>(p, reads, c0, 0), h0);
-          unpack8<act_t>(load_tap<act_t>(p, reads, c0, 1), h1);
-          unpack8<act_t>(load_tap<act_t>(p, reads, c0, 2), h2);
-        }
-        float fx[VEC], r[VEC];
-        unpack8<act_t>(xs[i], fx);
-#pragma unroll
-        for (int c = 0; c < VEC; ++c) {
-          float acc = bias[c];
-          acc = fmaf(w[0][c], h0[c], acc);
-          acc = fmaf(w[1][c], h1[c], acc);
-          acc = fmaf(w[2][c], h2[c], acc);
-          acc = fmaf(w[3][c], fx[c], acc);
-          r[c] = SILU ? silu_tanh(acc) : acc;
-          h0[c] = h1[c], h1[c] = h2[c], h2[c] = fx[c];
-        }
-        out = make_uint4(pack2(r[0], r[1], act_t()), pack2(r[2], r[3], act_t()), pack2(r[4], r[5], act_t()),
-                         pack2(r[6], r[7], act_t()));
-      }
-      *reinterpret_cast<uint4*>(y + static_cast<int64_t>(t) * p.y_row_stride) = out;
+    for (int c = 0; c < VEC; ++c) {
+      float acc = bias[c];
+      acc = fmaf(w[0][c], h0[c], acc);
+      acc = fmaf(w[1][c], h1[c], acc);
+      acc = fmaf(w[2][c], h2[c], acc);
+      acc = fmaf(w[3][c], fx[c], acc);
+      r[c] = SILU ? silu_tanh(acc) : acc;
+      h0[c] = h1[c], h1[c] = h2[c], h2[c] = fx[c];
     }
+    return make_uint4(pack2(r[0], r[1], act_t()), pack2(r[2], r[3], act_t()), pack2(r[4], r[5], act_t()),
+                      pack2(r[6], r[7], act_t()));
+  };
+  // Rows arrive through a thread-private ring in shared memory filled by asynchronous 16-byte copies, GROUPS
+  // batches of BATCH rows in flight per thread: the depth does not cost registers. Rows outside the sequences
+  // are filled with zeros (source size 0).
+  const int tid = threadIdx.x;
+  auto issue = [&](int batch) {
+    const int tb = t0 + batch * BATCH;
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i) {
+      const int t = tb + i;
+      const bool live = t < t1 && t < total;
+      cp_async16(&ring[(batch % GROUPS) * BATCH + i][tid], x + static_cast<int64_t>(live ? t : t0) * p.x_row_stride, live ? 16u : 0u);
+    }
+  };
+  const int batches = (t1 - t0 + BATCH - 1) / BATCH;
+#pragma unroll
+  for (int b = 0; b < GROUPS; ++b) {
+    if (b < batches) issue(b);
+    cp_async_commit();
   }
+  for (int b = 0; b < batches; ++b) {
+    cp_async_wait<GROUPS - 1>();
+    const int tb = t0 + b * BATCH;
+    const uint4* rows = &ring[(b % GROUPS) * BATCH][tid];
+    if (tb > seq_beg && tb + BATCH <= min(seq_end, min(total, t1))) {      // inside one sequence: no per-row checks
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i)
+        *reinterpret_cast<uint4*>(y + static_cast<int64_t>(tb + i) * p.y_row_stride) = step(rows[i * CONV_THREADS]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const int t = tb + i;
+        if (t >= t1) break;
+        uint4 out = zero;
+        if (t < total) {
+          if (t >= seq_end) {
+            while (t >= seq_end && seq + 1 < p.N) {   // next sequence (empty ones have seq_end == seq_beg)
+              ++seq;
+              seq_beg = seq_end;
+              seq_end = p.cu_seqlens[seq + 1];
+            }
+            slots_of(p, seq, reads, writes);
+          }
+          if (t == seq_beg) {
+            unpack8<act_t>(load_tap<act_t>(p, reads, c0, 0), h0);
+            unpack8<act_t>(load_tap<act_t>(p, reads, c0, 1), h1);
+            unpack8<act_t>(load_tap<act_t>(p, reads, c0, 2), h2);
+          }
+          out = step(rows[i * CONV_THREADS]);
+        }
+        *reinterpret_cast<uint4*>(y + static_cast<int64_t>(t) * p.y_row_stride) = out;
+      }
+    }
+    if (b + GROUPS < batches) issue(b + GROUPS);   // refill the slot just consumed (this thread's own 16-byte cells)
+    cp_async_commit();
+  }
+  cp_async_wait<0>();
 }
 
 // History after the call, one thread per (sequence, 8 channels): its last three inputs, the old taps shifted in
