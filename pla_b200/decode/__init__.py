@@ -10,6 +10,7 @@ from typing import Optional, Union
 import torch
 
 from .._ops import ops
+from ..caselist import show_call
 
 __all__ = [
     "fused_sigmoid_gating_delta_rule_forward_k_last",
@@ -68,6 +69,7 @@ def fused_sigmoid_gating_delta_rule_forward_k_last(
         out = torch.empty(v.shape, dtype=v.dtype, device=v.device)
     elif out.shape != v.shape or out.dtype != v.dtype:
         raise RuntimeError("out must match v in shape and dtype")
+    show_call(q, v, bool(is_kda), cu_seqlens, lower_bound=lower_bound)
     ops.decode_k_last(
         A_log, a, dt_bias, float(softplus_beta), float(softplus_threshold), q, k, v, b,
         initial_state_source, initial_state_indices, float(scale), bool(use_qk_l2norm_in_kernel),

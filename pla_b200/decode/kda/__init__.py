@@ -11,6 +11,7 @@ from typing import Optional, Tuple
 import torch
 
 from ..._ops import ops
+from ...caselist import show_call
 
 __all__ = ["fused_recurrent_kda", "fused_kda_decode_mega_forward"]
 
@@ -65,6 +66,7 @@ def fused_recurrent_kda(
         out = torch.empty(v.shape, dtype=v.dtype, device=v.device)
     elif out.shape != v.shape or out.dtype != v.dtype:
         raise ValueError("out must match v in shape and dtype")
+    show_call(q, v, True, cu_seqlens, lower_bound=lower_bound)
     ops.fused_recurrent_kda(q, k, v, raw_g, raw_beta, A_log, dt_bias,
                             None if lower_bound is None else float(lower_bound), initial_state, cu_seqlens,
                             ssm_state_indices, num_accepted_tokens, out, bool(is_sglang), status)

@@ -6,6 +6,7 @@ from typing import Optional, Tuple
 import torch
 
 from ..._ops import ops
+from ...caselist import show_call
 
 DK = 128
 DV = 128
@@ -91,6 +92,7 @@ def flashkda_fwd(
         raise ValueError("raw_cu_seqlens must have N+1 entries")
     if not out.is_contiguous() or tuple(out.shape) != (T, H, DV):
         raise ValueError("out must be contiguous [total_tokens, H, DV]")
+    show_call(q, v, True, cu32, raw_cu_seqlens, lower_bound, prefill=True)
     bet = beta if beta.stride(-1) == 1 else beta.contiguous()
     gg = g if (g.stride(2) == 1 and g.stride(1) == 128) else g.contiguous()
     lb = None if lower_bound is None else float(lower_bound)

@@ -12,6 +12,7 @@ from typing import Optional, Sequence, Tuple, Union
 import torch
 
 from ..._ops import ops
+from ...caselist import show_call
 
 DK = 128
 DV = 128
@@ -190,6 +191,7 @@ def chunk_gated_delta_rule_fwd(
             raise ValueError("final_state_dtype must match the initial_state dtype")
         state_dtype = final_state_dtype
 
+    show_call(q, v, False, cu32, None if isinstance(raw_cu_seqlens, torch.Tensor) else raw_cu_seqlens, prefill=True)
     o = torch.empty((1, T, H, DV), dtype=q.dtype, device=q.device)
     if use_raw:
         gate, bet = raw_gate_a.reshape(T, H) if raw_gate_a.ndim != 2 else raw_gate_a, \
