@@ -405,10 +405,16 @@ __global__ void __launch_bounds__(128) chunk_inverse_kernel(const pla_b200_gdn_c
   ChunkPos pos;
   const bool found = live && locate_chunk(p.cu_seqlens, p.N, gc, pos);
   if (found) {
+    // 16 asynchronous 16-byte copies per thread, all in flight at once (a load / store loop through registers
+    // pays the DRAM latency once per iteration)
     const float4* Lg = reinterpret_cast<const float4*>(ws + ws_lmat(p.max_chunks, p.H, p.HV, gc, hv));
+#pragma unroll
     for (int i = t6; i < C * C / 4; i += 64)
-      *reinterpret_cast<float4*>(&Ls[s][(i >> 4) * L_STRIDE + (i & 15) * 4]) = Lg[i];
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&Ls[s][(i >> 4) * L_STRIDE + (i & 15) * 4])),
+                   "l"(Lg + i)
+                   : "memory");
   }
+  asm volatile("cp.async.wait_all;" ::: "memory");
   __syncthreads();
   if (!found) return;
   const int cb = inverse_column_block(t6);
