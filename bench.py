@@ -452,7 +452,7 @@ def run_prefill_cp(args):
     mine = [x[sl] for x in (q, k, v, gate, beta)]
     steps = min(args.steps, 5) if (kda and args.kda_backend == "recurrent") else args.steps
 
-    ranges_on_one_gpu = world == 1 and not kda
+    ranges_on_one_gpu = world == 1 and (not kda or args.kda_backend == "chunked")
     if ranges_on_one_gpu:
         # one GPU: the same prescan / fold / segment scheme over token ranges inside the GPU, through the facade
         from pla_b200.prefill.flashqla import ops as fq
@@ -460,7 +460,16 @@ def run_prefill_cp(args):
         slot0 = torch.zeros(1, dtype=torch.int32, device=dev)
         cu1 = torch.tensor([0, T], dtype=torch.int32, device=dev)
 
+    if ranges_on_one_gpu and kda:
+        from pla_b200.prefill.flashkdapro import flashkda_fwd
+        out1 = torch.empty(T, H, D, dtype=torch.bfloat16, device=dev)
+        status1 = torch.zeros(1, dtype=torch.int32, device=dev)
+
     def step():
+        if ranges_on_one_gpu and kda:
+            flashkda_fwd(q, k, v, gate, beta, A_log, dt_bias, out1, None, None, state_pool=pool1, state_indices=slot0,
+                         raw_cu_seqlens=(0, T), backend="chunked", status=status1)
+            return out1, pool1[0]
         if ranges_on_one_gpu:
             res = fq.chunk_gated_delta_rule_fwd(q[None], k[None], v[None], None, None, initial_state=pool1,
                                                 initial_state_indices=slot0, cu_seqlens=cu1, output_final_state=False,

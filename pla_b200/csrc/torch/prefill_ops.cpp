@@ -446,10 +446,10 @@ at::Tensor kda_prefill_chunked(const at::Tensor& q, const at::Tensor& k, const a
                                const Optional& in_indices, const Optional& state_out, const Optional& out_indices,
                                const Optional& workspace, bool transposed, bool normalize_qk, double scale,
                                std::optional<double> lower_bound, bool update_in_place, int64_t max_chunks,
-                               int64_t stage, bool prescan, const Optional& status) {
+                               int64_t stage, bool prescan, const Optional& status, const Optional& range_mask) {
   return run_chunked(q, k, v, gate, beta, A_log, dt_bias, out, c10::nullopt, cu_seqlens, state_in, in_indices,
                      state_out, out_indices, transposed, normalize_qk, scale, false, update_in_place, max_chunks, stage,
-                     status, workspace, prescan, true, lower_bound);
+                     status, workspace, prescan, true, lower_bound, range_mask);
 }
 
 }  // namespace
@@ -537,7 +537,7 @@ TORCH_LIBRARY_FRAGMENT(pla_b200, m) {
       "kda_prefill_chunked(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor A_log, Tensor dt_bias, "
       "Tensor(a!) out, Tensor cu_seqlens, Tensor(b!)? state_in, Tensor? in_indices, Tensor(c!)? state_out, "
       "Tensor? out_indices, Tensor(w!)? workspace, bool transposed, bool normalize_qk, float scale, "
-      "float? lower_bound, bool update_in_place, int max_chunks, int stage, bool prescan, Tensor(d!)? status) -> Tensor",
+      "float? lower_bound, bool update_in_place, int max_chunks, int stage, bool prescan, Tensor(d!)? status, Tensor? range_mask=None) -> Tensor",
       &pla_ops::kda_prefill_chunked);
   m.def(
       "gdn_prefill_chunked(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor? A_log, Tensor? dt_bias, "

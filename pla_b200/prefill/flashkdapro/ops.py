@@ -37,6 +37,7 @@ def flashkda_fwd(
     *,
     backend: str = "auto",
     status: Optional[torch.Tensor] = None,
+    auto_cp: bool = True,
 ) -> None:
     """KDA prefill over packed varlen tokens; writes ``out`` in full (rows past ``cu_seqlens[-1]``
     zero) and ``final_state`` or the pool slots. The gate is the safe gate
@@ -47,7 +48,10 @@ def flashkda_fwd(
     references every 16 tokens; needs the decay of every key channel to stay within 80 nats per 16 tokens,
     which the safe gate with ``lower_bound >= -5`` guarantees; a violation sets bit 16 of ``status``),
     ``"recurrent"`` = exact fp32 token recurrence, ``"auto"`` = chunked for the safe gate with
-    ``-5 <= lower_bound < 0``, recurrent otherwise.
+    ``-5 <= lower_bound < 0``, recurrent otherwise. ``auto_cp`` (keyword-only, default on): with host offsets
+    (``raw_cu_seqlens``) and an fp32 ``state_pool``, the chunked backend cuts long sequences of a batch with
+    fewer (sequence, head) chains than SMs into token ranges that run in parallel (the job of the reference's
+    intra-card planner, src/prefill/flashkdapro/host/torch_extension_cute.cc:179-215).
     """
     if backend not in ("auto", "chunked", "recurrent"):
         raise ValueError("backend must be auto, chunked or recurrent")
@@ -100,6 +104,26 @@ def flashkda_fwd(
         backend = "chunked" if (lb is not None and -5.0 <= lb < 0.0) else "recurrent"
     if backend == "chunked":
         max_chunks = T // 64 + (cu32.numel() - 1)
+        plan = None
+        if (auto_cp and in_place and raw_cu_seqlens is not None and state_pool.dtype == torch.float32
+                and state_pool.is_contiguous() and state_indices.dtype == torch.int32):
+            # few (sequence, head) chains for the SMs: long sequences run as several token ranges (prescan of every
+            # range, fold of the (offset, transition) pairs, then the ranges in parallel); see flashqla.ops
+            from ..flashqla.ops import _range_tensors
+            offs = [int(x) for x in raw_cu_seqlens]
+            plan = _range_tensors(offs, H, q.device)
+        if plan is not None:
+            cu_ranges, seg_first, prescan_mask, last_mask, seq_of = plan
+            chunks = sum((b - a + 63) // 64 for a, b in zip(offs, offs[1:]))
+            args = (_rows(q), _rows(k), _rows(v), gg, bet, A_log.contiguous(), dt_bias.contiguous(), out, cu_ranges)
+            tail = (False, True, float(scale), lb, False, chunks)
+            ws = ops.kda_prefill_chunked(*args, None, None, None, None, None, *tail, 1, False, status)
+            pairs = torch.empty((prescan_mask.numel(), H, 2, DV, DK), dtype=torch.float32, device=q.device)
+            ops.kda_prefill_chunked(*args, None, None, pairs, None, ws, *tail, 2, True, status, prescan_mask)
+            state_in = ops.cp_fold_segments(pairs, seg_first, state_pool, state_indices.contiguous(), status)
+            out_idx = torch.where(last_mask, state_indices[seq_of], torch.full_like(prescan_mask, -1))
+            ops.kda_prefill_chunked(*args, state_in, None, state_pool, out_idx, ws, *tail, 2, False, status)
+            return None
         ops.kda_prefill_chunked(
             _rows(q), _rows(k), _rows(v), gg, bet, A_log.contiguous(), dt_bias.contiguous(), out, cu32,
             initial_state, in_idx, None if in_place else final_state, out_idx, None, False, True, float(scale), lb,

@@ -183,6 +183,50 @@ def test_kda_chunked_long_unaligned(native_built, lower_bound, a_lo, a_hi):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("lower_bound,a_lo,a_hi", [(-5.0, 0.0, 2.5), (None, -4.0, -2.0)])
+def test_kda_token_ranges_inside_the_gpu(native_built, lower_bound, a_lo, a_hi):
+    """auto_cp of the KDA facade: a 3300-token sequence of a small batch runs as three token ranges (prescan,
+    fold, parallel ranges); the pool is updated in place exactly as by the single chains, against the oracle."""
+    from pla_b200.prefill.flashkdapro import flashkda_fwd
+    from pla_b200.prefill.flashqla import ops as fq
+    g = torch.Generator().manual_seed(321)
+    H, lengths = 2, [3300, 0, 1300, 70]
+    T = sum(lengths)
+    offs = [0]
+    for n in lengths:
+        offs.append(offs[-1] + n)
+    plan = fq.plan_token_ranges(offs, H, 148)
+    assert plan is not None and plan[1][1] == 3
+    q, k, v, gg = (torch.randn(T, H, D, generator=g).bfloat16() for _ in range(4))
+    gates = torch.randn(T, H, generator=g)
+    if lower_bound is None:
+        gates -= 3.0                                   # small beta: the transitions of the ranges stay of order one
+    gates = gates.bfloat16()
+    A_log = a_lo + (a_hi - a_lo) * torch.rand(H, generator=g)
+    dt_bias = torch.randn(H, D, generator=g) * 0.1
+    pool = torch.randn(6, H, D, D, generator=g) * 0.3
+    slots = [4, 0, 2, 5]
+    exp_out, exp_state, _ = odec.klast_forward(q=q, k=k, v=v, a=gg, b=gates, A_log=A_log, dt_bias=dt_bias.reshape(-1),
+                                               state=pool, slot_indices=slots, lengths=lengths, scale=D ** -0.5,
+                                               is_kda=True, lower_bound=lower_bound)
+    outs = {}
+    for auto_cp in (False, True):
+        dpool = pool.cuda()
+        out = torch.empty(T, H, D, dtype=torch.bfloat16, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        flashkda_fwd(q.cuda(), k.cuda(), v.cuda(), gg.cuda(), gates.cuda(), A_log.cuda(), dt_bias.cuda(), out,
+                     lower_bound=lower_bound, state_pool=dpool,
+                     state_indices=torch.tensor(slots, dtype=torch.int32, device="cuda"), raw_cu_seqlens=tuple(offs),
+                     backend="chunked", status=status, auto_cp=auto_cp)
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        assert_out_close(out, exp_out, f"auto_cp={auto_cp}")
+        assert_state_close(dpool.cpu(), exp_state, f"auto_cp={auto_cp}")
+        outs[auto_cp] = out.cpu()
+    assert_out_close(outs[True], outs[False], "ranges vs single chains")
+
+
+@pytest.mark.gpu
 def test_kda_chunked_reports_decay_out_of_range(native_built):
     """An unbounded softplus gate that decays a channel by more than 80 nats inside 16 tokens cannot be
     represented by the sub-block references: the call flags it instead of returning silently wrong numbers."""
