@@ -15,6 +15,7 @@ Per rank:
   5. segment     the ordinary chain from ``S_in(r)``; the last rank's final state is the sequence's
 
 The last rank's (M, B) is never used, so it skips step 2 and contributes zeros to the gather.
+A rank with fewer chains than SMs applies the same scheme once more inside its range (``plan_rank_ranges``).
 GDN runs the chunk-64 tensor-core kernels; KDA (per-channel decay: M = prod diag(gamma_t)(I - beta_t k_t k_t^T),
 the same row-wise affine form) runs the token-recurrent kernel in its prescan mode.
 """
@@ -29,39 +30,101 @@ D = 128
 CHUNK = 64
 
 
-class CudaSegmentKernels:
-    """Steps 1, 2 and 5 on the rank's GPU (pla_b200_gdn_prefill_chunked, stages 1 and 2)."""
+def plan_rank_ranges(tokens: int, chains: int, n_sm: int, min_chunks: int = 16):
+    """Token ranges INSIDE one rank (same idea as the split across ranks, one level down): a rank with fewer
+    chains than SMs cuts its tokens into ``p`` ranges on chunk boundaries; it then prescans all ``p`` ranges (two
+    chains each), composes their pairs into the rank's pair, and after the exchange runs the ranges in parallel.
+    Cost in waves of ``n_sm`` chains: ``(waves(2 p n) + waves(p n)) / p`` against ``waves(2 n) + waves(n)``
+    unsplit; ``p`` grows while that lowers the cost by 10 % or more. Returns the range offsets ``[0, ..., tokens]``
+    or ``None`` when one range is best. Pure host code."""
+    chunks = (tokens + CHUNK - 1) // CHUNK
+    waves = lambda x: -(-x // n_sm)
+    base = float(waves(2 * chains) + waves(chains))
+    best, parts = base, 1
+    for p in range(2, max(1, min(chunks // min_chunks, 64)) + 1):
+        cost = (waves(2 * p * chains) + waves(p * chains)) / p
+        if cost < 0.9 * best:
+            best, parts = cost, p
+    if parts == 1 or best > 0.8 * base:
+        return None
+    return [min(tokens, (chunks * i // parts) * CHUNK) for i in range(parts)] + [tokens]
 
-    def __init__(self, q, k, v, gate, beta, A_log, dt_bias, scale, normalize_qk, gate_activated):
+
+class CudaSegmentKernels:
+    """Steps 1, 2 and 5 on the rank's GPU (pla_b200_gdn_prefill_chunked, stages 1 and 2). When the rank has
+    fewer chains than SMs its tokens run as several ranges (``plan_rank_ranges``; ``split=False`` turns it off)."""
+
+    def __init__(self, q, k, v, gate, beta, A_log, dt_bias, scale, normalize_qk, gate_activated, split=True):
         from .._ops import ops  # raises ImportError when the native libraries are missing
         self._ops = ops
         self.a = (q, k, v, gate, beta, A_log, dt_bias)
         self.scale, self.normalize_qk, self.gate_activated = float(scale), bool(normalize_qk), bool(gate_activated)
+        self._setup(q, v, split)
+
+    def _setup(self, q, v, split):
         T, H = v.shape[0], v.shape[1]
         self.T, self.H = T, H
-        self.cu = torch.tensor([0, T], dtype=torch.int32, device=q.device)
+        offs = None
+        if split and q.is_cuda and T > 0:
+            offs = plan_rank_ranges(T, H, torch.cuda.get_device_properties(q.device).multi_processor_count)
+        self.parts = 1 if offs is None else len(offs) - 1
+        self.cu = torch.tensor([0, T] if offs is None else offs, dtype=torch.int32, device=q.device)
         self.max_chunks = (T + CHUNK - 1) // CHUNK
         self.out = torch.empty(T, H, D, dtype=q.dtype, device=q.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=q.device)
         self.ws = None
+        self.pairs = None       # [parts + 1, H, 2, 128, 128]: pairs of this rank's ranges (+ one unused entry)
 
-    def _stage(self, stage, prescan, state_in, state_out):
+    def _stage(self, stage, prescan, state_in, state_out, range_mask=None, out_indices=None):
         q, k, v, gate, beta, A_log, dt_bias = self.a
         self.ws = self._ops.gdn_prefill_chunked_stage(
             q, k, v, gate, beta, A_log, dt_bias, self.out, None, self.cu, state_in, state_out, self.ws, False,
-            self.normalize_qk, self.scale, self.gate_activated, self.max_chunks, stage, prescan, self.status, None, None)
+            self.normalize_qk, self.scale, self.gate_activated, self.max_chunks, stage, prescan, self.status,
+            range_mask, out_indices)
 
     def prepare(self):
         self._stage(1, False, None, None)
 
+    def _prescan_ranges(self, every_range: bool):
+        dev = self.out.device
+        self.pairs = torch.empty(self.parts + 1, self.H, 2, D, D, dtype=torch.float32, device=dev)
+        mask = None
+        if not every_range:     # the last range's pair is not needed when only the incoming states are wanted
+            mask = torch.zeros(self.parts, dtype=torch.int32, device=dev)
+            mask[-1] = -1
+        self._stage(2, True, None, self.pairs[:self.parts], mask)
+
     def prescan(self) -> torch.Tensor:
-        mb = torch.empty(1, self.H, 2, D, D, dtype=torch.float32, device=self.out.device)
-        self._stage(2, True, None, mb)
-        return mb[0]
+        dev = self.out.device
+        if self.parts == 1:
+            mb = torch.empty(1, self.H, 2, D, D, dtype=torch.float32, device=dev)
+            self._stage(2, True, None, mb)
+            return mb[0]
+        # pairs of all ranges, then the rank's pair: B from a zero state through all of them, M from the identity
+        # through the transitions alone (offsets zeroed)
+        self._prescan_ranges(True)
+        offset = self._ops.cp_fold_prefix(self.pairs, None, self.parts, self.status)
+        only_m = self.pairs.clone()
+        only_m[:, :, 0] = 0
+        eye = torch.eye(D, dtype=torch.float32, device=dev).expand(self.H, D, D).contiguous()
+        transition = self._ops.cp_fold_prefix(only_m, eye, self.parts, self.status)
+        return torch.stack([offset, transition], dim=1)
 
     def segment(self, state_in: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-        final = torch.empty(1, self.H, D, D, dtype=torch.float32, device=self.out.device)
-        self._stage(2, False, state_in[None].contiguous(), final)
+        dev = self.out.device
+        final = torch.empty(1, self.H, D, D, dtype=torch.float32, device=dev)
+        if self.parts == 1:
+            self._stage(2, False, state_in[None].contiguous(), final)
+            return self.out, final[0]
+        if self.pairs is None:
+            self._prescan_ranges(False)
+        seg_first = torch.tensor([0, self.parts], dtype=torch.int32, device=dev)
+        slot0 = torch.zeros(1, dtype=torch.int32, device=dev)
+        states = self._ops.cp_fold_segments(self.pairs[:self.parts], seg_first, state_in[None].contiguous(), slot0,
+                                            self.status)
+        out_idx = torch.full((self.parts,), -1, dtype=torch.int32, device=dev)
+        out_idx[-1] = 0
+        self._stage(2, False, states, final, None, out_idx)
         return self.out, final[0]
 
     def check(self):
@@ -71,28 +134,26 @@ class CudaSegmentKernels:
 
 
 class KdaChunkedSegmentKernels:
-    """Steps 1, 2 and 5 for KDA with the chunk-64 tensor-core kernels (pla_b200_kda_prefill_chunked)."""
+    """Steps 1, 2 and 5 for KDA with the chunk-64 tensor-core kernels (pla_b200_kda_prefill_chunked); ranges
+    inside the rank as for GDN."""
 
-    def __init__(self, q, k, v, gate, beta, A_log, dt_bias, scale, normalize_qk, lower_bound):
+    def __init__(self, q, k, v, gate, beta, A_log, dt_bias, scale, normalize_qk, lower_bound, split=True):
         from .._ops import ops  # raises ImportError when the native libraries are missing
         self._ops = ops
         self.a = (q, k, v, gate, beta, A_log, dt_bias)
         self.scale, self.normalize_qk = float(scale), bool(normalize_qk)
         self.lower_bound = None if lower_bound is None else float(lower_bound)
-        T, H = v.shape[0], v.shape[1]
-        self.T, self.H = T, H
-        self.cu = torch.tensor([0, T], dtype=torch.int32, device=q.device)
-        self.max_chunks = (T + CHUNK - 1) // CHUNK
-        self.out = torch.empty(T, H, D, dtype=q.dtype, device=q.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=q.device)
-        self.ws = None
+        self._setup(q, v, split)
 
-    def _stage(self, stage, prescan, state_in, state_out):
+    def _stage(self, stage, prescan, state_in, state_out, range_mask=None, out_indices=None):
         q, k, v, gate, beta, A_log, dt_bias = self.a
         self.ws = self._ops.kda_prefill_chunked(
-            q, k, v, gate, beta, A_log, dt_bias, self.out, self.cu, state_in, None, state_out, None, self.ws, False,
-            self.normalize_qk, self.scale, self.lower_bound, False, self.max_chunks, stage, prescan, self.status)
+            q, k, v, gate, beta, A_log, dt_bias, self.out, self.cu, state_in, None, state_out, out_indices, self.ws,
+            False, self.normalize_qk, self.scale, self.lower_bound, False, self.max_chunks, stage, prescan, self.status,
+            range_mask)
 
+    _setup = CudaSegmentKernels._setup
+    _prescan_ranges = CudaSegmentKernels._prescan_ranges
     prepare = CudaSegmentKernels.prepare
     prescan = CudaSegmentKernels.prescan
     segment = CudaSegmentKernels.segment

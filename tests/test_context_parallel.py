@@ -160,3 +160,17 @@ def test_token_range_plan_properties():
         assert all((x - offs[s]) % 64 == 0 for x in mine[1:-1])
         assert last[seg_first[s]:seg_first[s + 1]] == [False] * (seg_first[s + 1] - seg_first[s] - 1) + [True]
     assert len(last) * 4 <= 2 * 148
+
+
+def test_rank_range_plan_properties():
+    """Ranges inside a rank: chunk-aligned cuts that tile the rank's tokens, at least 16 chunks each, none when the
+    rank is short or already has enough chains."""
+    from pla_b200.prefill.context_parallel import plan_rank_ranges
+    assert plan_rank_ranges(1000, 4, 148) is None                 # 16 chunks: nothing to cut
+    assert plan_rank_ranges(65536, 296, 148) is None              # two full waves of chains already
+    for tokens, chains in [(65536, 24), (8192, 24), (131072, 32), (2240, 2), (40001, 8)]:
+        offs = plan_rank_ranges(tokens, chains, 148)
+        assert offs is not None and offs[0] == 0 and offs[-1] == tokens
+        assert all(b > a for a, b in zip(offs, offs[1:])) and all(x % 64 == 0 for x in offs[:-1])
+        assert all(b - a >= 16 * 64 or b == tokens for a, b in zip(offs, offs[1:]))
+    assert len(plan_rank_ranges(65536, 24, 148)) - 1 == 6         # 24 chains: six ranges, a quarter of the chain steps

@@ -24,13 +24,16 @@ def make(T, Hg, H, seed):
     return q, k, v, gate, beta, A_log, dt_bias, S0
 
 
-def test_prescan_pairs_match_the_oracle(native_built):
+@pytest.mark.parametrize("T", [200, 2240])
+def test_prescan_pairs_match_the_oracle(native_built, T):
+    """T = 2240: the rank runs as two token ranges and composes their pairs into its own."""
     from pla_b200.prefill import context_parallel as cp
-    T, Hg, H = 200, 1, 2
+    Hg, H = 1, 2
     q, k, v, gate, beta, A_log, dt_bias, _ = make(T, Hg, H, 11)
     ref = OracleSegmentKernels(q, k, v, gate, beta, A_log, dt_bias, D ** -0.5).prescan()
     kern = cp.CudaSegmentKernels(q.cuda(), k.cuda(), v.cuda(), gate.cuda(), beta.cuda(), A_log.cuda(), dt_bias.cuda(),
                                  D ** -0.5, True, False)
+    assert kern.parts == (2 if T == 2240 else 1)
     kern.prepare()
     mb = kern.prescan()
     kern.check()
@@ -38,7 +41,7 @@ def test_prescan_pairs_match_the_oracle(native_built):
     assert_state_close(mb[:, 1].cpu(), ref[:, 1], "transition M")
 
 
-@pytest.mark.parametrize("splits", [(400, 0, 333, 767), (64, 64), (1000,)])
+@pytest.mark.parametrize("splits", [(400, 0, 333, 767), (64, 64), (1000,), (2240, 2300), (2500,)])
 def test_emulated_ranks_match_single_pass_and_oracle(native_built, splits):
     from pla_b200._ops import ops
     from pla_b200.prefill import context_parallel as cp
@@ -92,13 +95,12 @@ def make_kda(T, H, seed):
     return q, k, v, gate, beta, A_log, dt_bias, S0
 
 
-@pytest.mark.parametrize("chunked", [False, True])
+@pytest.mark.parametrize("chunked,splits", [(False, (90, 37, 0, 61)), (True, (90, 37, 0, 61)), (True, (2240, 2100))])
 @pytest.mark.parametrize("lower_bound", [-5.0, None])
-def test_kda_emulated_ranks_match_oracle(native_built, lower_bound, chunked):
+def test_kda_emulated_ranks_match_oracle(native_built, lower_bound, chunked, splits):
     """KDA: prescan pairs of the token-recurrent kernel against the oracle, then ranks emulated one after
-    another against the serial oracle recurrence."""
+    another against the serial oracle recurrence. The long split runs every rank as two token ranges."""
     from pla_b200.prefill import context_parallel as cp
-    splits = (90, 37, 0, 61)
     T, H, W = sum(splits), 2, len(splits)
     q, k, v, gate, beta, A_log, dt_bias, S0 = make_kda(T, H, 31)
     dev = torch.device("cuda")
@@ -118,7 +120,9 @@ def test_kda_emulated_ranks_match_oracle(native_built, lower_bound, chunked):
             ref = OracleSegmentKernels(q[sl], k[sl], v[sl], gate[sl], beta[sl], A_log, dt_bias, D ** -0.5, is_kda=True,
                                        lower_bound=lower_bound).prescan()
             assert_state_close(plans[0].transfer[:, 0].cpu(), ref[:, 0], "offset B")
-            assert_state_close(plans[0].transfer[:, 1].cpu(), ref[:, 1], "transition M")
+            # over thousands of tokens the transition shrinks far below the offset, and its tf32 rounding errors
+            # (relative to its own small norm) grow with the chunk count; the states it produces are checked below
+            assert_state_close(plans[0].transfer[:, 1].cpu(), ref[:, 1], "transition M", tol=1e-3 if n < 1000 else 5e-3)
         lo += n
     gathered = torch.stack([p.transfer for p in plans])
     outs, state = [], None
