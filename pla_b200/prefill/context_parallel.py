@@ -50,6 +50,30 @@ def plan_rank_ranges(tokens: int, chains: int, n_sm: int, min_chunks: int = 16):
     return [min(tokens, (chunks * i // parts) * CHUNK) for i in range(parts)] + [tokens]
 
 
+_rank_plans: dict = {}
+
+
+def _rank_plan_tensors(T: int, H: int, device, split: bool):
+    """Device copies of a rank's range plan, kept per (tokens, heads, device): serving repeats the shapes, and
+    every small host-to-device copy is a stall on the launch path."""
+    key = (T, H, str(device), bool(split))
+    hit = _rank_plans.get(key)
+    if hit is not None:
+        return hit
+    offs = None
+    if split and device.type == "cuda" and T > 0:
+        offs = plan_rank_ranges(T, H, torch.cuda.get_device_properties(device).multi_processor_count)
+    parts = 1 if offs is None else len(offs) - 1
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
+    plan = dict(parts=parts, cu=i32([0, T] if offs is None else offs), skip_last=i32([0] * (parts - 1) + [-1]),
+                seg_first=i32([0, parts]), slot0=i32([0]), last_writes=i32([-1] * (parts - 1) + [0]),
+                eye=torch.eye(D, dtype=torch.float32, device=device).expand(H, D, D).contiguous() if parts > 1 else None)
+    if len(_rank_plans) >= 32:
+        _rank_plans.clear()
+    _rank_plans[key] = plan
+    return plan
+
+
 class CudaSegmentKernels:
     """Steps 1, 2 and 5 on the rank's GPU (pla_b200_gdn_prefill_chunked, stages 1 and 2). When the rank has
     fewer chains than SMs its tokens run as several ranges (``plan_rank_ranges``; ``split=False`` turns it off)."""
@@ -64,11 +88,8 @@ class CudaSegmentKernels:
     def _setup(self, q, v, split):
         T, H = v.shape[0], v.shape[1]
         self.T, self.H = T, H
-        offs = None
-        if split and q.is_cuda and T > 0:
-            offs = plan_rank_ranges(T, H, torch.cuda.get_device_properties(q.device).multi_processor_count)
-        self.parts = 1 if offs is None else len(offs) - 1
-        self.cu = torch.tensor([0, T] if offs is None else offs, dtype=torch.int32, device=q.device)
+        self.plan = _rank_plan_tensors(T, H, q.device, split)
+        self.parts, self.cu = self.plan["parts"], self.plan["cu"]
         self.max_chunks = (T + CHUNK - 1) // CHUNK
         self.out = torch.empty(T, H, D, dtype=q.dtype, device=q.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=q.device)
@@ -88,11 +109,8 @@ class CudaSegmentKernels:
     def _prescan_ranges(self, every_range: bool):
         dev = self.out.device
         self.pairs = torch.empty(self.parts + 1, self.H, 2, D, D, dtype=torch.float32, device=dev)
-        mask = None
-        if not every_range:     # the last range's pair is not needed when only the incoming states are wanted
-            mask = torch.zeros(self.parts, dtype=torch.int32, device=dev)
-            mask[-1] = -1
-        self._stage(2, True, None, self.pairs[:self.parts], mask)
+        # the last range's pair is not needed when only the incoming states are wanted
+        self._stage(2, True, None, self.pairs[:self.parts], None if every_range else self.plan["skip_last"])
 
     def prescan(self) -> torch.Tensor:
         dev = self.out.device
@@ -106,8 +124,7 @@ class CudaSegmentKernels:
         offset = self._ops.cp_fold_prefix(self.pairs, None, self.parts, self.status)
         only_m = self.pairs.clone()
         only_m[:, :, 0] = 0
-        eye = torch.eye(D, dtype=torch.float32, device=dev).expand(self.H, D, D).contiguous()
-        transition = self._ops.cp_fold_prefix(only_m, eye, self.parts, self.status)
+        transition = self._ops.cp_fold_prefix(only_m, self.plan["eye"], self.parts, self.status)
         return torch.stack([offset, transition], dim=1)
 
     def segment(self, state_in: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -118,13 +135,9 @@ class CudaSegmentKernels:
             return self.out, final[0]
         if self.pairs is None:
             self._prescan_ranges(False)
-        seg_first = torch.tensor([0, self.parts], dtype=torch.int32, device=dev)
-        slot0 = torch.zeros(1, dtype=torch.int32, device=dev)
-        states = self._ops.cp_fold_segments(self.pairs[:self.parts], seg_first, state_in[None].contiguous(), slot0,
-                                            self.status)
-        out_idx = torch.full((self.parts,), -1, dtype=torch.int32, device=dev)
-        out_idx[-1] = 0
-        self._stage(2, False, states, final, None, out_idx)
+        states = self._ops.cp_fold_segments(self.pairs[:self.parts], self.plan["seg_first"], state_in[None].contiguous(),
+                                            self.plan["slot0"], self.status)
+        self._stage(2, False, states, final, None, self.plan["last_writes"])
         return self.out, final[0]
 
     def check(self):
