@@ -261,6 +261,9 @@ typedef struct pla_b200_cp_fold_args {
   float* state_out;            /* [HV, 128, 128]: fold over ranks 0 .. rank-1 of S <- S M_j + B_j */
   int32_t HV, rank, world;
   int32_t* status;
+  int32_t compose;             /* 1: compose pairs 0 .. rank-1 into ONE pair instead (initial_state unused):
+                                  state_out = [HV, 2, 128, 128], offset (fold from zero) then transition
+                                  (M_0 M_1 ... M_{rank-1}); `rank` may equal `world` */
 } pla_b200_cp_fold_args;
 
 int pla_b200_cp_fold_prefix(const pla_b200_cp_fold_args* args, void* stream);

@@ -24,12 +24,20 @@ __global__ void __launch_bounds__(FOLD_THREADS) cp_fold_kernel(const pla_b200_cp
   extern __shared__ __align__(128) unsigned char smem_raw[];
   FoldSmem& sh = *reinterpret_cast<FoldSmem*>(smem_raw);
   const int tid = threadIdx.x;
-  const int rs = blockIdx.x % (D / ROWS), hv = blockIdx.x / (D / ROWS);
+  const int rs = blockIdx.x % (D / ROWS);
+  const int hv = (blockIdx.x / (D / ROWS)) % p.HV;
+  // compose mode: the second half of the grid carries the transition (rows of the identity through the M_j
+  // alone), the first half the offset (zero rows through the full pairs)
+  const bool transition = p.compose != 0 && blockIdx.x >= static_cast<unsigned>(p.HV) * (D / ROWS);
   const int row0 = rs * ROWS;
   const int col = tid & 127, rg = tid >> 7;   // this thread: column `col` of rows rg*8 .. rg*8+7
 
-  for (int i = tid; i < ROWS * D; i += FOLD_THREADS)
-    sh.s[i] = p.initial_state != nullptr ? p.initial_state[static_cast<int64_t>(hv) * TILE + row0 * D + i] : 0.0f;
+  for (int i = tid; i < ROWS * D; i += FOLD_THREADS) {
+    float x = 0.0f;
+    if (transition) x = (row0 + i / D == i % D) ? 1.0f : 0.0f;
+    else if (p.compose == 0 && p.initial_state != nullptr) x = p.initial_state[static_cast<int64_t>(hv) * TILE + row0 * D + i];
+    sh.s[i] = x;
+  }
   if (tid == 0) {
     mbar_init(&sh.bar, 1);
     fence_mbar_init();
@@ -44,7 +52,7 @@ __global__ void __launch_bounds__(FOLD_THREADS) cp_fold_kernel(const pla_b200_cp
     }
     float acc[8];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) acc[r] = pair[(row0 + rg * 8 + r) * D + col];   // B rows
+    for (int r = 0; r < 8; ++r) acc[r] = transition ? 0.0f : pair[(row0 + rg * 8 + r) * D + col];   // B rows
     const bool ok = mbar_wait(&sh.bar, j & 1);
     if (__syncthreads_or(!ok)) {
       if (tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_WAIT_TIMEOUT);
@@ -66,7 +74,10 @@ __global__ void __launch_bounds__(FOLD_THREADS) cp_fold_kernel(const pla_b200_cp
     for (int r = 0; r < 8; ++r) sh.s[(rg * 8 + r) * D + col] = acc[r];
     __syncthreads();
   }
-  for (int i = tid; i < ROWS * D; i += FOLD_THREADS) p.state_out[static_cast<int64_t>(hv) * TILE + row0 * D + i] = sh.s[i];
+  // plain fold: [HV, 128, 128]; compose: [HV, 2, 128, 128]
+  float* dst = p.state_out + (p.compose != 0 ? (static_cast<int64_t>(hv) * 2 + (transition ? 1 : 0)) * TILE
+                                             : static_cast<int64_t>(hv) * TILE) + row0 * D;
+  for (int i = tid; i < ROWS * D; i += FOLD_THREADS) dst[i] = sh.s[i];
 }
 
 // Ranges of one sequence inside one GPU: every range's incoming state, in order.
@@ -161,8 +172,8 @@ extern "C" int pla_b200_cp_fold_prefix(const pla_b200_cp_fold_args* args, void* 
   using namespace pla;
   PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
   const pla_b200_cp_fold_args& a = *args;
-  PLA_REQUIRE(a.HV > 0 && a.rank >= 0 && a.world > 0 && a.rank < a.world, PLA_B200_E_INVALID,
-              "fold needs HV > 0 and 0 <= rank < world");
+  PLA_REQUIRE(a.HV > 0 && a.rank >= 0 && a.world > 0 && (a.compose != 0 ? a.rank <= a.world : a.rank < a.world),
+              PLA_B200_E_INVALID, "fold needs HV > 0 and 0 <= rank < world (<= world when composing)");
   PLA_REQUIRE(a.state_out != nullptr && (a.rank == 0 || a.pairs != nullptr), PLA_B200_E_INVALID,
               "pairs and state_out are required");
   PLA_REQUIRE(a.rank == 0 || aligned16(a.pairs), PLA_B200_E_ALIGN, "pairs must be 16-byte aligned");
@@ -173,7 +184,7 @@ extern "C" int pla_b200_cp_fold_prefix(const pla_b200_cp_fold_args* args, void* 
     PLA_CUDA_OK(cudaFuncSetAttribute(cp_fold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(FoldSmem)));
     configured[dev] = true;
   }
-  cp_fold_kernel<<<static_cast<unsigned>(a.HV) * (D / ROWS), FOLD_THREADS, sizeof(FoldSmem),
+  cp_fold_kernel<<<static_cast<unsigned>(a.HV) * (D / ROWS) * (a.compose != 0 ? 2u : 1u), FOLD_THREADS, sizeof(FoldSmem),
                    static_cast<cudaStream_t>(stream)>>>(a);
   PLA_CUDA_OK(cudaGetLastError());
   return PLA_B200_OK;

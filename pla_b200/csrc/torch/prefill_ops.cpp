@@ -412,6 +412,28 @@ at::Tensor cp_fold_segments(const at::Tensor& pairs, const at::Tensor& seg_first
   return out;
 }
 
+// The first `count` pairs composed into one (offset, transition) pair: [H, 2, 128, 128].
+at::Tensor cp_compose_pairs(const at::Tensor& pairs, int64_t count, const Optional& status) {
+  check_cuda(pairs, "pairs");
+  TORCH_CHECK(pairs.scalar_type() == at::kFloat && pairs.is_contiguous() && pairs.dim() == 5 && pairs.size(2) == 2 &&
+                  pairs.size(3) == 128 && pairs.size(4) == 128,
+              "pairs must be contiguous fp32 [n, H, 2, 128, 128]");
+  TORCH_CHECK(count >= 0 && count <= pairs.size(0), "count out of range");
+  const int64_t H = pairs.size(1);
+  c10::cuda::CUDAGuard guard(pairs.device());
+  at::Tensor out = at::empty({H, 2, 128, 128}, pairs.options());
+  pla_b200_cp_fold_args f{};
+  f.pairs = pairs.data_ptr<float>();
+  f.state_out = out.data_ptr<float>();
+  f.HV = static_cast<int32_t>(H);
+  f.rank = static_cast<int32_t>(count);
+  f.world = static_cast<int32_t>(pairs.size(0));
+  f.compose = 1;
+  f.status = status.has_value() ? const_cast<int32_t*>(i32_ptr(status, "status")) : nullptr;
+  if (!bypass_exec()) check_abi(pla_b200_cp_fold_prefix(&f, stream_of(pairs)), "cp compose");
+  return out;
+}
+
 // Fold of the gathered (offset, transition) pairs of the ranks before `rank` into the state entering its range.
 at::Tensor cp_fold_prefix(const at::Tensor& pairs, const Optional& initial_state, int64_t rank, const Optional& status) {
   check_cuda(pairs, "pairs");
@@ -533,6 +555,7 @@ TORCH_LIBRARY_FRAGMENT(pla_b200, m) {
       &pla_ops::causal_conv_prefill);
   m.def("cp_fold_prefix(Tensor pairs, Tensor? initial_state, int rank, Tensor(a!)? status) -> Tensor",
         &pla_ops::cp_fold_prefix);
+  m.def("cp_compose_pairs(Tensor pairs, int count, Tensor(a!)? status) -> Tensor", &pla_ops::cp_compose_pairs);
   m.def(
       "kda_prefill_chunked(Tensor q, Tensor k, Tensor v, Tensor gate, Tensor beta, Tensor A_log, Tensor dt_bias, "
       "Tensor(a!) out, Tensor cu_seqlens, Tensor(b!)? state_in, Tensor? in_indices, Tensor(c!)? state_out, "

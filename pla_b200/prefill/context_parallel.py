@@ -67,7 +67,7 @@ def _rank_plan_tensors(T: int, H: int, device, split: bool):
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
     plan = dict(parts=parts, cu=i32([0, T] if offs is None else offs), skip_last=i32([0] * (parts - 1) + [-1]),
                 seg_first=i32([0, parts]), slot0=i32([0]), last_writes=i32([-1] * (parts - 1) + [0]),
-                eye=torch.eye(D, dtype=torch.float32, device=device).expand(H, D, D).contiguous() if parts > 1 else None)
+                )
     if len(_rank_plans) >= 32:
         _rank_plans.clear()
     _rank_plans[key] = plan
@@ -94,7 +94,7 @@ class CudaSegmentKernels:
         self.out = torch.empty(T, H, D, dtype=q.dtype, device=q.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=q.device)
         self.ws = None
-        self.pairs = None       # [parts + 1, H, 2, 128, 128]: pairs of this rank's ranges (+ one unused entry)
+        self.pairs = None       # [parts, H, 2, 128, 128]: pairs of this rank's ranges
 
     def _stage(self, stage, prescan, state_in, state_out, range_mask=None, out_indices=None):
         q, k, v, gate, beta, A_log, dt_bias = self.a
@@ -108,7 +108,7 @@ class CudaSegmentKernels:
 
     def _prescan_ranges(self, every_range: bool):
         dev = self.out.device
-        self.pairs = torch.empty(self.parts + 1, self.H, 2, D, D, dtype=torch.float32, device=dev)
+        self.pairs = torch.empty(self.parts, self.H, 2, D, D, dtype=torch.float32, device=dev)
         # the last range's pair is not needed when only the incoming states are wanted
         self._stage(2, True, None, self.pairs[:self.parts], None if every_range else self.plan["skip_last"])
 
@@ -118,14 +118,10 @@ class CudaSegmentKernels:
             mb = torch.empty(1, self.H, 2, D, D, dtype=torch.float32, device=dev)
             self._stage(2, True, None, mb)
             return mb[0]
-        # pairs of all ranges, then the rank's pair: B from a zero state through all of them, M from the identity
-        # through the transitions alone (offsets zeroed)
+        # pairs of all ranges, then the rank's pair in one launch: the offset from a zero state through all of them,
+        # the transition from the identity through the M_j alone
         self._prescan_ranges(True)
-        offset = self._ops.cp_fold_prefix(self.pairs, None, self.parts, self.status)
-        only_m = self.pairs.clone()
-        only_m[:, :, 0] = 0
-        transition = self._ops.cp_fold_prefix(only_m, self.plan["eye"], self.parts, self.status)
-        return torch.stack([offset, transition], dim=1)
+        return self._ops.cp_compose_pairs(self.pairs[:self.parts], self.parts, self.status)
 
     def segment(self, state_in: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         dev = self.out.device

@@ -152,4 +152,12 @@ def test_fold_kernel_matches_torch_fold(native_built):
             got = ops.cp_fold_prefix(dp, dinit, rank, status)
             want = cp.fold_transfers(init, pairs, rank)
             torch.testing.assert_close(got.cpu(), want, rtol=1e-4, atol=1e-5)
+    # composition of the first n pairs into one: applying it equals applying the n pairs in turn
+    for n in range(W + 1):
+        one = ops.cp_compose_pairs(dp, n, status).cpu()
+        assert one.shape == (H, 2, D, D)
+        want = cp.fold_transfers(S0, pairs, n)
+        torch.testing.assert_close(torch.baddbmm(one[:, 0], S0, one[:, 1]), want, rtol=1e-4, atol=1e-5)
+        if n == 0:
+            assert torch.equal(one, cp.identity_transfer(H, "cpu"))
     assert status.item() == 0
