@@ -1,7 +1,7 @@
 """Generates the golden fixtures by running the REFERENCE's own PyTorch oracles.
 
 Run where the reference tree is mounted:
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference [klast|replay|prefill|sglang|mega|conv]
 Nothing from the reference is copied: its functions are loaded from the tree at
 run time, fed the seeded inputs of ``cases.py`` and only their outputs are saved.
 """
@@ -19,7 +19,9 @@ HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE))
 import cases  # noqa: E402
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if __name__ == "__main__" and len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py /path/to/reference [klast|replay|prefill|sglang|mega|conv]")
+REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("reference")
 
 
 def load_function(path: Path, name: str, namespace: dict):
