@@ -43,9 +43,11 @@ SEED = 20261125 + 1
 METRIC = "gdn_decode_state_bandwidth_B256"
 UNIT = "GB/s"
 WORKLOAD = "config1: GDN decode B=256 Hqk=16 HV=32 d=128, fp32 k-last pool 1024 slots, random non-consecutive slots"
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
-# profiles/ (captured at B=64 and scaled by the tiles processed); None until captured.
-TRAFFIC_BYTES_PER_TILE = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the full workload (B=256, 32 heads: 8192 tiles),
+# from the one-pass ncu capture summarised in profiles/: 541.4 MB read + 476.2 MB written = 1017.6 MB for
+# 1073.7 MB of algorithmic bytes (the last ~60 MB written are still dirty in L2 when the kernel ends).
+# Reported for that workload only (smaller launches leave a larger share of their writes in L2).
+TRAFFIC_BYTES_FULL_LAUNCH = 541374720 + 476201728
 
 
 def measured_peaks():
@@ -284,7 +286,7 @@ def run_ours(args):
             "gpu_launches": args.steps,
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_source": f"of {peak_src}",
-                         "traffic": (None if TRAFFIC_BYTES_PER_TILE is None else TRAFFIC_BYTES_PER_TILE * B * hvl),
+                         "traffic": TRAFFIC_BYTES_FULL_LAUNCH if (B == 256 and hvl == HV and world == 1) else None,
                          "algorithmic_bytes_per_launch": local_state_bytes},
             "cpu_baseline": cpu,
             "clocks": clocks,
