@@ -1,0 +1,107 @@
+"""Parity at the full benchmark sizes through size-independent properties: the decode step is jointly linear in
+(state, v); slots a step does not address stay bit-identical; a sequence's prefill result does not depend on the
+batch around it; the chunked evaluation agrees with the exact token recurrence on the GPU; sampled requests
+against the CPU oracle."""
+import math
+
+import pytest
+import torch
+
+from helpers import assert_out_close, assert_state_close
+from oracle import decode as odec
+
+pytestmark = pytest.mark.gpu
+D = 128
+
+
+def test_config1_decode_is_linear_in_state_and_v_and_leaves_other_slots_alone(native_built):
+    from pla_b200.decode import fused_sigmoid_gating_delta_rule_forward_k_last as forward
+    B, H, HV, SLOTS = 256, 16, 32, 1024
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(20261125 + 1)
+    rn = lambda *s: torch.randn(*s, generator=g, device=dev)
+    q, k = rn(1, B, H, D).bfloat16(), rn(1, B, H, D).bfloat16()
+    a, b = rn(1, B, HV).bfloat16(), rn(1, B, HV).bfloat16()
+    A_log = torch.rand(HV, generator=g, device=dev) * math.log(16.0)
+    dt_bias = (rn(HV) * 0.1).bfloat16()
+    idx = torch.randperm(SLOTS, generator=g, device=dev)[:B].to(torch.int32)
+    cu = torch.arange(B + 1, dtype=torch.int32, device=dev)
+    # v1, v2 and v1 + v2 all exactly representable in bf16: multiples of 1/8 below 4
+    v1 = (torch.randint(-16, 17, (1, B, HV, D), generator=g, device=dev).float() / 8).bfloat16()
+    v2 = (torch.randint(-16, 17, (1, B, HV, D), generator=g, device=dev).float() / 8).bfloat16()
+    S1 = rn(SLOTS, HV, D, D) * 0.02
+    S2 = rn(SLOTS, HV, D, D) * 0.02
+    outs, pools = [], []
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    for S, v in ((S1, v1), (S2, v2), (S1 + S2, (v1.float() + v2.float()).bfloat16())):
+        pool = S.clone()
+        o = forward(A_log, a, dt_bias, 1.0, 20.0, q, k, v, b, pool, idx, D ** -0.5, True, cu, False, False, None, None,
+                    None, None, status=status)
+        outs.append(o.float())
+        pools.append(pool)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    used = idx.long()
+    lin = (pools[0][used] + pools[1][used] - pools[2][used]).norm() / pools[2][used].norm()
+    assert lin.item() <= 1e-5, lin.item()
+    # outputs are rounded to bf16 once each: the sum of two roundings against one
+    assert (outs[0] + outs[1] - outs[2]).abs().max().item() <= 2e-2
+    others = torch.ones(SLOTS, dtype=torch.bool, device=dev)
+    others[used] = False
+    assert torch.equal(pools[0][others], S1[others]) and torch.equal(pools[2][others], (S1 + S2)[others])
+    # four sampled requests of the full launch against the CPU oracle
+    pick = [0, 77, 128, 255]
+    sel = torch.tensor(pick, device=dev)
+    exp_out, exp_state, _ = odec.klast_forward(
+        q=q[0, sel].cpu(), k=k[0, sel].cpu(), v=v1[0, sel].cpu(), a=a[0, sel].cpu(), b=b[0, sel].cpu(), A_log=A_log.cpu(),
+        dt_bias=dt_bias.cpu(), state=S1[used[sel]].cpu(), slot_indices=list(range(len(pick))), lengths=[1] * len(pick),
+        scale=D ** -0.5)
+    assert_out_close(outs[0][0, sel].cpu(), exp_out)
+    assert_state_close(pools[0][used[sel]].cpu(), exp_state)
+
+
+def test_config3_prefill_sequences_do_not_depend_on_the_batch_and_match_the_recurrence(native_built):
+    from pla_b200._ops import ops
+    from pla_b200.prefill.flashqla import ops as fq
+    dev = "cuda"
+    g = torch.Generator().manual_seed(20261125 + 3)
+    lengths = torch.randint(512, 8193, (8,), generator=g).tolist()
+    T, Hg, H = sum(lengths), 16, 32
+    offs = [0]
+    for n in lengths:
+        offs.append(offs[-1] + n)
+    gd = torch.Generator(device=dev).manual_seed(7)
+    rn = lambda *s: torch.randn(*s, generator=gd, device=dev)
+    q, k, v = rn(1, T, Hg, D).bfloat16(), rn(1, T, Hg, D).bfloat16(), rn(1, T, H, D).bfloat16()
+    ga, gb = rn(T, H).bfloat16(), rn(T, H).bfloat16()
+    A_log = torch.rand(H, generator=gd, device=dev) * math.log(16.0)
+    dt_bias = rn(H) * 0.1
+    pool0 = rn(16, H, D, D) * 0.02
+    slots = torch.randperm(16, generator=g)[:8].to(torch.int32).to(dev)
+
+    def run(sl, offsets, idx, pool):
+        return fq.chunk_gated_delta_rule_fwd(
+            q[:, sl], k[:, sl], v[:, sl], None, None, initial_state=pool, initial_state_indices=idx,
+            cu_seqlens=torch.tensor(offsets, dtype=torch.int32, device=dev), output_final_state=False, auto_cp=False,
+            normalize_qk=True, raw_cu_seqlens=tuple(offsets), raw_gate_a=ga[sl], raw_beta_b=gb[sl], A_log=A_log,
+            dt_bias=dt_bias)[2][0]
+
+    pool = pool0.clone()
+    out = run(slice(0, T), offs, slots, pool)
+    for s in (2, 7):                                   # the same sequences alone: bit-identical rows and states
+        alone = pool0.clone()
+        o = run(slice(offs[s], offs[s + 1]), [0, lengths[s]], slots[s:s + 1], alone)
+        assert torch.equal(o, out[offs[s]:offs[s + 1]])
+        assert torch.equal(alone[slots[s].item()], pool[slots[s].item()])
+    # the exact token recurrence on the GPU over the whole batch
+    ref_pool = pool0.clone()
+    ref = torch.empty(T, H, D, dtype=torch.bfloat16, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.prefill_recurrent(q[0], k[0], v[0], ga, gb, A_log, dt_bias, ref, torch.tensor(offs, dtype=torch.int32, device=dev),
+                          ref_pool, slots, None, None, False, False, True, D ** -0.5, None, False, True, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert_out_close(out, ref, "chunked vs token recurrence")
+    assert_state_close(pool[slots.long()], ref_pool[slots.long()], "chunked vs token recurrence")
+    untouched = [s for s in range(16) if s not in slots.tolist()]
+    assert torch.equal(pool[untouched], pool0[untouched])
