@@ -42,6 +42,12 @@ constexpr int PM_BYTES = C * C * 4;     // P: rows = token i, K = token j
 constexpr int VEC_BYTES = 4 * C * 4;    // G[64], beta[64], exp(G)[64], exp(G_last - G)[64]
 constexpr int HBLOB = KQ_BYTES + KNT_BYTES;            // per (chunk, q/k head)
 constexpr int VBLOB = TM_BYTES + PM_BYTES + VEC_BYTES;  // per (chunk, value head)
+// T and P are lower triangular (diagonal included). In their images ([K / 4 = column group jg][row i][4 columns])
+// the rows i < 4 jg of column group jg are all zero: they are neither written to the workspace nor copied back.
+// Column group jg is one contiguous piece, rows 4 jg .. 63.
+__host__ __device__ constexpr int tri_piece_offset(int jg) { return (jg * C + 4 * jg) * 16; }
+__host__ __device__ constexpr int tri_piece_bytes(int jg) { return (C - 4 * jg) * 16; }
+constexpr int TRI_BYTES = 16 * (C / 4 * C - 4 * (C / 4) * (C / 4 - 1) / 2);   // 8704: all sixteen pieces
 
 __host__ __device__ inline int64_t ws_hblob(int64_t gc, int h, int H) { return (gc * H + h) * HBLOB; }
 __host__ __device__ inline int64_t ws_vblob(int64_t max_chunks, int H, int HV, int64_t gc, int hv) {
@@ -363,6 +369,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 2) gdn_chunk_prepare_kernel(cons
             reinterpret_cast<float4*>(ws + ws_lmat(p.max_chunks, p.H, p.HV, gc, hv)) + i_row * (C / 4) + ch * 8;
 #pragma unroll
         for (int jc = 0; jc < 8; ++jc) {
+          if (32 * ch + 4 * jc >= i_row) continue;   // a piece at or beyond the diagonal: all zero, never read
           float x[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
@@ -375,6 +382,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 2) gdn_chunk_prepare_kernel(cons
         float4* __restrict__ Pimg = reinterpret_cast<float4*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv) + TM_BYTES);
 #pragma unroll
         for (int jc = 0; jc < 8; ++jc) {
+          if (32 * ch + 4 * jc > i_row) continue;    // rows above a column group's piece (tri_piece_offset)
           float x[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
@@ -410,9 +418,10 @@ __global__ void __launch_bounds__(128) chunk_inverse_kernel(const pla_b200_gdn_c
     const float4* Lg = reinterpret_cast<const float4*>(ws + ws_lmat(p.max_chunks, p.H, p.HV, gc, hv));
 #pragma unroll
     for (int i = t6; i < C * C / 4; i += 64)
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&Ls[s][(i >> 4) * L_STRIDE + (i & 15) * 4])),
-                   "l"(Lg + i)
-                   : "memory");
+      if (4 * (i & 15) < (i >> 4))   // row i >> 4, columns 4 (i & 15) ..: pieces at or beyond the diagonal are never read
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&Ls[s][(i >> 4) * L_STRIDE + (i & 15) * 4])),
+                     "l"(Lg + i)
+                     : "memory");
   }
   asm volatile("cp.async.wait_all;" ::: "memory");
   __syncthreads();
@@ -422,8 +431,10 @@ __global__ void __launch_bounds__(128) chunk_inverse_kernel(const pla_b200_gdn_c
   float Tcol[C];
   invert_column(Ls[s], cb, col, Tcol);
   float* Timg = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv));
+  // only the rows of the column group's piece (tri_piece_offset); the rows above it are zero and are not stored
 #pragma unroll
-  for (int i = 0; i < C; ++i) Timg[(col >> 2) * (C * 4) + i * 4 + (col & 3)] = tc05::to_tf32(Tcol[i]);
+  for (int i = 0; i < C; ++i)
+    if (i >= (col & ~3)) Timg[(col >> 2) * (C * 4) + i * 4 + (col & 3)] = tc05::to_tf32(Tcol[i]);
 }
 
 // ================================================================================================
@@ -709,6 +720,7 @@ __global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(
       float4* __restrict__ Lg = reinterpret_cast<float4*>(ws + ws_lmat(p.max_chunks, p.H, p.HV, gc, h)) + i_row * (C / 4) + cs * 4;
 #pragma unroll
       for (int jc = 0; jc < 4; ++jc) {
+        if (cs * 16 + jc * 4 >= i_row) continue;     // a piece at or beyond the diagonal: all zero, never read
         float x[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) x[u] = (cs * 16 + jc * 4 + u < i_row) ? bi * d0[jc * 4 + u] : 0.0f;
@@ -718,6 +730,7 @@ __global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(
       float4* __restrict__ Pimg = reinterpret_cast<float4*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, h) + TM_BYTES);
 #pragma unroll
       for (int jc = 0; jc < 4; ++jc) {
+        if (cs * 16 + jc * 4 > i_row) continue;      // rows above a column group's piece (tri_piece_offset)
         float x[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -877,6 +890,11 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
     sh.abort = 0;
     fence_mbar_init();
   }
+  // rows of the T and P images above their triangular pieces: zero for the whole run (the copies never touch them)
+  for (int i = tid; i < (TM_BYTES + PM_BYTES) / 16; i += CHAIN_THREADS)
+    (i < TM_BYTES / 16 ? reinterpret_cast<uint4*>(sh.tm)[i] : reinterpret_cast<uint4*>(sh.pm)[i - TM_BYTES / 16]) =
+        make_uint4(0u, 0u, 0u, 0u);
+  fence_async_smem();
   if (warp == 1) tc05::tmem_alloc(&sh.tmem_base, 512);
   tc05::fence_before_sync();
   __syncthreads();
@@ -891,13 +909,22 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
         mbar_expect_tx(&sh.full_kq, KQ_BYTES);
         bulk_load(sh.kq, ws + ws_hblob(gc0 + c, h, p.H), KQ_BYTES, &sh.full_kq);
       };
+      // T (and, for GDN, P) come back as the sixteen pieces of their lower triangles; the rows above the pieces
+      // were zeroed once when the CTA started
+      auto load_tri = [&](float* dst, const unsigned char* src, uint64_t* bar) {
+#pragma unroll 1
+        for (int jg = 0; jg < C / 4; ++jg)
+          bulk_load(reinterpret_cast<unsigned char*>(dst) + tri_piece_offset(jg), src + tri_piece_offset(jg),
+                    tri_piece_bytes(jg), bar);
+      };
       auto load_t = [&](int c) {
-        mbar_expect_tx(&sh.full_t, TM_BYTES);
-        bulk_load(sh.tm, ws + ws_vblob(p.max_chunks, p.H, p.HV, gc0 + c, hv), TM_BYTES, &sh.full_t);
+        mbar_expect_tx(&sh.full_t, TRI_BYTES);
+        load_tri(sh.tm, ws + ws_vblob(p.max_chunks, p.H, p.HV, gc0 + c, hv), &sh.full_t);
       };
       auto load_pk = [&](int c) {
-        mbar_expect_tx(&sh.full_pk, PM_BYTES + KNT_BYTES);
-        bulk_load(sh.pm, ws + ws_vblob(p.max_chunks, p.H, p.HV, gc0 + c, hv) + TM_BYTES, PM_BYTES, &sh.full_pk);
+        const unsigned char* pm_g = ws + ws_vblob(p.max_chunks, p.H, p.HV, gc0 + c, hv) + TM_BYTES;
+        mbar_expect_tx(&sh.full_pk, TRI_BYTES + KNT_BYTES);
+        load_tri(sh.pm, pm_g, &sh.full_pk);
         bulk_load(sh.knt, ws + ws_hblob(gc0 + c, h, p.H) + KQ_BYTES, KNT_BYTES, &sh.full_pk);
       };
       auto load_vec = [&](int c) {
