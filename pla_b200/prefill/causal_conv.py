@@ -4,6 +4,7 @@ counterpart of the conv that the reference fuses into its decode step,
 src/decode/k-last/fused_kda_decode_mega_kernel.cuh:36-79)."""
 from __future__ import annotations
 
+import weakref
 from typing import Optional
 
 import torch
@@ -14,17 +15,18 @@ _weight_cache: dict = {}
 
 
 def _taps_fp32(weight: torch.Tensor) -> torch.Tensor:
-    """[channels, 4] fp32 copy of the taps, cached per weight tensor and version (weights do not change while serving)."""
+    """[channels, 4] fp32 copy of the taps, cached per live weight tensor and version (weights do not change while
+    serving). The entry holds a weak reference to the tensor it was made from: a new tensor that happens to reuse
+    the address and id of a freed one never matches."""
     if weight.dtype == torch.float32 and weight.is_contiguous():
         return weight
-    key = (weight.data_ptr(), weight._version, tuple(weight.shape), weight.dtype, str(weight.device))
     hit = _weight_cache.get(id(weight))
-    if hit is not None and hit[0] == key:
-        return hit[1]
+    if hit is not None and hit[0]() is weight and hit[1] == weight._version:
+        return hit[2]
     if len(_weight_cache) >= 64:
         _weight_cache.clear()
     taps = weight.float().contiguous()
-    _weight_cache[id(weight)] = (key, taps)
+    _weight_cache[id(weight)] = (weakref.ref(weight), weight._version, taps)
     return taps
 
 
