@@ -122,3 +122,27 @@ def test_cuda_conv_contract_errors(native_built):
                                 None, status)
     torch.cuda.synchronize()
     assert status.item() == 8 and torch.count_nonzero(y) == 0 and torch.all(state == 1)   # bad slot: flagged, nothing kept
+
+
+@pytest.mark.gpu
+def test_cuda_conv_empty_inputs(native_built):
+    """No rows, no sequences, only empty sequences: nothing faults, rows outside every sequence are zero and the
+    histories stay as they were."""
+    from pla_b200._ops import ops
+    w = torch.ones(64, 4, device="cuda")
+    state = torch.full((3, 64, 3), 2.0, dtype=torch.bfloat16, device="cuda")
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    y = ops.causal_conv_prefill(torch.zeros(0, 64, dtype=torch.bfloat16, device="cuda"), w, None, state, i32([0, 0]), i32([1]),
+                                None, True, False, None, None)
+    assert y.shape == (0, 64)
+    x = torch.ones(70, 64, dtype=torch.bfloat16, device="cuda")
+    y = ops.causal_conv_prefill(x, w, None, state, i32([0]), i32([]), None, True, False, None, None)
+    assert torch.count_nonzero(y) == 0
+    y = ops.causal_conv_prefill(x, w, None, state, i32([0, 0, 0]), i32([2, 0]), None, True, False, None, None)
+    torch.cuda.synchronize()
+    assert torch.count_nonzero(y) == 0 and torch.all(state == 2.0)
+    # one row after two empty sequences: history 2,2,2 then the row: 2 + 2 + 2 + 1 = 7, no activation
+    y = ops.causal_conv_prefill(x[:1], w, None, state, i32([0, 0, 0, 1]), i32([2, 0, 1]), None, False, False, None, None)
+    torch.cuda.synchronize()
+    assert torch.all(y == 7.0) and torch.all(state[1, :, 2] == 1.0) and torch.all(state[1, :, :2] == 2.0)
+    assert torch.all(state[0] == 2.0) and torch.all(state[2] == 2.0)
