@@ -105,3 +105,51 @@ def test_config3_prefill_sequences_do_not_depend_on_the_batch_and_match_the_recu
     assert_state_close(pool[slots.long()], ref_pool[slots.long()], "chunked vs token recurrence")
     untouched = [s for s in range(16) if s not in slots.tolist()]
     assert torch.equal(pool[untouched], pool0[untouched])
+
+
+def test_config2_verify_then_commit_at_full_size(native_built):
+    """ReplaySSM at the benchmark size (32 heads, 64 request rows x 4 draft tokens, 512 pages): verify leaves the
+    checkpoints alone, and the committed checkpoints and conv histories equal the fp64 fold of the records the
+    device wrote, for every request."""
+    from types import SimpleNamespace
+
+    import numpy as np
+
+    import cases
+    from oracle import replay as orep
+    from pla_b200.decode.kda_replayssm_vllm import KDAReplayCommitContext, KDAReplayRecords, kda_replay_verify
+    H, N, Q, pages = 32, 64, 4, 512
+    rs = np.random.RandomState(20261125 + 2)
+    layer = cases.replay_layer(rs, pages, H, Q, "SD", device="cuda")
+    x = cases.replay_inputs(rs, H, N * Q, device="cuda")
+    layer.replay_records = KDAReplayRecords.allocate(N, H, Q, "cuda")
+    slots = torch.tensor((rs.permutation(pages - 1)[:N] + 1).astype("int32"), device="cuda")
+    cu = torch.arange(0, N * Q + 1, Q, dtype=torch.int32, device="cuda")
+    sampled = torch.tensor(rs.randint(1, Q + 1, N).astype("int32"), device="cuda")
+    out = torch.empty(N * Q, H * D, dtype=torch.bfloat16, device="cuda")
+    ctx = KDAReplayCommitContext.create([layer], Q, N, conv_state_layout="SD")
+    old_state = layer.kv_cache[1].clone()
+    old_conv = cases.conv_ds(layer).clone()
+    kw = {k_: v_ for k_, v_ in x.items() if k_ != "storage"}
+    kda_replay_verify(**kw, conv_state=layer.kv_cache[0], checkpoint_state=layer.kv_cache[1],
+                      records=layer.replay_records, query_start_loc=cu, state_indices=slots, conv_state_layout="SD",
+                      out=out)
+    torch.cuda.synchronize()
+    assert torch.equal(layer.kv_cache[1], old_state) and torch.equal(cases.conv_ds(layer), old_conv)
+    assert torch.isfinite(out.float()).all()
+    plan = ctx.commit(sampled, slots, cu, token_capacity=N * Q)
+    torch.cuda.synchronize()
+    plan_l = [getattr(plan, k).tolist() for k in ("commit_lens", "final_state_indices", "boundary_state_indices",
+                                                  "boundary_recovery_lens")]
+    assert plan_l[0] == sampled.tolist()
+    rec = layer.replay_records
+    host = SimpleNamespace(**{k: getattr(rec, k).cpu() for k in ("rawv", "rawk", "g", "beta", "conv")})
+    state, conv = orep.commit_apply(old_state.cpu(), old_conv.cpu(), host, plan_l, slots.tolist())
+    got = layer.kv_cache[1].cpu()
+    used = slots.long().cpu()
+    err = ((got[used] - state[used]).norm() / state[used].norm()).item()
+    assert err <= 5e-6, err
+    others = torch.ones(pages, dtype=torch.bool)
+    others[used] = False
+    assert torch.equal(got[others], old_state.cpu()[others])
+    assert torch.equal(cases.conv_ds(layer).cpu(), conv)
