@@ -153,3 +153,49 @@ def test_config2_verify_then_commit_at_full_size(native_built):
     others[used] = False
     assert torch.equal(got[others], old_state.cpu()[others])
     assert torch.equal(cases.conv_ds(layer).cpu(), conv)
+
+
+@pytest.mark.parametrize("kda", [False, True])
+def test_config4_token_ranges_match_single_chains_at_full_size(native_built, kda):
+    """One long sequence (GDN 64K tokens, 8 / 24 heads; KDA 128K tokens, 32 heads, weak softplus decay so that the
+    transitions of the ranges matter): running it as token ranges inside the GPU gives the outputs and the final
+    state of the single chain per head."""
+    dev = "cuda"
+    T, Hg, H = (131072, 32, 32) if kda else (65536, 8, 24)
+    g = torch.Generator(device=dev).manual_seed(44)
+    rn = lambda *s: torch.randn(*s, generator=g, device=dev)
+    q = torch.nn.functional.normalize(rn(T, Hg, D), dim=-1).bfloat16()
+    k = torch.nn.functional.normalize(rn(T, Hg, D), dim=-1).bfloat16()
+    v = rn(T, H, D).bfloat16()
+    gate = (rn(T, H, D) if kda else rn(T, H)).bfloat16()
+    # small beta and very weak decay: erasure and decay over a whole range stay of order one, so the state entering
+    # a range is still visible at its end (with the benchmark's gates it is forgotten and the two runs are bit-equal)
+    beta = (rn(T, H) - (6.0 if kda else 4.0)).bfloat16()  # KDA ranges are 43K tokens long
+    u = torch.rand(H, generator=g, device=dev)
+    A_log = -9.0 + u
+    dt_bias = rn(H, D) * 0.1 if kda else rn(H) * 0.1
+    S0 = rn(1, H, D, D) * 0.5
+    slot0 = torch.zeros(1, dtype=torch.int32, device=dev)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    res = {}
+    for auto_cp in (False, True):
+        pool = S0.clone()
+        if kda:
+            from pla_b200.prefill.flashkdapro import flashkda_fwd
+            out = torch.empty(T, H, D, dtype=torch.bfloat16, device=dev)
+            status = torch.zeros(1, dtype=torch.int32, device=dev)
+            flashkda_fwd(q, k, v, gate, beta, A_log, dt_bias, out, None, None, state_pool=pool, state_indices=slot0,
+                         raw_cu_seqlens=(0, T), backend="chunked", status=status, auto_cp=auto_cp)
+            assert status.item() == 0
+        else:
+            from pla_b200.prefill.flashqla import ops as fq
+            out = fq.chunk_gated_delta_rule_fwd(q[None], k[None], v[None], None, None, initial_state=pool,
+                                                initial_state_indices=slot0, cu_seqlens=cu, output_final_state=False,
+                                                auto_cp=auto_cp, normalize_qk=True, raw_cu_seqlens=(0, T),
+                                                raw_gate_a=gate, raw_beta_b=beta, A_log=A_log, dt_bias=dt_bias)[2][0]
+        torch.cuda.synchronize()
+        res[auto_cp] = (out.float(), pool)
+    assert torch.isfinite(res[True][0]).all()
+    assert not torch.equal(res[True][0], res[False][0])          # the ranges really ran (different rounding)
+    assert_out_close(res[True][0], res[False][0], "ranges vs single chains")
+    assert_state_close(res[True][1], res[False][1], "ranges vs single chains")
