@@ -489,7 +489,9 @@ extern "C" int pla_b200_decode_klast(const pla_b200_klast_args* args, void* stre
               "state dtype must be fp32 or bf16");
   PLA_REQUIRE(a.state == nullptr || a.state_slot_stride >= static_cast<int64_t>(a.HV) * 16384, PLA_B200_E_INVALID,
               "state slot pitch must cover HV*128*128 elements");
-  PLA_REQUIRE(a.state == nullptr || (aligned16(a.state) && a.state_slot_stride % 4 == 0), PLA_B200_E_ALIGN,
+  PLA_REQUIRE(a.state == nullptr ||
+                  (aligned16(a.state) && a.state_slot_stride % (a.state_dtype == PLA_B200_F32 ? 4 : 8) == 0),
+              PLA_B200_E_ALIGN,
               "state pool base and slot pitch must be 16-byte aligned");
   PLA_REQUIRE(a.state_out == nullptr || (aligned16(a.state_out) && (a.prescan || (a.state_out_slot_stride % 4 == 0 &&
                                          a.state_out_slot_stride >= static_cast<int64_t>(a.HV) * 16384))),
@@ -507,11 +509,15 @@ extern "C" int pla_b200_decode_klast(const pla_b200_klast_args* args, void* stre
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // rows_per_cta: 0 = pick (streaming kernel when the call qualifies), 16 = streaming kernel or error,
   // 32/64/128 = the one-block-per-CTA kernel.
-  if (a.rows_per_cta == 16 || a.rows_per_cta == 1)
+  if (a.rows_per_cta == 16 || a.rows_per_cta == 17 || a.rows_per_cta == 1)
     PLA_REQUIRE(klast_stream_eligible(a), PLA_B200_E_INVALID,
                 "rows_per_cta=16 / 1 select the single-token decode kernels, which need a plain single-token call");
-  if (a.rows_per_cta == 1) return launch_klast_rows(a, s);
-  if ((a.rows_per_cta == 0 || a.rows_per_cta == 16) && klast_stream_eligible(a)) return launch_klast_stream(a, s);
+  if (a.rows_per_cta == 1) {
+    PLA_REQUIRE(a.state_dtype == PLA_B200_F32, PLA_B200_E_INVALID, "rows_per_cta=1 needs an fp32 pool");
+    return launch_klast_rows(a, s);
+  }
+  if ((a.rows_per_cta == 0 || a.rows_per_cta == 16 || a.rows_per_cta == 17) && klast_stream_eligible(a))
+    return launch_klast_stream(a, s);
   if (a.act_dtype == PLA_B200_BF16)
     return a.is_kda ? launch_shape<__nv_bfloat16, true>(a, s) : launch_shape<__nv_bfloat16, false>(a, s);
   return a.is_kda ? launch_shape<__half, true>(a, s) : launch_shape<__half, false>(a, s);
@@ -524,7 +530,7 @@ extern "C" int pla_b200_prefill_recurrent(const pla_b200_klast_args* args, void*
   PLA_REQUIRE(args->slot_row_stride == 0 && args->cache == nullptr && args->parents == nullptr,
               PLA_B200_E_INVALID, "prefill takes no snapshot cache, parent table or 2-D slot table");
   pla_b200_klast_args a = *args;
-  if (a.rows_per_cta == 0 || a.rows_per_cta == 16) a.rows_per_cta = 32;  // most CTAs per sequence
+  if (a.rows_per_cta == 0 || a.rows_per_cta == 16 || a.rows_per_cta == 17) a.rows_per_cta = 32;  // most CTAs per sequence
   if (a.t_max < 2) a.t_max = 2;                                         // always the multi-step kernel
   return pla_b200_decode_klast(&a, stream);
 }

@@ -41,6 +41,14 @@ KLAST_CASES = {
     "gdn_tree":          dict(mode="tree", is_kda=False, H=2, HV=2, B=3, T=6, act="bf16"),
     "gdn_ragged":        dict(mode="ragged", is_kda=False, H=2, HV=4, B=3, T=4, act="bf16"),
     "kda_ragged":        dict(mode="ragged", is_kda=True, H=2, HV=2, B=3, T=6, act="f16"),
+    # bf16 state pools (and snapshot caches), the second half of the reference's state_dtype parametrisation
+    # (tests/test_k_last_state_dtype.py:159-163)
+    "gdn_decode_sbf16":    dict(mode="decode", is_kda=False, H=2, HV=4, B=3, T=1, act="bf16", state="bf16"),
+    "kda_decode_sbf16":    dict(mode="decode", is_kda=True, H=2, HV=2, B=3, T=1, act="f16", state="bf16"),
+    "gdn_verify_sbf16":    dict(mode="verify", is_kda=False, H=1, HV=2, B=3, T=4, act="bf16", state="bf16"),
+    "gdn_writeback_sbf16": dict(mode="writeback", is_kda=False, H=2, HV=2, B=3, T=3, act="f16", state="bf16"),
+    "kda_tree_safe_sbf16": dict(mode="tree", is_kda=True, H=1, HV=2, B=3, T=5, act="bf16", lower_bound=-5.0,
+                                state="bf16"),
 }
 
 
@@ -61,13 +69,14 @@ def klast_case(name: str, seed: int = 2026):
         lengths = [T, T // 2, 0]
     nt = sum(lengths)
     slots = max(7, B + 2)
-    backing = _t(rs, slots, HV * D * D + 256, dtype=torch.float32, scale=0.1)
+    state_dtype = torch.bfloat16 if c.get("state") == "bf16" else torch.float32
+    backing = _t(rs, slots, HV * D * D + 256, dtype=torch.float32, scale=0.1).to(state_dtype)
     state = backing[:, : HV * D * D].view(slots, HV, D, D)
     state_ids = [3, 0, -1]
     cache_ids = [2, 0, 1]
     cache = None
     if mode != "decode":
-        cache = torch.full((max(4, B + 1), T + 3, HV, D, D), -7.0, dtype=torch.float32)
+        cache = torch.full((max(4, B + 1), T + 3, HV, D, D), -7.0, dtype=state_dtype)
     parents = None
     if mode == "tree":
         parents = torch.tensor([[max(0, t - 2) for t in range(T)]] * B, dtype=torch.int32)

@@ -97,7 +97,7 @@ def _decode_shard_worker(rank, world, port, result_dir):
     try:
         bench.B, bench.SLOTS = 6, 12
         hv_lo, hv_hi = rank * bench.HV // world, (rank + 1) * bench.HV // world
-        host, const, slot_sets, hl, hvl = bench.make_inputs(hv_lo, hv_hi, "cpu")
+        host, const, slot_sets, hl, hvl = bench.make_decode_inputs(hv_lo, hv_hi)
         g = torch.Generator().manual_seed(99)
         pool = (torch.randn(bench.SLOTS, bench.HV, D, D, generator=g) * 0.02)[:, hv_lo:hv_hi].contiguous()
         mixed = host["mixed"]
@@ -123,7 +123,7 @@ def test_decode_head_shards_reassemble_to_the_unsharded_step(tmp_path):
     saved = (bench.B, bench.SLOTS)
     try:
         bench.B, bench.SLOTS = 6, 12
-        host, const, slot_sets, hl, hvl = bench.make_inputs(0, bench.HV, "cpu")
+        host, const, slot_sets, hl, hvl = bench.make_decode_inputs(0, bench.HV)
         g = torch.Generator().manual_seed(99)
         pool = torch.randn(bench.SLOTS, bench.HV, D, D, generator=g) * 0.02
         mixed = host["mixed"]

@@ -29,15 +29,22 @@ def to_cuda(args, backing):
     return out, backing_d
 
 
-@pytest.mark.parametrize("rows", [0, 1, 16, 32, 64, 128])
+@pytest.mark.parametrize("rows", [0, 1, 16, 17, 32, 64, 128])
 @pytest.mark.parametrize("name", sorted(cases.KLAST_CASES))
 def test_klast_matches_oracle_and_fixture(native_built, name, rows):
+    """Every kernel choice (0 = the library's pick, 1 = row-per-thread, 16 / 17 = streaming with sixteen / twelve
+    warps, 32 / 64 / 128 = one block per CTA) on fp32 and bf16 pools (tests/test_k_last_state_dtype.py:159-220)."""
     from pla_b200.decode import fused_sigmoid_gating_delta_rule_forward_k_last as forward
     args, backing, lengths, state_ids, cache_ids = cases.klast_case(name)
-    if rows in (1, 16) and cases.KLAST_CASES[name]["mode"] != "decode":
+    if rows in (1, 16, 17) and cases.KLAST_CASES[name]["mode"] != "decode":
         dargs, _ = to_cuda(args, backing)
         with pytest.raises(RuntimeError, match="single-token decode kernels"):
             forward(**dargs, rows_per_cta=rows)   # these kernels only take plain single-token calls
+        return
+    if rows == 1 and backing.dtype != torch.float32:
+        dargs, _ = to_cuda(args, backing)
+        with pytest.raises(RuntimeError, match="fp32 pool"):
+            forward(**dargs, rows_per_cta=rows)
         return
     exp_out, exp_state, exp_cache = odec.klast_forward(**cases.oracle_kwargs(args, lengths, state_ids, cache_ids))
     dargs, dbacking = to_cuda(args, backing)
@@ -48,6 +55,7 @@ def test_klast_matches_oracle_and_fixture(native_built, name, rows):
     assert status.item() == 0
     assert out.shape == args["v"].shape and out.dtype == args["v"].dtype
     assert dargs["initial_state_source"].data_ptr() == state_ptr
+    assert dargs["initial_state_source"].dtype == backing.dtype
     assert_out_close(out[0], exp_out, "out vs oracle")
     state = dargs["initial_state_source"].cpu()
     assert_state_close(state, exp_state, "state vs oracle")
@@ -113,6 +121,49 @@ def test_config0_gdn_decode(native_built, pad_one):
             assert torch.equal(pool[s], c["pool"][s])
     if pad_one:
         assert torch.count_nonzero(out[0, B // 2]) == 0
+
+
+@pytest.mark.parametrize("state_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("is_kda", [False, True])
+def test_stream_unit_ranges_cut_tiles_anywhere(native_built, is_kda, state_dtype):
+    """150 requests x 6 heads = 14,400 units of 8 rows over 148 x 16 warps: every warp's range (6 or 7 units) starts
+    and ends in the middle of a tile; padded requests and an out-of-pool slot sit inside the ranges."""
+    from pla_b200.decode import fused_sigmoid_gating_delta_rule_forward_k_last as forward
+    B, H, HV, slots = 150, 2, 6, 160
+    g = torch.Generator().manual_seed(31)
+    q = torch.randn(B, H, 128, generator=g).bfloat16()
+    k = torch.randn(B, H, 128, generator=g).bfloat16()
+    v = torch.randn(B, HV, 128, generator=g).bfloat16()
+    a = torch.randn(B, HV * 128 if is_kda else HV, generator=g).bfloat16().view(B, HV, -1).squeeze(-1)
+    b = torch.randn(B, HV, generator=g).bfloat16()
+    A_log = torch.rand(HV, generator=g) * 2.0
+    dt_bias = (torch.randn(HV * 128 if is_kda else HV, generator=g) * 0.1).bfloat16()
+    pool = (torch.randn(slots, HV, 128, 128, generator=g) * 0.05).to(state_dtype)
+    idx = torch.randperm(slots, generator=g)[:B].to(torch.int32)
+    idx[7] = -1
+    idx[8] = -1
+    idx[93] = -1
+    exp_out, exp_state, _ = odec.klast_forward(
+        q=q, k=k, v=v, a=a, b=b, A_log=A_log, dt_bias=dt_bias.view(HV, -1).squeeze(-1), state=pool,
+        slot_indices=idx.tolist(), lengths=[1] * B, scale=128 ** -0.5, is_kda=is_kda)
+    dpool = pool.cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cu = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+    for rows in (16, 17) if state_dtype == torch.float32 else (16,):
+        dpool.copy_(pool)
+        out = forward(A_log.cuda(), a.cuda()[None], dt_bias.cuda(), 1.0, 20.0, q.cuda()[None], k.cuda()[None],
+                      v.cuda()[None], b.cuda()[None], dpool, idx.cuda(), 128 ** -0.5, True, cu, is_kda, False, None, None,
+                      None, None, status=status, rows_per_cta=rows)
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        assert_out_close(out[0], exp_out)
+        assert_state_close(dpool.cpu(), exp_state)
+        assert torch.count_nonzero(out[0, [7, 8, 93]]) == 0
+        used = set(i for i in idx.tolist() if i >= 0)
+        host = dpool.cpu()
+        for s_ in range(slots):
+            if s_ not in used:
+                assert torch.equal(host[s_], pool[s_])
 
 
 @pytest.mark.parametrize("is_kda", [False, True])
