@@ -2,11 +2,16 @@
 // decode step): every (request, value head) 128x128 state is read once and
 // written once, in place. The pool holds fp32 or bf16; the arithmetic is fp32.
 //
-// One CTA per SM and every WARP is its own pipeline. The state of the whole
-// call is a sequence of UNITS of 8 consecutive V rows (4 KiB fp32, 2 KiB bf16;
-// 16 units per (slot, hv) tile); warp w of W owns the contiguous unit range
-// [w U / W, (w + 1) U / W), so the work of any two warps differs by at most one
-// unit whatever the batch and head count. A warp walks its range TASK by task
+// At most one CTA per SM and every WARP is its own pipeline. The state of the
+// whole call is a sequence of UNITS of 8 consecutive V rows (4 KiB fp32, 2 KiB
+// bf16; 16 units per (slot, hv) tile), cut into PIECES of 8, 4, 2 or 1 units;
+// warp w of W owns the contiguous piece range [w N / W, (w + 1) N / W). The
+// host picks the piece size and the grid so that ranges start and end on half
+// tiles whenever the call is large enough (a warp pays one set-up of the
+// token's q / k / gate per half tile it touches, and measured on B200 that
+// alignment is worth more than the last SMs: 128 CTAs with eight whole half
+// tiles per warp beat 148 CTAs with ragged ranges by 6 %), and smaller pieces
+// only spread a small batch over more warps. A warp walks its range TASK by task
 // (a task = the units of its range inside one half tile of 64 rows): lane 0
 // keeps NS-1 bulk loads (TMA engine, mbarrier completion) in flight into the
 // warp's private shared-memory ring, the warp updates the landed unit in place
@@ -20,6 +25,9 @@
 // bf16 pools as k_last_load_state4 / k_last_store_state4 (:81-112): widened on load,
 // rounded to nearest on store, outputs formed from the unrounded fp32 state.
 #include <atomic>
+#ifdef PLA_B200_TUNE_ENV
+#include <stdlib.h>
+#endif
 
 #include "common.cuh"
 #include "decode_klast.h"
@@ -42,7 +50,6 @@ struct Layout {
   static constexpr int CPL = 16 / static_cast<int>(sizeof(state_t));  // columns per 16-byte piece: 4 or 8
   static constexpr int NI = 16 / CPL;                                 // pieces per lane and row: 4 or 2
   static constexpr uint32_t UNIT_BYTES = RU * D * sizeof(state_t);
-  static constexpr int UNIT_ELEMS = RU * D;
   // first column of the e-th group of four columns (e = 0..3) of lane j
   __device__ static __forceinline__ int col4(int e, int j) {
     if constexpr (CPL == 4) return (e * 8 + j) * 4;
@@ -89,6 +96,7 @@ __device__ __forceinline__ Task describe(const pla_b200_klast_args& p, int task,
   x.row0 = part * TASK_ROWS;
   const int n = t / p.HV;
   int bos = n, eos = n + 1;
+  const int slot = p.slot_indices[n];   // issued together with the offsets: one memory round trip, not two
   if (p.cu_seqlens != nullptr) {
     bos = p.cu_seqlens[n];
     eos = p.cu_seqlens[n + 1];
@@ -99,7 +107,6 @@ __device__ __forceinline__ Task describe(const pla_b200_klast_args& p, int task,
     return x;
   }
   x.tok = bos;
-  const int slot = p.slot_indices[n];
   const bool pad = (p.pad == PLA_B200_PAD_SGLANG) ? (slot < 0) : (slot <= 0);
   if (pad) {
     x.kind = kZero;
@@ -205,7 +212,7 @@ __device__ __forceinline__ float group8_sum(float x) {
 
 template <typename act_t, bool IS_KDA, typename state_t, int NWARP, int NS>
 __global__ void __launch_bounds__(NWARP * 32, 1) klast_stream_kernel(const pla_b200_klast_args p,
-                                                                     const int n_units) {
+                                                                     const int n_pieces, const int piece) {
   using L = Layout<state_t>;
   constexpr uint32_t UNIT_BYTES = L::UNIT_BYTES;
   constexpr int CPL = L::CPL, NI = L::NI;
@@ -225,12 +232,19 @@ __global__ void __launch_bounds__(NWARP * 32, 1) klast_stream_kernel(const pla_b
 
   const int64_t gw = static_cast<int64_t>(blockIdx.x) * NWARP + warp;
   const int64_t GW = static_cast<int64_t>(gridDim.x) * NWARP;
-  const int g0 = static_cast<int>(n_units * gw / GW), g1 = static_cast<int>(n_units * (gw + 1) / GW);
+  const int g0 = static_cast<int>(n_pieces * gw / GW) * piece, g1 = static_cast<int>(n_pieces * (gw + 1) / GW) * piece;
   if (g0 >= g1) return;
   const int t_first = g0 / UPT, t_end = (g1 + UPT - 1) / UPT;
 
   Task cur = describe<state_t>(p, t_first, g0, g1);
-  Task nxt = describe<state_t>(p, t_first + 1, g0, g1);
+  // The first loads only need the next task when the first one is too short to fill the ring; otherwise the
+  // next task's metadata (dependent global loads) is fetched behind them.
+  const bool short_first = cur.kind != kActive || cur.se - cur.sb < NS - 1;
+  Task nxt;
+  nxt.kind = kSkip;
+  nxt.sb = nxt.se = 0;
+  nxt.gptr = nullptr;
+  if (short_first) nxt = describe<state_t>(p, t_first + 1, g0, g1);
   Raw<act_t, IS_KDA> raw;
   prefetch<act_t, IS_KDA, state_t>(p, cur, r, j, raw);
   if (lane == 0 && cur.kind == kActive) {
@@ -243,6 +257,8 @@ __global__ void __launch_bounds__(NWARP * 32, 1) klast_stream_kernel(const pla_b
       }
     }
   }
+
+  if (!short_first) nxt = describe<state_t>(p, t_first + 1, g0, g1);
 
   // Ring position of the unit being computed and of the next load; both only
   // advance on active units so that they stay in step across padded tasks.
@@ -258,17 +274,18 @@ __global__ void __launch_bounds__(NWARP * 32, 1) klast_stream_kernel(const pla_b
       float kk[16], qq[16], gg[IS_KDA ? 16 : 1];
       float gs = 1.0f;
       {
-        float qs = 0.f, ks = 0.f;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           cvt4<act_t>(raw.q[e], qq + 4 * e);
           cvt4<act_t>(raw.k[e], kk + 4 * e);
         }
+        float qp[4] = {0.f, 0.f, 0.f, 0.f}, kp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
-          qs = fmaf(qq[c], qq[c], qs);
-          ks = fmaf(kk[c], kk[c], ks);
+          qp[c >> 2] = fmaf(qq[c], qq[c], qp[c >> 2]);
+          kp[c >> 2] = fmaf(kk[c], kk[c], kp[c >> 2]);
         }
+        const float qs = (qp[0] + qp[1]) + (qp[2] + qp[3]), ks = (kp[0] + kp[1]) + (kp[2] + kp[3]);
         float qr = p.scale, kr = 1.0f;
         if (p.use_qk_l2norm) {
           qr = rsqrtf(group8_sum(qs) + 1e-6f) * p.scale;
@@ -301,12 +318,15 @@ __global__ void __launch_bounds__(NWARP * 32, 1) klast_stream_kernel(const pla_b
 #pragma unroll
       for (int s = 0; s < UPT; ++s) vcur[s] = raw.v[s];
       act_t* orow = static_cast<act_t*>(p.o) + (static_cast<int64_t>(cur.tok) * p.HV + cur.hv) * D + cur.row0 + r * 2;
-      const int pf = (cur.sb + cur.se) >> 1;   // where the next task's inputs are requested
+      // The next task's inputs are requested half way through a whole task (`raw` of this task is fully
+      // consumed by then), or right away when this warp's part of the task does not reach that unit.
+      const bool pf_mid = cur.sb <= UPT / 2 && UPT / 2 < cur.se;
+      if (!pf_mid) prefetch<act_t, IS_KDA, state_t>(p, nxt, r, j, raw);
 
 #pragma unroll
       for (int sub = 0; sub < UPT; ++sub) {
         if (sub < cur.sb || sub >= cur.se) continue;             // warp-uniform: another warp's units
-        if (sub == pf) prefetch<act_t, IS_KDA, state_t>(p, nxt, r, j, raw);  // `raw` of this task is fully consumed
+        if (sub == UPT / 2) prefetch<act_t, IS_KDA, state_t>(p, nxt, r, j, raw);   // pf_mid holds here
         unsigned char* blk = ring + stage * UNIT_BYTES;
         // warp-uniform verdict, so that no lane is left alone at a later __syncwarp
         if (!__all_sync(0xffffffffu, mbar_wait(&bars[stage], (parity >> stage) & 1u))) {
@@ -320,33 +340,35 @@ __global__ void __launch_bounds__(NWARP * 32, 1) klast_stream_kernel(const pla_b
         for (int pp = 0; pp < 2; ++pp) {
           uint4* srow = reinterpret_cast<uint4*>(blk + (r * 2 + pp) * (D * sizeof(state_t)));
           float st[16];
-          float d = 0.0f;
+          float dp[4] = {0.f, 0.f, 0.f, 0.f};   // four short dependency chains instead of one of sixteen
 #pragma unroll
           for (int i = 0; i < NI; ++i) {
             widen<state_t>(srow[i * 8 + j], st + i * CPL);
 #pragma unroll
             for (int c = 0; c < CPL; ++c) {
-              if constexpr (IS_KDA) st[i * CPL + c] *= gg[i * CPL + c];
-              d = fmaf(st[i * CPL + c], kk[i * CPL + c], d);
+              const int e = i * CPL + c;
+              if constexpr (IS_KDA) st[e] *= gg[e];
+              dp[e >> 2] = fmaf(st[e], kk[e], dp[e >> 2]);
             }
           }
-          d = group8_sum(d);
+          float d = group8_sum((dp[0] + dp[1]) + (dp[2] + dp[3]));
           if constexpr (!IS_KDA) d *= gs;  // scalar decay folded: (g S) k = g (S k)
           const float vn = (to_f32(vpair[pp]) - d) * beta;
-          float oacc = 0.0f;
+          float op[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int i = 0; i < NI; ++i) {
 #pragma unroll
             for (int c = 0; c < CPL; ++c) {
-              float s_ = st[i * CPL + c];
+              const int e = i * CPL + c;
+              float s_ = st[e];
               if constexpr (!IS_KDA) s_ *= gs;
-              s_ = fmaf(kk[i * CPL + c], vn, s_);
-              oacc = fmaf(s_, qq[i * CPL + c], oacc);
-              st[i * CPL + c] = s_;
+              s_ = fmaf(kk[e], vn, s_);
+              op[e >> 2] = fmaf(s_, qq[e], op[e >> 2]);
+              st[e] = s_;
             }
             srow[i * 8 + j] = narrow<state_t>(st + i * CPL);
           }
-          ov[pp] = group8_sum(oacc);
+          ov[pp] = group8_sum((op[0] + op[1]) + (op[2] + op[3]));
         }
         if (j == 0) {
           if (p.o_f32 != nullptr) {
@@ -418,6 +440,30 @@ __global__ void __launch_bounds__(NWARP * 32, 1) klast_stream_kernel(const pla_b
   if (lane == 0) bulk_wait_read<0>();
 }
 
+// Piece size (units) and grid for a call of `n_units` units. Largest piece (8 = a half tile, then 4, 2, 1) that
+// still gives two thirds of the SMs a piece per warp; then the grid in [2/3 of the SMs, all SMs] with the least
+// idle warp-time, ceil(pieces / warps) * warps / pieces, ties going to the larger grid.
+void plan_stream_grid(int64_t n_units, int nwarp, int sms, int* piece_out, int* grid_out) {
+  const int lo = (2 * sms + 2) / 3;
+  int piece = UPT;
+  while (piece > 1 && n_units / piece < static_cast<int64_t>(lo) * nwarp) piece >>= 1;
+  const int64_t n_pieces = n_units / piece;       // n_units is a multiple of 16
+  int grid = static_cast<int>((n_pieces + nwarp - 1) / nwarp);
+  if (grid > lo) {
+    double best = 1e30;
+    for (int g = lo; g <= sms; ++g) {
+      const int64_t warps = static_cast<int64_t>(g) * nwarp;
+      const double waste = static_cast<double>((n_pieces + warps - 1) / warps * warps) / static_cast<double>(n_pieces);
+      if (waste <= best + 1e-12) {
+        best = waste;
+        grid = g;
+      }
+    }
+  }
+  *piece_out = piece;
+  *grid_out = grid < 1 ? 1 : grid;
+}
+
 template <typename act_t, bool IS_KDA, typename state_t, int NWARP, int NS>
 int launch_cfg(const pla_b200_klast_args& a, cudaStream_t stream) {
   constexpr int kSmem = NWARP * NS * static_cast<int>(Layout<state_t>::UNIT_BYTES) + NWARP * NS * 8;
@@ -431,10 +477,13 @@ int launch_cfg(const pla_b200_klast_args& a, cudaStream_t stream) {
   }
   const int64_t n_units = static_cast<int64_t>(a.B) * a.HV * UNITS_PER_TILE;
   PLA_REQUIRE(n_units < (1ll << 31), PLA_B200_E_TOO_LARGE, "B*HV too large for the streaming decode kernel");
-  // every SM takes part as soon as a warp gets two units; the unit ranges are balanced to within one unit
-  const int64_t want = (n_units + 2 * NWARP - 1) / (2 * NWARP);
-  const int grid = static_cast<int>(want < sm_count() ? want : sm_count());
-  kern<<<grid, NWARP * 32, kSmem, stream>>>(a, static_cast<int>(n_units));
+  int piece = 0, grid = 0;
+  plan_stream_grid(n_units, NWARP, sm_count(), &piece, &grid);
+#ifdef PLA_B200_TUNE_ENV
+  if (const char* e = getenv("PLA_B200_STREAM_GRID")) grid = atoi(e) > 0 && atoi(e) < grid ? atoi(e) : grid;
+  if (const char* e = getenv("PLA_B200_STREAM_PIECE")) piece = atoi(e) > 0 ? atoi(e) : piece;
+#endif
+  kern<<<grid, NWARP * 32, kSmem, stream>>>(a, static_cast<int>(n_units / piece), piece);
   PLA_CUDA_OK(cudaGetLastError());
   return PLA_B200_OK;
 }
