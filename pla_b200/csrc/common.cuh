@@ -71,6 +71,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
+// The same with a suspend-time hint: the waiting thread may sleep in hardware for up to `ns` nanoseconds or until
+// the phase completes, instead of returning after the default (short) slice. A warp that polls in a loop
+// competes for issue slots with the working warps of its scheduler; one that sleeps does not.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_addr(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return done != 0;
+}
+
 // Bounded wait: gives up after `limit` polls (each poll itself blocks for a
 // hardware-defined slice), returning false so the caller can flag a timeout
 // instead of spinning forever.

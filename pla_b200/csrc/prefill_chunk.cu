@@ -39,7 +39,7 @@ constexpr int KQ_BYTES = 128 * D * 4;   // rows 0-63 Kn, rows 64-127 Qn*scale; K
 constexpr int KNT_BYTES = D * C * 4;    // rows = feature k (128), K = token (64)
 constexpr int TM_BYTES = C * C * 4;     // T: rows = token i, K = token j
 constexpr int PM_BYTES = C * C * 4;     // P: rows = token i, K = token j
-constexpr int VEC_BYTES = 4 * C * 4;    // G[64], beta[64], exp(G)[64], exp(G_last - G)[64]
+constexpr int VEC_BYTES = 4 * C * 4;    // beta exp(G)[64], beta[64], exp(G)[64], exp(G_last - G)[64]
 constexpr int HBLOB = KQ_BYTES + KNT_BYTES;            // per (chunk, q/k head)
 constexpr int VBLOB = TM_BYTES + PM_BYTES + VEC_BYTES;  // per (chunk, value head)
 // T and P are lower triangular (diagonal included). In their images ([K / 4 = column group jg][row i][4 columns])
@@ -329,12 +329,13 @@ __global__ void __launch_bounds__(PREP_THREADS, 2) gdn_chunk_prepare_kernel(cons
       // vectors for the chain
       float* vec = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv) + TM_BYTES + PM_BYTES);
       const float g_last = __shfl_sync(0xffffffffu, s1, 31);
-      vec[lane] = s0;
-      vec[lane + 32] = s1;
+      const float e0 = __expf(s0), e1 = __expf(s1);
+      vec[lane] = b2[0] * e0;            // W = beta V - (beta e^G) (Kn S): one multiply-add per element in the chain
+      vec[lane + 32] = b2[1] * e1;
       vec[C + lane] = b2[0];
       vec[C + lane + 32] = b2[1];
-      vec[2 * C + lane] = __expf(s0);
-      vec[2 * C + lane + 32] = __expf(s1);
+      vec[2 * C + lane] = e0;
+      vec[2 * C + lane + 32] = e1;
       vec[3 * C + lane] = __expf(g_last - s0);
       vec[3 * C + lane + 32] = __expf(g_last - s1);
     }
@@ -678,7 +679,7 @@ __global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(
     const int c = tid - 128;
     vec[2 * C + c] = __expf(sh.gc[c]);
     if (c < C) {
-      vec[c] = 0.f;
+      vec[c] = sh.beta[c];               // the decay is folded into the operands: W = beta V - beta (K+ S)
       vec[C + c] = sh.beta[c];
     }
   }
@@ -755,7 +756,7 @@ __global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(
 //   MMA1  D1[v, 0:64 | 64:128] = S^T(TMEM, fp32 read as tf32) x [Kn; Qn]^T       -> (Kn S)^T | (Qn S)^T
 //   E1    W^T[v, c] = beta_c (V[c, v] - e^{G_c} (Kn S)^T[v, c])                   -> over D1[:, 0:64]
 //   MMA2  D2[v, i]  = W^T(TMEM) x T^T                                             -> V'^T
-//   E2    A3 = V'^T (over D2),  A4[v, c] = e^{G_C - G_c} V'^T[v, c] (over D1[:, 0:64]);  S *= e^{G_C}
+//   E2    A4[v, c] = e^{G_C - G_c} V'^T[v, c] (over D1[:, 0:64]);  A3 = V'^T stays in D2 as MMA2 left it;  S *= e^{G_C}
 //   MMA3  D3[v, i]  = A3(TMEM) x P^T                                              -> intra-chunk output
 //   MMA4  S[v, k]  += A4(TMEM) x Kn^T-image                                       -> state update
 //   E3    O[i, v]   = e^{G_i} (Qn S)^T[v, i] + D3[v, i]
@@ -764,19 +765,21 @@ __global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(
 // Warps: 0 = bulk-copy producer, 1 = MMA issuer (and TMEM owner), 2..9 = two epilogue warpgroups that
 // split the columns of every accumulator between them (a warp may only touch TMEM lanes 32*(warp%4)..+31),
 // 10 = V loader (global rows of any alignment -> shared memory, one chunk ahead), 11 = output storer
-// (bulk stores of the chunk's output rows from shared memory).
+// (bulk stores of the chunk's output rows from shared memory), 12..15 = state scalers: S *= e^{G_C} between MMA1 and
+// MMA4 of a chunk, off the epilogue warps' timeline (tensor-memory loads and stores wait while an MMA runs, and
+// this step sits under MMA2).
 constexpr uint32_t COL_S = 0, COL_D1 = 128, COL_D2 = 384, COL_D3 = 448;
 constexpr uint32_t kWaitLimit = 1u << 20;
 
 // Optional phase timestamps of chain CTA 0 (development builds only: -DPLA_B200_DEBUG_CLOCKS).
 #ifdef PLA_B200_DEBUG_CLOCKS
-__device__ long long g_dbg_clock[2][16][8];
+__device__ long long g_dbg_clock[2][16][16];
 #define DBG_CLOCK(role, c, k) \
   do { if (blockIdx.x == 0 && (c) < 16) g_dbg_clock[role][c][k] = clock64(); } while (0)
 #else
 #define DBG_CLOCK(role, c, k) do {} while (0)
 #endif
-constexpr int CHAIN_THREADS = 384;
+constexpr int CHAIN_THREADS = 512;
 constexpr int E_THREADS = 256;
 constexpr int V_PITCH = 136;  // halfwords per staged V row: 128 + room for one leading / trailing halfword, 16-byte multiple
 
@@ -791,9 +794,42 @@ struct ChainSmem {
   alignas(8) uint64_t full_kq, full_t, full_pk, full_vec[2];
   uint64_t v_full[2], v_free[2], o_full, o_free;
   uint64_t mma1_done, mma2_done, mma34_done;
-  uint64_t s_ready, a2_ready, a34_ready, e_done;
+  uint64_t s_ready, a2_ready, a34_ready, e_done, s_scaled;
   uint32_t tmem_base;
   volatile int abort;
+};
+
+// Lazy state scaling (GDN, scalar decay per chunk). Tensor-memory loads and stores are the scarce resource of
+// this kernel (about 100 bytes per cycle and SM), and multiplying the whole 64 KiB state by e^{G_C} every chunk
+// was 40 % of that traffic. Instead the accumulator holds S / sigma for a scalar sigma that every role tracks
+// from the chunk vectors: reads of the state (MMA1's results) are multiplied by sigma in the epilogues that
+// touch them anyway, the update operand A4 is divided by the new sigma, and the stored state is only touched
+// when sigma would leave [2^-40, 1] -- or not at all when the chunk's own decay is below 2^-40, where the
+// update simply overwrites the state (the dropped term is below fp32 resolution).
+constexpr float kSigmaFloor = 9.094947e-13f;   // 2^-40
+enum : int { kLazy = 0, kOverwrite = 1, kRescale = 2 };
+struct LazyScale {
+  float sigma = 1.0f;     // true state = sigma * accumulator
+  // One chunk with total decay `gamma`: returns the mode; `read` scales this chunk's reads of the state, `a4` its
+  // update operand, `factor` is what a kRescale pass multiplies the accumulator by before the update.
+  __device__ __forceinline__ int step(float gamma, float& read, float& a4, float& factor) {
+    read = sigma;
+    a4 = 1.0f;
+    factor = 1.0f;
+    if (!(gamma >= kSigmaFloor)) {   // also catches a decay that underflowed to zero
+      sigma = 1.0f;
+      return kOverwrite;
+    }
+    const float next = sigma * gamma;
+    if (next < kSigmaFloor) {
+      factor = next;
+      sigma = 1.0f;
+      return kRescale;
+    }
+    sigma = next;
+    a4 = __fdividef(1.0f, next);
+    return kLazy;
+  }
 };
 
 // Bounded wait that also gives up when another role has already given up.
@@ -881,6 +917,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
     mbar_init(&sh.a2_ready, E_THREADS);
     mbar_init(&sh.a34_ready, E_THREADS);
     mbar_init(&sh.e_done, E_THREADS);
+    mbar_init(&sh.s_scaled, 128);
     mbar_init(&sh.v_full[0], 32);
     mbar_init(&sh.v_full[1], 32);
     mbar_init(&sh.v_free[0], E_THREADS);
@@ -965,9 +1002,14 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
       const uint64_t knt_desc = tc05::smem_desc(sh.knt, 128 * 16, 128);
       constexpr uint32_t i128 = tc05::idesc_tf32(128, 128), i64 = tc05::idesc_tf32(128, 64);
       bool ok = chain_wait(sh, &sh.s_ready, 0);
+      LazyScale lazy;
+      const bool kda_m = p.is_kda != 0;
       for (int c = 0; c < nch && ok; ++c) {
         const uint32_t ph = c & 1;
         const uint32_t d1 = tb + COL_D1 + ph * 128;
+        if (!(ok = chain_wait(sh, &sh.full_vec[ph], (c >> 1) & 1))) break;
+        float rd, a4s, fac;
+        const int mode = kda_m ? kRescale : lazy.step(sh.vec[ph][2 * C + C - 1], rd, a4s, fac);
         if (!(ok = chain_wait(sh, &sh.full_kq, ph))) break;
         tc05::fence_after_sync();
         DBG_CLOCK(0, c, 0);
@@ -984,15 +1026,19 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
           tc05::mma_tf32_ts(tb + COL_D2, d1 + j * 8, tc05::desc_advance(t_desc, j * 2 * 64 * 16), i64, j > 0);
         tc05::mma_commit(&sh.mma2_done);
         DBG_CLOCK(0, c, 3);
-        if (!(ok = chain_wait(sh, &sh.a34_ready, ph) && chain_wait(sh, &sh.full_pk, ph))) break;
+        // MMA3 reads V'^T where MMA2 left it (same shape, so the tensor core orders the two) and runs while the
+        // epilogue turns the same accumulator into A4
+        if (!(ok = chain_wait(sh, &sh.full_pk, ph))) break;
+#pragma unroll
+        for (int j = 0; j < C / 8; ++j)
+          tc05::mma_tf32_ts(tb + COL_D3, tb + COL_D2 + j * 8, tc05::desc_advance(p_desc, j * 2 * 64 * 16), i64, j > 0);
+        if (!(ok = chain_wait(sh, &sh.a34_ready, ph) && chain_wait(sh, &sh.s_scaled, ph))) break;
         tc05::fence_after_sync();
         DBG_CLOCK(0, c, 4);
 #pragma unroll
         for (int j = 0; j < C / 8; ++j)
-          tc05::mma_tf32_ts(tb + COL_D3, tb + COL_D2 + j * 8, tc05::desc_advance(p_desc, j * 2 * 64 * 16), i64, j > 0);
-#pragma unroll
-        for (int j = 0; j < C / 8; ++j)
-          tc05::mma_tf32_ts(tb + COL_S, d1 + j * 8, tc05::desc_advance(knt_desc, j * 2 * 128 * 16), i128, true);
+          tc05::mma_tf32_ts(tb + COL_S, d1 + j * 8, tc05::desc_advance(knt_desc, j * 2 * 128 * 16), i128,
+                            mode != kOverwrite || j > 0);
         tc05::mma_commit(&sh.mma34_done);
         DBG_CLOCK(0, c, 5);
       }
@@ -1053,6 +1099,36 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh.o_free);
     }
+  } else if (warp >= 12) {
+    // ------------------------------------------------------------------ state scalers (128 threads)
+    // S *= e^{G_C} (GDN) or, per key channel, e^{G_C}[k] (KDA: vec[128 + k]) once MMA1 of the chunk has read S;
+    // MMA4 of the chunk waits for it.
+    const uint32_t tS = tb + (static_cast<uint32_t>((warp & 3) * 32) << 16) + COL_S;
+    const bool kda = p.is_kda != 0;
+    LazyScale lazy;
+    for (int c = 0; c < nch; ++c) {
+      const uint32_t ph = c & 1;
+      const float* vec = sh.vec[ph];
+      if (!chain_wait(sh, &sh.full_vec[ph], (c >> 1) & 1)) break;
+      float rd, a4s, fac = 1.0f;
+      const int mode = kda ? kRescale : lazy.step(vec[2 * C + C - 1], rd, a4s, fac);
+      if (!chain_wait(sh, &sh.mma1_done, ph)) break;
+      tc05::fence_after_sync();
+      if (mode == kRescale) {       // KDA: every chunk, per key channel; GDN: only when sigma runs out of range
+#pragma unroll 1
+        for (int q4 = 0; q4 < 4; ++q4) {
+          float s[32];
+          tc05::tmem_ld32(tS + q4 * 32, s);
+          tc05::wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) s[j] *= kda ? vec[2 * C + q4 * 32 + j] : fac;
+          tc05::tmem_st32(tS + q4 * 32, s);
+        }
+        tc05::wait_st();
+      }
+      tc05::fence_before_sync();
+      mbar_arrive(&sh.s_scaled);
+    }
   } else {
     // ------------------------------------------------------------------ epilogue warpgroups (2 x 128 threads)
     const int quad = warp & 3;
@@ -1090,12 +1166,15 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
     }
 
     bool ok = true;
+    LazyScale lazy;
     for (int c = 0; c < nch && ok; ++c) {
       const uint32_t ph = c & 1;
       const uint32_t tD1 = tb + lane_base + COL_D1 + ph * 128;
       const int n = min(C, len - c * C);
       const float* vec = sh.vec[ph];
       if (!(ok = chain_wait(sh, &sh.full_vec[ph], (c >> 1) & 1))) break;
+      float rd = 1.0f, a4s = 1.0f, fac;
+      if (!kda) (void)lazy.step(vec[2 * C + C - 1], rd, a4s, fac);
       if (m == 0 && wg == 0) DBG_CLOCK(1, c, 3);
       if (!(ok = chain_wait(sh, &sh.v_full[ph], (c >> 1) & 1))) break;
       const act_t* vrows = reinterpret_cast<const act_t*>(sh.v[ph]);
@@ -1103,57 +1182,81 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
       const int64_t v_e0 = static_cast<int64_t>(reinterpret_cast<uintptr_t>(p.v) >> 1) + static_cast<int64_t>(hv) * D +
                            (bos + static_cast<int64_t>(c) * C + cg) * p.v_tok_stride;
       const int v_sh0 = static_cast<int>(v_e0 & 7), v_shs = static_cast<int>(p.v_tok_stride & 7);
+      // this thread's V elements of the chunk, fetched while MMA1 still runs
+      float w[32];
+      if (v_shs == 0) {
+        const act_t* vcol = vrows + cg * V_PITCH + v_sh0 + m;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) w[j] = to_f32(vcol[j * V_PITCH]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) w[j] = to_f32(vrows[(cg + j) * V_PITCH + ((v_sh0 + j * v_shs) & 7) + m]);
+      }
       if (!(ok = chain_wait(sh, &sh.mma1_done, ph))) break;
       tc05::fence_after_sync();
       if (m == 0 && wg == 0) DBG_CLOCK(1, c, 1);
-      // ---- E1: W^T over (Kn S)^T ----
+      // ---- E1: W^T = beta V^T - (beta e^G) (Kn S)^T over (Kn S)^T. This code is bound by instruction issue
+      // (two epilogue warps per scheduler): coefficients come as 128-bit broadcast loads, the V element needs no
+      // address arithmetic when every row of the chunk has the same alignment shift (token stride a multiple
+      // of 16 bytes) and is fetched before MMA1 is waited for; then one multiply, one multiply-add and one integer
+      // add (rounding) per element. ----
       {
         float x[32];
         tc05::tmem_ld32(tD1 + cg, x);
+        const float4* be4 = reinterpret_cast<const float4*>(vec + cg);        // beta e^G (KDA: beta)
+        const float4* b4 = reinterpret_cast<const float4*>(vec + C + cg);     // beta
         tc05::wait_ld();
+        if (m == 0 && wg == 0) DBG_CLOCK(1, c, 8);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int i = cg + j;
-          const float eg = kda ? 1.0f : vec[2 * C + i];
-          x[j] = tc05::to_tf32(vec[C + i] * (to_f32(vrows[i * V_PITCH + ((v_sh0 + j * v_shs) & 7) + m]) - eg * x[j]));
+        for (int j4 = 0; j4 < 8; ++j4) {
+          float4 be = be4[j4];
+          const float4 b = b4[j4];
+          be.x *= rd; be.y *= rd; be.z *= rd; be.w *= rd;     // the accumulator holds S / sigma
+          x[4 * j4 + 0] = tc05::pre_round_tf32(fmaf(-be.x, x[4 * j4 + 0], b.x * w[4 * j4 + 0]));
+          x[4 * j4 + 1] = tc05::pre_round_tf32(fmaf(-be.y, x[4 * j4 + 1], b.y * w[4 * j4 + 1]));
+          x[4 * j4 + 2] = tc05::pre_round_tf32(fmaf(-be.z, x[4 * j4 + 2], b.z * w[4 * j4 + 2]));
+          x[4 * j4 + 3] = tc05::pre_round_tf32(fmaf(-be.w, x[4 * j4 + 3], b.w * w[4 * j4 + 3]));
         }
+        if (m == 0 && wg == 0) DBG_CLOCK(1, c, 9);
         tc05::tmem_st32(tD1 + cg, x);
       }
       tc05::wait_st();
+      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 10);
       tc05::fence_before_sync();
       mbar_arrive(&sh.a2_ready);
       if (m == 0 && wg == 0) DBG_CLOCK(1, c, 2);
       mbar_arrive(&sh.v_free[ph]);
-      // ---- S *= e^{G_C} (MMA1 has consumed S; MMA4 comes after a34_ready) ----
-      {
-        const float gC = vec[2 * C + C - 1];
-#pragma unroll 1
-        for (int q4 = 2 * wg; q4 < 2 * wg + 2; ++q4) {
-          float s[32];
-          tc05::tmem_ld32(tS + q4 * 32, s);
-          tc05::wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) s[j] *= kda ? vec[2 * C + q4 * 32 + j] : gC;
-          tc05::tmem_st32(tS + q4 * 32, s);
-        }
-      }
       if (!(ok = chain_wait(sh, &sh.mma2_done, ph))) break;
       tc05::fence_after_sync();
       if (m == 0 && wg == 0) DBG_CLOCK(1, c, 4);
-      // ---- E2: A3 = V'^T in place, A4 = decayed copy over W^T ----
+      // ---- E2: A4 = decayed V'^T (rounded to nearest: it feeds the state) over W^T. A3 = V'^T is read by MMA3
+      // straight from the accumulator: the tensor core truncates it to tf32, which only the intra-chunk part of
+      // the 16-bit outputs sees. ----
       {
-        float x[32], y[32];
+        float x[32];
         tc05::tmem_ld32(tD2 + cg, x);
         tc05::wait_ld();
+        if (m == 0 && wg == 0) DBG_CLOCK(1, c, 11);
+        if (kda) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          y[j] = tc05::to_tf32((kda ? 1.0f : vec[3 * C + cg + j]) * x[j]);
-          x[j] = tc05::to_tf32(x[j]);
+          for (int j = 0; j < 32; ++j) x[j] = tc05::pre_round_tf32(x[j]);
+        } else {
+          const float4* d4 = reinterpret_cast<const float4*>(vec + 3 * C + cg);   // e^{G_C - G}
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            float4 d = d4[j4];
+            d.x *= a4s; d.y *= a4s; d.z *= a4s; d.w *= a4s;   // the update lands in S / sigma_new
+            x[4 * j4 + 0] = tc05::pre_round_tf32(d.x * x[4 * j4 + 0]);
+            x[4 * j4 + 1] = tc05::pre_round_tf32(d.y * x[4 * j4 + 1]);
+            x[4 * j4 + 2] = tc05::pre_round_tf32(d.z * x[4 * j4 + 2]);
+            x[4 * j4 + 3] = tc05::pre_round_tf32(d.w * x[4 * j4 + 3]);
+          }
         }
-        tc05::tmem_st32(tD2 + cg, x);
-        tc05::tmem_st32(tD1 + cg, y);
+        if (m == 0 && wg == 0) DBG_CLOCK(1, c, 12);
+        tc05::tmem_st32(tD1 + cg, x);
       }
       tc05::wait_st();
+      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 13);
       tc05::fence_before_sync();
       mbar_arrive(&sh.a34_ready);
       if (m == 0 && wg == 0) DBG_CLOCK(1, c, 5);
@@ -1170,8 +1273,21 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
         if (m == 0 && wg == 0) DBG_CLOCK(1, c, 0);
         act_t* so = reinterpret_cast<act_t*>(sh.o);
         // values first, stores second: the stores may alias `vec` as far as the compiler knows
+        if (kda) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) qs[j] = fmaf(kda ? 1.0f : vec[2 * C + cg + j], qs[j], d3[j]);
+          for (int j = 0; j < 32; ++j) qs[j] += d3[j];
+        } else {
+          const float4* e4 = reinterpret_cast<const float4*>(vec + 2 * C + cg);   // e^G
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            float4 e = e4[j4];
+            e.x *= rd; e.y *= rd; e.z *= rd; e.w *= rd;
+            qs[4 * j4 + 0] = fmaf(e.x, qs[4 * j4 + 0], d3[4 * j4 + 0]);
+            qs[4 * j4 + 1] = fmaf(e.y, qs[4 * j4 + 1], d3[4 * j4 + 1]);
+            qs[4 * j4 + 2] = fmaf(e.z, qs[4 * j4 + 2], d3[4 * j4 + 2]);
+            qs[4 * j4 + 3] = fmaf(e.w, qs[4 * j4 + 3], d3[4 * j4 + 3]);
+          }
+        }
 #pragma unroll
         for (int j = 0; j < 32; ++j) so[(cg + j) * D + m] = from_f32<act_t>(qs[j]);
         mbar_arrive(&sh.o_full);  // the storer reads with ordinary loads: no proxy fence needed
@@ -1191,6 +1307,8 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
         float s[32];
         tc05::tmem_ld32(tS + q4 * 32, s);
         tc05::wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) s[j] *= lazy.sigma;
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
           *reinterpret_cast<float4*>(dst + q4 * 32 + j) = make_float4(s[j], s[j + 1], s[j + 2], s[j + 3]);
@@ -1215,8 +1333,8 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
         for (int j = 0; j < 32; ++j) {
           const int kx = q4 * 32 + j;
           const int64_t e = base + (p.state_transposed ? static_cast<int64_t>(kx) * D + m : static_cast<int64_t>(m) * D + kx);
-          if (f32_state) static_cast<float*>(dst)[e] = s[j];
-          else static_cast<__nv_bfloat16*>(dst)[e] = __float2bfloat16_rn(s[j]);
+          if (f32_state) static_cast<float*>(dst)[e] = s[j] * lazy.sigma;
+          else static_cast<__nv_bfloat16*>(dst)[e] = __float2bfloat16_rn(s[j] * lazy.sigma);
         }
       }
     }

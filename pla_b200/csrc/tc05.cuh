@@ -123,6 +123,11 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
 __device__ __forceinline__ float to_tf32(float x) {
   return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
 }
+// Half of that rounding, for a value that only the tensor core will read (a TMEM A operand): after adding half
+// a tf32 unit to the bit pattern, the tensor core's own truncation of the low 13 bits completes the round to
+// nearest. One integer add per element (cvt.rna.tf32.f32 was measured at 8 cycles per warp instruction, which
+// made the chain kernel's epilogue conversion-bound).
+__device__ __forceinline__ float pre_round_tf32(float x) { return __uint_as_float(__float_as_uint(x) + 0x1000u); }
 
 }  // namespace tc05
 }  // namespace pla

@@ -85,7 +85,7 @@ def test_prepare_stage_operand_images(native_built, name):
                     G = torch.zeros(C); b = torch.zeros(C)
                     G[:n] = torch.cumsum(g[t0:t0 + n, hv], 0); G[n:] = G[n - 1]
                     b[:n] = beta[t0:t0 + n, hv]
-                    torch.testing.assert_close(vec[:64], G, rtol=1e-4, atol=1e-5)
+                    torch.testing.assert_close(vec[:64], b * torch.exp(G), rtol=1e-4, atol=1e-6)
                     torch.testing.assert_close(vec[64:128], b, rtol=1e-4, atol=1e-6)
                     torch.testing.assert_close(g_cum[t0:t0 + n, hv].cpu(), G[:n], rtol=1e-4, atol=1e-5)
                     Gam = torch.exp(G[:, None] - G[None, :])
