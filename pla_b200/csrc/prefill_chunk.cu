@@ -97,28 +97,53 @@ constexpr int L_STRIDE = 68;  // padded row of the fp32 L matrix (floats); rows 
 __device__ __forceinline__ int inverse_column_block(int t6) {
   return (t6 < 32) ? ((t6 & 16) ? 3 : 0) : ((t6 & 16) ? 2 : 1);
 }
+__device__ __forceinline__ constexpr int l_row(int i) { return i * L_STRIDE; }
 __device__ __forceinline__ void invert_column(const float* __restrict__ L, int cb, int col, float (&Tcol)[C]) {
+  // Rows go in blocks of four. The part of a row's sum over the columns before its block does not depend on the
+  // other rows of the block, so the four rows run side by side (sixteen independent multiply-add chains); only
+  // the block's own 4 x 4 triangle is sequential. That cuts the dependent steps from 64 rows to 16 blocks.
 #pragma unroll
   for (int i = 0; i < C; ++i) Tcol[i] = 0.0f;
 #pragma unroll
-  for (int i = 0; i < C; ++i) {
-    if (cb <= (i >> 4)) {
-      const float4* Lrow = reinterpret_cast<const float4*>(L + i * L_STRIDE);
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  for (int rb = 0; rb < C / 4; ++rb) {
+    if (cb <= (rb >> 2)) {
+      float acc[4][4];
 #pragma unroll
-      for (int jb = 0; jb <= (i >> 4); ++jb) {
-        if (cb <= jb) {
+      for (int u = 0; u < 4; ++u)
 #pragma unroll
-          for (int j4 = jb * 4; j4 < jb * 4 + 4 && j4 < (i + 3) / 4; ++j4) {
-            const float4 l = Lrow[j4];  // entries at j >= i are zero
-            a0 = fmaf(l.x, Tcol[4 * j4 + 0], a0);
-            a1 = fmaf(l.y, Tcol[4 * j4 + 1], a1);
-            a2 = fmaf(l.z, Tcol[4 * j4 + 2], a2);
-            a3 = fmaf(l.w, Tcol[4 * j4 + 3], a3);
+        for (int k = 0; k < 4; ++k) acc[u][k] = 0.0f;
+#pragma unroll
+      for (int jq = 0; jq < C / 16; ++jq) {   // 16-column groups from the thread's column block on
+        if (cb <= jq) {
+#pragma unroll
+          for (int jb = jq * 4; jb < jq * 4 + 4 && jb < rb; ++jb) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const float4 l = reinterpret_cast<const float4*>(L + l_row(4 * rb + u))[jb];
+              acc[u][0] = fmaf(l.x, Tcol[4 * jb + 0], acc[u][0]);
+              acc[u][1] = fmaf(l.y, Tcol[4 * jb + 1], acc[u][1]);
+              acc[u][2] = fmaf(l.z, Tcol[4 * jb + 2], acc[u][2]);
+              acc[u][3] = fmaf(l.w, Tcol[4 * jb + 3], acc[u][3]);
+            }
           }
         }
       }
-      Tcol[i] = ((i == col) ? 1.0f : 0.0f) - ((a0 + a1) + (a2 + a3));
+      // the block's own triangle (the piece of row 4 rb is not staged and not needed: nothing left of its diagonal)
+      const int r0 = 4 * rb;
+      const float4 l1 = reinterpret_cast<const float4*>(L + l_row(r0 + 1))[rb];
+      const float4 l2 = reinterpret_cast<const float4*>(L + l_row(r0 + 2))[rb];
+      const float4 l3 = reinterpret_cast<const float4*>(L + l_row(r0 + 3))[rb];
+      const float t0 = ((r0 == col) ? 1.0f : 0.0f) - ((acc[0][0] + acc[0][1]) + (acc[0][2] + acc[0][3]));
+      const float t1 = ((r0 + 1 == col) ? 1.0f : 0.0f) -
+                       (((acc[1][0] + acc[1][1]) + (acc[1][2] + acc[1][3])) + l1.x * t0);
+      const float t2 = ((r0 + 2 == col) ? 1.0f : 0.0f) -
+                       (((acc[2][0] + acc[2][1]) + (acc[2][2] + acc[2][3])) + fmaf(l2.y, t1, l2.x * t0));
+      const float t3 = ((r0 + 3 == col) ? 1.0f : 0.0f) -
+                       (((acc[3][0] + acc[3][1]) + (acc[3][2] + acc[3][3])) + fmaf(l3.z, t2, fmaf(l3.y, t1, l3.x * t0)));
+      Tcol[r0] = t0;
+      Tcol[r0 + 1] = t1;
+      Tcol[r0 + 2] = t2;
+      Tcol[r0 + 3] = t3;
     }
   }
 }
