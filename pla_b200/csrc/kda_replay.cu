@@ -296,6 +296,229 @@ __global__ void __launch_bounds__(VNT, 2) kda_verify_kernel(const pla_b200_kda_v
   }
 }
 
+// ------------------------------------------------------------------ verify, closed-form window (Q <= 8)
+// Verify never writes the checkpoint, so the window's outputs are linear in it. Row by row of the state
+// (s_t = the row after token t, A_t = diag(gamma_t) (I - beta_t k_t k_t^T), k_t normalised):
+//     s_t = s_{t-1} A_t + beta_t v_t[row] k_t^T          =>
+//     o_t[row] = s_t . q_t = s_0 . Qeff_t + sum_{j <= t} c_{j,t} v_j[row],
+//     Qeff_t = A_1 ... A_t q_t,      c_{j,t} = beta_j k_j^T (A_{j+1} ... A_t q_t)
+// (the reference forms the same window in closed form, src/decode/kda_replayssm/kda_mtp_verify.cu:630-653).
+// Qeff_t and c_{.,t} come from one backward sweep per token over k, gamma, beta (warp t: x = q_t; for j = t..1:
+// d = k_j . x, c_{j,t} = beta_j d, x = gamma_j (x - beta_j d k_j)) -- O(Q^2) vectors of 128, no state involved.
+// The 64 KiB state is then read ONCE, straight from global memory into registers, four rows per warp at a time
+// with the next four already requested, and each row gives its Q dot products (lane j of a row's eight lanes
+// also carries the c_{j,t} v_j term into the reduction). No shared-memory copy of the state, no dependent
+// per-token sweeps over it; 85 registers, so three CTAs share an SM and cover each other's set-up.
+constexpr int CQ = 8;   // longest window of the closed-form kernel
+struct WindowSmem {
+  float q[CQ][D];      // conv + SiLU outputs (unnormalised), then Qeff
+  float k[CQ][D];      // conv + SiLU outputs (unnormalised), then normalised
+  float gam[CQ][D];
+  float v[CQ][D];
+  float o[CQ][D];
+  float c[CQ][CQ];     // c[j][t]
+  float part[CQ][2][4];
+  float beta[CQ];
+};
+
+__global__ void __launch_bounds__(VNT, 3) kda_verify_window_kernel(const pla_b200_kda_verify_args p) {
+  __shared__ __align__(16) WindowSmem sh;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.x % p.H;
+  const int n = blockIdx.x / p.H;
+
+  const int64_t begin = idx_at(p.cu, n), end = idx_at(p.cu, n + 1);
+  const int64_t slot = idx_at(p.slot_idx, n);
+  // rows whose metadata is unusable are left completely alone
+  if (idx_at(p.cu, 0) != 0 || begin < 0 || end < begin || end > p.T || end - begin > window_capacity(p) || slot >= p.slots ||
+      begin == end)
+    return;
+  const int n_tok = static_cast<int>(end - begin);   // <= CQ: the host only picks this kernel for Q <= CQ
+  const int64_t out_stride = static_cast<int64_t>(p.H) * D;
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(h) * D;
+  if (slot <= p.null_block_id) {  // padding row: zero its output interval, touch nothing else
+    for (int i = tid; i < n_tok * D; i += VNT) out[(begin + i / D) * out_stride + (i % D)] = __float2bfloat16(0.0f);
+    return;
+  }
+
+  // ---- this thread's share of the checkpoint, requested first: warp w owns rows 16 w .. 16 w + 15, eight lanes per
+  // row, lane j of a row the columns (i * 8 + j) * 4 .. + 3
+  const int j8 = lane & 7;
+  const float4* srow0 = reinterpret_cast<const float4*>(p.state + slot * p.state_slot_stride + static_cast<int64_t>(h) * TILE) +
+                        (warp * 16 + (lane >> 3)) * (D / 4) + j8;   // row pass ps: + ps * 4 rows; piece i: + i * 8
+  float4 st[2][4];   // [buffer][piece]: the row pass being worked on and the next one
+#pragma unroll
+  for (int i = 0; i < 4; ++i) st[0][i] = __ldg(srow0 + i * 8);
+
+  const int64_t rec_row = p.row_by_slot ? slot : n;
+  const int64_t win_row = (p.row_by_slot && p.scratch_idx.data != nullptr) ? idx_at(p.scratch_idx, n) : n;
+  const bool is_v = tid >= D;
+  const int c = tid & (D - 1);
+  const int ch = h * D + c;             // channel of this thread inside its q / k / gate or v tensor
+  const __nv_bfloat16* gin = static_cast<const __nv_bfloat16*>(p.raw_g) + begin * p.g_tok_stride + ch;
+  const __nv_bfloat16* bin = static_cast<const __nv_bfloat16*>(p.raw_beta) + begin * p.beta_tok_stride + h;
+
+  // conv taps and the sliding 3-tap history in registers: (q, k) for the first half, v for the second
+  float wa[4], wb[4], ha[3], hb[3];
+  const __nv_bfloat16 *xa, *xb = nullptr;
+  int64_t xa_stride, xb_stride = 0;
+  __nv_bfloat16 *wina, *winb = nullptr;
+  int64_t wina_step, wina_tap, winb_step = 0, winb_tap = 0;
+  {
+    const float* w0 = is_v ? p.w_v : p.w_q;
+    const __nv_bfloat16* cs0 = static_cast<const __nv_bfloat16*>(is_v ? p.cs_v : p.cs_q);
+    const pla_b200_conv_strides& st0 = is_v ? p.cs_v_strides : p.cs_q_strides;
+    const pla_b200_window_strides& ws0 = is_v ? p.win_v_strides : p.win_q_strides;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) wa[w] = w0[ch * 4 + w];
+#pragma unroll
+    for (int w = 0; w < 3; ++w) ha[w] = __bfloat162float(cs0[slot * st0.slot + ch * st0.channel + w * st0.tap]);
+    xa = static_cast<const __nv_bfloat16*>(is_v ? p.x_v : p.x_q) + begin * (is_v ? p.xv_tok_stride : p.xq_tok_stride) + ch;
+    xa_stride = is_v ? p.xv_tok_stride : p.xq_tok_stride;
+    wina = static_cast<__nv_bfloat16*>(is_v ? p.win_v : p.win_q) + win_row * ws0.row + ch * ws0.channel;
+    wina_step = ws0.step;
+    wina_tap = ws0.tap;
+    if (!is_v) {
+      const __nv_bfloat16* cs1 = static_cast<const __nv_bfloat16*>(p.cs_k);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) wb[w] = p.w_k[ch * 4 + w];
+#pragma unroll
+      for (int w = 0; w < 3; ++w)
+        hb[w] = __bfloat162float(cs1[slot * p.cs_k_strides.slot + ch * p.cs_k_strides.channel + w * p.cs_k_strides.tap]);
+      xb = static_cast<const __nv_bfloat16*>(p.x_k) + begin * p.xk_tok_stride + ch;
+      xb_stride = p.xk_tok_stride;
+      winb = static_cast<__nv_bfloat16*>(p.win_k) + win_row * p.win_k_strides.row + ch * p.win_k_strides.channel;
+      winb_step = p.win_k_strides.step;
+      winb_tap = p.win_k_strides.tap;
+    }
+  }
+  const float A_log = p.A_log[h];
+  const float dtb = is_v ? 0.f : p.dt_bias[ch];
+  const int64_t rec0 = (rec_row * p.H + h) * p.Q;       // record row of step 0, in 128-element rows
+  __nv_bfloat16* rra = static_cast<__nv_bfloat16*>(is_v ? p.rec_rawv : p.rec_rawk) + rec0 * D + c;
+  float* rg = p.rec_g + rec0 * D + c;
+
+  // ---- per (token, channel): conv + SiLU, gate, records; four tokens' inputs are fetched ahead of their stores
+  for (int t0 = 0; t0 < n_tok; t0 += VTS) {
+    const int nt = min(VTS, n_tok - t0);
+    float in_a[VTS], in_b[VTS], in_g[VTS], in_beta[VTS];
+#pragma unroll
+    for (int s = 0; s < VTS; ++s) {
+      in_a[s] = in_b[s] = in_g[s] = in_beta[s] = 0.f;
+      if (s < nt) {
+        const int t = t0 + s;
+        in_a[s] = __bfloat162float(xa[t * xa_stride]);
+        if (!is_v) {
+          in_b[s] = __bfloat162float(xb[t * xb_stride]);
+          in_g[s] = __bfloat162float(gin[t * p.g_tok_stride]);
+        } else if (c == 0) {
+          in_beta[s] = __bfloat162float(bin[t * p.beta_tok_stride]);
+        }
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < VTS; ++s) {
+      if (s >= nt) break;
+      const int t = t0 + s;
+      const float fa = in_a[s];
+      float ca = fa * wa[3];
+#pragma unroll
+      for (int w = 0; w < 3; ++w) ca += ha[w] * wa[w];
+      ca = silu(ca);
+      ha[0] = ha[1]; ha[1] = ha[2]; ha[2] = fa;
+#pragma unroll
+      for (int w = 0; w < 3; ++w) wina[t * wina_step + w * wina_tap] = __float2bfloat16(ha[w]);  // exact: values came from bf16
+      if (is_v) {
+        sh.v[t][c] = ca;
+        rra[static_cast<int64_t>(t) * D] = __float2bfloat16(ca);
+        if (c == 0) {
+          const float beta = sigmoidf_fast(in_beta[s]);
+          sh.beta[t] = beta;
+          p.rec_beta[rec0 + t] = beta;
+        }
+      } else {
+        const float fb = in_b[s];
+        float cb = fb * wb[3];
+#pragma unroll
+        for (int w = 0; w < 3; ++w) cb += hb[w] * wb[w];
+        cb = silu(cb);
+        hb[0] = hb[1]; hb[1] = hb[2]; hb[2] = fb;
+#pragma unroll
+        for (int w = 0; w < 3; ++w) winb[t * winb_step + w * winb_tap] = __float2bfloat16(hb[w]);
+        const float gk = log_decay(in_g[s] + dtb, A_log, p.gate, p.softplus_beta, p.softplus_threshold, p.lower_bound);
+        rra[static_cast<int64_t>(t) * D] = __float2bfloat16(cb);
+        rg[static_cast<int64_t>(t) * D] = gk;
+        sh.q[t][c] = ca;
+        sh.k[t][c] = cb;
+        sh.gam[t][c] = __expf(gk);
+        const float sq = warp_sum(ca * ca), sk = warp_sum(cb * cb);
+        if (lane == 0) {
+          sh.part[t][0][warp] = sq;
+          sh.part[t][1][warp] = sk;
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- normalise k in place (all warps), then warp t sweeps back from token t: Qeff_t over q[t], c[.][t]
+  for (int i = tid; i < n_tok * D; i += VNT) {
+    const int t = i / D;
+    const float sk = (sh.part[t][1][0] + sh.part[t][1][1]) + (sh.part[t][1][2] + sh.part[t][1][3]);
+    sh.k[t][i % D] *= rsqrtf(sk + 1e-6f);
+  }
+  __syncthreads();
+  if (warp < n_tok) {
+    const int t = warp;
+    const float sq = (sh.part[t][0][0] + sh.part[t][0][1]) + (sh.part[t][0][2] + sh.part[t][0][3]);
+    const float qr = rsqrtf(sq + 1e-6f) * p.scale;
+    float4 x = reinterpret_cast<const float4*>(sh.q[t])[lane];
+    x.x *= qr; x.y *= qr; x.z *= qr; x.w *= qr;
+    for (int jt = t; jt >= 0; --jt) {
+      const float4 kk = reinterpret_cast<const float4*>(sh.k[jt])[lane];
+      const float4 gg = reinterpret_cast<const float4*>(sh.gam[jt])[lane];
+      const float d = warp_sum(dot4(kk, x));
+      const float bd = sh.beta[jt] * d;
+      if (lane == 0) sh.c[jt][t] = bd;
+      x.x = gg.x * fmaf(-bd, kk.x, x.x);
+      x.y = gg.y * fmaf(-bd, kk.y, x.y);
+      x.z = gg.z * fmaf(-bd, kk.z, x.z);
+      x.w = gg.w * fmaf(-bd, kk.w, x.w);
+    }
+    __syncwarp();
+    reinterpret_cast<float4*>(sh.q[t])[lane] = x;   // q[t] is only read by this warp before this point
+  }
+  __syncthreads();
+
+  // ---- one pass over the state: four rows per warp at a time, the next four in flight
+#pragma unroll
+  for (int ps = 0; ps < 4; ++ps) {
+    if (ps + 1 < 4) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) st[(ps + 1) & 1][i] = __ldg(srow0 + (ps + 1) * 4 * (D / 4) + i * 8);
+    }
+    const int row = warp * 16 + ps * 4 + (lane >> 3);
+    for (int t = 0; t < n_tok; ++t) {
+      // lane j of the row's eight lanes brings c[j][t] v_j[row] (j <= t) into the sum: CQ = 8 terms at most
+      float acc = (j8 <= t) ? sh.c[j8][t] * sh.v[j8][row] : 0.0f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc += dot4(st[ps & 1][i], reinterpret_cast<const float4*>(sh.q[t])[i * 8 + j8]);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      if (j8 == 0) sh.o[t][row] = acc;
+    }
+  }
+  __syncthreads();
+  if (p.out_f32 != nullptr) {
+    float* of = p.out_f32 + static_cast<int64_t>(h) * D;
+    for (int i = tid; i < n_tok * D; i += VNT) of[(begin + i / D) * out_stride + (i % D)] = sh.o[i / D][i % D];
+  } else {
+    for (int i = tid; i < n_tok * D; i += VNT)
+      out[(begin + i / D) * out_stride + (i % D)] = __float2bfloat16(sh.o[i / D][i % D]);
+  }
+}
+
 // Gated RMSNorm of the staged fp32 outputs: one CTA per (request, head), one warp per token,
 // four channels per lane. Rows that verify left alone (unusable metadata, padding) stay as they are.
 __global__ void __launch_bounds__(NT) kda_onorm_kernel(const pla_b200_kda_verify_args p) {
@@ -704,7 +927,13 @@ extern "C" int pla_b200_kda_replay_verify(const pla_b200_kda_verify_args* args, 
   PLA_REQUIRE(!onorm || (a.onorm_gate && a.onorm_weight && a.out_f32 && aligned16(a.out_f32) &&
                          aligned16(a.onorm_weight) && a.onorm_eps >= 0.0f),
               PLA_B200_E_INVALID, "the fused output norm needs gate, weight, eps >= 0 and a 16-byte aligned fp32 staging buffer");
-  kda_verify_kernel<<<static_cast<unsigned>(ctas), VNT, sizeof(VerifySmem), static_cast<cudaStream_t>(stream)>>>(a);
+  // windows of up to eight tokens: closed form, the state streamed once into registers; longer ones: the
+  // token-by-token kernel on a shared-memory copy of the state
+  const int window = a.win_steps > 0 && a.win_steps < a.Q ? a.win_steps : a.Q;
+  if (window <= CQ)
+    kda_verify_window_kernel<<<static_cast<unsigned>(ctas), VNT, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  else
+    kda_verify_kernel<<<static_cast<unsigned>(ctas), VNT, sizeof(VerifySmem), static_cast<cudaStream_t>(stream)>>>(a);
   PLA_CUDA_OK(cudaGetLastError());
   if (onorm) {
     kda_onorm_kernel<<<static_cast<unsigned>(a.N) * a.H, NT, 0, static_cast<cudaStream_t>(stream)>>>(a);

@@ -179,6 +179,7 @@ def conv_ds(layer):
 REPLAY_VERIFY_CASES = {
     "sd_q4_h2": ("SD", 4, 2), "ds_q4_h2": ("DS", 4, 2), "sd_q1_h1": ("SD", 1, 1), "ds_q5_h1": ("DS", 5, 1),
     "sd_q8_h1": ("SD", 8, 1),
+    "ds_q10_h1": ("DS", 10, 1),     # longer than eight tokens: the token-by-token verify kernel
 }
 
 
