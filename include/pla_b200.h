@@ -461,7 +461,7 @@ int pla_b200_kda_replay_plan_static(const pla_b200_kda_commit_args* args, void* 
 /* ======================================================================== *
  * Fused KDA decode step (Kimi K3): causal conv (width 4) + SiLU over the packed q|k|v projections with
  * the 3-tap conv state shifted in place, L2 norms, per-channel gate, single-token recurrence on the fp32
- * k-last state in place, optional gated output RMSNorm. Replaces the launchers behind
+ * k-last state in place, optional gated output RMSNorm -- one launch, no scratch. Replaces the launchers behind
  * fused_kda_decode_mega_forward (src/decode/k-last/fused_kda_decode_mega.cu; device contract
  * src/decode/k-last/fused_kda_decode_mega_kernel.cuh:36-79). A slot < 0 is padding: zero output row,
  * nothing else read or written; slot 0 is an ordinary slot.
@@ -487,8 +487,8 @@ typedef struct pla_b200_kda_mega_args {
   int64_t gate_row_stride;
   const float* norm_weight;    /* [128], with output_gate */
   float norm_eps;
-  void* mixed;                 /* scratch [B, 3*H*128] activation dtype, 16-byte aligned: conv outputs */
-  float* out_f32;              /* scratch [B, H*128] fp32, 16-byte aligned; required with output_gate */
+  void* mixed;                 /* unused (the step runs as one kernel and keeps the conv outputs on the SM); may be NULL */
+  float* out_f32;              /* unused; may be NULL */
   int32_t B, H;
   int32_t act_dtype;           /* pla_b200_dtype: BF16 or F16 */
   int32_t gate;                /* pla_b200_gate */

@@ -1,119 +1,165 @@
-// Fused KDA decode step: conv + SiLU with in-place conv-state shift, then the single-token KDA recurrence
-// of the streaming k-last kernel on the packed conv outputs, then the optional gated output RMSNorm
-// (src/decode/k-last/fused_kda_decode_mega_kernel.cuh:36-79; reference math
-// scripts/decode/kda_fusion/compare_kda_decode_fusion.py:252-308).
-// Three launches on one stream: the state traffic (128 KiB per request and head) is all in the second one.
+// Fused KDA decode step in ONE kernel: causal conv (width 4) + SiLU with the in-place shift of the 3-tap conv
+// state, L2 norms, per-channel gate, the single-token KDA recurrence on the fp32 k-last state in place, and the
+// optional gated output RMSNorm (src/decode/k-last/fused_kda_decode_mega_kernel.cuh:148-732, grid (1, H, B) at
+// :58-72; reference math scripts/decode/kda_fusion/compare_kda_decode_fusion.py:252-308).
+//
+// One CTA per (request, head), 256 threads. The first state rows are requested before anything else; threads
+// 0..127 then form the head's q and k channels (conv + SiLU, history shifted), the decay and the norm sums,
+// threads 128..255 the v channels; nothing of that leaves the SM. The 64 KiB state tile is streamed through
+// registers, never shared memory: warp w owns rows 16 w .. 16 w + 15, eight lanes per row, four rows at a time
+// with the next four in flight; each row is decayed, corrected and written back where it came from, and its
+// output value stays in shared memory for the norm over the head's 128 values. No scratch buffers.
 #include "common.cuh"
-#include "decode_klast.h"
 
 namespace pla {
 namespace {
 
 constexpr int D = 128;
+constexpr int TILE = D * D;
+constexpr int MT = 256;
 
 __device__ __forceinline__ float silu_f(float x) { return x * sigmoidf_fast(x); }
 
-// One thread per (request, channel): y = silu(w . [t0, t1, t2, x] + bias) -> mixed; conv state <- [t1, t2, x].
+struct MegaSmem {
+  alignas(16) float q[D];
+  alignas(16) float k[D];
+  alignas(16) float gam[D];
+  float v[D];
+  float o[D];
+  float part[3][4];
+  float beta;
+};
+
 template <typename act_t>
-__global__ void __launch_bounds__(256) kda_mega_conv_kernel(const pla_b200_kda_mega_args p) {
-  const int b = blockIdx.y;
+__global__ void __launch_bounds__(MT, 3) kda_mega_fused_kernel(const pla_b200_kda_mega_args p) {
+  __shared__ MegaSmem sh;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.x % p.H, b = blockIdx.x / p.H;
   const int dim = p.H * D;
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;   // channel in [0, 3*dim)
-  if (c >= 3 * dim) return;
   const int slot = p.state_indices[b];
-  if (slot < 0) return;                                  // padding row: the decode kernel zeroes its output
-  if (slot >= p.slots) {
-    if (p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_BAD_SLOT);
+  act_t* outp = static_cast<act_t*>(p.out) + (static_cast<int64_t>(b) * p.H + h) * D;
+  if (slot < 0 || slot >= p.slots) {       // padding row (or a slot outside the pool): zero output, nothing else
+    if (slot >= p.slots && tid == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_BAD_SLOT);
+    if (tid < D / 2) reinterpret_cast<uint32_t*>(outp)[tid] = 0u;
     return;
   }
-  const int seg = c / dim, ch = c - seg * dim;
-  act_t* cs = static_cast<act_t*>(p.conv_state) + static_cast<int64_t>(slot) * p.conv_strides.slot +
-              static_cast<int64_t>(c) * p.conv_strides.channel;
-  const act_t t0 = cs[0], t1 = cs[p.conv_strides.tap], t2 = cs[2 * p.conv_strides.tap];
-  const act_t xn = static_cast<const act_t*>(p.x)[static_cast<int64_t>(b) * p.x_row_stride + c];
-  const float* w = p.weight + static_cast<int64_t>(seg) * 4 * dim + ch;
-  float acc = p.bias != nullptr ? p.bias[c] : 0.0f;
-  acc = fmaf(w[0], to_f32(t0), acc);
-  acc = fmaf(w[dim], to_f32(t1), acc);
-  acc = fmaf(w[2 * dim], to_f32(t2), acc);
-  acc = fmaf(w[3 * dim], to_f32(xn), acc);
-  static_cast<act_t*>(p.mixed)[static_cast<int64_t>(b) * 3 * dim + c] = from_f32<act_t>(silu_f(acc));
-  cs[0] = t1;                                            // bit-exact shift of the history
-  cs[p.conv_strides.tap] = t2;
-  cs[2 * p.conv_strides.tap] = xn;
-}
 
-// Gated RMSNorm of the staged fp32 outputs: one warp per (request, head), four channels per lane.
-template <typename act_t>
-__global__ void __launch_bounds__(128) kda_mega_norm_kernel(const pla_b200_kda_mega_args p) {
-  const int lane = threadIdx.x & 31;
-  const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (item >= p.B * p.H) return;
-  const int b = item / p.H, h = item % p.H;
-  const int slot = p.state_indices[b];
-  if (slot < 0 || slot >= p.slots) return;               // output row already zero
-  const int64_t e = (static_cast<int64_t>(b) * p.H + h) * D + lane * 4;
-  const float4 o = *reinterpret_cast<const float4*>(p.out_f32 + e);
-  const float r = rsqrtf(warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w) * (1.0f / D) + p.norm_eps);
-  const float4 w = reinterpret_cast<const float4*>(p.norm_weight)[lane];
-  const act_t* g = static_cast<const act_t*>(p.output_gate) + static_cast<int64_t>(b) * p.gate_row_stride + h * D + lane * 4;
-  act_t* dst = static_cast<act_t*>(p.out) + e;
-  dst[0] = from_f32<act_t>(o.x * r * w.x * sigmoidf_fast(to_f32(g[0])));
-  dst[1] = from_f32<act_t>(o.y * r * w.y * sigmoidf_fast(to_f32(g[1])));
-  dst[2] = from_f32<act_t>(o.z * r * w.z * sigmoidf_fast(to_f32(g[2])));
-  dst[3] = from_f32<act_t>(o.w * r * w.w * sigmoidf_fast(to_f32(g[3])));
+  // ---- the first four state rows of this warp, requested before the conv work
+  const int j8 = lane & 7;
+  float4* srow0 = reinterpret_cast<float4*>(p.state + static_cast<int64_t>(slot) * p.state_slot_stride +
+                                            static_cast<int64_t>(h) * TILE) +
+                  (warp * 16 + (lane >> 3)) * (D / 4) + j8;   // row pass ps: + ps * 4 rows; piece i: + i * 8
+  float4 st[2][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) st[0][i] = srow0[i * 8];
+
+  // ---- conv + SiLU of one channel, history shifted in place (bit-exact copies)
+  const int c = tid & (D - 1);
+  const int ch = h * D + c;
+  auto conv = [&](int seg) -> float {
+    const int cc = seg * dim + ch;
+    act_t* cs = static_cast<act_t*>(p.conv_state) + static_cast<int64_t>(slot) * p.conv_strides.slot +
+                static_cast<int64_t>(cc) * p.conv_strides.channel;
+    const act_t t0 = cs[0], t1 = cs[p.conv_strides.tap], t2 = cs[2 * p.conv_strides.tap];
+    const act_t xn = static_cast<const act_t*>(p.x)[static_cast<int64_t>(b) * p.x_row_stride + cc];
+    const float* w = p.weight + static_cast<int64_t>(seg) * 4 * dim + ch;
+    float acc = p.bias != nullptr ? p.bias[cc] : 0.0f;
+    acc = fmaf(w[0], to_f32(t0), acc);
+    acc = fmaf(w[dim], to_f32(t1), acc);
+    acc = fmaf(w[2 * dim], to_f32(t2), acc);
+    acc = fmaf(w[3 * dim], to_f32(xn), acc);
+    cs[0] = t1;
+    cs[p.conv_strides.tap] = t2;
+    cs[2 * p.conv_strides.tap] = xn;
+    return silu_f(acc);
+  };
+  if (tid < D) {
+    const float q = conv(0), k = conv(1);
+    const float x = to_f32(static_cast<const act_t*>(p.raw_g)[static_cast<int64_t>(b) * dim + ch]) + p.dt_bias[ch];
+    sh.gam[c] = __expf(log_decay(x, p.A_log[h], p.gate, 1.0f, 20.0f, p.lower_bound));
+    sh.q[c] = q;
+    sh.k[c] = k;
+    const float sq = warp_sum(q * q), sk = warp_sum(k * k);
+    if (lane == 0) {
+      sh.part[0][warp] = sq;
+      sh.part[1][warp] = sk;
+    }
+  } else {
+    sh.v[c] = conv(2);
+    if (c == 0) sh.beta = sigmoidf_fast(to_f32(static_cast<const act_t*>(p.raw_beta)[static_cast<int64_t>(b) * p.beta_row_stride + h]));
+  }
+  __syncthreads();
+  if (tid < D) {   // normalised q (times the scale) and k, in place
+    sh.q[c] *= rsqrtf((sh.part[0][0] + sh.part[0][1]) + (sh.part[0][2] + sh.part[0][3]) + 1e-6f) * p.scale;
+    sh.k[c] *= rsqrtf((sh.part[1][0] + sh.part[1][1]) + (sh.part[1][2] + sh.part[1][3]) + 1e-6f);
+  }
+  __syncthreads();
+  const float beta = sh.beta;
+
+  // ---- the recurrence, four rows per warp at a time
+#pragma unroll
+  for (int ps = 0; ps < 4; ++ps) {
+    if (ps + 1 < 4) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) st[(ps + 1) & 1][i] = srow0[(ps + 1) * 4 * (D / 4) + i * 8];
+    }
+    const int row = warp * 16 + ps * 4 + (lane >> 3);
+    float4 kk[4];
+    float d = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 g = reinterpret_cast<const float4*>(sh.gam)[i * 8 + j8];
+      kk[i] = reinterpret_cast<const float4*>(sh.k)[i * 8 + j8];
+      float4& s4 = st[ps & 1][i];
+      s4.x *= g.x; s4.y *= g.y; s4.z *= g.z; s4.w *= g.w;
+      d += dot4(s4, kk[i]);
+    }
+    d += __shfl_xor_sync(0xffffffffu, d, 1);
+    d += __shfl_xor_sync(0xffffffffu, d, 2);
+    d += __shfl_xor_sync(0xffffffffu, d, 4);
+    const float vn = (sh.v[row] - d) * beta;
+    float o = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 q4 = reinterpret_cast<const float4*>(sh.q)[i * 8 + j8];
+      float4& s4 = st[ps & 1][i];
+      s4.x = fmaf(vn, kk[i].x, s4.x);
+      s4.y = fmaf(vn, kk[i].y, s4.y);
+      s4.z = fmaf(vn, kk[i].z, s4.z);
+      s4.w = fmaf(vn, kk[i].w, s4.w);
+      o += dot4(s4, q4);
+      srow0[ps * 4 * (D / 4) + i * 8] = s4;
+    }
+    o += __shfl_xor_sync(0xffffffffu, o, 1);
+    o += __shfl_xor_sync(0xffffffffu, o, 2);
+    o += __shfl_xor_sync(0xffffffffu, o, 4);
+    if (j8 == 0) sh.o[row] = o;
+  }
+  __syncthreads();
+
+  // ---- output row, with the gated RMSNorm over the head's 128 values when asked for
+  if (tid < D) {
+    float o = sh.o[c];
+    if (p.output_gate != nullptr) {
+      const float ss = warp_sum(o * o);
+      if (lane == 0) sh.part[2][warp] = ss;
+    }
+    if (p.output_gate != nullptr) {
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // threads 0..127 only
+      const float r = rsqrtf(((sh.part[2][0] + sh.part[2][1]) + (sh.part[2][2] + sh.part[2][3])) * (1.0f / D) + p.norm_eps);
+      const float gate = to_f32(static_cast<const act_t*>(p.output_gate)[static_cast<int64_t>(b) * p.gate_row_stride + ch]);
+      o = o * r * p.norm_weight[c] * sigmoidf_fast(gate);
+    }
+    outp[c] = from_f32<act_t>(o);
+  }
 }
 
 template <typename act_t>
 int launch_mega(const pla_b200_kda_mega_args& a, cudaStream_t s) {
-  const int dim = a.H * D;
-  kda_mega_conv_kernel<act_t><<<dim3((3 * dim + 255) / 256, a.B), 256, 0, s>>>(a);
+  const int64_t ctas = static_cast<int64_t>(a.B) * a.H;
+  PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "B*H exceeds the grid limit");
+  kda_mega_fused_kernel<act_t><<<static_cast<unsigned>(ctas), MT, 0, s>>>(a);
   PLA_CUDA_OK(cudaGetLastError());
-
-  pla_b200_klast_args k{};
-  const act_t* mixed = static_cast<const act_t*>(a.mixed);
-  k.q = mixed;
-  k.k = mixed + dim;
-  k.v = mixed + 2 * dim;
-  k.q_tok_stride = k.k_tok_stride = k.v_tok_stride = 3 * static_cast<int64_t>(dim);
-  k.a = a.raw_g;
-  k.a_tok_stride = dim;
-  k.b = a.raw_beta;
-  k.b_tok_stride = a.beta_row_stride;
-  k.A_log = a.A_log;
-  k.A_log_dtype = PLA_B200_F32;
-  k.dt_bias = a.dt_bias;
-  k.dt_bias_dtype = PLA_B200_F32;
-  k.act_dtype = a.act_dtype;
-  k.state = a.state;
-  k.state_slot_stride = a.state_slot_stride;
-  k.num_slots = a.slots;
-  k.state_dtype = PLA_B200_F32;
-  k.slot_indices = a.state_indices;
-  k.o = a.out;
-  k.o_f32 = a.output_gate != nullptr ? a.out_f32 : nullptr;
-  k.B = a.B;
-  k.t_max = 1;
-  k.H = a.H;
-  k.HV = a.H;
-  k.scale = a.scale;
-  k.softplus_beta = 1.0f;
-  k.softplus_threshold = 20.0f;
-  k.lower_bound = a.lower_bound;
-  k.gate = a.gate;
-  k.is_kda = 1;
-  k.use_qk_l2norm = 1;
-  k.pad = PLA_B200_PAD_SGLANG;                           // slot < 0 is padding, slot 0 is real
-  k.rows_per_cta = 16;                                   // the streaming kernel
-  k.status = a.status;
-  PLA_REQUIRE(klast_stream_eligible(k), PLA_B200_E_ALIGN,
-              "fused KDA decode needs 8-byte aligned raw_g rows and 4-byte aligned out");
-  const int rc = launch_klast_stream(k, s);
-  if (rc != PLA_B200_OK) return rc;
-  if (a.output_gate != nullptr) {
-    kda_mega_norm_kernel<act_t><<<(a.B * a.H + 3) / 4, 128, 0, s>>>(a);
-    PLA_CUDA_OK(cudaGetLastError());
-  }
   return PLA_B200_OK;
 }
 
@@ -127,21 +173,19 @@ extern "C" int pla_b200_kda_decode_mega(const pla_b200_kda_mega_args* args, void
   PLA_REQUIRE(a.B >= 0 && a.H > 0 && a.slots > 0, PLA_B200_E_INVALID, "B >= 0, H > 0, slots > 0 required");
   if (a.B == 0) return PLA_B200_OK;
   PLA_REQUIRE(a.x && a.weight && a.conv_state && a.raw_g && a.raw_beta && a.A_log && a.dt_bias && a.state_indices &&
-                  a.state && a.out && a.mixed,
+                  a.state && a.out,
               PLA_B200_E_INVALID, "fused KDA decode: a required pointer is NULL");
   PLA_REQUIRE(a.act_dtype == PLA_B200_BF16 || a.act_dtype == PLA_B200_F16, PLA_B200_E_INVALID,
               "activation dtype must be bf16 or fp16");
   PLA_REQUIRE((a.output_gate != nullptr) == (a.norm_weight != nullptr), PLA_B200_E_INVALID,
               "output_gate and norm_weight must be supplied together");
-  PLA_REQUIRE(a.output_gate == nullptr || (a.out_f32 != nullptr && aligned16(a.out_f32) && aligned16(a.norm_weight) &&
-                                           a.norm_eps >= 0.0f),
-              PLA_B200_E_INVALID, "the output norm needs eps >= 0 and 16-byte aligned staging and weight");
-  PLA_REQUIRE(aligned16(a.mixed) && aligned16(a.state) && a.state_slot_stride % 4 == 0 &&
+  PLA_REQUIRE(a.output_gate == nullptr || a.norm_eps >= 0.0f, PLA_B200_E_INVALID, "the output norm needs eps >= 0");
+  PLA_REQUIRE(aligned16(a.state) && a.state_slot_stride % 4 == 0 &&
                   a.state_slot_stride >= static_cast<int64_t>(a.H) * 16384,
-              PLA_B200_E_ALIGN, "scratch and state must be 16-byte aligned; slot pitch must cover H*128*128");
+              PLA_B200_E_ALIGN, "state must be 16-byte aligned; slot pitch must cover H*128*128");
+  PLA_REQUIRE((reinterpret_cast<uintptr_t>(a.out) & 3) == 0, PLA_B200_E_ALIGN, "out must be 4-byte aligned");
   PLA_REQUIRE(a.gate == PLA_B200_GATE_SOFTPLUS || (a.gate == PLA_B200_GATE_SAFE && a.lower_bound < 0.0f),
               PLA_B200_E_INVALID, "the safe gate needs lower_bound < 0");
-  PLA_REQUIRE(a.B <= 65535, PLA_B200_E_TOO_LARGE, "batch exceeds the grid limit");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return a.act_dtype == PLA_B200_BF16 ? launch_mega<__nv_bfloat16>(a, s) : launch_mega<__half>(a, s);
 }

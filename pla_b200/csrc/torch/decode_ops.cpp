@@ -376,7 +376,7 @@ void fused_recurrent_kda(const at::Tensor& q, const at::Tensor& k, const at::Ten
 
 // Fused KDA decode step; tensor contract of fused_kda_decode_mega_forward
 // (src/decode/k-last/fused_sigmoid_gating.cpp:136-144, docs/readme.md:232-267). Writes conv_state, state and
-// out in place. Scratch (conv outputs, fp32 outputs for the norm) comes from the caching allocator.
+// out in place; one kernel, no scratch.
 void kda_decode_mega(const at::Tensor& x, const at::Tensor& weight, const std::optional<at::Tensor>& bias,
                      at::Tensor conv_state, const at::Tensor& raw_g, const at::Tensor& raw_beta,
                      const at::Tensor& a_log, const at::Tensor& dt_bias, const at::Tensor& state_indices,
@@ -437,9 +437,6 @@ void kda_decode_mega(const at::Tensor& x, const at::Tensor& weight, const std::o
   g.state_slot_stride = state.stride(0);
   g.slots = static_cast<int32_t>(state.size(0));
   g.out = out.data_ptr();
-  at::Tensor mixed = at::empty({B, 3 * dim}, x.options());
-  g.mixed = mixed.data_ptr();
-  at::Tensor staging;
   if (output_gate.has_value()) {
     const at::Tensor& gate = *output_gate;
     TORCH_CHECK(gate.scalar_type() == x.scalar_type() && gate.numel() == B * dim && gate.stride(-1) == 1 &&
@@ -449,12 +446,10 @@ void kda_decode_mega(const at::Tensor& x, const at::Tensor& weight, const std::o
                     norm_weight->device() == x.device(),
                 "norm_weight must be contiguous fp32 [128]");
     TORCH_CHECK(std::isfinite(norm_eps) && norm_eps >= 0.0, "norm_eps must be finite and non-negative");
-    staging = at::empty({B, dim}, x.options().dtype(at::kFloat));
     g.output_gate = gate.data_ptr();
     g.gate_row_stride = gate.stride(gate.dim() - 3);
     g.norm_weight = norm_weight->data_ptr<float>();
     g.norm_eps = static_cast<float>(norm_eps);
-    g.out_f32 = staging.data_ptr<float>();
   }
   g.B = static_cast<int32_t>(B);
   g.H = static_cast<int32_t>(H);
