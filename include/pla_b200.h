@@ -57,6 +57,12 @@ enum pla_b200_pad { PLA_B200_PAD_SGLANG = 0, PLA_B200_PAD_VLLM = 1 };
 
 const char* pla_b200_last_error(void);
 int pla_b200_abi_version(void);
+/* When an entry point is called with `status` == NULL, its kernels OR their PLA_B200_DEV_* bits into a status
+ * word that the library keeps on each GPU instead, so that a device-detected problem (a wait that ran out, a
+ * slot outside the pool, a decay out of range) is never silent. This call copies the current device's word to
+ * `*out` (it waits for the device's earlier work, so keep it off the hot path) and, with `clear` != 0, resets
+ * it. No counterpart in the reference, whose kernels trap instead. */
+int pla_b200_device_status(int32_t* out, int clear);
 
 /* ======================================================================== *
  * k-last decode / MTP verify

@@ -37,3 +37,13 @@ ops = torch.ops.pla_b200
 
 def last_error() -> str:
     return native.pla_b200_last_error().decode()
+
+
+def device_status(clear: bool = False) -> int:
+    """PLA_B200_DEV_* bits that kernels on the current CUDA device reported while the caller passed no ``status``
+    tensor (``pla_b200_device_status``). Waits for the device's earlier work: poll it off the hot path."""
+    word = ctypes.c_int32(0)
+    rc = native.pla_b200_device_status(ctypes.byref(word), 1 if clear else 0)
+    if rc != 0:
+        raise RuntimeError(f"pla_b200_device_status failed: {last_error()}")
+    return int(word.value)

@@ -34,6 +34,13 @@ void set_error(const char* fmt, ...);
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int sm_count();  // multiprocessors of the current device (cached per device)
+// Device address of the library's own status word on the current GPU (NULL when it cannot be resolved):
+// every entry point substitutes it for a NULL `status` argument.
+int32_t* device_status_word();
+template <typename Args>
+inline void default_status(Args& a) {
+  if (a.status == nullptr) a.status = device_status_word();
+}
 
 // -------------------------------------------------------------- device side
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {

@@ -260,7 +260,8 @@ __global__ void __launch_bounds__(CONV_THREADS) conv_history_kernel(const pla_b2
 extern "C" int pla_b200_causal_conv_prefill(const pla_b200_conv_prefill_args* args, void* stream) {
   using namespace pla;
   PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
-  const pla_b200_conv_prefill_args& a = *args;
+  pla_b200_conv_prefill_args a = *args;
+  default_status(a);
   PLA_REQUIRE(a.N >= 0 && a.tokens >= 0 && a.channels > 0 && a.channels % VEC == 0, PLA_B200_E_INVALID,
               "conv needs N >= 0, tokens >= 0 and a channel count that is a multiple of 8");
   PLA_REQUIRE(a.act_dtype == PLA_B200_BF16 || a.act_dtype == PLA_B200_F16, PLA_B200_E_INVALID,

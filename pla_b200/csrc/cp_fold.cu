@@ -147,7 +147,8 @@ __global__ void __launch_bounds__(FOLD_THREADS) cp_fold_segments_kernel(const pl
 extern "C" int pla_b200_cp_fold_segments(const pla_b200_cp_fold_segments_args* args, void* stream) {
   using namespace pla;
   PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
-  const pla_b200_cp_fold_segments_args& a = *args;
+  pla_b200_cp_fold_segments_args a = *args;
+  default_status(a);
   PLA_REQUIRE(a.HV > 0 && a.sequences >= 0, PLA_B200_E_INVALID, "fold needs HV > 0 and sequences >= 0");
   if (a.sequences == 0) return PLA_B200_OK;
   PLA_REQUIRE(a.pairs && a.seg_first && a.state_in && aligned16(a.pairs), PLA_B200_E_INVALID,
@@ -171,7 +172,8 @@ extern "C" int pla_b200_cp_fold_segments(const pla_b200_cp_fold_segments_args* a
 extern "C" int pla_b200_cp_fold_prefix(const pla_b200_cp_fold_args* args, void* stream) {
   using namespace pla;
   PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
-  const pla_b200_cp_fold_args& a = *args;
+  pla_b200_cp_fold_args a = *args;
+  default_status(a);
   PLA_REQUIRE(a.HV > 0 && a.rank >= 0 && a.world > 0 && (a.compose != 0 ? a.rank <= a.world : a.rank < a.world),
               PLA_B200_E_INVALID, "fold needs HV > 0 and 0 <= rank < world (<= world when composing)");
   PLA_REQUIRE(a.state_out != nullptr && (a.rank == 0 || a.pairs != nullptr), PLA_B200_E_INVALID,

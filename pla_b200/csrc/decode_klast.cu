@@ -469,7 +469,8 @@ int launch_shape(const pla_b200_klast_args& a, cudaStream_t stream) {
 extern "C" int pla_b200_decode_klast(const pla_b200_klast_args* args, void* stream) {
   using namespace pla;
   PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
-  const pla_b200_klast_args& a = *args;
+  pla_b200_klast_args a = *args;
+  default_status(a);
   PLA_REQUIRE(a.B >= 0 && a.t_max >= 0, PLA_B200_E_INVALID, "B and t_max must be non-negative");
   if (a.B == 0 || a.t_max == 0) return PLA_B200_OK;
   PLA_REQUIRE(a.H > 0 && a.HV >= a.H && a.HV % a.H == 0, PLA_B200_E_INVALID,

@@ -180,7 +180,8 @@ int launch(const pla_b200_vlast_args& a, cudaStream_t stream) {
 extern "C" int pla_b200_decode_vlast(const pla_b200_vlast_args* args, void* stream) {
   using namespace pla;
   PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
-  const pla_b200_vlast_args& a = *args;
+  pla_b200_vlast_args a = *args;
+  default_status(a);
   PLA_REQUIRE(a.B >= 0, PLA_B200_E_INVALID, "B must be non-negative");
   if (a.B == 0) return PLA_B200_OK;
   PLA_REQUIRE(a.H > 0 && a.HV >= a.H && a.HV % a.H == 0, PLA_B200_E_INVALID,

@@ -169,7 +169,8 @@ int launch_mega(const pla_b200_kda_mega_args& a, cudaStream_t s) {
 extern "C" int pla_b200_kda_decode_mega(const pla_b200_kda_mega_args* args, void* stream) {
   using namespace pla;
   PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
-  const pla_b200_kda_mega_args& a = *args;
+  pla_b200_kda_mega_args a = *args;
+  default_status(a);
   PLA_REQUIRE(a.B >= 0 && a.H > 0 && a.slots > 0, PLA_B200_E_INVALID, "B >= 0, H > 0, slots > 0 required");
   if (a.B == 0) return PLA_B200_OK;
   PLA_REQUIRE(a.x && a.weight && a.conv_state && a.raw_g && a.raw_beta && a.A_log && a.dt_bias && a.state_indices &&

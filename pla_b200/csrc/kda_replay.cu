@@ -899,7 +899,8 @@ int launch_plan(const pla_b200_kda_commit_args& a, cudaStream_t s) {
 extern "C" int pla_b200_kda_replay_verify(const pla_b200_kda_verify_args* args, void* stream) {
   using namespace pla;
   PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
-  const pla_b200_kda_verify_args& a = *args;
+  pla_b200_kda_verify_args a = *args;
+  default_status(a);
   PLA_REQUIRE(a.null_block_id == -1 || a.null_block_id == 0 || a.row_by_slot, PLA_B200_E_INVALID,
               "null_block_id must be -1 or 0");
   PLA_REQUIRE(a.H > 0 && a.N >= 0 && a.Q >= 1 && a.Q <= 32 && a.T >= 0 && a.slots > 0, PLA_B200_E_INVALID,
@@ -952,7 +953,8 @@ extern "C" int pla_b200_kda_ring_verify(const pla_b200_kda_verify_args* args, vo
 extern "C" int pla_b200_kda_fold_layers(const pla_b200_kda_fold_args* args, void* stream) {
   using namespace pla;
   PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
-  const pla_b200_kda_fold_args& a = *args;
+  pla_b200_kda_fold_args a = *args;
+  default_status(a);
   PLA_REQUIRE(a.layers > 0 && a.B >= 0 && a.H > 0 && a.HV >= a.H && a.HV % a.H == 0 && a.L >= 1 && a.L <= 32 &&
                   a.slots > 0,
               PLA_B200_E_INVALID, "fold requires grouped heads, positive dimensions, and ring length 1..32");
@@ -999,15 +1001,18 @@ extern "C" int pla_b200_kda_conv_scatter(const pla_b200_kda_conv_scatter_args* a
 extern "C" int pla_b200_kda_replay_plan(const pla_b200_kda_commit_args* args, void* stream) {
   using namespace pla;
   PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
-  const int rc = check_commit(*args);
+  pla_b200_kda_commit_args a = *args;
+  default_status(a);
+  const int rc = check_commit(a);
   if (rc != PLA_B200_OK) return rc;
-  return launch_plan(*args, static_cast<cudaStream_t>(stream));
+  return launch_plan(a, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int pla_b200_kda_replay_commit(const pla_b200_kda_commit_args* args, void* stream) {
   using namespace pla;
   PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
-  const pla_b200_kda_commit_args& a = *args;
+  pla_b200_kda_commit_args a = *args;
+  default_status(a);
   int rc = check_commit(a);
   if (rc != PLA_B200_OK) return rc;
   PLA_REQUIRE(a.layers != nullptr && a.n_layers > 0, PLA_B200_E_INVALID, "invalid layer pointer table");

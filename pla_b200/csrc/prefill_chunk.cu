@@ -1440,6 +1440,7 @@ extern "C" int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args,
   using namespace pla;
   PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
   pla_b200_gdn_chunk_args a = *args;
+  default_status(a);
   a.is_kda = 0;
   const int rc0 = check_chunk_args(a, pla_b200_gdn_chunk_workspace_bytes(a.max_chunks, a.H, a.HV));
   if (rc0 != PLA_B200_OK) return rc0;
@@ -1482,6 +1483,7 @@ extern "C" int pla_b200_kda_prefill_chunked(const pla_b200_gdn_chunk_args* args,
   using namespace pla;
   PLA_REQUIRE(args != nullptr, PLA_B200_E_INVALID, "args is NULL");
   pla_b200_gdn_chunk_args a = *args;
+  default_status(a);
   a.is_kda = 1;
   const int rc0 = check_chunk_args(a, pla_b200_kda_chunk_workspace_bytes(a.max_chunks, a.H));
   if (rc0 != PLA_B200_OK) return rc0;

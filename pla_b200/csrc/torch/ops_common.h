@@ -7,7 +7,10 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
 
+#include <cuda_runtime_api.h>
+
 #include <cstdlib>
+#include <cstring>
 #include <optional>
 #include <string>
 
@@ -37,16 +40,22 @@ inline void check_abi(int rc, const char* op) {
 inline bool bypass_exec() {
   static const bool on = [] {
     const char* v = std::getenv("PLA_BYPASS_EXEC");
-    return v != nullptr && v[0] != '\0' && !(v[0] == '0' && v[1] == '\0');
+    return v != nullptr && std::strcmp(v, "1") == 0;   // exactly "1", as in the reference
   }();
   return on;
 }
 
 // PLA_SANITY_CHECK=1 (read at every call, as in the reference: src/sanity_check.h): value-level checks of
 // the index metadata on the host. They synchronise the stream and copy to the host: a debugging aid.
+// While the current stream is being captured into a CUDA graph the checks are skipped (a copy to the host would
+// invalidate the capture), as the reference does; a failing capture-status query raises.
 inline bool sanity_check() {
   const char* v = std::getenv("PLA_SANITY_CHECK");
-  return v != nullptr && v[0] != '\0' && !(v[0] == '0' && v[1] == '\0');
+  if (v == nullptr || std::strcmp(v, "1") != 0) return false;
+  cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+  const cudaError_t err = cudaStreamIsCapturing(c10::cuda::getCurrentCUDAStream().stream(), &capture);
+  TORCH_CHECK(err == cudaSuccess, "PLA_SANITY_CHECK: cudaStreamIsCapturing failed: ", cudaGetErrorString(err));
+  return capture == cudaStreamCaptureStatusNone;
 }
 
 // Value checks on host copies of the index metadata. They return a message (empty = fine) and the op raises

@@ -369,9 +369,12 @@ at::Tensor gdn_prefill_chunked_stage(const at::Tensor& q, const at::Tensor& k, c
                                      const Optional& workspace, bool transposed, bool normalize_qk, double scale,
                                      bool gate_activated, int64_t max_chunks, int64_t stage, bool prescan,
                                      const Optional& status, const Optional& range_mask, const Optional& out_indices) {
-  return run_chunked(q, k, v, gate, beta, A_log, dt_bias, out, g_cum, cu_seqlens, state_in, c10::nullopt, state_out,
-                     out_indices, transposed, normalize_qk, scale, gate_activated, false, max_chunks, stage, status,
-                     workspace, prescan, false, std::nullopt, range_mask);
+  // `range_mask`: for a prescan, ranges with a negative entry are skipped; for the segment pass it is the slot of
+  // every range inside `state_in` (a negative entry makes the range padding: zero output rows, no state touched)
+  return run_chunked(q, k, v, gate, beta, A_log, dt_bias, out, g_cum, cu_seqlens, state_in,
+                     prescan ? Optional() : range_mask, state_out, out_indices, transposed, normalize_qk, scale,
+                     gate_activated, false, max_chunks, stage, status, workspace, prescan, false, std::nullopt,
+                     prescan ? range_mask : Optional());
 }
 
 // Incoming state of every token range of every sequence from the prescan pairs (intra-GPU split).

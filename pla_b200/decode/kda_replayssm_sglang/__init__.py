@@ -62,27 +62,32 @@ def fused_kda_decode_mtp_dspark(
     fp32 attention output. ``lower_bound=None`` (not in the reference, which requires the safe gate)
     selects the softplus gate. ``status`` (int32[1], not in the reference) receives device-detected
     errors."""
-    rings = (replayssm_rawv, replayssm_rawk, replayssm_g, replayssm_beta)
-    if any(r is None for r in rings):
-        raise ValueError("fused_kda_decode_mtp_dspark implements CACHE_RING only; pass all four replayssm_* rings.")
-    onorm_args = (onorm_gate, onorm_weight, onorm_eps)
-    apply_onorm = all(value is not None for value in onorm_args)
-    if any(value is not None for value in onorm_args) and not apply_onorm:
-        raise ValueError("fused output norm requires onorm_gate, onorm_weight, and onorm_eps")
-    if scale is None:
-        scale = TILE_K ** -0.5
-    if out is None:
-        out = torch.empty_like(x_v, memory_format=torch.contiguous_format)
+    records = {"replayssm_rawv": replayssm_rawv, "replayssm_rawk": replayssm_rawk, "replayssm_g": replayssm_g,
+               "replayssm_beta": replayssm_beta}
+    absent = [name for name, ring in records.items() if ring is None]
+    if absent:
+        raise ValueError("the verify step records into the four replay rings (ring-cache mode is the only one built); "
+                         f"missing: {', '.join(absent)}")
+    gate, weight, eps = _output_norm(onorm_gate, onorm_weight, onorm_eps)
+    result = out if out is not None else torch.empty_like(x_v, memory_format=torch.contiguous_format)
     ops.kda_ring_verify(
         x_q, x_k, x_v, g, beta, w_q.contiguous(), w_k.contiguous(), w_v.contiguous(), cs_q, cs_k, cs_v,
-        A_log.contiguous(), dt_bias.contiguous(), recurrent_state, out,
+        A_log.contiguous(), dt_bias.contiguous(), recurrent_state, result,
         intermediate_conv_q, intermediate_conv_k, intermediate_conv_v,
-        replayssm_rawv, replayssm_rawk, replayssm_g, replayssm_beta,
-        ssm_state_indices, intermediate_state_indices, cu_seqlens, float(scale),
-        None if lower_bound is None else float(lower_bound),
-        onorm_gate if apply_onorm else None, onorm_weight if apply_onorm else None,
-        float(onorm_eps) if apply_onorm else None, status)
-    return out
+        records["replayssm_rawv"], records["replayssm_rawk"], records["replayssm_g"], records["replayssm_beta"],
+        ssm_state_indices, intermediate_state_indices, cu_seqlens, float(TILE_K ** -0.5 if scale is None else scale),
+        None if lower_bound is None else float(lower_bound), gate, weight, eps, status)
+    return result
+
+
+def _output_norm(gate, weight, eps):
+    """The fused output norm takes its three arguments together or not at all."""
+    given = [value is not None for value in (gate, weight, eps)]
+    if not any(given):
+        return None, None, None
+    if not all(given):
+        raise ValueError("the fused output norm needs onorm_gate, onorm_weight and onorm_eps together")
+    return gate, weight, float(eps)
 
 
 def commit_kda_replayssm_after_verify(
@@ -102,19 +107,24 @@ def commit_kda_replayssm_after_verify(
     ``spec_state`` carries ``temporal [layers, slots, HV, 128, 128]``, ``replayssm_rawv/rawk/g/beta``,
     and the lists ``conv`` / ``intermediate_conv_window``. ``conv_state_layout="width_dim"`` takes
     conv pools ``[layers, slots, width, dim]`` and scratch through transpose views."""
-    if conv_state_layout not in ("dim_width", "width_dim"):
-        raise AssertionError("conv_state_layout must be dim_width or width_dim")
-    if len(spec_state.conv) != len(spec_state.intermediate_conv_window):
-        raise AssertionError("conv pools and conv windows must pair up")
-    num_k_heads = spec_state.replayssm_rawk.shape[2]
+    layouts = {"dim_width": False, "width_dim": True}
+    if conv_state_layout not in layouts:
+        raise AssertionError(f"conv_state_layout is one of {sorted(layouts)}, got {conv_state_layout!r}")
+    pools, windows = list(spec_state.conv), list(spec_state.intermediate_conv_window)
+    if len(pools) != len(windows):
+        raise AssertionError(f"{len(pools)} conv pools but {len(windows)} conv-window scratch tensors")
     ops.kda_fold_all_layers(
         spec_state.temporal, spec_state.replayssm_rawv, spec_state.replayssm_rawk, spec_state.replayssm_g,
         spec_state.replayssm_beta, state_batch_indices, accept_lens, mamba_track_indices, mamba_steps_to_track,
-        int(num_k_heads), int(null_block_id), status)
-    for conv_states, interm_conv in zip(spec_state.conv, spec_state.intermediate_conv_window):
-        if conv_state_layout == "width_dim":
-            conv_states = conv_states.transpose(-1, -2)
-            interm_conv = interm_conv.transpose(-1, -2)
-        ops.kda_conv_window_scatter(conv_states, interm_conv, state_batch_indices, last_correct_step_indices)
-        if mamba_track_indices is not None and mamba_steps_to_track is not None:
-            ops.kda_conv_window_scatter(conv_states, interm_conv, mamba_track_indices, mamba_steps_to_track)
+        int(spec_state.replayssm_rawk.shape[2]), int(null_block_id), status)
+    # conv rollback: the window after the last accepted step goes to the request's slot, and the window after the
+    # tracked step to the tracking slot when tracking is on
+    targets = [(state_batch_indices, last_correct_step_indices)]
+    if mamba_track_indices is not None and mamba_steps_to_track is not None:
+        targets.append((mamba_track_indices, mamba_steps_to_track))
+    width_major = layouts[conv_state_layout]
+    for pool, window in zip(pools, windows):
+        if width_major:     # [.., width, dim] pools: the op addresses [.., dim, width] through transposed views
+            pool, window = pool.transpose(-1, -2), window.transpose(-1, -2)
+        for slots, steps in targets:
+            ops.kda_conv_window_scatter(pool, window, slots, steps)

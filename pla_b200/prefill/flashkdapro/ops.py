@@ -1,6 +1,8 @@
 """KDA prefill entry point with the reference's signature (pla/prefill/flashkdapro/ops.py:66-219)."""
 from __future__ import annotations
 
+import math
+import weakref
 from typing import Optional, Tuple
 
 import torch
@@ -15,6 +17,32 @@ DV = 128
 def _rows(t: torch.Tensor) -> torch.Tensor:
     """[tokens, H, 128] readable in place when one token's features are contiguous; else materialised."""
     return t if (t.stride(2) == 1 and t.stride(1) == 128) else t.contiguous()
+
+
+# Largest gate input the static bound below assumes: 16-bit projections of a trained layer stay far inside it,
+# and an input beyond it still cannot go unnoticed (the chunked kernel sets PLA_B200_DEV_DECAY_RANGE).
+_GATE_INPUT_BOUND = 20.0
+_bound_cache = weakref.WeakKeyDictionary()      # A_log tensor object -> (dt_bias object id, versions, verdict)
+
+
+def _softplus_decay_is_bounded(A_log: torch.Tensor, dt_bias: torch.Tensor) -> bool:
+    """True when the softplus gate ``-exp(A_log) * softplus(x + dt_bias)`` cannot decay a key channel by more than
+    80 nats inside 16 tokens (what the chunked kernels' 16-token reference points can represent) for inputs
+    ``|x| <= 20``:  16 * exp(max A_log) * softplus(20 + max dt_bias) <= 80.  The two maxima are read from the device
+    once per pair of parameter tensors: the verdict is remembered for the tensor OBJECTS (and their versions), so a
+    layer that passes its parameters pays one device read in its lifetime; a caller that builds new tensors for
+    every call pays it every call."""
+    stamp = (id(dt_bias), A_log._version, dt_bias._version)
+    hit = _bound_cache.get(A_log)
+    if hit is not None and hit[0] == stamp:
+        return hit[1]
+    a_max = float(A_log.detach().float().max())
+    b_max = float(dt_bias.detach().float().max())
+    x = _GATE_INPUT_BOUND + b_max
+    softplus = x if x > 20.0 else math.log1p(math.exp(x))
+    verdict = 16.0 * math.exp(a_max) * softplus <= 80.0
+    _bound_cache[A_log] = (stamp, verdict)
+    return verdict
 
 
 def flashkda_fwd(
@@ -48,7 +76,9 @@ def flashkda_fwd(
     references every 16 tokens; needs the decay of every key channel to stay within 80 nats per 16 tokens,
     which the safe gate with ``lower_bound >= -5`` guarantees; a violation sets bit 16 of ``status``),
     ``"recurrent"`` = exact fp32 token recurrence, ``"auto"`` = chunked for the safe gate with
-    ``-5 <= lower_bound < 0``, recurrent otherwise. ``auto_cp`` (keyword-only, default on): with host offsets
+    ``-5 <= lower_bound < 0`` and for a softplus gate whose parameters keep the decay inside that range
+    (``16 exp(max A_log) softplus(20 + max dt_bias) <= 80``, e.g. ``A_log <= -1.4``; checked once per parameter
+    tensor), recurrent otherwise. ``auto_cp`` (keyword-only, default on): with host offsets
     (``raw_cu_seqlens``) and an fp32 ``state_pool``, the chunked backend cuts long sequences of a batch with
     fewer (sequence, head) chains than SMs into token ranges that run in parallel (the job of the reference's
     intra-card planner, src/prefill/flashkdapro/host/torch_extension_cute.cc:179-215).
@@ -101,7 +131,10 @@ def flashkda_fwd(
     gg = g if (g.stride(2) == 1 and g.stride(1) == 128) else g.contiguous()
     lb = None if lower_bound is None else float(lower_bound)
     if backend == "auto":
-        backend = "chunked" if (lb is not None and -5.0 <= lb < 0.0) else "recurrent"
+        if lb is not None:
+            backend = "chunked" if -5.0 <= lb < 0.0 else "recurrent"
+        else:
+            backend = "chunked" if _softplus_decay_is_bounded(A_log, dt_bias) else "recurrent"
     if backend == "chunked":
         max_chunks = T // 64 + (cu32.numel() - 1)
         plan = None
@@ -117,12 +150,18 @@ def flashkda_fwd(
             chunks = sum((b - a + 63) // 64 for a, b in zip(offs, offs[1:]))
             args = (_rows(q), _rows(k), _rows(v), gg, bet, A_log.contiguous(), dt_bias.contiguous(), out, cu_ranges)
             tail = (False, True, float(scale), lb, False, chunks)
+            # a sequence with a negative slot is padding, as in the unsplit kernel: zero output rows, slot untouched
+            seq_slot = state_indices[seq_of]
+            minus = torch.full_like(prescan_mask, -1)
             ws = ops.kda_prefill_chunked(*args, None, None, None, None, None, *tail, 1, False, status)
             pairs = torch.empty((prescan_mask.numel(), H, 2, DV, DK), dtype=torch.float32, device=q.device)
-            ops.kda_prefill_chunked(*args, None, None, pairs, None, ws, *tail, 2, True, status, prescan_mask)
+            ops.kda_prefill_chunked(*args, None, None, pairs, None, ws, *tail, 2, True, status,
+                                    torch.where(seq_slot < 0, minus, prescan_mask))
             state_in = ops.cp_fold_segments(pairs, seg_first, state_pool, state_indices.contiguous(), status)
-            out_idx = torch.where(last_mask, state_indices[seq_of], torch.full_like(prescan_mask, -1))
-            ops.kda_prefill_chunked(*args, state_in, None, state_pool, out_idx, ws, *tail, 2, False, status)
+            range_slot = torch.where(seq_slot < 0, minus,
+                                     torch.arange(prescan_mask.numel(), dtype=torch.int32, device=q.device))
+            out_idx = torch.where(last_mask, seq_slot, minus)
+            ops.kda_prefill_chunked(*args, state_in, range_slot, state_pool, out_idx, ws, *tail, 2, False, status)
             return None
         ops.kda_prefill_chunked(
             _rows(q), _rows(k), _rows(v), gg, bet, A_log.contiguous(), dt_bias.contiguous(), out, cu32,

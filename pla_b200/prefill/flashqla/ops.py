@@ -43,6 +43,76 @@ def _offsets(cu_seqlens, num_tokens, raw_cu_seqlens, device):
     return cu32
 
 
+class ChunkFactor:
+    """The ``A`` by-product of :func:`chunk_gated_delta_rule_fwd`: per token and value head the token's row of
+    ``(I + tril(diag(beta) K K^T . Gamma, -1))^-1`` of its 64-token chunk, ``[1, T, H, 64]`` fp32 (the reference's is
+    the same factor of its 32-token chunks, ``[1, T, H, 32]``). The kernels keep it as tensor-core operand images
+    in the call's workspace, so it is only laid out as a tensor when somebody looks: any attribute, index or torch
+    function applied to this object works on :meth:`materialize`'s result. Rows past ``cu_seqlens[-1]`` are zero.
+    Values carry tf32 rounding (they are the operand the tensor core reads)."""
+
+    _KQ_BYTES, _KNT_BYTES, _VBLOB = 128 * 128 * 4, 128 * 64 * 4, 64 * 64 * 4 * 2 + 1024
+
+    def __init__(self, workspace, cu32, tokens, qk_heads, v_heads, max_chunks):
+        self._ws, self._cu, self._geom = workspace, cu32, (int(tokens), int(qk_heads), int(v_heads), int(max_chunks))
+        self._tensor = None
+
+    def materialize(self) -> torch.Tensor:
+        if self._tensor is None:
+            T, Hg, H, max_chunks = self._geom
+            dev = self._ws.device
+            base = max_chunks * Hg * (self._KQ_BYTES + self._KNT_BYTES)
+            blobs = self._ws[base:base + max_chunks * H * self._VBLOB].view(max_chunks, H, self._VBLOB)
+            # image [column group][row][4 columns] -> [row, column]; only the pieces on or below the diagonal were
+            # ever written, the rest of the image is scratch
+            tiles = blobs[:, :, :CHUNK_SIZE * CHUNK_SIZE * 4].contiguous().view(torch.float32)
+            tiles = tiles.view(max_chunks, H, CHUNK_SIZE // 4, CHUNK_SIZE, 4).permute(0, 1, 3, 2, 4)
+            tiles = tiles.reshape(max_chunks, H, CHUNK_SIZE, CHUNK_SIZE)
+            lower = torch.ones(CHUNK_SIZE, CHUNK_SIZE, dtype=torch.bool, device=dev).tril()
+            tiles = torch.where(lower, tiles, torch.zeros((), device=dev))
+            cu = self._cu.to(torch.int64)
+            lens = (cu[1:] - cu[:-1]).clamp_min(0)
+            first_chunk = torch.cumsum((lens + CHUNK_SIZE - 1) // CHUNK_SIZE, 0) - (lens + CHUNK_SIZE - 1) // CHUNK_SIZE
+            tok = torch.arange(T, device=dev)
+            seq = torch.searchsorted(cu[1:].contiguous(), tok, right=True).clamp_max(lens.numel() - 1)
+            inside = (tok - cu[seq]).clamp_min(0)
+            live = (tok >= cu[seq]) & (tok < cu[seq + 1])
+            rows = tiles[(first_chunk[seq] + inside // CHUNK_SIZE).clamp_max(max_chunks - 1), :, inside % CHUNK_SIZE]
+            self._tensor = torch.where(live[:, None, None], rows, torch.zeros((), device=dev))[None]
+        return self._tensor
+
+    def __getattr__(self, name):            # only reached for names this class does not define
+        return getattr(self.materialize(), name)
+
+    def __getitem__(self, index):
+        return self.materialize()[index]
+
+    def __len__(self):
+        return 1
+
+    def __repr__(self):
+        state = "materialised" if self._tensor is not None else "deferred"
+        return f"ChunkFactor([1, {self._geom[0]}, {self._geom[2]}, {CHUNK_SIZE}], {state})"
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        unwrap = lambda x: x.materialize() if isinstance(x, ChunkFactor) else x
+        return func(*[unwrap(a) for a in args], **{k_: unwrap(v_) for k_, v_ in (kwargs or {}).items()})
+
+
+def _forward_operator(name):
+    def method(self, *args):
+        return getattr(self.materialize(), name)(*[a.materialize() if isinstance(a, ChunkFactor) else a for a in args])
+    method.__name__ = name
+    return method
+
+
+for _op in ("__add__", "__radd__", "__sub__", "__rsub__", "__mul__", "__rmul__", "__truediv__", "__rtruediv__", "__neg__",
+            "__matmul__", "__rmatmul__", "__pow__", "__abs__", "__float__", "__iter__"):
+    setattr(ChunkFactor, _op, _forward_operator(_op))
+del _op
+
+
 _plan_cache: "OrderedDict" = None  # type: ignore[assignment]
 
 
@@ -141,12 +211,13 @@ def chunk_gated_delta_rule_fwd(
     ``g = -exp(A_log) * softplus(a + dt_bias)`` and ``beta = sigmoid(b)`` are formed in the kernel.
     Evaluated chunk-wise (chunk 64, WY/UT transform) on the tensor cores. ``g_cum`` is the
     chunk-local cumulative log decay ``[1, T, H]`` fp32 at chunk size 64 (the reference uses 32);
-    the reference's ``A`` by-product is not materialised in its layout and is returned as
-    ``None`` (nothing downstream of inference reads it). ``auto_cp`` (default on): with host offsets
+    ``A`` is a :class:`ChunkFactor`: the chunk-64 counterpart ``[1, T, H, 64]`` of the reference's factor, laid out
+    as a tensor on first use (inference never reads it, so the call itself does not pay for it). ``auto_cp`` (default on): with host offsets
     (``raw_cu_seqlens``) and an indexed fp32 pool, batches with fewer (sequence, head) chains than SMs have
     their long sequences cut into token ranges that run as independent chains (prescan of every range,
     fold of the (offset, transition) pairs, then the ranges in parallel from their incoming states); a
-    negative slot index then means "start from zero, drop the final state". ``overlap_warmup_threshold`` and
+    a negative slot index marks a padding sequence either way (zero output rows, no state read or written).
+    ``overlap_warmup_threshold`` and
     ``force_tc01_cp_candidate`` tune the reference's planner and are accepted and ignored.
     """
     if not q.is_cuda:
@@ -218,24 +289,36 @@ def chunk_gated_delta_rule_fwd(
         n_ranges = prescan_mask.numel()
         stage_args = (q[0], k[0], v[0], gate, bet, A_log, dt_bias, o[0])
         tail = (False, bool(normalize_qk), float(scale), not use_raw, int(max_chunks))
+        # a sequence with a negative slot is padding, exactly as in the unsplit kernel: its ranges are neither
+        # prescanned nor run (zero output rows), its slot is never read or written
+        seq_slot = initial_state_indices[seq_of]
+        minus = torch.full_like(prescan_mask, -1)
         ws = ops.gdn_prefill_chunked_stage(*stage_args, g_cum[0], cu_ranges, None, None, None, *tail, 1, False, None,
                                            None, None)
         pairs = torch.empty((n_ranges, H, 2, DV, DK), dtype=torch.float32, device=q.device)
         ops.gdn_prefill_chunked_stage(*stage_args, None, cu_ranges, None, pairs, ws, *tail, 2, True, None,
-                                      prescan_mask, None)
+                                      torch.where(seq_slot < 0, minus, prescan_mask), None)
         state_in = ops.cp_fold_segments(pairs, seg_first, initial_state, initial_state_indices, None)
-        out_idx = torch.where(last_mask, initial_state_indices[seq_of], torch.full_like(prescan_mask, -1))
+        range_slot = torch.where(seq_slot < 0, minus, torch.arange(n_ranges, dtype=torch.int32, device=q.device))
+        out_idx = torch.where(last_mask, seq_slot, minus)
         ops.gdn_prefill_chunked_stage(*stage_args, None, cu_ranges, state_in, initial_state, ws, *tail, 2, False, None,
-                                      None, out_idx)
-        final_state = initial_state[initial_state_indices.long()] if output_final_state else None
-        return g_cum, None, o, None, final_state
-    ops.gdn_prefill_chunked(
+                                      range_slot, out_idx)
+        final_state = _gather_final(initial_state, initial_state_indices) if output_final_state else None
+        return g_cum, ChunkFactor(ws, cu32, T, Hg, H, max_chunks), o, None, final_state
+    ws = ops.gdn_prefill_chunked(
         q[0], k[0], v[0], gate, bet, A_log, dt_bias, o[0], g_cum[0], cu32, initial_state,
         initial_state_indices if indexed else None, state_out, None, not indexed, bool(normalize_qk),
         float(scale), not use_raw, indexed, int(max_chunks), 0, None)
     if indexed and output_final_state:
-        final_state = initial_state[initial_state_indices.long()]
-    return g_cum, None, o, None, final_state
+        final_state = _gather_final(initial_state, initial_state_indices)
+    return g_cum, ChunkFactor(ws, cu32, T, Hg, H, max_chunks), o, None, final_state
+
+
+def _gather_final(pool: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """Final states of the batch out of the indexed pool; a padding sequence (negative slot) gets zeros."""
+    idx = slots.long()
+    rows = pool[idx.clamp_min(0)]
+    return torch.where((idx < 0)[:, None, None, None], torch.zeros((), dtype=pool.dtype, device=pool.device), rows)
 
 
 def gdn_prefill_packed_qkv_fwd(
@@ -262,32 +345,8 @@ def gdn_prefill_packed_qkv_fwd(
     contiguous, the token stride may exceed the row width and the view may start at any element
     (Q/K/V are consumed in place as aliases of the buffer). Same return contract as
     :func:`chunk_gated_delta_rule_fwd`."""
-    if not packed_qkv.is_cuda:
-        raise ValueError("packed_qkv must be a CUDA tensor")
-    if packed_qkv.ndim != 2:
-        raise ValueError("packed_qkv must be rank-2 [T,QKV]")
-    if packed_qkv.dtype not in (torch.float16, torch.bfloat16):
-        raise ValueError("packed_qkv must be fp16 or bf16")
-    if packed_qkv.stride(1) != 1:
-        raise ValueError("packed_qkv features must be contiguous")
-    if num_qk_heads <= 0 or num_v_heads <= 0:
-        raise ValueError("num_qk_heads and num_v_heads must be positive")
-    T = packed_qkv.size(0)
-    if T == 0:
-        raise ValueError("GDN packed prefill does not support an empty token dimension")
     Hg, H = int(num_qk_heads), int(num_v_heads)
-    qk_width = Hg * DK
-    width = 2 * qk_width + H * DV
-    if packed_qkv.size(1) != width:
-        raise ValueError(f"packed_qkv width must be {width} for H={H}, Hg={Hg}, got {packed_qkv.size(1)}")
-    pitch = packed_qkv.stride(0)
-    if pitch < width:
-        raise ValueError("packed_qkv token stride must cover the complete Q|K|V row")
-    off = packed_qkv.storage_offset()
-    batch_stride = max(T, 1) * pitch
-    q = packed_qkv.as_strided((1, T, Hg, DK), (batch_stride, pitch, DK, 1), off)
-    k = packed_qkv.as_strided((1, T, Hg, DK), (batch_stride, pitch, DK, 1), off + qk_width)
-    v = packed_qkv.as_strided((1, T, H, DV), (batch_stride, pitch, DV, 1), off + 2 * qk_width)
+    q, k, v = _packed_views(packed_qkv, Hg, H)
     return chunk_gated_delta_rule_fwd(
         q, k, v, None, None, scale=scale, initial_state=initial_state,
         initial_state_indices=initial_state_indices, cu_seqlens=cu_seqlens,
@@ -295,3 +354,29 @@ def gdn_prefill_packed_qkv_fwd(
         overlap_warmup_threshold=overlap_warmup_threshold, force_tc01_cp_candidate=force_tc01_cp_candidate,
         normalize_qk=True, raw_cu_seqlens=raw_cu_seqlens, raw_gate_a=raw_gate_a, raw_beta_b=raw_beta_b,
         A_log=A_log, dt_bias=dt_bias, final_state_dtype=final_state_dtype)
+
+
+def _packed_views(rows: torch.Tensor, Hg: int, H: int):
+    """q, k, v of a packed ``[T, Hg*128 | Hg*128 | H*128]`` buffer as ``[1, T, heads, 128]`` views that alias it
+    (no copy; the row pitch and the buffer's offset inside its storage carry over)."""
+    if Hg <= 0 or H <= 0:
+        raise ValueError(f"head counts must be positive, got num_qk_heads={Hg}, num_v_heads={H}")
+    problems = []
+    if not rows.is_cuda:
+        problems.append("it must live on a CUDA device")
+    if rows.ndim != 2:
+        problems.append(f"it must be [T, Q|K|V], got {rows.ndim} dimensions")
+    if rows.dtype not in (torch.float16, torch.bfloat16):
+        problems.append(f"it must be fp16 or bf16, got {rows.dtype}")
+    if problems:
+        raise ValueError("packed_qkv: " + "; ".join(problems))
+    want = (2 * Hg + H) * DK
+    if rows.size(0) == 0:
+        raise ValueError("packed_qkv: an empty token dimension is not supported")
+    if rows.size(1) != want:
+        raise ValueError(f"packed_qkv: a row holds {rows.size(1)} features, but Hg={Hg}, H={H} need {want}")
+    if rows.stride(1) != 1:
+        raise ValueError("packed_qkv: the features of a token must be contiguous (the token pitch is free)")
+    qk = Hg * DK
+    split = lambda lo, heads: rows[:, lo:lo + heads * DK].unflatten(1, (heads, DK)).unsqueeze(0)
+    return split(0, Hg), split(qk, Hg), split(2 * qk, H)

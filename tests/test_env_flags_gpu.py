@@ -65,3 +65,42 @@ print('bypass ok')
     env = dict(os.environ, PLA_BYPASS_EXEC="1")
     res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0 and "bypass ok" in res.stdout, res.stdout + res.stderr
+
+
+def test_flags_are_on_only_for_the_value_one_and_checks_pause_during_graph_capture(native_built, monkeypatch):
+    """The reference enables PLA_SANITY_CHECK only for the value "1" (src/sanity_check.h) and skips the value checks
+    while the stream is being captured (a copy to the host would invalidate the capture)."""
+    from pla_b200.decode import fused_sigmoid_gating_delta_rule_forward_k_last as fwd
+    args, pool = decode_args(bad_slot=True)
+    for value in ("false", "yes", "2", ""):
+        monkeypatch.setenv("PLA_SANITY_CHECK", value)
+        fwd(*args)                               # not "1": no host-side value check, the kernel flags the slot itself
+    torch.cuda.synchronize()
+    monkeypatch.setenv("PLA_SANITY_CHECK", "1")
+    good, _ = decode_args()
+    fwd(*good)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fwd(*good)                               # would raise "operation not permitted when stream is capturing"
+    graph.replay()
+    torch.cuda.synchronize()
+
+
+def test_library_status_word_catches_what_a_missing_status_tensor_would_lose(native_built):
+    """No status tensor: the bad slot is reported through the library's own status word on the device."""
+    from pla_b200._ops import device_status
+    from pla_b200.decode import fused_sigmoid_gating_delta_rule_forward_k_last as fwd
+    device_status(clear=True)
+    args, pool = decode_args(bad_slot=True)
+    before = pool.clone()
+    out = fwd(*args)
+    torch.cuda.synchronize()
+    assert device_status() & 8                   # PLA_B200_DEV_BAD_SLOT
+    assert torch.count_nonzero(out[0, 1]) == 0   # the request with the bad slot got zero rows
+    assert torch.equal(pool[[2, 3]], before[[2, 3]])   # slots 2 and 3 belong to no request
+    assert device_status(clear=True) & 8 and device_status() == 0
+    good, _ = decode_args()
+    fwd(*good)
+    torch.cuda.synchronize()
+    assert device_status() == 0

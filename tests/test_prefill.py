@@ -242,3 +242,39 @@ def test_kda_chunked_reports_decay_out_of_range(native_built):
                  backend="chunked", status=status)
     torch.cuda.synchronize()
     assert status.item() & 16
+
+
+def test_auto_backend_bound_for_the_softplus_gate(native_built):
+    """``backend="auto"`` sends a softplus gate to the chunk-64 tensor-core kernels exactly when its parameters keep
+    the decay of 16 tokens within 80 nats for gate inputs up to 20 (16 exp(max A_log) softplus(20 + max dt_bias) <= 80):
+    the benchmark's weak-decay gates A_log ~ U(-4, -2) qualify, A_log = -1 does not."""
+    from pla_b200.prefill.flashkdapro.ops import _softplus_decay_is_bounded
+    weak = -4.0 + 2.0 * torch.rand(32, generator=torch.Generator().manual_seed(1))
+    bias = torch.randn(32, 128, generator=torch.Generator().manual_seed(2)) * 0.1
+    assert _softplus_decay_is_bounded(weak, bias)
+    assert _softplus_decay_is_bounded(torch.full((4,), -1.5), torch.zeros(4, 128))
+    assert not _softplus_decay_is_bounded(torch.full((4,), -1.0), torch.zeros(4, 128))
+    assert not _softplus_decay_is_bounded(torch.tensor([-4.0, 1.0]), torch.zeros(2, 128))
+    assert not _softplus_decay_is_bounded(torch.full((4,), -1.5), torch.full((4, 128), 6.0))
+
+
+@pytest.mark.gpu
+def test_auto_backend_runs_the_chunked_kernels_for_weak_softplus_gates(native_built):
+    from pla_b200.prefill.flashkdapro import flashkda_fwd
+    H, T = 2, 300
+    g = torch.Generator(device="cuda").manual_seed(4)
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")
+    q, k, v, gate = (rn(T, H, D).bfloat16() for _ in range(4))
+    beta = rn(T, H).bfloat16()
+    A_log = -4.0 + 2.0 * torch.rand(H, generator=g, device="cuda")
+    dt_bias = rn(H, D) * 0.1
+    outs = {}
+    for backend in ("auto", "chunked", "recurrent"):
+        out = torch.empty(T, H, D, dtype=torch.bfloat16, device="cuda")
+        final = torch.empty(1, H, D, D, device="cuda")
+        flashkda_fwd(q, k, v, gate, beta, A_log, dt_bias, out, None, None, final_state=final, backend=backend)
+        outs[backend] = (out.float(), final)
+    torch.cuda.synchronize()
+    assert torch.equal(outs["auto"][0], outs["chunked"][0]) and torch.equal(outs["auto"][1], outs["chunked"][1])
+    assert_out_close(outs["auto"][0], outs["recurrent"][0], "chunked vs token recurrence")
+    assert_state_close(outs["auto"][1], outs["recurrent"][1], "chunked vs token recurrence")

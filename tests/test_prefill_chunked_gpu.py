@@ -302,3 +302,83 @@ def test_intra_gpu_token_ranges_match_single_chains(native_built, weak_decay):
         assert torch.equal(res[4].cpu(), dpool.cpu()[slots])
     assert torch.equal(results[True][3], results[False][3])                  # g_cum is the same by-product
     assert_out_close(results[True][0], results[False][0], "ranges vs single chains")
+
+
+def test_negative_slot_is_padding_with_and_without_token_ranges(native_built):
+    """A sequence whose slot index is negative is padding in both evaluations of the same call: zero output rows,
+    no slot read or written, zero rows in the returned final states; the other sequences are unaffected."""
+    from pla_b200.prefill.flashqla import ops as fq
+    g = torch.Generator().manual_seed(23)
+    Hg, H = 1, 2
+    lengths = [3300, 1300, 70]
+    T = sum(lengths)
+    offs = [0, 3300, 4600, 4670]
+    assert fq.plan_token_ranges(offs, H, 148) is not None
+    q, k, v = (torch.randn(1, T, n, D, generator=g).bfloat16() for n in (Hg, Hg, H))
+    gates = torch.randn(T, 2 * H, generator=g).bfloat16()
+    A_log = torch.rand(H, generator=g) * 2.0
+    dt_bias = torch.randn(H, generator=g) * 0.1
+    pool = torch.randn(6, H, D, D, generator=g) * 0.05
+    slots = [-1, 2, 5]
+    live = torch.arange(T) >= offs[1]
+    exp_out, exp_state, _ = odec.klast_forward(q=q[0], k=k[0], v=v[0], a=gates[:, :H], b=gates[:, H:], A_log=A_log,
+                                               dt_bias=dt_bias, state=pool, slot_indices=slots, lengths=lengths,
+                                               scale=D ** -0.5)
+    dev = "cuda"
+    outs = {}
+    for auto_cp in (False, True):
+        dpool = pool.to(dev)
+        dg = gates.to(dev)
+        res = fq.chunk_gated_delta_rule_fwd(
+            q.to(dev), k.to(dev), v.to(dev), None, None, initial_state=dpool,
+            initial_state_indices=torch.tensor(slots, dtype=torch.int32, device=dev),
+            cu_seqlens=torch.tensor(offs, dtype=torch.int32, device=dev), output_final_state=True, auto_cp=auto_cp,
+            normalize_qk=True, raw_cu_seqlens=tuple(offs), raw_gate_a=dg[:, :H], raw_beta_b=dg[:, H:],
+            A_log=A_log.to(dev), dt_bias=dt_bias.to(dev))
+        torch.cuda.synchronize()
+        out, final = res[2][0].cpu(), res[4].cpu()
+        assert torch.count_nonzero(out[~live]) == 0, f"auto_cp={auto_cp}: the padding sequence must give zero rows"
+        assert_out_close(out[live], exp_out[live], f"auto_cp={auto_cp}")
+        assert_state_close(dpool.cpu(), exp_state, f"auto_cp={auto_cp}")
+        for s_ in (0, 1, 3, 4):
+            assert torch.equal(dpool[s_].cpu(), pool[s_])
+        assert torch.count_nonzero(final[0]) == 0 and torch.equal(final[1:], dpool.cpu()[[2, 5]])
+        outs[auto_cp] = out
+    assert_out_close(outs[True], outs[False], "ranges vs single chains")
+
+
+@pytest.mark.parametrize("name", sorted(cases.PREFILL_CASES))
+def test_chunk_factor_by_product(native_built, name):
+    """``A`` of the facade's return tuple (pla/prefill/flashqla/ops.py:247-248 of the reference returns it second): a
+    deferred object that lays the chunk-64 factor out as [1, T, H, 64] on first use -- each token's row of
+    (I + tril(diag(beta) K K^T . Gamma, -1))^-1, zero rows past the last sequence."""
+    from pla_b200.prefill.flashqla import gdn_prefill_packed_qkv_fwd
+    from pla_b200.prefill.flashqla.ops import ChunkFactor
+    c = cases.gdn_prefill_case(name, device="cuda")
+    cpu = cases.gdn_prefill_case(name)
+    Hg, H, T = cpu["Hg"], cpu["H"], cpu["T"]
+    g_cum, A, o, none, final = gdn_prefill_packed_qkv_fwd(
+        c["packed"], c["a"], c["b"], c["A_log"], c["dt_bias"], torch.tensor(cpu["cu"], dtype=torch.int32, device="cuda"),
+        num_qk_heads=Hg, num_v_heads=H, initial_state=c["pool"],
+        initial_state_indices=torch.tensor(cpu["slots"], dtype=torch.int32, device="cuda"), output_final_state=False,
+        raw_cu_seqlens=tuple(cpu["cu"]))
+    assert isinstance(A, ChunkFactor) and none is None
+    assert tuple(A.shape) == (1, T, H, C) and A.dtype == torch.float32       # touching it lays it out
+    got = (A * 1.0)[0].cpu()                                                   # operators and torch functions
+    assert torch.equal(got, A[0].cpu()) and torch.equal(torch.mul(A, 1.0)[0].cpu(), got)
+    kw = cases.gdn_prefill_oracle_kwargs(cpu)
+    kn = odec.l2norm(kw["k"].float())
+    g = odec.log_decay(cpu["a"].float() + cpu["dt_bias"], cpu["A_log"][None], None)
+    beta = torch.sigmoid(cpu["b"].float())
+    R = H // Hg
+    for s, n_seq in enumerate(cpu["lengths"]):
+        for ci in range((n_seq + C - 1) // C):
+            t0 = cpu["cu"][s] + ci * C
+            n = min(C, n_seq - ci * C)
+            for hv in range(H):
+                K = kn[t0:t0 + n, hv // R]
+                G = torch.cumsum(g[t0:t0 + n, hv], 0)
+                L = torch.tril(beta[t0:t0 + n, hv, None] * (K @ K.t()) * torch.exp(G[:, None] - G[None, :]), -1)
+                T_ref = torch.linalg.solve_triangular(torch.eye(n) + L, torch.eye(n), upper=False)
+                torch.testing.assert_close(got[t0:t0 + n, hv, :n], T_ref, rtol=5e-3, atol=2e-3)
+    assert torch.count_nonzero(got[cpu["cu"][-1]:]) == 0
