@@ -63,6 +63,11 @@ int pla_b200_abi_version(void);
  * `*out` (it waits for the device's earlier work, so keep it off the hot path) and, with `clear` != 0, resets
  * it. No counterpart in the reference, whose kernels trap instead. */
 int pla_b200_device_status(int32_t* out, int clear);
+/* sizeof() of an argument structure of this header by name (e.g. "pla_b200_klast_args") and offsetof() of one of
+ * its fields, as compiled into the library; -1 for an unknown name. For bindings that mirror the structures in
+ * another language and want to check their layout at load time. No counterpart in the reference (pybind). */
+int64_t pla_b200_struct_size(const char* type);
+int64_t pla_b200_field_offset(const char* type, const char* field);
 
 /* ======================================================================== *
  * k-last decode / MTP verify

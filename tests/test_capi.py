@@ -52,3 +52,16 @@ def test_host_contract_errors_raise_runtime_error(native_built):
         fwd(torch.zeros(2), torch.zeros(1, 1, 2, dtype=torch.bfloat16), torch.zeros(2, dtype=torch.bfloat16), 1.0, 20.0,
             x, x, x, torch.zeros(1, 1, 2, dtype=torch.bfloat16), torch.zeros(2, 2, 128, 128),
             torch.zeros(1, dtype=torch.int32), None, True, None, False, False, None, None, None, None)
+
+
+def test_every_argument_structure_is_mirrored_with_the_library_layout(native_built):
+    """pla_b200/capi.py builds its ctypes structures from the header; the library reports the compiled sizeof and
+    offsetof of every field (csrc/abi_layout.cu, generated from the same header): all of them must agree, and the
+    generated table must be the one the current header gives."""
+    from pla_b200 import capi
+    lib = capi.load()
+    capi.check_layout(lib)
+    assert len(capi.STRUCTS) == 14
+    assert (ROOT / "pla_b200" / "csrc" / "abi_layout.cu").read_text() == capi.emit_layout()
+    assert lib.pla_b200_struct_size(b"no_such_struct") == -1
+    assert lib.pla_b200_field_offset(b"pla_b200_klast_args", b"no_such_field") == -1
