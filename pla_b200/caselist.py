@@ -8,7 +8,8 @@ tools read (``parse_pla_string_re``, tests/utils.py:135-170): a model tag, ``[D]
 ``seqlen_q`` rows per request, optional ``verify_lens``) or ``[P]`` (packed prefill with ``cu_seqlens_q``), then
 ``key:value`` pairs. ``replay`` builds seeded synthetic inputs of a record's shape, runs this library's op for it
 on the GPU and times it; with ``check=True`` prefill records are also evaluated by the exact token recurrence on
-the GPU and the two results compared. ``python -m pla_b200.caselist FILE_OR_DIR`` replays lists.
+the GPU and the two results compared. ``python -m pla_b200.caselist FILE_OR_DIR`` replays lists. ``build_inputs`` /
+``run_inputs`` are the two halves of a replay, for callers that want to judge the results themselves.
 
 ``PLA_SHOW_PARAMS=1`` makes the facades print the record of every call (``show_case``), so a serving run on this
 library yields lists the reference's tools can replay, and the reverse.
@@ -205,25 +206,19 @@ def _time(fn, steps, warmup):
     return e0.elapsed_time(e1) / steps
 
 
-def replay(case: Dict, *, device="cuda", steps: int = 20, warmup: int = 3, check: bool = False, seed: int = 0) -> Dict:
-    """Run the op of one record on seeded synthetic inputs (q, k, v ~ N(0,1); raw gates ~ N(0,1); A_log ~
-    U(0, ln 16); pools ~ N(0, 0.02)). Returns ``{"tag", "ms", "tokens", ...}``; decode records add ``state_GBps``
-    (fp32 tiles read and written per step), prefill records ``Mtok_per_s``; with ``check`` prefill records add the
-    maximum output difference and the relative state difference against the exact token recurrence."""
+def build_inputs(case: Dict, *, device="cuda", seed: int = 0) -> Dict:
+    """Seeded synthetic inputs of a record's shape (q, k, v ~ N(0,1); raw gates ~ N(0,1); A_log ~ U(0, ln 16);
+    pool ~ N(0, 0.02); slot 0 left free): everything ``run_inputs`` needs, as a dict of tensors and scalars."""
     import torch
-    from .decode import fused_sigmoid_gating_delta_rule_forward_k_last as gdn_decode
-    from .decode.kda import fused_recurrent_kda
-    from .prefill.flashkdapro.ops import flashkda_fwd
-    from .prefill.flashqla.ops import chunk_gated_delta_rule_fwd
-
     H, HV = _check_dims(case)
     dt = _dtype(case)
     kda = case["op"] == "kda_attn"
+    if kda and H != HV:
+        raise NotImplementedError("KDA records have one value head per key head")
     dev = torch.device(device)
     g = torch.Generator(device=dev).manual_seed(seed)
     rn = lambda *s: torch.randn(*s, generator=g, device=dev)
     B = int(case["batch_size"])
-    lb = case.get("gate_lower_bound", -5.0) if kda else None
     if case["phase"] == "D":
         Tq = int(case.get("seqlen_q", 1))
         lens = case.get("verify_lens") or [Tq] * B
@@ -235,66 +230,80 @@ def replay(case: Dict, *, device="cuda", steps: int = 20, warmup: int = 3, check
         if offs is None:
             raise ValueError("a prefill record needs cu_seqlens_q")
     T = offs[-1]
-    cu = torch.tensor(offs, dtype=torch.int32, device=dev)
-    q, k, v = rn(1, T, H, D).to(dt), rn(1, T, H, D).to(dt), rn(1, T, HV, D).to(dt)
-    A_log = torch.rand(HV, generator=g, device=dev) * math.log(16.0)
-    slots = B + 1
-    pool = rn(slots, HV, D, D) * 0.02
-    idx = (torch.randperm(B, generator=g, device=dev) + 1).to(torch.int32)        # slot 0 left free (vLLM null block)
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
-    res = {"tag": case.get("_raw_line") or "", "tokens": T, "batch": B}
-    if kda and H != HV:
-        raise NotImplementedError("KDA records have one value head per key head")
-
-    if case["phase"] == "D":
-        if kda:
-            raw_g, raw_beta = rn(1, T, H, D).to(dt), rn(1, T, H).to(dt)
-            dt_bias = rn(H, D) * 0.1
-            fn = lambda: fused_recurrent_kda(q, k, v, raw_g, raw_beta, A_log, dt_bias, lb, pool, cu, idx, status=status)
-        else:
-            a, b = rn(1, T, HV).to(dt), rn(1, T, HV).to(dt)
-            dt_bias = (rn(HV) * 0.1).to(dt)
-            fn = lambda: gdn_decode(A_log, a, dt_bias, 1.0, 20.0, q, k, v, b, pool, idx, D ** -0.5, True, cu, False, False,
-                                    None, None, None, None, status=status)
-        ms = _time(fn, steps, warmup)
-        res.update(ms=ms, state_GBps=2 * B * HV * D * D * 4 / ms / 1e6)
+    x = dict(kda=kda, phase=case["phase"], H=H, HV=HV, B=B, T=T, offs=offs, dtype=dt,
+             lower_bound=case.get("gate_lower_bound") if kda else None)
+    x["cu"] = torch.tensor(offs, dtype=torch.int32, device=dev)
+    x["q"], x["k"], x["v"] = rn(T, H, D).to(dt), rn(T, H, D).to(dt), rn(T, HV, D).to(dt)
+    x["A_log"] = torch.rand(HV, generator=g, device=dev) * math.log(16.0)
+    x["pool"] = rn(B + 1, HV, D, D) * 0.02
+    x["idx"] = (torch.randperm(B, generator=g, device=dev) + 1).to(torch.int32)   # slot 0 left free (vLLM null block)
+    x["status"] = torch.zeros(1, dtype=torch.int32, device=dev)
+    if kda:
+        x["gate"], x["beta"], x["dt_bias"] = rn(T, H, D).to(dt), rn(T, H).to(dt), rn(H, D) * 0.1
     else:
-        if kda:
-            raw_g, raw_beta = rn(T, H, D).to(dt), rn(T, H).to(dt)
-            dt_bias = rn(H, D) * 0.1
-            out = torch.empty(T, H, D, dtype=dt, device=dev)
+        x["gate"], x["beta"] = rn(T, HV).to(dt), rn(T, HV).to(dt)
+        # the decode op takes dt_bias in the activation dtype, the prefill ops in fp32
+        x["dt_bias"] = (rn(HV) * 0.1).to(dt) if case["phase"] == "D" else rn(HV) * 0.1
+    return x
 
-            def run(backend, p):
-                flashkda_fwd(q[0], k[0], v[0], raw_g, raw_beta, A_log, dt_bias, out, None, lb, None, None, cu, p, idx,
-                             tuple(offs), backend=backend, status=status)
-                return out
-            fn = lambda: run("auto", pool)
-        else:
-            a, b = rn(T, HV).to(dt), rn(T, HV).to(dt)
-            dt_bias = rn(HV) * 0.1
 
-            def run(backend, p):
-                if backend == "recurrent":
-                    from ._ops import ops
-                    o = torch.empty(T, HV, D, dtype=dt, device=dev)
-                    ops.prefill_recurrent(q[0], k[0], v[0], a, b, A_log, dt_bias, o, cu, p, idx, None, None, False, False, True,
-                                          D ** -0.5, None, False, True, status)
-                    return o
-                return chunk_gated_delta_rule_fwd(q, k, v, None, None, initial_state=p, initial_state_indices=idx,
-                                                  cu_seqlens=cu, output_final_state=False, normalize_qk=True,
-                                                  raw_cu_seqlens=tuple(offs), raw_gate_a=a, raw_beta_b=b, A_log=A_log,
-                                                  dt_bias=dt_bias)[2][0]
-            fn = lambda: run("auto", pool)
-        if check:
-            p1, p2 = pool.clone(), pool.clone()
-            o1 = run("auto", p1).float().clone()
-            o2 = run("recurrent", p2).float()
-            res.update(out_max_abs_diff=float((o1 - o2).abs().max()) if T else 0.0,
-                       state_rel_l2_diff=float((p1 - p2).norm() / p2.norm().clamp_min(1e-30)))
-        ms = _time(fn, steps, warmup)
-        res.update(ms=ms, Mtok_per_s=T / ms / 1e3)
+def run_inputs(x: Dict, pool=None, backend: str = "auto"):
+    """One call of this library's op for the record behind ``x`` on ``pool`` (default: ``x["pool"]``, updated in
+    place). Returns the output rows ``[T, HV, 128]``. ``backend="recurrent"`` evaluates a prefill record with the
+    exact token recurrence on the GPU instead of the chunked kernels."""
+    import torch
+    from .decode import fused_sigmoid_gating_delta_rule_forward_k_last as gdn_decode
+    from .decode.kda import fused_recurrent_kda
+    from .prefill.flashkdapro.ops import flashkda_fwd
+    from .prefill.flashqla.ops import chunk_gated_delta_rule_fwd
+    p = x["pool"] if pool is None else pool
+    q, k, v, T, H, HV, dt = x["q"], x["k"], x["v"], x["T"], x["H"], x["HV"], x["dtype"]
+    if x["phase"] == "D":
+        if x["kda"]:
+            out, _ = fused_recurrent_kda(q[None], k[None], v[None], x["gate"][None], x["beta"][None], x["A_log"], x["dt_bias"],
+                                         x["lower_bound"], p, x["cu"], x["idx"], status=x["status"])
+            return out[0]
+        return gdn_decode(x["A_log"], x["gate"][None], x["dt_bias"], 1.0, 20.0, q[None], k[None], v[None], x["beta"][None], p,
+                          x["idx"], D ** -0.5, True, x["cu"], False, False, None, None, None, None, status=x["status"])[0]
+    if x["kda"]:
+        out = torch.empty(T, H, D, dtype=dt, device=q.device)
+        flashkda_fwd(q, k, v, x["gate"], x["beta"], x["A_log"], x["dt_bias"], out, None, x["lower_bound"], None, None, x["cu"],
+                     p, x["idx"], tuple(x["offs"]), backend=backend, status=x["status"])
+        return out
+    if backend == "recurrent":
+        from ._ops import ops
+        out = torch.empty(T, HV, D, dtype=dt, device=q.device)
+        ops.prefill_recurrent(q, k, v, x["gate"], x["beta"], x["A_log"], x["dt_bias"], out, x["cu"], p, x["idx"], None, None,
+                              False, False, True, D ** -0.5, None, False, True, x["status"])
+        return out
+    return chunk_gated_delta_rule_fwd(q[None], k[None], v[None], None, None, initial_state=p, initial_state_indices=x["idx"],
+                                      cu_seqlens=x["cu"], output_final_state=False, normalize_qk=True,
+                                      raw_cu_seqlens=tuple(x["offs"]), raw_gate_a=x["gate"], raw_beta_b=x["beta"],
+                                      A_log=x["A_log"], dt_bias=x["dt_bias"])[2][0]
+
+
+def replay(case: Dict, *, device="cuda", steps: int = 20, warmup: int = 3, check: bool = False, seed: int = 0) -> Dict:
+    """Run the op of one record on ``build_inputs``' tensors and time it. Returns ``{"tag", "ms", "tokens", ...}``;
+    decode records add ``state_GBps`` (fp32 tiles read and written per step), prefill records ``Mtok_per_s``; with
+    ``check`` prefill records add the maximum output difference and the relative state difference between the
+    chunked kernels and the exact token recurrence, both on the GPU (the test suite checks replayed records against
+    its CPU oracle instead: ``tests/test_caselist.py``)."""
+    import torch
+    x = build_inputs(case, device=device, seed=seed)
+    res = {"tag": case.get("_raw_line") or "", "tokens": x["T"], "batch": x["B"]}
+    if x["phase"] == "P" and check:
+        p1, p2 = x["pool"].clone(), x["pool"].clone()
+        o1 = run_inputs(x, p1).float().clone()
+        o2 = run_inputs(x, p2, backend="recurrent").float()
+        res.update(out_max_abs_diff=float((o1 - o2).abs().max()) if x["T"] else 0.0,
+                   state_rel_l2_diff=float((p1 - p2).norm() / p2.norm().clamp_min(1e-30)))
+    ms = _time(lambda: run_inputs(x), steps, warmup)
+    if x["phase"] == "D":
+        res.update(ms=ms, state_GBps=2 * x["B"] * x["HV"] * D * D * 4 / ms / 1e6)
+    else:
+        res.update(ms=ms, Mtok_per_s=x["T"] / ms / 1e3)
     torch.cuda.synchronize()
-    res["status"] = int(status.item())
+    res["status"] = int(x["status"].item())
     return res
 
 

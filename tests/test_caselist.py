@@ -19,8 +19,8 @@ def test_parse_reads_every_field_and_skips_foreign_records():
     p = cases[3]
     assert p["num_heads_qk"] == 2 and p["num_heads_v"] == 4 and p["norm_eps"] == 1e-06 and p["ssm_dtype"] == "fp32"
     assert cl.offsets_of(p) == [0, 130, 170, 500] and cl.offsets_of(cases[0]) is None
-    found = cl.collect(SAMPLE.parent)
-    assert len(found) == 1 and len(found[0]["cases"]) == 5
+    found = {Path(f["file"]).name: len(f["cases"]) for f in cl.collect(SAMPLE.parent)}
+    assert found == {"sample_cases.list": 5, "corpus_sample.list": 320}
     with pytest.raises(ValueError):
         cl.parse_case("seqlen_q:1,batch_size:2")
 
@@ -84,3 +84,104 @@ def test_replay_of_the_sample_list(native_built):
     assert [r["tokens"] for r in rows] == [8, 12, 11, 500, 300]
     for r in rows[3:]:
         assert r["out_max_abs_diff"] <= 2e-2 and r["state_rel_l2_diff"] <= 1e-3
+
+
+# ---- the reference's corpus: census of all of it, replay of a sample of it --------------------------------------------
+GOLDEN = SAMPLE.parent
+CORPUS_SAMPLE = GOLDEN / "corpus_sample.list"
+
+
+def _census():
+    import json
+    return json.loads((GOLDEN / "corpus_census.json").read_text())
+
+
+def test_corpus_sample_covers_every_shape_group_of_the_census():
+    """The committed sample holds at least two records of every (operator, phase, heads, dtype, query length, gate
+    bound) group the corpus has, and every one of them parses; what the formatter prints of it parses back to the same values."""
+    import sys
+    sys.path.insert(0, str(GOLDEN))
+    from make_caselist_sample import group_key
+    census = _census()
+    assert census["served_records"] == sum(g["records"] for g in census["groups"].values()) == 56467
+    assert len(census["groups"]) == 143
+    cases = cl.read_caselist(CORPUS_SAMPLE)
+    assert len(cases) == 320
+    seen = {}
+    for c in cases:
+        seen[group_key(c)] = seen.get(group_key(c), 0) + 1
+        offs = cl.offsets_of(c)
+        assert (offs is None) == (c["phase"] == "D")
+        again = cl.format_case(c["batch_size"], int(c.get("seqlen_q", 0)), 128, 128, c["num_heads_qk"], c["num_heads_v"],
+                               c["dtype"], c["op"] == "kda_attn", offs, gate_lower_bound=c.get("gate_lower_bound", -5.0),
+                               force_prefill=c["phase"] == "P")
+        back = cl.parse_case(again)       # corpus records carry more fields (norm_eps, ssm_dtype ...) than a call prints
+        assert all(c[key] == val for key, val in back.items() if key != "_raw_line" and key in c), (back, c)
+    assert set(seen) == set(census["groups"])
+    assert all(n >= 2 or census["groups"][k]["records"] == 1 for k, n in seen.items())
+
+
+def test_census_of_the_whole_reference_corpus():
+    """With the reference tree at hand (PLA_REFERENCE_CASELIST = its caselist folder): every one of its records
+    parses, and the per-group census equals the committed one."""
+    import os
+    import sys
+    root = os.environ.get("PLA_REFERENCE_CASELIST")
+    if not root or not Path(root).is_dir():
+        pytest.skip("PLA_REFERENCE_CASELIST does not name the reference's caselist folder")
+    sys.path.insert(0, str(GOLDEN))
+    from make_caselist_sample import census, pick
+    table, groups = census(root)
+    assert table == _census()
+    assert pick(groups) == [c["_raw_line"] for c in cl.read_caselist(CORPUS_SAMPLE)]
+
+
+def _oracle_check(x, out, pool_before, pool_after):
+    """One value head (the last) of up to three sequences of a replayed record against the CPU oracle: outputs of
+    their first ``cap`` tokens (the recurrence is causal), and the final state where the whole sequence fits."""
+    from helpers import assert_out_close, assert_state_close
+    from oracle import decode as odec
+    cap = 320
+    hv = x["HV"] - 1
+    kh = hv // (x["HV"] // x["H"])
+    offs, B = x["offs"], x["B"]
+    for n in sorted({0, B // 2, B - 1}):
+        lo, full = offs[n], offs[n + 1] - offs[n]
+        T = min(full, cap)
+        if T == 0:
+            continue
+        sl = slice(lo, lo + T)
+        slot = int(x["idx"][n])
+        exp_out, exp_state, _ = odec.klast_forward(
+            q=x["q"][sl, kh:kh + 1].cpu(), k=x["k"][sl, kh:kh + 1].cpu(), v=x["v"][sl, hv:hv + 1].cpu(),
+            a=x["gate"][sl, hv:hv + 1].cpu(), b=x["beta"][sl, hv:hv + 1].cpu(), A_log=x["A_log"][hv:hv + 1].cpu(),
+            dt_bias=x["dt_bias"][hv:hv + 1].float().cpu(), state=pool_before[slot:slot + 1, hv:hv + 1].cpu(),
+            slot_indices=[0], lengths=[T], scale=D ** -0.5, is_kda=x["kda"], lower_bound=x["lower_bound"])
+        assert_out_close(out[sl, hv:hv + 1].cpu(), exp_out, f"request {n}")
+        if T == full:
+            assert_state_close(pool_after[slot:slot + 1, hv:hv + 1].cpu(), exp_state, f"request {n}")
+
+
+D = 128
+
+
+@pytest.mark.gpu
+def test_replay_of_the_corpus_sample_against_the_oracle(native_built):
+    """Every sampled record of the reference's corpus through this library's op for it (decode, multi-token verify
+    and packed prefill; GDN and KDA; 1 to 4,015 requests; 2 to 32,768 tokens), a head subset against the oracle."""
+    cases = cl.read_caselist(CORPUS_SAMPLE)
+    done = 0
+    for i, case in enumerate(cases):
+        x = cl.build_inputs(case, seed=i)
+        before = x["pool"].clone()
+        out = cl.run_inputs(x)
+        torch.cuda.synchronize()
+        assert int(x["status"].item()) == 0, case["_raw_line"][:120]
+        assert torch.equal(x["pool"][0], before[0]), "slot 0 is never addressed"
+        try:
+            _oracle_check(x, out, before, x["pool"])
+        except AssertionError as e:
+            raise AssertionError(f"record {i}: {case['_raw_line'][:160]}: {e}") from e
+        done += 1
+        del x, before, out
+    assert done == 320
