@@ -50,12 +50,12 @@ METRIC = "gdn_decode_state_bandwidth_B256"
 UNIT = "GB/s"
 WORKLOAD = "config1: GDN decode B=256 Hqk=16 HV=32 d=128, fp32 k-last pool 1024 slots, random non-consecutive slots"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the full decode workload (B=256, 32 heads: 8192
-# tiles), from the one-pass ncu capture summarised in profiles/: 541.4 MB read + 476.2 MB written = 1017.6 MB for
-# 1073.7 MB of algorithmic bytes (the last ~60 MB written are still dirty in L2 when the kernel ends).
-# Reported for that workload only (smaller launches leave a larger share of their writes in L2).
-TRAFFIC_BYTES_FULL_LAUNCH = 541374720 + 476201728
-# The same sum over the kernels of one config-3 prefill step (prepare + chain), from profiles/.
-PREFILL_TRAFFIC_BYTES = None
+# tiles), from the one-pass ncu capture summarised in profiles/ (mean of three launches): 541.3 MB read + 479.4 MB
+# written = 1020.7 MB for 1073.7 MB of algorithmic bytes (the last ~57 MB written are still dirty in L2 when the
+# kernel ends). Reported for that workload only (smaller launches leave a larger share of their writes in L2).
+TRAFFIC_BYTES_FULL_LAUNCH = 541260885 + 479420075
+# The same sum over the kernels of one config-3 prefill step (prepare, inverse, chain: one launch each), from profiles/.
+PREFILL_TRAFFIC_BYTES = 4_151_043_840
 PREFILL_FLOP_PER_TOKEN_HV = 133803     # chunk-equivalent tensor work per token and value head
 PREFILL_FLOP_PER_TOKEN_HQK = 32768     # ... and per q/k head (K K^T and Q K^T)
 

@@ -16,8 +16,9 @@ Per rank:
 
 The last rank's (M, B) is never used, so it skips step 2 and contributes zeros to the gather.
 A rank with fewer chains than SMs applies the same scheme once more inside its range (``plan_rank_ranges``).
-GDN runs the chunk-64 tensor-core kernels; KDA (per-channel decay: M = prod diag(gamma_t)(I - beta_t k_t k_t^T),
-the same row-wise affine form) runs the token-recurrent kernel in its prescan mode.
+GDN and KDA (per-channel decay: M = prod diag(gamma_t)(I - beta_t k_t k_t^T), the same row-wise affine form) both
+run the chunk-64 tensor-core kernels, whose chain has a prescan mode; for a KDA gate whose decay is not bounded
+(``flashkda_fwd`` documents the rule) the token-recurrent kernel's prescan mode takes over.
 """
 from __future__ import annotations
 
@@ -312,14 +313,17 @@ def kda_prefill_context_parallel(
 ):
     """KDA counterpart of :func:`gdn_prefill_context_parallel` (same ranges, same exchange).
     ``backend``: ``"chunked"`` (tensor-core kernels; decay bounded as ``flashkda_fwd`` documents),
-    ``"recurrent"`` (exact token recurrence), ``"auto"`` = chunked for the safe gate with
-    ``-5 <= lower_bound < 0``."""
+    ``"recurrent"`` (exact token recurrence), ``"auto"`` = the choice ``flashkda_fwd(backend="auto")`` makes:
+    chunked for the safe gate with ``-5 <= lower_bound < 0`` and for a softplus gate whose parameters bound the
+    decay of 16 tokens by 80 nats."""
     if scale is None:
         scale = D ** -0.5
     kernels = segment_kernels
     if kernels is None:
         if backend == "auto":
-            backend = "chunked" if (lower_bound is not None and -5.0 <= lower_bound < 0.0) else "recurrent"
+            from .flashkdapro.ops import _softplus_decay_is_bounded
+            safe = lower_bound is not None and -5.0 <= lower_bound < 0.0
+            backend = "chunked" if safe or (lower_bound is None and _softplus_decay_is_bounded(A_log, dt_bias)) else "recurrent"
         if backend == "chunked":
             kernels = KdaChunkedSegmentKernels(q, k, v, g, beta, A_log, dt_bias, scale, normalize_qk, lower_bound)
         else:
