@@ -78,6 +78,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
+// Asks for the 128-byte line at `p` to be brought into L2 (no register, no dependency: a hint that lets the DRAM
+// fetch of data needed a phase later run under the current phase).
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // The same with a suspend-time hint: the waiting thread may sleep in hardware for up to `ns` nanoseconds or until
 // the phase completes, instead of returning after the default (short) slice. A warp that polls in a loop
 // competes for issue slots with the working warps of its scheduler; one that sleeps does not.

@@ -52,6 +52,8 @@ __global__ void __launch_bounds__(MT, 3) kda_mega_fused_kernel(const pla_b200_kd
   float4 st[2][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) st[0][i] = srow0[i * 8];
+  // the other twelve (row pass, 128-byte line) pairs of these rows go to L2 meanwhile, one per lane of the row's eight
+  for (int idx = j8; idx < 12; idx += 8) prefetch_l2(srow0 - j8 + (1 + idx / 4) * 4 * (D / 4) + (idx % 4) * 8);
 
   // ---- conv + SiLU of one channel, history shifted in place (bit-exact copies)
   const int c = tid & (D - 1);
