@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/pla_b200.h"
 
 namespace pla {
@@ -77,6 +79,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
+
+// "Done once per device" flags for a kernel's launch attributes (dynamic shared memory size), shared by the host
+// threads that may call an entry point at the same time. Devices past the table are configured on every call.
+struct DeviceOnce {
+  std::atomic<bool> done[64];
+  bool needed(int dev) const { return dev < 0 || dev >= 64 || !done[dev].load(std::memory_order_acquire); }
+  void mark(int dev) {
+    if (dev >= 0 && dev < 64) done[dev].store(true, std::memory_order_release);
+  }
+};
 
 // Asks for the 128-byte line at `p` to be brought into L2 (no register, no dependency: a hint that lets the DRAM
 // fetch of data needed a phase later run under the current phase).

@@ -155,12 +155,12 @@ extern "C" int pla_b200_cp_fold_segments(const pla_b200_cp_fold_segments_args* a
               "pairs (16-byte aligned), seg_first and state_in are required");
   PLA_REQUIRE(a.pool == nullptr || (a.slots > 0 && a.pool_slot_stride >= static_cast<int64_t>(a.HV) * TILE),
               PLA_B200_E_INVALID, "the pool needs slots > 0 and a slot pitch that covers HV*128*128");
-  static bool configured[64] = {};
+  static DeviceOnce configured;
   int dev = 0;
   PLA_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
+  if (configured.needed(dev)) {
     PLA_CUDA_OK(cudaFuncSetAttribute(cp_fold_segments_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(FoldSmem)));
-    configured[dev] = true;
+    configured.mark(dev);
   }
   const int64_t ctas = static_cast<int64_t>(a.sequences) * a.HV * (D / ROWS);
   PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "fold grid too large");
@@ -179,12 +179,12 @@ extern "C" int pla_b200_cp_fold_prefix(const pla_b200_cp_fold_args* args, void* 
   PLA_REQUIRE(a.state_out != nullptr && (a.rank == 0 || a.pairs != nullptr), PLA_B200_E_INVALID,
               "pairs and state_out are required");
   PLA_REQUIRE(a.rank == 0 || aligned16(a.pairs), PLA_B200_E_ALIGN, "pairs must be 16-byte aligned");
-  static bool configured[64] = {};
+  static DeviceOnce configured;
   int dev = 0;
   PLA_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
+  if (configured.needed(dev)) {
     PLA_CUDA_OK(cudaFuncSetAttribute(cp_fold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(FoldSmem)));
-    configured[dev] = true;
+    configured.mark(dev);
   }
   cp_fold_kernel<<<static_cast<unsigned>(a.HV) * (D / ROWS) * (a.compose != 0 ? 2u : 1u), FOLD_THREADS, sizeof(FoldSmem),
                    static_cast<cudaStream_t>(stream)>>>(a);

@@ -422,12 +422,12 @@ template <typename act_t, int BV, int NT, int TS, bool IS_KDA>
 int launch_one(const pla_b200_klast_args& a, cudaStream_t stream) {
   using L = KlastSmem<BV, TS, IS_KDA>;
   auto kern = klast_kernel<act_t, BV, NT, TS, IS_KDA>;
-  static bool configured[64] = {};
+  static DeviceOnce configured;
   int dev = 0;
   PLA_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
+  if (configured.needed(dev)) {
     PLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
-    configured[dev] = true;
+    configured.mark(dev);
   }
   int64_t ctas = static_cast<int64_t>(a.B) * a.HV * (D / BV);
   if (a.o_total_rows > 0 && !a.prescan) ctas += 64;  // CTAs that zero the padded output suffix

@@ -203,12 +203,12 @@ __global__ void __launch_bounds__(NT, 2) klast_rows_kernel(const pla_b200_klast_
 template <typename act_t, bool IS_KDA>
 int launch_rows(const pla_b200_klast_args& a, cudaStream_t stream) {
   auto kern = klast_rows_kernel<act_t, IS_KDA>;
-  static bool configured[64] = {};
+  static DeviceOnce configured;
   int dev = 0;
   PLA_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
+  if (configured.needed(dev)) {
     PLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(RowsSmem)));
-    configured[dev] = true;
+    configured.mark(dev);
   }
   const int64_t ctas = static_cast<int64_t>(a.B) * a.HV;
   PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "B*HV exceeds the grid limit");

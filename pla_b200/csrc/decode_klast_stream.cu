@@ -468,12 +468,12 @@ template <typename act_t, bool IS_KDA, typename state_t, int NWARP, int NS>
 int launch_cfg(const pla_b200_klast_args& a, cudaStream_t stream) {
   constexpr int kSmem = NWARP * NS * static_cast<int>(Layout<state_t>::UNIT_BYTES) + NWARP * NS * 8;
   auto kern = klast_stream_kernel<act_t, IS_KDA, state_t, NWARP, NS>;
-  static std::atomic<bool> configured[64];   // per instantiation and device; devices past 64 configure every call
+  static DeviceOnce configured;   // per instantiation
   int dev = 0;
   PLA_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
+  if (configured.needed(dev)) {
     PLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
-    if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
+    configured.mark(dev);
   }
   const int64_t n_units = static_cast<int64_t>(a.B) * a.HV * UNITS_PER_TILE;
   PLA_REQUIRE(n_units < (1ll << 31), PLA_B200_E_TOO_LARGE, "B*HV too large for the streaming decode kernel");

@@ -160,12 +160,12 @@ __global__ void __launch_bounds__(NT) vlast_kernel(const pla_b200_vlast_args p) 
 template <typename act_t>
 int launch(const pla_b200_vlast_args& a, cudaStream_t stream) {
   auto kern = vlast_kernel<act_t>;
-  static bool configured[64] = {};
+  static DeviceOnce configured;
   int dev = 0;
   PLA_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
+  if (configured.needed(dev)) {
     PLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, VlastSmem::kBytes));
-    configured[dev] = true;
+    configured.mark(dev);
   }
   const int64_t ctas = static_cast<int64_t>(a.B) * a.HV;
   PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "B*HV exceeds the grid limit");

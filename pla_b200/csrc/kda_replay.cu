@@ -915,12 +915,12 @@ extern "C" int pla_b200_kda_replay_verify(const pla_b200_kda_verify_args* args, 
               PLA_B200_E_ALIGN, "state must be float4-aligned fp32 [slots,H,128,128] with contiguous pages");
   PLA_REQUIRE(a.gate == PLA_B200_GATE_SOFTPLUS || a.lower_bound < 0.0f, PLA_B200_E_INVALID,
               "scale/lower_bound must be finite fp32; bound < 0");
-  static bool configured[64] = {};
+  static DeviceOnce configured;
   int dev = 0;
   PLA_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
+  if (configured.needed(dev)) {
     PLA_CUDA_OK(cudaFuncSetAttribute(kda_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(VerifySmem)));
-    configured[dev] = true;
+    configured.mark(dev);
   }
   const int64_t ctas = static_cast<int64_t>(a.N) * a.H;
   PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "N*H exceeds the grid limit");
@@ -965,12 +965,12 @@ extern "C" int pla_b200_kda_fold_layers(const pla_b200_kda_fold_args* args, void
               "tracking indices and steps must be supplied together");
   PLA_REQUIRE(aligned16(a.state) && a.state_slot_stride % 4 == 0 && a.state_layer_stride % 4 == 0, PLA_B200_E_ALIGN,
               "recurrent state must be 16-byte aligned");
-  static bool configured[64] = {};
+  static DeviceOnce configured;
   int dev = 0;
   PLA_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
+  if (configured.needed(dev)) {
     PLA_CUDA_OK(cudaFuncSetAttribute(fold_layers_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(Smem)));
-    configured[dev] = true;
+    configured.mark(dev);
   }
   const int64_t ctas = static_cast<int64_t>(a.B) * a.layers * a.HV * NVS;
   PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "fold grid too large");
@@ -1019,12 +1019,12 @@ extern "C" int pla_b200_kda_replay_commit(const pla_b200_kda_commit_args* args, 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   rc = launch_plan(a, s);
   if (rc != PLA_B200_OK || a.N == 0) return rc;
-  static bool configured[64] = {};
+  static DeviceOnce configured;
   int dev = 0;
   PLA_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
+  if (configured.needed(dev)) {
     PLA_CUDA_OK(cudaFuncSetAttribute(fold_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(Smem)));
-    configured[dev] = true;
+    configured.mark(dev);
   }
   FoldGrid g;
   const int64_t fold = static_cast<int64_t>(a.N) * a.n_layers * a.H * NVS;

@@ -1414,14 +1414,14 @@ int launch_chain_stage(const pla_b200_gdn_chunk_args& a, cudaStream_t s) {
   PLA_REQUIRE(aligned16(a.o), PLA_B200_E_ALIGN, "o must be 16-byte aligned");
   auto launch_chain = [&](auto kern) -> int {
     // one flag per kernel instantiation: both dtypes share this lambda's body (same function-pointer type)
-    static bool configured_by_dtype[2][64] = {};
-    bool* configured = configured_by_dtype[a.act_dtype == PLA_B200_BF16 ? 0 : 1];
+    static DeviceOnce configured_by_dtype[2];
+    DeviceOnce& configured = configured_by_dtype[a.act_dtype == PLA_B200_BF16 ? 0 : 1];
     int dev = 0;
     PLA_CUDA_OK(cudaGetDevice(&dev));
-    if (dev < 64 && !configured[dev]) {
+    if (configured.needed(dev)) {
       PLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(ChainSmem) + 1024)));
-      configured[dev] = true;
+      configured.mark(dev);
     }
     const int64_t ctas = a.prescan ? static_cast<int64_t>(a.N) * a.HV * 2 : static_cast<int64_t>(a.N) * a.HV + 32;
     PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "N*HV exceeds the grid limit");
@@ -1449,14 +1449,14 @@ extern "C" int pla_b200_gdn_prefill_chunked(const pla_b200_gdn_chunk_args* args,
   const int64_t items = static_cast<int64_t>(a.max_chunks) * a.H;
   auto launch_prepare = [&](auto kern) -> int {
     // one flag per kernel instantiation: both dtypes share this lambda's body (same function-pointer type)
-    static bool configured_by_dtype[2][64] = {};
-    bool* configured = configured_by_dtype[a.act_dtype == PLA_B200_BF16 ? 0 : 1];
+    static DeviceOnce configured_by_dtype[2];
+    DeviceOnce& configured = configured_by_dtype[a.act_dtype == PLA_B200_BF16 ? 0 : 1];
     int dev = 0;
     PLA_CUDA_OK(cudaGetDevice(&dev));
-    if (dev < 64 && !configured[dev]) {
+    if (configured.needed(dev)) {
       PLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(PrepSmem) + 1024)));
-      configured[dev] = true;
+      configured.mark(dev);
     }
     kern<<<static_cast<unsigned>(items), PREP_THREADS, sizeof(PrepSmem) + 1024, s>>>(a);
     PLA_CUDA_OK(cudaGetLastError());
@@ -1497,14 +1497,14 @@ extern "C" int pla_b200_kda_prefill_chunked(const pla_b200_gdn_chunk_args* args,
   const int64_t items = static_cast<int64_t>(a.max_chunks) * a.H;
   auto launch_prepare = [&](auto kern) -> int {
     // one flag per kernel instantiation: both dtypes share this lambda's body (same function-pointer type)
-    static bool configured_by_dtype[2][64] = {};
-    bool* configured = configured_by_dtype[a.act_dtype == PLA_B200_BF16 ? 0 : 1];
+    static DeviceOnce configured_by_dtype[2];
+    DeviceOnce& configured = configured_by_dtype[a.act_dtype == PLA_B200_BF16 ? 0 : 1];
     int dev = 0;
     PLA_CUDA_OK(cudaGetDevice(&dev));
-    if (dev < 64 && !configured[dev]) {
+    if (configured.needed(dev)) {
       PLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(KdaPrepSmem) + 1024)));
-      configured[dev] = true;
+      configured.mark(dev);
     }
     kern<<<static_cast<unsigned>(items), KDA_PREP_THREADS, sizeof(KdaPrepSmem) + 1024, s>>>(a);
     PLA_CUDA_OK(cudaGetLastError());
