@@ -151,26 +151,32 @@ __device__ __forceinline__ void invert_column(const float* __restrict__ L, int c
 constexpr int PREP_THREADS = 256;
 constexpr int PREP_HEADS = 8;   // value heads of one q/k head handled per pass
 constexpr int L_BYTES = C * C * 4;
-// fp32 L matrices [chunk][value head][64][64] behind the operand images
+// fp32 L matrices [chunk][value head][column group of 4][row][4] behind the operand images (the layout of the T and
+// P images, so that a warp that holds 32 rows of one column group stores 512 contiguous bytes)
 __host__ __device__ inline int64_t ws_lmat(int64_t max_chunks, int H, int HV, int64_t gc, int hv) {
   return max_chunks * (H * static_cast<int64_t>(HBLOB) + HV * static_cast<int64_t>(VBLOB)) +
          (gc * HV + hv) * static_cast<int64_t>(L_BYTES);
 }
 
+constexpr int KQ_QUARTER = KQ_BYTES / 4;   // bytes of the [Kn; Qn] image for 32 of the 128 features (8 feature groups)
 struct PrepSmem {
-  alignas(1024) float kq[KQ_BYTES / 4];
+  alignas(1024) float kq[2][KQ_QUARTER / 4];   // two quarters of the [Kn; Qn] image in flight
   alignas(16) uint32_t stg[128 * 68];    // staged raw k rows (0..63) and q rows (64..127)
   float G[PREP_HEADS][C];
   float beta[PREP_HEADS][C];
   float rnorm[128];
-  alignas(8) uint64_t bar;
+  alignas(8) uint64_t bar[2];            // MMAs that read quarter buffer b have finished
   uint32_t tmem_base;
 };
 
 // Launch 1 of the GDN prepare: operand images, Kn Kn^T | Qn Kn^T on the tensor core, gates, L (fp32, to the
-// workspace) and the P image. 256 threads, two CTAs per SM. Launch 2 (`chunk_inverse_kernel`) inverts I + L.
+// workspace) and the P image. 256 threads, 71 KiB of shared memory and 78 registers, so three CTAs share an SM and
+// cover each other's phases: the [Kn; Qn] image never exists as a whole in shared memory -- it is built a quarter
+// of the features at a time into two 16 KiB buffers, each quarter feeding four MMA steps of the one accumulator
+// and one bulk store to the workspace while the next quarter is built into the other buffer.
+// Launch 2 (`chunk_inverse_kernel`) inverts I + L.
 template <typename act_t>
-__global__ void __launch_bounds__(PREP_THREADS, 2) gdn_chunk_prepare_kernel(const pla_b200_gdn_chunk_args p) {
+__global__ void __launch_bounds__(PREP_THREADS, 3) gdn_chunk_prepare_kernel(const pla_b200_gdn_chunk_args p) {
   extern __shared__ unsigned char smem_dyn[];
   // the launch reserves 1 KiB of slack so that the operand images can be aligned by hand
   unsigned char* smem_raw = smem_dyn + ((1024u - (smem_addr(smem_dyn) & 1023u)) & 1023u);
@@ -184,7 +190,8 @@ __global__ void __launch_bounds__(PREP_THREADS, 2) gdn_chunk_prepare_kernel(cons
 
   if (warp == 0) tc05::tmem_alloc(&sh.tmem_base, 64);
   if (tid == 0) {
-    mbar_init(&sh.bar, 1);
+    mbar_init(&sh.bar[0], 1);
+    mbar_init(&sh.bar[1], 1);
     fence_mbar_init();
   }
   constexpr int STG = 68;  // staged row pitch in 32-bit words = 17 x 16 bytes
@@ -238,8 +245,19 @@ __global__ void __launch_bounds__(PREP_THREADS, 2) gdn_chunk_prepare_kernel(cons
   }
   __syncthreads();
 
-  // ---- operand images: thread = (token c, quarter of the features) for the k row AND the q row ----
+  // ---- operand images and the MMA chain  D0[128 x 64] = [Kn; Qn] (128 x 128) * Kn^T, a quarter of the features
+  // at a time. Thread = (token c, two of the quarter's eight feature groups) for the k row AND the q row. ----
   unsigned char* ws = static_cast<unsigned char*>(p.workspace);
+  uint32_t tbase = 0;
+  // gives up on a wait that ran out: status bit, drain the bulk stores, free the tensor memory
+  auto bail = [&]() {
+    if (tid == 0) {
+      if (p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_WAIT_TIMEOUT);
+      bulk_wait_read<0>();
+    }
+    __syncthreads();
+    if (warp == 0) tc05::tmem_dealloc(sh.tmem_base, 64);
+  };
   {
     const int c = tid & 63, qq = tid >> 6;
     const bool live = c < pos.n;
@@ -249,56 +267,77 @@ __global__ void __launch_bounds__(PREP_THREADS, 2) gdn_chunk_prepare_kernel(cons
     const uint32_t* __restrict__ krow = sh.stg + c * STG + (shk >> 1);
     const uint32_t* __restrict__ qrow = sh.stg + (64 + c) * STG + (shq >> 1);
     const bool oddk = shk & 1, oddq = shq & 1;
-    // restrict: the staged rows (read), the operand image and the workspace (written) never overlap;
-    // without it every load waits for the previous store
-    float4* __restrict__ kq4 = reinterpret_cast<float4*>(sh.kq);
-    float* __restrict__ knt_g = reinterpret_cast<float*>(ws + ws_hblob(gc, h, p.H) + KQ_BYTES);
-#pragma unroll 4
-    for (int kc = qq * 8; kc < qq * 8 + 8; ++kc) {
-      float4 xk = make_float4(0.f, 0.f, 0.f, 0.f), xq = xk;
-      if (live) {
-        const uint32_t k0 = oddk ? __funnelshift_r(krow[2 * kc], krow[2 * kc + 1], 16) : krow[2 * kc];
-        const uint32_t k1 = oddk ? __funnelshift_r(krow[2 * kc + 1], krow[2 * kc + 2], 16) : krow[2 * kc + 1];
-        const uint32_t q0 = oddq ? __funnelshift_r(qrow[2 * kc], qrow[2 * kc + 1], 16) : qrow[2 * kc];
-        const uint32_t q1 = oddq ? __funnelshift_r(qrow[2 * kc + 1], qrow[2 * kc + 2], 16) : qrow[2 * kc + 1];
-        const act_t* a0 = reinterpret_cast<const act_t*>(&k0);
-        const act_t* a1 = reinterpret_cast<const act_t*>(&k1);
-        const act_t* b0 = reinterpret_cast<const act_t*>(&q0);
-        const act_t* b1 = reinterpret_cast<const act_t*>(&q1);
-        xk = make_float4(tc05::to_tf32(to_f32(a0[0]) * rnk), tc05::to_tf32(to_f32(a0[1]) * rnk),
-                         tc05::to_tf32(to_f32(a1[0]) * rnk), tc05::to_tf32(to_f32(a1[1]) * rnk));
-        xq = make_float4(tc05::to_tf32(to_f32(b0[0]) * rnq), tc05::to_tf32(to_f32(b0[1]) * rnq),
-                         tc05::to_tf32(to_f32(b1[0]) * rnq), tc05::to_tf32(to_f32(b1[1]) * rnq));
+    // transposed image [token group][feature][4 tokens]: the four lanes of a token group trade their 4 x 4 block
+    // (two exchange steps), then lane r holds feature 4 kc + r of the group's four tokens and stores 16 bytes;
+    // the four lanes together write 64 contiguous bytes
+    float4* __restrict__ knt4 = reinterpret_cast<float4*>(ws + ws_hblob(gc, h, p.H) + KQ_BYTES) + (c >> 2) * D + (lane & 3);
+    const bool b0 = lane & 1, b1 = lane & 2;
+#pragma unroll 1
+    for (int q = 0; q < 4; ++q) {
+      const int b = q & 1;
+      if (q >= 2) {   // buffer b again: the MMAs of quarter q - 2 are done with it and its bulk store has read it
+        bool ok = true;
+        if (tid == 0) {
+          bulk_wait_read<1>();
+          ok = mbar_wait(&sh.bar[b], 0, 1u << 20);
+        }
+        if (__syncthreads_or(!ok)) {
+          bail();
+          return;
+        }
       }
-      kq4[kc * 128 + c] = xk;
-      kq4[kc * 128 + 64 + c] = xq;
-      // transposed image (rows = feature, K = token) straight to the workspace
-      float* __restrict__ dst = knt_g + (c >> 2) * (D * 4) + (kc * 4) * 4 + (c & 3);
-      dst[0] = xk.x;
-      dst[4] = xk.y;
-      dst[8] = xk.z;
-      dst[12] = xk.w;
-    }
-  }
-  fence_async_smem();   // the images are read by the tensor core and by a bulk store (async proxy)
-  tc05::fence_before_sync();
-  __syncthreads();
-  tc05::fence_after_sync();
-  const uint32_t tbase = sh.tmem_base;
-
-  // ---- one MMA chain  D0[128 x 64] = [Kn; Qn] (128 x 128) * Kn^T; the finished image goes to the
-  // workspace with one bulk store meanwhile ----
-  if (tid == 0) {
-    const uint64_t a_desc = tc05::smem_desc(sh.kq, 128 * 16, 128);
-    constexpr uint32_t idesc = tc05::idesc_tf32(128, 64);
+      // restrict: the staged rows (read), the operand image and the workspace (written) never overlap;
+      // without it every load waits for the previous store
+      float4* __restrict__ kq4 = reinterpret_cast<float4*>(sh.kq[b]);
 #pragma unroll
-    for (int j = 0; j < D / 8; ++j) {
-      const uint64_t d = tc05::desc_advance(a_desc, j * 2 * 128 * 16);
-      tc05::mma_tf32_ss(tbase, d, d, idesc, j > 0);  // B = the first 64 rows of the same image
+      for (int u = 0; u < 2; ++u) {
+        const int kl = 2 * qq + u, kc = 8 * q + kl;   // feature group inside the quarter / inside the row
+        float4 xk = make_float4(0.f, 0.f, 0.f, 0.f), xq = xk;
+        if (live) {
+          const uint32_t k0 = oddk ? __funnelshift_r(krow[2 * kc], krow[2 * kc + 1], 16) : krow[2 * kc];
+          const uint32_t k1 = oddk ? __funnelshift_r(krow[2 * kc + 1], krow[2 * kc + 2], 16) : krow[2 * kc + 1];
+          const uint32_t q0 = oddq ? __funnelshift_r(qrow[2 * kc], qrow[2 * kc + 1], 16) : qrow[2 * kc];
+          const uint32_t q1 = oddq ? __funnelshift_r(qrow[2 * kc + 1], qrow[2 * kc + 2], 16) : qrow[2 * kc + 1];
+          const act_t* a0 = reinterpret_cast<const act_t*>(&k0);
+          const act_t* a1 = reinterpret_cast<const act_t*>(&k1);
+          const act_t* e0 = reinterpret_cast<const act_t*>(&q0);
+          const act_t* e1 = reinterpret_cast<const act_t*>(&q1);
+          xk = make_float4(tc05::to_tf32(to_f32(a0[0]) * rnk), tc05::to_tf32(to_f32(a0[1]) * rnk),
+                           tc05::to_tf32(to_f32(a1[0]) * rnk), tc05::to_tf32(to_f32(a1[1]) * rnk));
+          xq = make_float4(tc05::to_tf32(to_f32(e0[0]) * rnq), tc05::to_tf32(to_f32(e0[1]) * rnq),
+                           tc05::to_tf32(to_f32(e1[0]) * rnq), tc05::to_tf32(to_f32(e1[1]) * rnq));
+        }
+        kq4[kl * 128 + c] = xk;
+        kq4[kl * 128 + 64 + c] = xq;
+        // step 1: even lanes collect the even features of the lane pair, odd lanes the odd ones
+        const float r0 = __shfl_xor_sync(0xffffffffu, b0 ? xk.x : xk.y, 1);
+        const float r1 = __shfl_xor_sync(0xffffffffu, b0 ? xk.z : xk.w, 1);
+        const float w00 = b0 ? r0 : xk.x, w01 = b0 ? xk.y : r0;    // [feature pair][token of the lane pair]
+        const float w10 = b0 ? r1 : xk.z, w11 = b0 ? xk.w : r1;
+        // step 2: lanes 0, 1 of the group collect features 0, 1; lanes 2, 3 features 2, 3
+        const float s0 = __shfl_xor_sync(0xffffffffu, b1 ? w00 : w10, 2);
+        const float s1 = __shfl_xor_sync(0xffffffffu, b1 ? w01 : w11, 2);
+        const float t0 = b1 ? w10 : w00, t1 = b1 ? w11 : w01;
+        knt4[kc * 4] = b1 ? make_float4(s0, s1, t0, t1) : make_float4(t0, t1, s0, s1);
+      }
+      fence_async_smem();   // the image is read by the tensor core and by a bulk store (async proxy)
+      tc05::fence_before_sync();
+      __syncthreads();
+      tc05::fence_after_sync();
+      tbase = sh.tmem_base;
+      if (tid == 0) {
+        const uint64_t a_desc = tc05::smem_desc(sh.kq[b], 128 * 16, 128);
+        constexpr uint32_t idesc = tc05::idesc_tf32(128, 64);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint64_t d = tc05::desc_advance(a_desc, j * 2 * 128 * 16);
+          tc05::mma_tf32_ss(tbase, d, d, idesc, q > 0 || j > 0);  // B = the first 64 rows of the same image
+        }
+        tc05::mma_commit(&sh.bar[b]);
+        bulk_store(ws + ws_hblob(gc, h, p.H) + q * KQ_QUARTER, sh.kq[b], KQ_QUARTER);
+        bulk_commit();
+      }
     }
-    tc05::mma_commit(&sh.bar);
-    bulk_store(ws + ws_hblob(gc, h, p.H), sh.kq, KQ_BYTES);
-    bulk_commit();
   }
 
   const int quad = warp & 3, ch = warp >> 2;   // TMEM lane quadrant, column half
@@ -365,14 +404,9 @@ __global__ void __launch_bounds__(PREP_THREADS, 2) gdn_chunk_prepare_kernel(cons
       vec[3 * C + lane + 32] = __expf(g_last - s1);
     }
     if (!have_d0) {
-      const bool ok = mbar_wait(&sh.bar, 0, 1u << 20);
+      const bool ok = mbar_wait(&sh.bar[1], 1, 1u << 20);   // the last quarter's MMAs (and, in order, all before)
       if (__syncthreads_or(!ok)) {
-        if (tid == 0) {
-          if (p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_WAIT_TIMEOUT);
-          bulk_wait_read<0>();
-        }
-        __syncthreads();
-        if (warp == 0) tc05::tmem_dealloc(tbase, 64);
+        bail();
         return;
       }
       tc05::fence_after_sync();
@@ -392,7 +426,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 2) gdn_chunk_prepare_kernel(cons
       if (!p_row) {
         const float bi = sh.beta[s][i_row];
         float4* __restrict__ Lg =
-            reinterpret_cast<float4*>(ws + ws_lmat(p.max_chunks, p.H, p.HV, gc, hv)) + i_row * (C / 4) + ch * 8;
+            reinterpret_cast<float4*>(ws + ws_lmat(p.max_chunks, p.H, p.HV, gc, hv)) + ch * 8 * C + i_row;
 #pragma unroll
         for (int jc = 0; jc < 8; ++jc) {
           if (32 * ch + 4 * jc >= i_row) continue;   // a piece at or beyond the diagonal: all zero, never read
@@ -402,7 +436,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 2) gdn_chunk_prepare_kernel(cons
             const int j = jc * 4 + u;
             x[u] = (32 * ch + j < i_row) ? bi * d0[j] * __expf(gi - Gs[j]) : 0.0f;
           }
-          Lg[jc] = make_float4(x[0], x[1], x[2], x[3]);
+          Lg[jc * C] = make_float4(x[0], x[1], x[2], x[3]);   // a warp's 32 rows: 512 contiguous bytes
         }
       } else {
         float4* __restrict__ Pimg = reinterpret_cast<float4*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv) + TM_BYTES);
@@ -443,10 +477,10 @@ __global__ void __launch_bounds__(128) chunk_inverse_kernel(const pla_b200_gdn_c
     // pays the DRAM latency once per iteration)
     const float4* Lg = reinterpret_cast<const float4*>(ws + ws_lmat(p.max_chunks, p.H, p.HV, gc, hv));
 #pragma unroll
-    for (int i = t6; i < C * C / 4; i += 64)
-      if (4 * (i & 15) < (i >> 4))   // row i >> 4, columns 4 (i & 15) ..: pieces at or beyond the diagonal are never read
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&Ls[s][(i >> 4) * L_STRIDE + (i & 15) * 4])),
-                     "l"(Lg + i)
+    for (int jg = 0; jg < C / 4; ++jg)
+      if (4 * jg < t6)   // row t6, columns 4 jg ..: pieces at or beyond the diagonal are never read (nor written)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&Ls[s][t6 * L_STRIDE + jg * 4])),
+                     "l"(Lg + jg * C + t6)
                      : "memory");
   }
   asm volatile("cp.async.wait_all;" ::: "memory");
@@ -743,14 +777,14 @@ __global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(
     // columns at or beyond 16 (a + 1) of chain a hold other chains' data: never selected below (j <= i_row)
     if (!p_row) {
       const float bi = sh.beta[i_row];
-      float4* __restrict__ Lg = reinterpret_cast<float4*>(ws + ws_lmat(p.max_chunks, p.H, p.HV, gc, h)) + i_row * (C / 4) + cs * 4;
+      float4* __restrict__ Lg = reinterpret_cast<float4*>(ws + ws_lmat(p.max_chunks, p.H, p.HV, gc, h)) + cs * 4 * C + i_row;
 #pragma unroll
       for (int jc = 0; jc < 4; ++jc) {
         if (cs * 16 + jc * 4 >= i_row) continue;     // a piece at or beyond the diagonal: all zero, never read
         float x[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) x[u] = (cs * 16 + jc * 4 + u < i_row) ? bi * d0[jc * 4 + u] : 0.0f;
-        Lg[jc] = make_float4(x[0], x[1], x[2], x[3]);
+        Lg[jc * C] = make_float4(x[0], x[1], x[2], x[3]);
       }
     } else {
       float4* __restrict__ Pimg = reinterpret_cast<float4*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, h) + TM_BYTES);
