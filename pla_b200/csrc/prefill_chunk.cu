@@ -149,7 +149,7 @@ __device__ __forceinline__ void invert_column(const float* __restrict__ L, int c
 }
 
 constexpr int PREP_THREADS = 256;
-constexpr int PREP_HEADS = 8;   // value heads of one q/k head handled per pass
+constexpr int PREP_HEADS = 4;   // value heads of one q/k head handled per pass
 constexpr int L_BYTES = C * C * 4;
 // fp32 L matrices [chunk][value head][column group of 4][row][4] behind the operand images (the layout of the T and
 // P images, so that a warp that holds 32 rows of one column group stores 512 contiguous bytes)
@@ -158,9 +158,10 @@ __host__ __device__ inline int64_t ws_lmat(int64_t max_chunks, int H, int HV, in
          (gc * HV + hv) * static_cast<int64_t>(L_BYTES);
 }
 
-constexpr int KQ_QUARTER = KQ_BYTES / 4;   // bytes of the [Kn; Qn] image for 32 of the 128 features (8 feature groups)
+constexpr int PREP_PARTS = 8;                      // the [Kn; Qn] image is built in this many slices of the features
+constexpr int KQ_PART = KQ_BYTES / PREP_PARTS;     // bytes of one slice: 16 features = 4 feature groups x 128 rows x 16 B
 struct PrepSmem {
-  alignas(1024) float kq[2][KQ_QUARTER / 4];   // two quarters of the [Kn; Qn] image in flight
+  alignas(1024) float kq[2][KQ_PART / 4];      // two slices of the [Kn; Qn] image in flight
   alignas(16) uint32_t stg[128 * 68];    // staged raw k rows (0..63) and q rows (64..127)
   float G[PREP_HEADS][C];
   float beta[PREP_HEADS][C];
@@ -170,13 +171,13 @@ struct PrepSmem {
 };
 
 // Launch 1 of the GDN prepare: operand images, Kn Kn^T | Qn Kn^T on the tensor core, gates, L (fp32, to the
-// workspace) and the P image. 256 threads, 71 KiB of shared memory and 78 registers, so three CTAs share an SM and
-// cover each other's phases: the [Kn; Qn] image never exists as a whole in shared memory -- it is built a quarter
-// of the features at a time into two 16 KiB buffers, each quarter feeding four MMA steps of the one accumulator
-// and one bulk store to the workspace while the next quarter is built into the other buffer.
+// workspace) and the P image. 256 threads, 54 KiB of shared memory and 64 registers, so four CTAs share an SM and
+// cover each other's phases: the [Kn; Qn] image never exists as a whole in shared memory -- it is built 16 features
+// at a time into two 8 KiB buffers, each slice feeding two MMA steps of the one accumulator and one bulk store to
+// the workspace while the next slice is built into the other buffer.
 // Launch 2 (`chunk_inverse_kernel`) inverts I + L.
 template <typename act_t>
-__global__ void __launch_bounds__(PREP_THREADS, 3) gdn_chunk_prepare_kernel(const pla_b200_gdn_chunk_args p) {
+__global__ void __launch_bounds__(PREP_THREADS, 4) gdn_chunk_prepare_kernel(const pla_b200_gdn_chunk_args p) {
   extern __shared__ unsigned char smem_dyn[];
   // the launch reserves 1 KiB of slack so that the operand images can be aligned by hand
   unsigned char* smem_raw = smem_dyn + ((1024u - (smem_addr(smem_dyn) & 1023u)) & 1023u);
@@ -245,8 +246,8 @@ __global__ void __launch_bounds__(PREP_THREADS, 3) gdn_chunk_prepare_kernel(cons
   }
   __syncthreads();
 
-  // ---- operand images and the MMA chain  D0[128 x 64] = [Kn; Qn] (128 x 128) * Kn^T, a quarter of the features
-  // at a time. Thread = (token c, two of the quarter's eight feature groups) for the k row AND the q row. ----
+  // ---- operand images and the MMA chain  D0[128 x 64] = [Kn; Qn] (128 x 128) * Kn^T, one slice of the features
+  // at a time. Thread = (token c, one of the slice's four feature groups) for the k row AND the q row. ----
   unsigned char* ws = static_cast<unsigned char*>(p.workspace);
   uint32_t tbase = 0;
   // gives up on a wait that ran out: status bit, drain the bulk stores, free the tensor memory
@@ -273,13 +274,13 @@ __global__ void __launch_bounds__(PREP_THREADS, 3) gdn_chunk_prepare_kernel(cons
     float4* __restrict__ knt4 = reinterpret_cast<float4*>(ws + ws_hblob(gc, h, p.H) + KQ_BYTES) + (c >> 2) * D + (lane & 3);
     const bool b0 = lane & 1, b1 = lane & 2;
 #pragma unroll 1
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < PREP_PARTS; ++q) {
       const int b = q & 1;
-      if (q >= 2) {   // buffer b again: the MMAs of quarter q - 2 are done with it and its bulk store has read it
+      if (q >= 2) {   // buffer b again: the MMAs of slice q - 2 are done with it and its bulk store has read it
         bool ok = true;
         if (tid == 0) {
           bulk_wait_read<1>();
-          ok = mbar_wait(&sh.bar[b], 0, 1u << 20);
+          ok = mbar_wait(&sh.bar[b], ((q >> 1) - 1) & 1, 1u << 20);
         }
         if (__syncthreads_or(!ok)) {
           bail();
@@ -289,9 +290,8 @@ __global__ void __launch_bounds__(PREP_THREADS, 3) gdn_chunk_prepare_kernel(cons
       // restrict: the staged rows (read), the operand image and the workspace (written) never overlap;
       // without it every load waits for the previous store
       float4* __restrict__ kq4 = reinterpret_cast<float4*>(sh.kq[b]);
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int kl = 2 * qq + u, kc = 8 * q + kl;   // feature group inside the quarter / inside the row
+      {
+        const int kl = qq, kc = 4 * q + kl;   // feature group inside the slice / inside the row
         float4 xk = make_float4(0.f, 0.f, 0.f, 0.f), xq = xk;
         if (live) {
           const uint32_t k0 = oddk ? __funnelshift_r(krow[2 * kc], krow[2 * kc + 1], 16) : krow[2 * kc];
@@ -329,12 +329,12 @@ __global__ void __launch_bounds__(PREP_THREADS, 3) gdn_chunk_prepare_kernel(cons
         const uint64_t a_desc = tc05::smem_desc(sh.kq[b], 128 * 16, 128);
         constexpr uint32_t idesc = tc05::idesc_tf32(128, 64);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 2; ++j) {
           const uint64_t d = tc05::desc_advance(a_desc, j * 2 * 128 * 16);
           tc05::mma_tf32_ss(tbase, d, d, idesc, q > 0 || j > 0);  // B = the first 64 rows of the same image
         }
         tc05::mma_commit(&sh.bar[b]);
-        bulk_store(ws + ws_hblob(gc, h, p.H) + q * KQ_QUARTER, sh.kq[b], KQ_QUARTER);
+        bulk_store(ws + ws_hblob(gc, h, p.H) + q * KQ_PART, sh.kq[b], KQ_PART);
         bulk_commit();
       }
     }
@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 3) gdn_chunk_prepare_kernel(cons
       vec[3 * C + lane + 32] = __expf(g_last - s1);
     }
     if (!have_d0) {
-      const bool ok = mbar_wait(&sh.bar[1], 1, 1u << 20);   // the last quarter's MMAs (and, in order, all before)
+      const bool ok = mbar_wait(&sh.bar[1], ((PREP_PARTS - 1) >> 1) & 1, 1u << 20);   // the last slice's MMAs (and, in order, all before)
       if (__syncthreads_or(!ok)) {
         bail();
         return;
