@@ -130,6 +130,12 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
       : "memory");
 }
 
+// Asks for `bytes` (multiple of 16) from a 16-byte aligned global address to be brought into L2; completes nothing
+// and writes nothing: a later bulk copy of the same range then finds it there.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gmem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem_src), "r"(bytes) : "memory");
+}
+
 // 1-D bulk copy shared -> global (bulk async-group completion).
 __device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst),

@@ -814,20 +814,27 @@ __global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(
 // group owns one v row and writes the next A operand straight back into TMEM:
 //   MMA1  D1[v, 0:64 | 64:128] = S^T(TMEM, fp32 read as tf32) x [Kn; Qn]^T       -> (Kn S)^T | (Qn S)^T
 //   E1    W^T[v, c] = beta_c (V[c, v] - e^{G_c} (Kn S)^T[v, c])                   -> over D1[:, 0:64]
-//   MMA2  D2[v, i]  = W^T(TMEM) x T^T                                             -> V'^T
-//   E2    A4[v, c] = e^{G_C - G_c} V'^T[v, c] (over D1[:, 0:64]);  A3 = V'^T stays in D2 as MMA2 left it;  S *= e^{G_C}
-//   MMA3  D3[v, i]  = A3(TMEM) x P^T                                              -> intra-chunk output
-//   MMA4  S[v, k]  += A4(TMEM) x Kn^T-image                                       -> state update
-//   E3    O[i, v]   = e^{G_i} (Qn S)^T[v, i] + D3[v, i]
-// D1 is double-buffered across chunks so that E3 of chunk c overlaps MMA1 of chunk c+1.
-// TMEM columns: S 0..127, D1[0] 128..255, D1[1] 256..383, D2 384..447, D3 448..511.
+//         O_inter[v, i] = e^{G_i} (Qn S)^T[v, i]                                  -> D3 (MMA3 accumulates onto it)
+//   MMA2  D2[v, 0:64 | 64:128] = W^T(TMEM) x [T; T']^T,  T' = diag(e^{G_C - G}) T  -> V'^T | (decayed V')^T
+//   MMA4  S[v, k]  += D2[:, 64:128](TMEM, as MMA2 left it) x Kn^T-image           -> state update
+//   MMA3  D3[v, i] += D2[:, 0:64](TMEM, as MMA2 left it) x P^T                    -> + intra-chunk output
+//   E3    O[i, v]   = D3[v, i] to 16 bits
+// The only epilogue between MMA1 and the state update is E1: the decay of the update rides on the B operand of
+// MMA2 (the scaler warps form T' from T in shared memory while MMA1 and E1 run), so MMA2's two results feed MMA3
+// and MMA4 directly. MMA3 of chunk c is issued behind MMA1 of chunk c + 1 (D3 is double-buffered for that), so
+// the serial path per chunk is MMA1 -> E1 -> MMA2 -> MMA4. Operands read straight from an accumulator are
+// truncated to tf32 by the tensor core (3 to 4e-4 -> 5 to 6e-4 state error on 4K-token sequences; bar 1e-3).
+// KDA has no scalar decay to fold (its images carry the decays): MMA2 is [128 x 64], the epilogue rounds V'^T to
+// nearest in place (E2) and MMA4 reads that.
+// TMEM columns: S 0..127, D1 128..255, D2 256..383, D3[0] 384..447, D3[1] 448..511.
+//
 // Warps: 0 = bulk-copy producer, 1 = MMA issuer (and TMEM owner), 2..9 = two epilogue warpgroups that
 // split the columns of every accumulator between them (a warp may only touch TMEM lanes 32*(warp%4)..+31),
 // 10 = V loader (global rows of any alignment -> shared memory, one chunk ahead), 11 = output storer
-// (bulk stores of the chunk's output rows from shared memory), 12..15 = state scalers: S *= e^{G_C} between MMA1 and
-// MMA4 of a chunk, off the epilogue warps' timeline (tensor-memory loads and stores wait while an MMA runs, and
-// this step sits under MMA2).
-constexpr uint32_t COL_S = 0, COL_D1 = 128, COL_D2 = 384, COL_D3 = 448;
+// (bulk stores of the chunk's output rows from shared memory), 12..15 = scalers: they form T' from T in shared
+// memory (GDN) and rescale the state between MMA1 and MMA4 of a chunk when that is due (KDA: every chunk, per key
+// channel; GDN: only when the lazy scale runs out of range), off the epilogue warps' timeline.
+constexpr uint32_t COL_S = 0, COL_D1 = 128, COL_D2 = 256, COL_D3 = 384;
 constexpr uint32_t kWaitLimit = 1u << 20;
 
 // Optional phase timestamps of chain CTA 0 (development builds only: -DPLA_B200_DEBUG_CLOCKS).
@@ -845,15 +852,15 @@ constexpr int V_PITCH = 136;  // halfwords per staged V row: 128 + room for one 
 struct ChainSmem {
   alignas(1024) float kq[KQ_BYTES / 4];
   alignas(1024) float knt[KNT_BYTES / 4];
-  alignas(1024) float tm[TM_BYTES / 4];
+  alignas(1024) float tm[2 * TM_BYTES / 4];   // [column group][128 rows][4]: rows 0..63 T, rows 64..127 T'
   alignas(1024) float pm[PM_BYTES / 4];
   alignas(16) float vec[2][VEC_BYTES / 4];
   alignas(128) unsigned short v[2][C * V_PITCH];   // raw 16-bit V rows of a chunk, double-buffered
   alignas(128) unsigned short o[C * D];      // output rows of a chunk, 16-bit
-  alignas(8) uint64_t full_kq, full_t, full_pk, full_vec[2];
+  alignas(8) uint64_t full_kq, full_t, full_p, full_k, full_vec[2];
   uint64_t v_full[2], v_free[2], o_full, o_free;
-  uint64_t mma1_done, mma2_done, mma34_done;
-  uint64_t s_ready, a2_ready, a34_ready, e_done, s_scaled;
+  uint64_t mma1_done, mma2_done, mma3_done, mma4_done;
+  uint64_t s_ready, a2_ready, a4_ready, tprime_ready, s_scaled;
   uint32_t tmem_base;
   volatile int abort;
 };
@@ -966,16 +973,18 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
   if (tid == 0) {
     mbar_init(&sh.full_kq, 1);
     mbar_init(&sh.full_t, 1);
-    mbar_init(&sh.full_pk, 1);
+    mbar_init(&sh.full_p, 1);
+    mbar_init(&sh.full_k, 1);
     mbar_init(&sh.full_vec[0], 1);
     mbar_init(&sh.full_vec[1], 1);
     mbar_init(&sh.mma1_done, 1);
     mbar_init(&sh.mma2_done, 1);
-    mbar_init(&sh.mma34_done, 1);
+    mbar_init(&sh.mma3_done, 1);
+    mbar_init(&sh.mma4_done, 1);
     mbar_init(&sh.s_ready, E_THREADS);
     mbar_init(&sh.a2_ready, E_THREADS);
-    mbar_init(&sh.a34_ready, E_THREADS);
-    mbar_init(&sh.e_done, E_THREADS);
+    mbar_init(&sh.tprime_ready, 128);
+    mbar_init(&sh.a4_ready, E_THREADS);
     mbar_init(&sh.s_scaled, 128);
     mbar_init(&sh.v_full[0], 32);
     mbar_init(&sh.v_full[1], 32);
@@ -986,9 +995,9 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
     sh.abort = 0;
     fence_mbar_init();
   }
-  // rows of the T and P images above their triangular pieces: zero for the whole run (the copies never touch them)
-  for (int i = tid; i < (TM_BYTES + PM_BYTES) / 16; i += CHAIN_THREADS)
-    (i < TM_BYTES / 16 ? reinterpret_cast<uint4*>(sh.tm)[i] : reinterpret_cast<uint4*>(sh.pm)[i - TM_BYTES / 16]) =
+  // rows of the T, T' and P images above their triangular pieces: zero for the whole run (nothing ever writes them)
+  for (int i = tid; i < (2 * TM_BYTES + PM_BYTES) / 16; i += CHAIN_THREADS)
+    (i < 2 * TM_BYTES / 16 ? reinterpret_cast<uint4*>(sh.tm)[i] : reinterpret_cast<uint4*>(sh.pm)[i - 2 * TM_BYTES / 16]) =
         make_uint4(0u, 0u, 0u, 0u);
   fence_async_smem();
   if (warp == 1) tc05::tmem_alloc(&sh.tmem_base, 512);
@@ -1006,22 +1015,24 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
         bulk_load(sh.kq, ws + ws_hblob(gc0 + c, h, p.H), KQ_BYTES, &sh.full_kq);
       };
       // T (and, for GDN, P) come back as the sixteen pieces of their lower triangles; the rows above the pieces
-      // were zeroed once when the CTA started
-      auto load_tri = [&](float* dst, const unsigned char* src, uint64_t* bar) {
+      // were zeroed once when the CTA started. `rows` = rows per column group of the image in shared memory.
+      auto load_tri = [&](float* dst, int rows, const unsigned char* src, uint64_t* bar) {
 #pragma unroll 1
         for (int jg = 0; jg < C / 4; ++jg)
-          bulk_load(reinterpret_cast<unsigned char*>(dst) + tri_piece_offset(jg), src + tri_piece_offset(jg),
+          bulk_load(reinterpret_cast<unsigned char*>(dst) + (jg * rows + 4 * jg) * 16, src + tri_piece_offset(jg),
                     tri_piece_bytes(jg), bar);
       };
       auto load_t = [&](int c) {
         mbar_expect_tx(&sh.full_t, TRI_BYTES);
-        load_tri(sh.tm, ws + ws_vblob(p.max_chunks, p.H, p.HV, gc0 + c, hv), &sh.full_t);
+        load_tri(sh.tm, 2 * C, ws + ws_vblob(p.max_chunks, p.H, p.HV, gc0 + c, hv), &sh.full_t);
       };
-      auto load_pk = [&](int c) {
-        const unsigned char* pm_g = ws + ws_vblob(p.max_chunks, p.H, p.HV, gc0 + c, hv) + TM_BYTES;
-        mbar_expect_tx(&sh.full_pk, TRI_BYTES + KNT_BYTES);
-        load_tri(sh.pm, pm_g, &sh.full_pk);
-        bulk_load(sh.knt, ws + ws_hblob(gc0 + c, h, p.H) + KQ_BYTES, KNT_BYTES, &sh.full_pk);
+      auto load_p = [&](int c) {
+        mbar_expect_tx(&sh.full_p, TRI_BYTES);
+        load_tri(sh.pm, C, ws + ws_vblob(p.max_chunks, p.H, p.HV, gc0 + c, hv) + TM_BYTES, &sh.full_p);
+      };
+      auto load_k = [&](int c) {
+        mbar_expect_tx(&sh.full_k, KNT_BYTES);
+        bulk_load(sh.knt, ws + ws_hblob(gc0 + c, h, p.H) + KQ_BYTES, KNT_BYTES, &sh.full_k);
       };
       auto load_vec = [&](int c) {
         mbar_expect_tx(&sh.full_vec[c & 1], VEC_BYTES);
@@ -1031,41 +1042,55 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
       load_vec(0);
       load_kq(0);
       load_t(0);
-      load_pk(0);
+      load_k(0);
+      load_p(0);
       if (nch > 1) load_vec(1);
-      for (int c = 1; c < nch; ++c) {
-        const uint32_t prev = (c - 1) & 1;
-        if (!chain_wait(sh, &sh.mma1_done, prev)) break;
-        load_kq(c);
-        if (!chain_wait(sh, &sh.mma2_done, prev)) break;
-        load_t(c);
-        if (!chain_wait(sh, &sh.mma34_done, prev)) break;
-        load_pk(c);
-        if (!chain_wait(sh, &sh.e_done, prev)) break;
-        if (c + 1 < nch) load_vec(c + 1);
+
+      // every buffer is refilled as soon as the last MMA that reads it has finished; the events of a chunk come in
+      // the order MMA1(c), MMA3(c - 1), MMA2(c), MMA4(c)
+      for (int c = 0; c < nch; ++c) {
+        const uint32_t ph = c & 1;
+        if (!chain_wait(sh, &sh.mma1_done, ph)) break;
+        if (c + 1 < nch) load_kq(c + 1);
+        if (c >= 1) {
+          if (!chain_wait(sh, &sh.mma3_done, ph ^ 1)) break;
+          load_p(c);
+        }
+        if (!chain_wait(sh, &sh.mma2_done, ph)) break;   // T, T' and this chunk's vectors have been consumed
+        if (c + 1 < nch) load_t(c + 1);
+        if (c + 2 < nch) load_vec(c + 2);
+        if (!chain_wait(sh, &sh.mma4_done, ph)) break;
+        if (c + 1 < nch) load_k(c + 1);
       }
       if (sh.abort) {
         // copies may still be in flight into this CTA's shared memory: bounded wait for each
         (void)mbar_wait(&sh.full_kq, 0, 1u << 16);
         (void)mbar_wait(&sh.full_kq, 1, 1u << 16);
-        (void)mbar_wait(&sh.full_pk, 0, 1u << 16);
-        (void)mbar_wait(&sh.full_pk, 1, 1u << 16);
+        (void)mbar_wait(&sh.full_k, 0, 1u << 16);
+        (void)mbar_wait(&sh.full_k, 1, 1u << 16);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint64_t kq_desc = tc05::smem_desc(sh.kq, 128 * 16, 128);
-      const uint64_t t_desc = tc05::smem_desc(sh.tm, 64 * 16, 128);
+      const uint64_t t_desc = tc05::smem_desc(sh.tm, 128 * 16, 128);    // [T; T']: 128 rows per column group
       const uint64_t p_desc = tc05::smem_desc(sh.pm, 64 * 16, 128);
       const uint64_t knt_desc = tc05::smem_desc(sh.knt, 128 * 16, 128);
       constexpr uint32_t i128 = tc05::idesc_tf32(128, 128), i64 = tc05::idesc_tf32(128, 64);
+      const uint32_t d1 = tb + COL_D1, d2 = tb + COL_D2;
       bool ok = chain_wait(sh, &sh.s_ready, 0);
       LazyScale lazy;
       const bool kda_m = p.is_kda != 0;
+      // intra-chunk output of chunk c: D3[c & 1] += V'^T x P^T, on the accumulator half that E1 seeded
+      auto mma3 = [&](int c) {
+#pragma unroll
+        for (int j = 0; j < C / 8; ++j)
+          tc05::mma_tf32_ts(tb + COL_D3 + (c & 1) * 64, d2 + j * 8, tc05::desc_advance(p_desc, j * 2 * 64 * 16), i64, true);
+        tc05::mma_commit(&sh.mma3_done);
+      };
       for (int c = 0; c < nch && ok; ++c) {
         const uint32_t ph = c & 1;
-        const uint32_t d1 = tb + COL_D1 + ph * 128;
         if (!(ok = chain_wait(sh, &sh.full_vec[ph], (c >> 1) & 1))) break;
         float rd, a4s, fac;
         const int mode = kda_m ? kRescale : lazy.step(sh.vec[ph][2 * C + C - 1], rd, a4s, fac);
@@ -1077,30 +1102,32 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
           tc05::mma_tf32_ts(d1, tb + COL_S + j * 8, tc05::desc_advance(kq_desc, j * 2 * 128 * 16), i128, j > 0);
         tc05::mma_commit(&sh.mma1_done);
         DBG_CLOCK(0, c, 1);
-        if (!(ok = chain_wait(sh, &sh.a2_ready, ph) && chain_wait(sh, &sh.full_t, ph))) break;
+        // the previous chunk's MMA3 runs under this chunk's E1 (its operands: D2 as MMA2 left it, P still in place)
+        if (c >= 1) {
+          if (!(ok = chain_wait(sh, &sh.full_p, ph ^ 1))) break;
+          mma3(c - 1);
+        }
+        if (!(ok = chain_wait(sh, &sh.a2_ready, ph) && chain_wait(sh, kda_m ? &sh.full_t : &sh.tprime_ready, ph))) break;
         tc05::fence_after_sync();
         DBG_CLOCK(0, c, 2);
+        // D2 = W^T x [T; T']^T: V'^T in columns 0..63 and, for GDN, the decayed V'^T in 64..127
 #pragma unroll
         for (int j = 0; j < C / 8; ++j)
-          tc05::mma_tf32_ts(tb + COL_D2, d1 + j * 8, tc05::desc_advance(t_desc, j * 2 * 64 * 16), i64, j > 0);
+          tc05::mma_tf32_ts(d2, d1 + j * 8, tc05::desc_advance(t_desc, j * 2 * 128 * 16), kda_m ? i64 : i128, j > 0);
         tc05::mma_commit(&sh.mma2_done);
         DBG_CLOCK(0, c, 3);
-        // MMA3 reads V'^T where MMA2 left it (same shape, so the tensor core orders the two) and runs while the
-        // epilogue turns the same accumulator into A4
-        if (!(ok = chain_wait(sh, &sh.full_pk, ph))) break;
-#pragma unroll
-        for (int j = 0; j < C / 8; ++j)
-          tc05::mma_tf32_ts(tb + COL_D3, tb + COL_D2 + j * 8, tc05::desc_advance(p_desc, j * 2 * 64 * 16), i64, j > 0);
-        if (!(ok = chain_wait(sh, &sh.a34_ready, ph) && chain_wait(sh, &sh.s_scaled, ph))) break;
+        if (!(ok = chain_wait(sh, &sh.full_k, ph) && chain_wait(sh, &sh.s_scaled, ph))) break;
+        if (kda_m && !(ok = chain_wait(sh, &sh.a4_ready, ph))) break;   // V'^T rounded in place (below)
         tc05::fence_after_sync();
         DBG_CLOCK(0, c, 4);
 #pragma unroll
         for (int j = 0; j < C / 8; ++j)
-          tc05::mma_tf32_ts(tb + COL_S, d1 + j * 8, tc05::desc_advance(knt_desc, j * 2 * 128 * 16), i128,
+          tc05::mma_tf32_ts(tb + COL_S, d2 + (kda_m ? 0 : C) + j * 8, tc05::desc_advance(knt_desc, j * 2 * 128 * 16), i128,
                             mode != kOverwrite || j > 0);
-        tc05::mma_commit(&sh.mma34_done);
+        tc05::mma_commit(&sh.mma4_done);
         DBG_CLOCK(0, c, 5);
       }
+      if (ok && chain_wait(sh, &sh.full_p, (nch - 1) & 1)) mma3(nch - 1);
     }
   } else if (warp == 10) {
     // ------------------------------------------------------------------ V loader
@@ -1159,18 +1186,36 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
       if (lane == 0) mbar_arrive(&sh.o_free);
     }
   } else if (warp >= 12) {
-    // ------------------------------------------------------------------ state scalers (128 threads)
-    // S *= e^{G_C} (GDN) or, per key channel, e^{G_C}[k] (KDA: vec[128 + k]) once MMA1 of the chunk has read S;
-    // MMA4 of the chunk waits for it.
+    // ------------------------------------------------------------------ scalers (128 threads)
+    // GDN: T' = diag(e^{G_C - G} / sigma_new) T into rows 64..127 of the [T; T'] image (thread = (row, half of the
+    // column groups); rounded to nearest, since T' carries the state update); then, when the lazy scale is due,
+    // S *= factor once MMA1 of the chunk has read S. KDA: S *= e^{G_C}[k] per key channel (vec[128 + k]) every
+    // chunk. MMA2 waits for T', MMA4 for the rescaled state.
     const uint32_t tS = tb + (static_cast<uint32_t>((warp & 3) * 32) << 16) + COL_S;
     const bool kda = p.is_kda != 0;
+    const int t7 = tid - 12 * 32, trow = t7 & 63, thalf = t7 >> 6;
     LazyScale lazy;
     for (int c = 0; c < nch; ++c) {
       const uint32_t ph = c & 1;
       const float* vec = sh.vec[ph];
       if (!chain_wait(sh, &sh.full_vec[ph], (c >> 1) & 1)) break;
-      float rd, a4s, fac = 1.0f;
+      float rd, a4s = 1.0f, fac = 1.0f;
       const int mode = kda ? kRescale : lazy.step(vec[2 * C + C - 1], rd, a4s, fac);
+      if (!kda) {
+        if (!chain_wait(sh, &sh.full_t, ph)) break;
+        const float d = vec[3 * C + trow] * a4s;
+        float4* t4 = reinterpret_cast<float4*>(sh.tm);
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const int jg = thalf * 8 + jj;
+          if (4 * jg > trow) continue;          // above the column group's piece: zero in both images
+          float4 x = t4[jg * 2 * C + trow];
+          x.x = tc05::to_tf32(x.x * d); x.y = tc05::to_tf32(x.y * d); x.z = tc05::to_tf32(x.z * d); x.w = tc05::to_tf32(x.w * d);
+          t4[jg * 2 * C + C + trow] = x;
+        }
+        fence_async_smem();                     // read by the tensor core (async proxy)
+        mbar_arrive(&sh.tprime_ready);
+      }
       if (!chain_wait(sh, &sh.mma1_done, ph)) break;
       tc05::fence_after_sync();
       if (mode == kRescale) {       // KDA: every chunk, per key channel; GDN: only when sigma runs out of range
@@ -1205,17 +1250,31 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
     {
       const int64_t in_base = static_cast<int64_t>(slot) * p.state_slot_stride + static_cast<int64_t>(hv) * TILE;
 #pragma unroll 1
+      // fp32 k-last tiles (the usual case): this thread's row is contiguous, eight 16-byte loads per 32 columns
+      // instead of 32 scalar ones (a warp instruction touches 32 lines either way)
+      const bool vec_state = f32_state && !p.state_transposed && !prescan && !p.state_init_zero &&
+                             ((reinterpret_cast<uintptr_t>(p.state) | static_cast<uintptr_t>(p.state_slot_stride * 4)) & 15) == 0;
       for (int q4 = 2 * wg; q4 < 2 * wg + 2; ++q4) {
         float s[32];
+        if (vec_state) {
+          const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.state) + in_base +
+                                                              static_cast<int64_t>(m) * D + q4 * 32);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int kx = q4 * 32 + j;
-          s[j] = prescan ? (kind == 1 && kx == m ? 1.0f : 0.0f)
-                 : p.state_init_zero
-                     ? 0.0f
-                     : load_any(p.state, p.state_dtype,
-                                              in_base + (p.state_transposed ? static_cast<int64_t>(kx) * D + m
-                                                                            : static_cast<int64_t>(m) * D + kx));
+          for (int j = 0; j < 8; ++j) {
+            const float4 x = __ldg(src + j);
+            s[4 * j] = x.x; s[4 * j + 1] = x.y; s[4 * j + 2] = x.z; s[4 * j + 3] = x.w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int kx = q4 * 32 + j;
+            s[j] = prescan ? (kind == 1 && kx == m ? 1.0f : 0.0f)
+                   : p.state_init_zero
+                       ? 0.0f
+                       : load_any(p.state, p.state_dtype,
+                                                in_base + (p.state_transposed ? static_cast<int64_t>(kx) * D + m
+                                                                              : static_cast<int64_t>(m) * D + kx));
+          }
         }
         tc05::tmem_st32(tS + q4 * 32, s);
       }
@@ -1226,9 +1285,25 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
 
     bool ok = true;
     LazyScale lazy;
+    const uint32_t tD1 = tb + lane_base + COL_D1;
+    // E3: output rows of chunk c, once its MMA3 has added the intra-chunk part to what E1 left in D3[c & 1]
+    auto e3 = [&](int c) -> bool {
+      if (!chain_wait(sh, &sh.mma3_done, c & 1)) return false;
+      tc05::fence_after_sync();
+      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 6);
+      float d3[32];
+      tc05::tmem_ld32(tD3 + (c & 1) * 64 + cg, d3);
+      if (c >= 1 && !chain_wait(sh, &sh.o_free, (c - 1) & 1)) return false;  // previous rows stored
+      tc05::wait_ld();
+      act_t* so = reinterpret_cast<act_t*>(sh.o);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) so[(cg + j) * D + m] = from_f32<act_t>(d3[j]);
+      mbar_arrive(&sh.o_full);  // the storer reads with ordinary loads: no proxy fence needed
+      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 7);
+      return true;
+    };
     for (int c = 0; c < nch && ok; ++c) {
       const uint32_t ph = c & 1;
-      const uint32_t tD1 = tb + lane_base + COL_D1 + ph * 128;
       const int n = min(C, len - c * C);
       const float* vec = sh.vec[ph];
       if (!(ok = chain_wait(sh, &sh.full_vec[ph], (c >> 1) & 1))) break;
@@ -1279,82 +1354,55 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
         if (m == 0 && wg == 0) DBG_CLOCK(1, c, 9);
         tc05::tmem_st32(tD1 + cg, x);
       }
+      // ---- ... and the part of the output rows that comes from the incoming state, e^G (Qn S)^T, into the
+      // accumulator that MMA3 adds the intra-chunk part to. (KDA: the decay is in the operand images.) ----
+      {
+        float qs[32];
+        tc05::tmem_ld32(tD1 + 64 + cg, qs);
+        tc05::wait_ld();
+        if (!kda) {
+          const float4* e4 = reinterpret_cast<const float4*>(vec + 2 * C + cg);   // e^G
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            float4 e = e4[j4];
+            e.x *= rd; e.y *= rd; e.z *= rd; e.w *= rd;
+            qs[4 * j4 + 0] *= e.x;
+            qs[4 * j4 + 1] *= e.y;
+            qs[4 * j4 + 2] *= e.z;
+            qs[4 * j4 + 3] *= e.w;
+          }
+        }
+        tc05::tmem_st32(tD3 + ph * 64 + cg, qs);
+      }
       tc05::wait_st();
       if (m == 0 && wg == 0) DBG_CLOCK(1, c, 10);
       tc05::fence_before_sync();
       mbar_arrive(&sh.a2_ready);
       if (m == 0 && wg == 0) DBG_CLOCK(1, c, 2);
       mbar_arrive(&sh.v_free[ph]);
-      if (!(ok = chain_wait(sh, &sh.mma2_done, ph))) break;
-      tc05::fence_after_sync();
-      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 4);
-      // ---- E2: A4 = decayed V'^T (rounded to nearest: it feeds the state) over W^T. A3 = V'^T is read by MMA3
-      // straight from the accumulator: the tensor core truncates it to tf32, which only the intra-chunk part of
-      // the 16-bit outputs sees. ----
-      {
+      // ---- E2, KDA only: V'^T is rounded to nearest where MMA2 left it before MMA4 reads it. Its update operand
+      // carries per-channel decays of up to e^80 in the images, and the products of hundreds of such transitions
+      // (the context-parallel pairs) feel the tensor core's truncation; GDN's scalar-decay update does not. ----
+      if (kda) {
+        if (!(ok = chain_wait(sh, &sh.mma2_done, ph))) break;
+        tc05::fence_after_sync();
         float x[32];
         tc05::tmem_ld32(tD2 + cg, x);
         tc05::wait_ld();
-        if (m == 0 && wg == 0) DBG_CLOCK(1, c, 11);
-        if (kda) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) x[j] = tc05::pre_round_tf32(x[j]);
-        } else {
-          const float4* d4 = reinterpret_cast<const float4*>(vec + 3 * C + cg);   // e^{G_C - G}
-#pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            float4 d = d4[j4];
-            d.x *= a4s; d.y *= a4s; d.z *= a4s; d.w *= a4s;   // the update lands in S / sigma_new
-            x[4 * j4 + 0] = tc05::pre_round_tf32(d.x * x[4 * j4 + 0]);
-            x[4 * j4 + 1] = tc05::pre_round_tf32(d.y * x[4 * j4 + 1]);
-            x[4 * j4 + 2] = tc05::pre_round_tf32(d.z * x[4 * j4 + 2]);
-            x[4 * j4 + 3] = tc05::pre_round_tf32(d.w * x[4 * j4 + 3]);
-          }
-        }
-        if (m == 0 && wg == 0) DBG_CLOCK(1, c, 12);
-        tc05::tmem_st32(tD1 + cg, x);
+        for (int j = 0; j < 32; ++j) x[j] = tc05::pre_round_tf32(x[j]);
+        tc05::tmem_st32(tD2 + cg, x);
+        tc05::wait_st();
+        tc05::fence_before_sync();
+        mbar_arrive(&sh.a4_ready);
       }
-      tc05::wait_st();
-      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 13);
-      tc05::fence_before_sync();
-      mbar_arrive(&sh.a34_ready);
-      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 5);
-      if (!(ok = chain_wait(sh, &sh.mma34_done, ph))) break;
-      tc05::fence_after_sync();
-      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 6);
-      // ---- E3: output rows of this chunk ----
-      {
-        float qs[32], d3[32];
-        tc05::tmem_ld32(tD1 + 64 + cg, qs);
-        tc05::tmem_ld32(tD3 + cg, d3);
-        if (c >= 1 && !(ok = chain_wait(sh, &sh.o_free, (c - 1) & 1))) break;  // previous rows stored
-        tc05::wait_ld();
-        if (m == 0 && wg == 0) DBG_CLOCK(1, c, 0);
-        act_t* so = reinterpret_cast<act_t*>(sh.o);
-        // values first, stores second: the stores may alias `vec` as far as the compiler knows
-        if (kda) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) qs[j] += d3[j];
-        } else {
-          const float4* e4 = reinterpret_cast<const float4*>(vec + 2 * C + cg);   // e^G
-#pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            float4 e = e4[j4];
-            e.x *= rd; e.y *= rd; e.z *= rd; e.w *= rd;
-            qs[4 * j4 + 0] = fmaf(e.x, qs[4 * j4 + 0], d3[4 * j4 + 0]);
-            qs[4 * j4 + 1] = fmaf(e.y, qs[4 * j4 + 1], d3[4 * j4 + 1]);
-            qs[4 * j4 + 2] = fmaf(e.z, qs[4 * j4 + 2], d3[4 * j4 + 2]);
-            qs[4 * j4 + 3] = fmaf(e.w, qs[4 * j4 + 3], d3[4 * j4 + 3]);
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) so[(cg + j) * D + m] = from_f32<act_t>(qs[j]);
-        mbar_arrive(&sh.o_full);  // the storer reads with ordinary loads: no proxy fence needed
-      }
-      tc05::fence_before_sync();
-      mbar_arrive(&sh.e_done);
-      if (m == 0 && wg == 0) DBG_CLOCK(1, c, 7);
+      // the previous chunk's output rows: its MMA3 was issued behind this chunk's MMA1
+      if (c >= 1 && !(ok = e3(c - 1))) break;
     }
+    if (ok) ok = e3(nch - 1);
+    // the state is final once the last MMA4 has landed
+    if (ok) ok = chain_wait(sh, &sh.mma4_done, (nch - 1) & 1);
+    tc05::fence_after_sync();
 
     // ---- final state ----
     if (ok && prescan) {
@@ -1388,12 +1436,20 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) gdn_chunk_chain_kernel(const
         float s[32];
         tc05::tmem_ld32(tS + q4 * 32, s);
         tc05::wait_ld();
+        if (f32_state && !p.state_transposed && (reinterpret_cast<uintptr_t>(static_cast<float*>(dst) + base) & 15) == 0) {
+          float4* out4 = reinterpret_cast<float4*>(static_cast<float*>(dst) + base + static_cast<int64_t>(m) * D + q4 * 32);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int kx = q4 * 32 + j;
-          const int64_t e = base + (p.state_transposed ? static_cast<int64_t>(kx) * D + m : static_cast<int64_t>(m) * D + kx);
-          if (f32_state) static_cast<float*>(dst)[e] = s[j] * lazy.sigma;
-          else static_cast<__nv_bfloat16*>(dst)[e] = __float2bfloat16_rn(s[j] * lazy.sigma);
+          for (int j = 0; j < 8; ++j)
+            out4[j] = make_float4(s[4 * j] * lazy.sigma, s[4 * j + 1] * lazy.sigma, s[4 * j + 2] * lazy.sigma,
+                                  s[4 * j + 3] * lazy.sigma);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int kx = q4 * 32 + j;
+            const int64_t e = base + (p.state_transposed ? static_cast<int64_t>(kx) * D + m : static_cast<int64_t>(m) * D + kx);
+            if (f32_state) static_cast<float*>(dst)[e] = s[j] * lazy.sigma;
+            else static_cast<__nv_bfloat16*>(dst)[e] = __float2bfloat16_rn(s[j] * lazy.sigma);
+          }
         }
       }
     }
