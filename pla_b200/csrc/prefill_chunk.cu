@@ -88,16 +88,18 @@ __device__ __forceinline__ int first_chunk_of(const int32_t* cu, int seq) {
 // ================================================================================================
 // prepare
 // ================================================================================================
-constexpr int L_STRIDE = 68;  // padded row of the fp32 L matrix (floats); rows stay 16-byte aligned
 
 // T = (I + L)^-1, one column per thread, rows by forward substitution, all in registers.
 // Columns are dealt to threads in 16-wide blocks; a column of block cb is zero above row 16*cb and
 // only needs rows / terms from its own block on. Blocks {0,3} share one warp and {1,2} the other,
-// which evens out the two warps' work. L: strictly lower triangle, fp32, row pitch L_STRIDE.
+// which evens out the two warps' work. L: strictly lower triangle, fp32, in the workspace's own layout
+// [column group of 4][row][4] (every read below is a warp-wide broadcast, so the layout costs no bank conflicts).
 __device__ __forceinline__ int inverse_column_block(int t6) {
   return (t6 < 32) ? ((t6 & 16) ? 3 : 0) : ((t6 & 16) ? 2 : 1);
 }
-__device__ __forceinline__ constexpr int l_row(int i) { return i * L_STRIDE; }
+__device__ __forceinline__ float4 l_piece(const float* L, int row, int jg) {
+  return reinterpret_cast<const float4*>(L)[jg * C + row];
+}
 __device__ __forceinline__ void invert_column(const float* __restrict__ L, int cb, int col, float (&Tcol)[C]) {
   // Rows go in blocks of four. The part of a row's sum over the columns before its block does not depend on the
   // other rows of the block, so the four rows run side by side (sixteen independent multiply-add chains); only
@@ -119,7 +121,7 @@ __device__ __forceinline__ void invert_column(const float* __restrict__ L, int c
           for (int jb = jq * 4; jb < jq * 4 + 4 && jb < rb; ++jb) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              const float4 l = reinterpret_cast<const float4*>(L + l_row(4 * rb + u))[jb];
+              const float4 l = l_piece(L, 4 * rb + u, jb);
               acc[u][0] = fmaf(l.x, Tcol[4 * jb + 0], acc[u][0]);
               acc[u][1] = fmaf(l.y, Tcol[4 * jb + 1], acc[u][1]);
               acc[u][2] = fmaf(l.z, Tcol[4 * jb + 2], acc[u][2]);
@@ -130,9 +132,9 @@ __device__ __forceinline__ void invert_column(const float* __restrict__ L, int c
       }
       // the block's own triangle (the piece of row 4 rb is not staged and not needed: nothing left of its diagonal)
       const int r0 = 4 * rb;
-      const float4 l1 = reinterpret_cast<const float4*>(L + l_row(r0 + 1))[rb];
-      const float4 l2 = reinterpret_cast<const float4*>(L + l_row(r0 + 2))[rb];
-      const float4 l3 = reinterpret_cast<const float4*>(L + l_row(r0 + 3))[rb];
+      const float4 l1 = l_piece(L, r0 + 1, rb);
+      const float4 l2 = l_piece(L, r0 + 2, rb);
+      const float4 l3 = l_piece(L, r0 + 3, rb);
       const float t0 = ((r0 == col) ? 1.0f : 0.0f) - ((acc[0][0] + acc[0][1]) + (acc[0][2] + acc[0][3]));
       const float t1 = ((r0 + 1 == col) ? 1.0f : 0.0f) -
                        (((acc[1][0] + acc[1][1]) + (acc[1][2] + acc[1][3])) + l1.x * t0);
@@ -463,7 +465,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 4) gdn_chunk_prepare_kernel(cons
 
 // L (fp32, strictly lower) -> T = (I + L)^-1 as a tf32 operand image. Two (chunk, value head) items per CTA.
 __global__ void __launch_bounds__(128) chunk_inverse_kernel(const pla_b200_gdn_chunk_args p, int items) {
-  __shared__ __align__(16) float Ls[2][C * L_STRIDE];
+  __shared__ __align__(16) float Ls[2][C * C];
   const int tid = threadIdx.x, s = tid >> 6, t6 = tid & 63;
   const int item = blockIdx.x * 2 + s;
   const bool live = item < items;
@@ -479,7 +481,7 @@ __global__ void __launch_bounds__(128) chunk_inverse_kernel(const pla_b200_gdn_c
 #pragma unroll
     for (int jg = 0; jg < C / 4; ++jg)
       if (4 * jg < t6)   // row t6, columns 4 jg ..: pieces at or beyond the diagonal are never read (nor written)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&Ls[s][t6 * L_STRIDE + jg * 4])),
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&Ls[s][(jg * C + t6) * 4])),
                      "l"(Lg + jg * C + t6)
                      : "memory");
   }
