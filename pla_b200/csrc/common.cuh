@@ -94,21 +94,6 @@ struct DeviceOnce {
 // fetch of data needed a phase later run under the current phase).
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
-// The same with a suspend-time hint: the waiting thread may sleep in hardware for up to `ns` nanoseconds or until
-// the phase completes, instead of returning after the default (short) slice. A warp that polls in a loop
-// competes for issue slots with the working warps of its scheduler; one that sleeps does not.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(smem_addr(bar)), "r"(parity), "r"(ns)
-      : "memory");
-  return done != 0;
-}
-
 // Bounded wait: gives up after `limit` polls (each poll itself blocks for a
 // hardware-defined slice), returning false so the caller can flag a timeout
 // instead of spinning forever.
@@ -128,12 +113,6 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
           smem_addr(smem_dst)),
       "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar))
       : "memory");
-}
-
-// Asks for `bytes` (multiple of 16) from a 16-byte aligned global address to be brought into L2; completes nothing
-// and writes nothing: a later bulk copy of the same range then finds it there.
-__device__ __forceinline__ void bulk_prefetch_l2(const void* gmem_src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem_src), "r"(bytes) : "memory");
 }
 
 // 1-D bulk copy shared -> global (bulk async-group completion).

@@ -25,9 +25,6 @@
 // bf16 pools as k_last_load_state4 / k_last_store_state4 (:81-112): widened on load,
 // rounded to nearest on store, outputs formed from the unrounded fp32 state.
 #include <atomic>
-#ifdef PLA_B200_TUNE_ENV
-#include <stdlib.h>
-#endif
 
 #include "common.cuh"
 #include "decode_klast.h"
@@ -479,10 +476,6 @@ int launch_cfg(const pla_b200_klast_args& a, cudaStream_t stream) {
   PLA_REQUIRE(n_units < (1ll << 31), PLA_B200_E_TOO_LARGE, "B*HV too large for the streaming decode kernel");
   int piece = 0, grid = 0;
   plan_stream_grid(n_units, NWARP, sm_count(), &piece, &grid);
-#ifdef PLA_B200_TUNE_ENV
-  if (const char* e = getenv("PLA_B200_STREAM_GRID")) grid = atoi(e) > 0 && atoi(e) < grid ? atoi(e) : grid;
-  if (const char* e = getenv("PLA_B200_STREAM_PIECE")) piece = atoi(e) > 0 ? atoi(e) : piece;
-#endif
   kern<<<grid, NWARP * 32, kSmem, stream>>>(a, static_cast<int>(n_units / piece), piece);
   PLA_CUDA_OK(cudaGetLastError());
   return PLA_B200_OK;
