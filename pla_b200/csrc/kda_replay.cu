@@ -751,12 +751,134 @@ __device__ void scatter_cta(const pla_b200_kda_commit_args& p, int cta, int tile
   const bool bound_ok = bc > 0 && boundary > p.null_block_id && boundary < p.slots;
   const int64_t fsrc = (static_cast<int64_t>(b) * p.Q + count - 1) * dim * 3;
   const int64_t bsrc = (static_cast<int64_t>(b) * p.Q + bc - 1) * dim * 3;
-  for (int i = tile * NT + threadIdx.x; i < dim * 3; i += tiles * NT) {
+  for (int i = tile * blockDim.x + threadIdx.x; i < dim * 3; i += tiles * blockDim.x) {
     const int c = i / 3, w = i % 3;
     const int64_t off = static_cast<int64_t>(c) * s_ch + w * s_tap;
     if (bound_ok) dst[static_cast<int64_t>(boundary) * s_slot + off] = src[bsrc + i];
     if (final_ok) dst[static_cast<int64_t>(final_slot) * s_slot + off] = src[fsrc + i];
   }
+}
+
+// Fold for windows of at most CQ tokens (the usual case), one CTA per (row, layer, head): the whole 64 KiB
+// checkpoint goes global -> registers -> global once, with no shared-memory copy. Warp w owns rows 16 w .. 16 w + 15
+// (eight lanes per row), four rows at a time with the next four already requested; the remaining rows are asked
+// into L2 (`prefetch.global.L2`) at the start, so that their DRAM fetch runs under the staging of the records.
+// The committed tokens' k, decay and v records sit in shared memory (12 KiB for eight tokens) and every row takes
+// all of them in turn before it is written to the final slot (and, after token `bc`, to the boundary slot).
+// Same arithmetic as `kda_step`, term by term.
+constexpr int FT = 256;
+struct TileSmem {
+  alignas(16) float k[CQ][D];
+  alignas(16) float gam[CQ][D];
+  float v[CQ][D];
+  float part[CQ][4];
+  float kinv[CQ];
+  float beta[CQ];
+};
+
+__device__ void fold_tile_cta(const pla_b200_kda_commit_args& p, int cta, TileSmem& sh) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, j8 = lane & 7;
+  const int hl = cta % (p.n_layers * p.H);
+  const int b = cta / (p.n_layers * p.H);
+  const int layer = hl / p.H, h = hl % p.H;
+  const int R = p.capacity;
+  const int n_commit = min(p.plan[b], CQ);   // the plan never commits more than Q <= CQ tokens
+  if (n_commit <= 0) return;
+  const int64_t slot = idx_at(p.source, b);
+  if (slot <= p.null_block_id || slot >= p.slots) return;
+  const int final_slot = p.plan[R + b], boundary = p.plan[2 * R + b], bc = p.plan[3 * R + b];
+  const int64_t* L = p.layers + static_cast<int64_t>(layer) * PLA_B200_REPLAY_COLUMNS;
+  float* pool = reinterpret_cast<float*>(L[PLA_B200_COL_STATE]);
+  const int64_t slot_stride = L[PLA_B200_COL_STATE_STRIDE];
+  const __nv_bfloat16* rawv = reinterpret_cast<const __nv_bfloat16*>(L[PLA_B200_COL_RAWV]);
+  const __nv_bfloat16* rawk = reinterpret_cast<const __nv_bfloat16*>(L[PLA_B200_COL_RAWK]);
+  const float* gate = reinterpret_cast<const float*>(L[PLA_B200_COL_GATE]);
+  const float* beta = reinterpret_cast<const float*>(L[PLA_B200_COL_BETA]);
+  const int64_t tile_off = static_cast<int64_t>(h) * TILE;
+
+  // this thread's pieces: row pass ps -> row 16 warp + 4 ps + lane / 8, piece i -> columns (i * 8 + j8) * 4 ..
+  const int64_t my_off = (warp * 16 + (lane >> 3)) * (D / 4) + j8;   // in 16-byte pieces
+  const float4* src0 = reinterpret_cast<const float4*>(pool + slot * slot_stride + tile_off) + my_off;
+  float4 st[2][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) st[0][i] = src0[i * 8];
+  for (int idx = j8; idx < 12; idx += 8) prefetch_l2(src0 - j8 + (1 + idx / 4) * 4 * (D / 4) + (idx % 4) * 8);
+
+  const int64_t rec0 = (static_cast<int64_t>(b) * p.H + h) * p.Q;
+  for (int s = 0; s < n_commit; ++s) {
+    const int64_t rec = (rec0 + s) * D;
+    if (tid < D) {
+      const float kf = __bfloat162float(rawk[rec + tid]);
+      sh.k[s][tid] = kf;
+      sh.gam[s][tid] = __expf(gate[rec + tid]);
+      const float sk = warp_sum(kf * kf);
+      if (lane == 0) sh.part[s][warp] = sk;
+    } else {
+      sh.v[s][tid - D] = __bfloat162float(rawv[rec + tid - D]);
+      if (tid == D) sh.beta[s] = beta[rec0 + s];
+    }
+  }
+  __syncthreads();
+  if (tid < n_commit) {
+    float sk = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) sk += sh.part[tid][w];
+    sh.kinv[tid] = 1.0f / sqrtf(sk + 1e-6f);  // division form, as the records are replayed
+  }
+  __syncthreads();
+
+  const bool final_ok = final_slot > p.null_block_id && final_slot < p.slots;
+  const bool bound_ok = bc > 0 && boundary > p.null_block_id && boundary < p.slots;
+  float4* dst_final = reinterpret_cast<float4*>(pool + static_cast<int64_t>(final_slot) * slot_stride + tile_off) + my_off;
+  float4* dst_bound = reinterpret_cast<float4*>(pool + static_cast<int64_t>(boundary) * slot_stride + tile_off) + my_off;
+#pragma unroll
+  for (int ps = 0; ps < 4; ++ps) {
+    if (ps + 1 < 4) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) st[(ps + 1) & 1][i] = src0[(ps + 1) * 4 * (D / 4) + i * 8];
+    }
+    const int row = warp * 16 + ps * 4 + (lane >> 3);
+    float4(&s4)[4] = st[ps & 1];
+    for (int t = 0; t < n_commit; ++t) {
+      const float kr = sh.kinv[t], bt = sh.beta[t], bk = bt * kr;
+      float4 kk[4];
+      float d = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 g = reinterpret_cast<const float4*>(sh.gam[t])[i * 8 + j8];
+        kk[i] = reinterpret_cast<const float4*>(sh.k[t])[i * 8 + j8];
+        s4[i].x *= g.x; s4[i].y *= g.y; s4[i].z *= g.z; s4[i].w *= g.w;
+        d += dot4(s4[i], kk[i]);
+      }
+      d += __shfl_xor_sync(0xffffffffu, d, 1);
+      d += __shfl_xor_sync(0xffffffffu, d, 2);
+      d += __shfl_xor_sync(0xffffffffu, d, 4);
+      const float vn = (sh.v[t][row] * bt - d * bk) * kr;   // (v - kr d) beta, times kr for the update
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        s4[i].x = fmaf(vn, kk[i].x, s4[i].x);
+        s4[i].y = fmaf(vn, kk[i].y, s4[i].y);
+        s4[i].z = fmaf(vn, kk[i].z, s4[i].z);
+        s4[i].w = fmaf(vn, kk[i].w, s4[i].w);
+      }
+      if (bound_ok && t == bc - 1) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst_bound[ps * 4 * (D / 4) + i * 8] = s4[i];
+      }
+    }
+    if (final_ok) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) dst_final[ps * 4 * (D / 4) + i * 8] = s4[i];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(FT, 3) fold_tile_scatter_kernel(const pla_b200_kda_commit_args p, const FoldGrid g) {
+  __shared__ TileSmem sh;
+  if (static_cast<int>(blockIdx.x) < g.fold_ctas)
+    fold_tile_cta(p, blockIdx.x, sh);
+  else
+    scatter_cta(p, blockIdx.x - g.fold_ctas, g.conv_tiles);
 }
 
 __global__ void __launch_bounds__(NT) fold_scatter_kernel(const pla_b200_kda_commit_args p, const FoldGrid g) {
@@ -1027,12 +1149,15 @@ extern "C" int pla_b200_kda_replay_commit(const pla_b200_kda_commit_args* args, 
     configured.mark(dev);
   }
   FoldGrid g;
-  const int64_t fold = static_cast<int64_t>(a.N) * a.n_layers * a.H * NVS;
-  g.conv_tiles = (3 * a.H * D * 3 + NT * 8 - 1) / (NT * 8);
+  const bool whole_tiles = a.Q <= CQ;   // at most CQ committed tokens per row: one CTA streams the whole tile
+  const int cta_threads = whole_tiles ? FT : NT;
+  const int64_t fold = static_cast<int64_t>(a.N) * a.n_layers * a.H * (whole_tiles ? 1 : NVS);
+  g.conv_tiles = (3 * a.H * D * 3 + cta_threads * 8 - 1) / (cta_threads * 8);
   const int64_t total = fold + static_cast<int64_t>(a.N) * a.n_layers * g.conv_tiles;
   PLA_REQUIRE(total < (1ll << 31), PLA_B200_E_TOO_LARGE, "commit grid too large");
   g.fold_ctas = static_cast<int>(fold);
-  fold_scatter_kernel<<<static_cast<unsigned>(total), NT, sizeof(Smem), s>>>(a, g);
+  if (whole_tiles) fold_tile_scatter_kernel<<<static_cast<unsigned>(total), FT, 0, s>>>(a, g);
+  else fold_scatter_kernel<<<static_cast<unsigned>(total), NT, sizeof(Smem), s>>>(a, g);
   PLA_CUDA_OK(cudaGetLastError());
   return PLA_B200_OK;
 }
