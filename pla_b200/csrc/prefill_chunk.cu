@@ -146,6 +146,23 @@ __device__ __forceinline__ void invert_column(const float* __restrict__ L, int c
   }
 }
 
+// 4 x 4 transpose across the four lanes of a group (lane % 4 = token inside a token group): in = this lane's four
+// values (features f .. f + 3 of its token), out = feature f + lane % 4 of the group's four tokens. Two exchange
+// steps. The transposed operand images [token group][feature][4 tokens] are written with it: lane r stores 16
+// bytes, the four lanes of a group 64 contiguous bytes (scalar stores touched eight lines per instruction).
+__device__ __forceinline__ float4 lane_transpose4(float4 x, bool b0, bool b1) {
+  // step 1: even lanes collect the even features of the lane pair, odd lanes the odd ones
+  const float r0 = __shfl_xor_sync(0xffffffffu, b0 ? x.x : x.y, 1);
+  const float r1 = __shfl_xor_sync(0xffffffffu, b0 ? x.z : x.w, 1);
+  const float w00 = b0 ? r0 : x.x, w01 = b0 ? x.y : r0;    // [feature pair][token of the lane pair]
+  const float w10 = b0 ? r1 : x.z, w11 = b0 ? x.w : r1;
+  // step 2: lanes 0, 1 of the group collect features 0, 1; lanes 2, 3 features 2, 3
+  const float s0 = __shfl_xor_sync(0xffffffffu, b1 ? w00 : w10, 2);
+  const float s1 = __shfl_xor_sync(0xffffffffu, b1 ? w01 : w11, 2);
+  const float t0 = b1 ? w10 : w00, t1 = b1 ? w11 : w01;
+  return b1 ? make_float4(s0, s1, t0, t1) : make_float4(t0, t1, s0, s1);
+}
+
 constexpr int PREP_THREADS = 256;
 constexpr int PREP_HEADS = 4;   // value heads of one q/k head handled per pass
 constexpr int L_BYTES = C * C * 4;
@@ -266,9 +283,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 4) gdn_chunk_prepare_kernel(cons
     const uint32_t* __restrict__ krow = sh.stg + c * STG + (shk >> 1);
     const uint32_t* __restrict__ qrow = sh.stg + (64 + c) * STG + (shq >> 1);
     const bool oddk = shk & 1, oddq = shq & 1;
-    // transposed image [token group][feature][4 tokens]: the four lanes of a token group trade their 4 x 4 block
-    // (two exchange steps), then lane r holds feature 4 kc + r of the group's four tokens and stores 16 bytes;
-    // the four lanes together write 64 contiguous bytes
+    // transposed image [token group][feature][4 tokens], through 4 x 4 lane transposes
     float4* __restrict__ knt4 = reinterpret_cast<float4*>(ws + ws_hblob(gc, h, p.H) + KQ_BYTES) + (c >> 2) * D + (lane & 3);
     const bool b0 = lane & 1, b1 = lane & 2;
 #pragma unroll 1
@@ -307,16 +322,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 4) gdn_chunk_prepare_kernel(cons
         }
         kq4[kl * 128 + c] = xk;
         kq4[kl * 128 + 64 + c] = xq;
-        // step 1: even lanes collect the even features of the lane pair, odd lanes the odd ones
-        const float r0 = __shfl_xor_sync(0xffffffffu, b0 ? xk.x : xk.y, 1);
-        const float r1 = __shfl_xor_sync(0xffffffffu, b0 ? xk.z : xk.w, 1);
-        const float w00 = b0 ? r0 : xk.x, w01 = b0 ? xk.y : r0;    // [feature pair][token of the lane pair]
-        const float w10 = b0 ? r1 : xk.z, w11 = b0 ? xk.w : r1;
-        // step 2: lanes 0, 1 of the group collect features 0, 1; lanes 2, 3 features 2, 3
-        const float s0 = __shfl_xor_sync(0xffffffffu, b1 ? w00 : w10, 2);
-        const float s1 = __shfl_xor_sync(0xffffffffu, b1 ? w01 : w11, 2);
-        const float t0 = b1 ? w10 : w00, t1 = b1 ? w11 : w01;
-        knt4[kc * 4] = b1 ? make_float4(s0, s1, t0, t1) : make_float4(t0, t1, s0, s1);
+        knt4[kc * 4] = lane_transpose4(xk, b0, b1);
       }
       fence_async_smem();   // the image is read by the tensor core and by a bulk store (async proxy)
       tc05::fence_before_sync();
@@ -666,7 +672,9 @@ __global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(
     const bool oddk = shk & 1, oddq = shq & 1;
     float4* __restrict__ kq4 = reinterpret_cast<float4*>(sh.kq);
     float4* __restrict__ kqs_g = reinterpret_cast<float4*>(ws + ws_hblob(gc, h, p.H));
-    float* __restrict__ ke_g = reinterpret_cast<float*>(ws + ws_hblob(gc, h, p.H) + KQ_BYTES);
+    // transposed image [token group][channel][4 tokens], through 4 x 4 lane transposes
+    float4* __restrict__ ke4 = reinterpret_cast<float4*>(ws + ws_hblob(gc, h, p.H) + KQ_BYTES) + (c >> 2) * D + (lane & 3);
+    const bool tb0 = lane & 1, tb1 = lane & 2;
     const float4* __restrict__ dmrow = reinterpret_cast<const float4*>(sh.dm + c * DM_PITCH);
     auto tf4 = [](float4 v) {
       return make_float4(tc05::to_tf32(v.x), tc05::to_tf32(v.y), tc05::to_tf32(v.z), tc05::to_tf32(v.w));
@@ -704,11 +712,7 @@ __global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(
         reinterpret_cast<float4*>(sh.km + km_offset(a))[kc * (16 * (a + 1)) + c] = tf4(mul4(bs, f));
       }
       const float4 ke = tf4(mul4(bs, reinterpret_cast<const float4*>(sh.egc[blk])[kc]));
-      float* __restrict__ dst = ke_g + (c >> 2) * (D * 4) + (kc * 4) * 4 + (c & 3);
-      dst[0] = ke.x;
-      dst[4] = ke.y;
-      dst[8] = ke.z;
-      dst[12] = ke.w;
+      ke4[kc * 4] = lane_transpose4(ke, tb0, tb1);
     }
   }
   fence_async_smem();
