@@ -195,6 +195,53 @@ def test_chunked_prefill_long_sequences_against_token_recurrence(native_built):
     assert_state_close(pool_a, pool_b, "chunked vs token-recurrent state")
 
 
+def test_chunked_prefill_every_state_scaling_mode(native_built):
+    """The chain keeps the state as S / sigma and decides per chunk, from the chunk's total decay, between three modes:
+    carry sigma along (weak decay), rescale the accumulator (sigma about to leave [2^-40, 1]) or overwrite it (the
+    chunk alone decays below 2^-40). One value head per decay strength from e^-0.02 to e^-700 per chunk, 24 chunks
+    each, so that every mode and every transition between modes occurs; outputs and states against the CPU oracle,
+    head by head."""
+    from pla_b200._ops import ops
+    g = torch.Generator().manual_seed(2040)
+    Hg, H = 2, 16
+    lengths = [1536, 700]
+    T = sum(lengths)
+    width = 2 * Hg * D + H * D
+    packed = torch.randn(T, width, generator=g).bfloat16()
+    gates = torch.randn(T, 2 * H, generator=g).bfloat16()
+    # mean log decay per token about -0.7 e^{A_log}: per chunk from -0.02 (A_log = -7.7) to -700 (A_log = 2.75)
+    A_log = torch.linspace(-7.7, 2.75, H)
+    dt_bias = torch.randn(H, generator=g) * 0.1
+    pool = torch.randn(4, H, D, D, generator=g) * 0.02
+    cu = [0, lengths[0], T]
+    q = packed[:, :Hg * D].reshape(T, Hg, D)
+    k = packed[:, Hg * D:2 * Hg * D].reshape(T, Hg, D)
+    v = packed[:, 2 * Hg * D:].reshape(T, H, D)
+    exp_out, exp_state, _ = odec.klast_forward(q=q, k=k, v=v, a=gates[:, :H], b=gates[:, H:], A_log=A_log,
+                                               dt_bias=dt_bias, state=pool, slot_indices=[3, 1], lengths=lengths,
+                                               scale=D ** -0.5)
+    dp = packed.cuda()
+    dq = dp.as_strided((T, Hg, D), (width, D, 1), 0)
+    dk = dp.as_strided((T, Hg, D), (width, D, 1), Hg * D)
+    dv = dp.as_strided((T, H, D), (width, D, 1), 2 * Hg * D)
+    dg = gates.cuda()
+    dpool = pool.cuda()
+    out = torch.empty(T, H, D, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.gdn_prefill_chunked(dq, dk, dv, dg[:, :H], dg[:, H:], A_log.cuda(), dt_bias.cuda(), out, None,
+                            torch.tensor(cu, dtype=torch.int32, device="cuda"), dpool,
+                            torch.tensor([3, 1], dtype=torch.int32, device="cuda"), None, None, False, True,
+                            D ** -0.5, False, True, sum((n + C - 1) // C for n in lengths), 0, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    got = dpool.cpu()
+    for h in range(H):
+        assert_out_close(out[:, h].cpu(), exp_out[:, h], f"value head {h} (A_log {A_log[h]:.2f})")
+        for slot in (3, 1):
+            assert_state_close(got[slot, h], exp_state[slot, h], f"value head {h} (A_log {A_log[h]:.2f}), slot {slot}")
+    assert torch.equal(got[[0, 2]], pool[[0, 2]])
+
+
 def test_chunked_prefill_rows_ending_at_the_allocation_end(native_built):
     """q, k, v that fill their allocations exactly (2 MiB each, 16-byte aligned rows): the staged row
     copies must not touch a byte past the last row."""
