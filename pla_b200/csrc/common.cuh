@@ -203,6 +203,13 @@ __device__ __forceinline__ float log_decay(float x, float A_log, int gate, float
   return -eA * sp;
 }
 
+// 2^x on the special-function unit (what __expf runs after its multiply by log2 e).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);

@@ -386,8 +386,10 @@ __global__ void __launch_bounds__(PREP_THREADS, 4) gdn_chunk_prepare_kernel(cons
         }
       }
       s1 += __shfl_sync(0xffffffffu, s0, 31);
-      sh.G[warp][lane] = s0;
-      sh.G[warp][lane + 32] = s1;
+      // in base-2 units: the L / P epilogue takes differences of these and raises 2 to them (one multiply per
+      // element less than through the natural exponential)
+      sh.G[warp][lane] = s0 * 1.4426950408889634f;
+      sh.G[warp][lane + 32] = s1 * 1.4426950408889634f;
       sh.beta[warp][lane] = b2[0];
       sh.beta[warp][lane + 32] = b2[1];
       if (p.g_cum != nullptr) {
@@ -438,7 +440,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 4) gdn_chunk_prepare_kernel(cons
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int j = jc * 4 + u;
-            x[u] = (32 * ch + j < i_row) ? bi * d0[j] * __expf(gi - Gs[j]) : 0.0f;
+            x[u] = (32 * ch + j < i_row) ? bi * d0[j] * fast_exp2(gi - Gs[j]) : 0.0f;
           }
           Lg[jc * C] = make_float4(x[0], x[1], x[2], x[3]);   // a warp's 32 rows: 512 contiguous bytes
         }
@@ -451,7 +453,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 4) gdn_chunk_prepare_kernel(cons
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int j = jc * 4 + u;
-            x[u] = (32 * ch + j <= i_row && i_row < pos.n) ? tc05::to_tf32(d0[j] * __expf(gi - Gs[j])) : 0.0f;
+            x[u] = (32 * ch + j <= i_row && i_row < pos.n) ? tc05::to_tf32(d0[j] * fast_exp2(gi - Gs[j])) : 0.0f;
           }
           Pimg[(ch * 8 + jc) * C + i_row] = make_float4(x[0], x[1], x[2], x[3]);
         }
