@@ -776,50 +776,42 @@ struct TileSmem {
   float beta[CQ];
 };
 
-__device__ void fold_tile_cta(const pla_b200_kda_commit_args& p, int cta, TileSmem& sh) {
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, j8 = lane & 7;
-  const int hl = cta % (p.n_layers * p.H);
-  const int b = cta / (p.n_layers * p.H);
-  const int layer = hl / p.H, h = hl % p.H;
-  const int R = p.capacity;
-  const int n_commit = min(p.plan[b], CQ);   // the plan never commits more than Q <= CQ tokens
-  if (n_commit <= 0) return;
-  const int64_t slot = idx_at(p.source, b);
-  if (slot <= p.null_block_id || slot >= p.slots) return;
-  const int final_slot = p.plan[R + b], boundary = p.plan[2 * R + b], bc = p.plan[3 * R + b];
-  const int64_t* L = p.layers + static_cast<int64_t>(layer) * PLA_B200_REPLAY_COLUMNS;
-  float* pool = reinterpret_cast<float*>(L[PLA_B200_COL_STATE]);
-  const int64_t slot_stride = L[PLA_B200_COL_STATE_STRIDE];
-  const __nv_bfloat16* rawv = reinterpret_cast<const __nv_bfloat16*>(L[PLA_B200_COL_RAWV]);
-  const __nv_bfloat16* rawk = reinterpret_cast<const __nv_bfloat16*>(L[PLA_B200_COL_RAWK]);
-  const float* gate = reinterpret_cast<const float*>(L[PLA_B200_COL_GATE]);
-  const float* beta = reinterpret_cast<const float*>(L[PLA_B200_COL_BETA]);
-  const int64_t tile_off = static_cast<int64_t>(h) * TILE;
+// What one whole-tile fold needs: where the tile is, where it goes, and the records of the tokens to apply
+// (k, gate and v records: 128 values per token, tokens 128 apart; beta: one value per token).
+struct TileFold {
+  const float* src;             // the 128 x 128 tile to fold
+  float* dst;                   // where the folded tile goes (may be `src`; nullptr: nowhere)
+  float* snap;                  // receives the tile as it is after token `snap_t` (nullptr: no snapshot)
+  int snap_t;
+  int n;                        // tokens to apply, at most CQ
+  const __nv_bfloat16 *rawk, *rawv;
+  const float *gate, *beta;
+};
 
+__device__ void fold_tile(const TileFold& f, TileSmem& sh) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, j8 = lane & 7;
   // this thread's pieces: row pass ps -> row 16 warp + 4 ps + lane / 8, piece i -> columns (i * 8 + j8) * 4 ..
   const int64_t my_off = (warp * 16 + (lane >> 3)) * (D / 4) + j8;   // in 16-byte pieces
-  const float4* src0 = reinterpret_cast<const float4*>(pool + slot * slot_stride + tile_off) + my_off;
+  const float4* src0 = reinterpret_cast<const float4*>(f.src) + my_off;
   float4 st[2][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) st[0][i] = src0[i * 8];
   for (int idx = j8; idx < 12; idx += 8) prefetch_l2(src0 - j8 + (1 + idx / 4) * 4 * (D / 4) + (idx % 4) * 8);
 
-  const int64_t rec0 = (static_cast<int64_t>(b) * p.H + h) * p.Q;
-  for (int s = 0; s < n_commit; ++s) {
-    const int64_t rec = (rec0 + s) * D;
+  for (int s = 0; s < f.n; ++s) {
     if (tid < D) {
-      const float kf = __bfloat162float(rawk[rec + tid]);
+      const float kf = __bfloat162float(f.rawk[s * D + tid]);
       sh.k[s][tid] = kf;
-      sh.gam[s][tid] = __expf(gate[rec + tid]);
+      sh.gam[s][tid] = __expf(f.gate[s * D + tid]);
       const float sk = warp_sum(kf * kf);
       if (lane == 0) sh.part[s][warp] = sk;
     } else {
-      sh.v[s][tid - D] = __bfloat162float(rawv[rec + tid - D]);
-      if (tid == D) sh.beta[s] = beta[rec0 + s];
+      sh.v[s][tid - D] = __bfloat162float(f.rawv[s * D + tid - D]);
+      if (tid == D) sh.beta[s] = f.beta[s];
     }
   }
   __syncthreads();
-  if (tid < n_commit) {
+  if (tid < f.n) {
     float sk = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) sk += sh.part[tid][w];
@@ -827,10 +819,8 @@ __device__ void fold_tile_cta(const pla_b200_kda_commit_args& p, int cta, TileSm
   }
   __syncthreads();
 
-  const bool final_ok = final_slot > p.null_block_id && final_slot < p.slots;
-  const bool bound_ok = bc > 0 && boundary > p.null_block_id && boundary < p.slots;
-  float4* dst_final = reinterpret_cast<float4*>(pool + static_cast<int64_t>(final_slot) * slot_stride + tile_off) + my_off;
-  float4* dst_bound = reinterpret_cast<float4*>(pool + static_cast<int64_t>(boundary) * slot_stride + tile_off) + my_off;
+  float4* dst = f.dst == nullptr ? nullptr : reinterpret_cast<float4*>(f.dst) + my_off;
+  float4* snap = f.snap == nullptr ? nullptr : reinterpret_cast<float4*>(f.snap) + my_off;
 #pragma unroll
   for (int ps = 0; ps < 4; ++ps) {
     if (ps + 1 < 4) {
@@ -839,7 +829,7 @@ __device__ void fold_tile_cta(const pla_b200_kda_commit_args& p, int cta, TileSm
     }
     const int row = warp * 16 + ps * 4 + (lane >> 3);
     float4(&s4)[4] = st[ps & 1];
-    for (int t = 0; t < n_commit; ++t) {
+    for (int t = 0; t < f.n; ++t) {
       const float kr = sh.kinv[t], bt = sh.beta[t], bk = bt * kr;
       float4 kk[4];
       float d = 0.0f;
@@ -861,16 +851,46 @@ __device__ void fold_tile_cta(const pla_b200_kda_commit_args& p, int cta, TileSm
         s4[i].z = fmaf(vn, kk[i].z, s4[i].z);
         s4[i].w = fmaf(vn, kk[i].w, s4[i].w);
       }
-      if (bound_ok && t == bc - 1) {
+      if (snap != nullptr && t == f.snap_t) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) dst_bound[ps * 4 * (D / 4) + i * 8] = s4[i];
+        for (int i = 0; i < 4; ++i) snap[ps * 4 * (D / 4) + i * 8] = s4[i];
       }
     }
-    if (final_ok) {
+    if (dst != nullptr) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) dst_final[ps * 4 * (D / 4) + i * 8] = s4[i];
+      for (int i = 0; i < 4; ++i) dst[ps * 4 * (D / 4) + i * 8] = s4[i];
     }
   }
+}
+
+__device__ void fold_tile_cta(const pla_b200_kda_commit_args& p, int cta, TileSmem& sh) {
+  const int hl = cta % (p.n_layers * p.H);
+  const int b = cta / (p.n_layers * p.H);
+  const int layer = hl / p.H, h = hl % p.H;
+  const int R = p.capacity;
+  const int n_commit = min(p.plan[b], CQ);   // the plan never commits more than Q <= CQ tokens
+  if (n_commit <= 0) return;
+  const int64_t slot = idx_at(p.source, b);
+  if (slot <= p.null_block_id || slot >= p.slots) return;
+  const int final_slot = p.plan[R + b], boundary = p.plan[2 * R + b], bc = p.plan[3 * R + b];
+  const int64_t* L = p.layers + static_cast<int64_t>(layer) * PLA_B200_REPLAY_COLUMNS;
+  float* pool = reinterpret_cast<float*>(L[PLA_B200_COL_STATE]);
+  const int64_t slot_stride = L[PLA_B200_COL_STATE_STRIDE];
+  const int64_t tile_off = static_cast<int64_t>(h) * TILE;
+  const int64_t rec0 = (static_cast<int64_t>(b) * p.H + h) * p.Q;
+  const bool final_ok = final_slot > p.null_block_id && final_slot < p.slots;
+  const bool bound_ok = bc > 0 && boundary > p.null_block_id && boundary < p.slots;
+  TileFold f;
+  f.src = pool + slot * slot_stride + tile_off;
+  f.dst = final_ok ? pool + static_cast<int64_t>(final_slot) * slot_stride + tile_off : nullptr;
+  f.snap = bound_ok ? pool + static_cast<int64_t>(boundary) * slot_stride + tile_off : nullptr;
+  f.snap_t = bc - 1;
+  f.n = n_commit;
+  f.rawk = reinterpret_cast<const __nv_bfloat16*>(L[PLA_B200_COL_RAWK]) + rec0 * D;
+  f.rawv = reinterpret_cast<const __nv_bfloat16*>(L[PLA_B200_COL_RAWV]) + rec0 * D;
+  f.gate = reinterpret_cast<const float*>(L[PLA_B200_COL_GATE]) + rec0 * D;
+  f.beta = reinterpret_cast<const float*>(L[PLA_B200_COL_BETA]) + rec0;
+  fold_tile(f, sh);
 }
 
 __global__ void __launch_bounds__(FT, 3) fold_tile_scatter_kernel(const pla_b200_kda_commit_args p, const FoldGrid g) {
@@ -969,6 +989,43 @@ __global__ void __launch_bounds__(NT) fold_layers_kernel(const pla_b200_kda_fold
     bulk_commit();
     bulk_wait_read<0>();
   }
+}
+
+// The same fold for rings of at most CQ steps, one CTA per (request, layer, value head) on the whole tile (see
+// `fold_tile`): the state is folded in place, the tracked snapshot taken after step `track_step`.
+__global__ void __launch_bounds__(FT, 3) fold_layers_tile_kernel(const pla_b200_kda_fold_args p) {
+  __shared__ TileSmem sh;
+  const int hvl = blockIdx.x % (p.layers * p.HV);
+  const int b = blockIdx.x / (p.layers * p.HV);
+  const int64_t layer = hvl / p.HV;
+  const int hv = hvl % p.HV, h = hv / (p.HV / p.H);
+  const int64_t slot = idx_at(p.slot_idx, b);
+  const int64_t n_commit = idx_at(p.accept_lens, b);
+  if (slot <= p.null_block_id || n_commit <= 0) return;
+  if (slot < 0 || slot >= p.slots || n_commit > p.L) {
+    if (threadIdx.x == 0 && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_BAD_SLOT);
+    return;
+  }
+  const bool has_track = p.track_idx.data != nullptr;
+  const int64_t t_track = has_track ? idx_at(p.track_step, b) : -1;
+  const int64_t slot_track = has_track ? idx_at(p.track_idx, b) : p.null_block_id;
+  const int64_t tile_off = static_cast<int64_t>(hv) * TILE;
+  float* pool = p.state + layer * p.state_layer_stride;
+  TileFold f;
+  f.src = pool + slot * p.state_slot_stride + tile_off;
+  f.dst = pool + slot * p.state_slot_stride + tile_off;
+  const bool track_ok = has_track && t_track >= 0 && t_track < n_commit && slot_track > p.null_block_id && slot_track >= 0 &&
+                        slot_track < p.slots;
+  f.snap = track_ok ? pool + slot_track * p.state_slot_stride + tile_off : nullptr;
+  f.snap_t = static_cast<int>(t_track);
+  f.n = static_cast<int>(n_commit);
+  f.rawv = static_cast<const __nv_bfloat16*>(p.rawv) + layer * p.rawv_layer_stride + slot * p.rawv_slot_stride +
+           static_cast<int64_t>(hv) * p.L * D;
+  f.rawk = static_cast<const __nv_bfloat16*>(p.rawk) + layer * p.rawk_layer_stride + slot * p.rawk_slot_stride +
+           static_cast<int64_t>(h) * p.L * D;
+  f.gate = p.gate + layer * p.gate_layer_stride + slot * p.gate_slot_stride + static_cast<int64_t>(hv) * p.L * D;
+  f.beta = p.beta + layer * p.beta_layer_stride + slot * p.beta_slot_stride + static_cast<int64_t>(hv) * p.L;
+  fold_tile(f, sh);
 }
 
 template <typename T>
@@ -1094,9 +1151,11 @@ extern "C" int pla_b200_kda_fold_layers(const pla_b200_kda_fold_args* args, void
     PLA_CUDA_OK(cudaFuncSetAttribute(fold_layers_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(Smem)));
     configured.mark(dev);
   }
-  const int64_t ctas = static_cast<int64_t>(a.B) * a.layers * a.HV * NVS;
+  const bool whole_tiles = a.L <= CQ;   // short rings: one CTA streams the whole tile through registers
+  const int64_t ctas = static_cast<int64_t>(a.B) * a.layers * a.HV * (whole_tiles ? 1 : NVS);
   PLA_REQUIRE(ctas < (1ll << 31), PLA_B200_E_TOO_LARGE, "fold grid too large");
-  fold_layers_kernel<<<static_cast<unsigned>(ctas), NT, sizeof(Smem), static_cast<cudaStream_t>(stream)>>>(a);
+  if (whole_tiles) fold_layers_tile_kernel<<<static_cast<unsigned>(ctas), FT, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  else fold_layers_kernel<<<static_cast<unsigned>(ctas), NT, sizeof(Smem), static_cast<cudaStream_t>(stream)>>>(a);
   PLA_CUDA_OK(cudaGetLastError());
   return PLA_B200_OK;
 }
