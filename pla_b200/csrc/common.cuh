@@ -183,7 +183,15 @@ __device__ __forceinline__ float4 load4(const T* p) {
 }
 
 // ---------------------------------------------------------------- math
-__device__ __forceinline__ float sigmoidf_fast(float x) { return 1.0f / (1.0f + __expf(-x)); }
+// 2^x on the special-function unit, flushing denormals: a single instruction. (`__expf` is this after a multiply by
+// log2 e, but without the flush it expands to a handful of instructions around the same unit.)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_exp(float x) { return fast_exp2(x * 1.4426950408889634f); }
+__device__ __forceinline__ float sigmoidf_fast(float x) { return __fdividef(1.0f, 1.0f + fast_exp(-x)); }
 
 // log-decay g (<= 0): the state is multiplied by exp(g).
 //   softplus form: g = -exp(A_log) * softplus(x), softplus with (beta, threshold)
@@ -201,13 +209,6 @@ __device__ __forceinline__ float log_decay(float x, float A_log, int gate, float
   const float bx = sp_beta * x;
   const float sp = (bx <= sp_thr) ? (1.0f / sp_beta) * __logf(1.0f + __expf(bx)) : x;
   return -eA * sp;
-}
-
-// 2^x on the special-function unit (what __expf runs after its multiply by log2 e).
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
 }
 
 __device__ __forceinline__ float warp_sum(float x) {
