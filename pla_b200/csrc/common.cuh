@@ -199,7 +199,7 @@ __device__ __forceinline__ float sigmoidf_fast(float x) { return __fdividef(1.0f
 // x = a + dt_bias. (src/pla_device_helpers.cuh:215-246)
 __device__ __forceinline__ float log_decay(float x, float A_log, int gate, float sp_beta,
                                            float sp_thr, float lower_bound) {
-  const float eA = __expf(A_log);
+  const float eA = fast_exp(A_log);
   if (gate == PLA_B200_GATE_SAFE) {
     // exp(A_log)*x formed as 0 when x == 0 so that a huge A_log cannot give inf*0
     // (src/decode/kda_replayssm/kda_mtp_verify.cu:88-92).
@@ -207,7 +207,7 @@ __device__ __forceinline__ float log_decay(float x, float A_log, int gate, float
     return lower_bound * sigmoidf_fast(z);
   }
   const float bx = sp_beta * x;
-  const float sp = (bx <= sp_thr) ? (1.0f / sp_beta) * __logf(1.0f + __expf(bx)) : x;
+  const float sp = (bx <= sp_thr) ? (1.0f / sp_beta) * __logf(1.0f + fast_exp(bx)) : x;
   return -eA * sp;
 }
 

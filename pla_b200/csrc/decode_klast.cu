@@ -236,9 +236,9 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
         if constexpr (IS_KDA) {
           const float* row = fa + tok * p.a_tok_stride + hv * D + lane * 4;
           reinterpret_cast<float4*>(s_gam + s * D)[lane] =
-              make_float4(__expf(row[0]), __expf(row[1]), __expf(row[2]), __expf(row[3]));
+              make_float4(fast_exp(row[0]), fast_exp(row[1]), fast_exp(row[2]), fast_exp(row[3]));
         } else if (lane == 0) {
-          s_gam[s] = __expf(fa[tok * p.a_tok_stride + hv]);
+          s_gam[s] = fast_exp(fa[tok * p.a_tok_stride + hv]);
         }
         if (lane == 0) s_beta[s] = static_cast<const float*>(p.b)[tok * p.b_tok_stride + hv];
         for (int i = lane; i < BV; i += 32) s_v[s * BV + i] = kind == 1 ? 0.0f : to_f32(gv[tok * p.v_tok_stride + i]);
@@ -249,18 +249,18 @@ __global__ void __launch_bounds__(NT) klast_kernel(const pla_b200_klast_args p) 
                                  : load4_scalar(ga + tok * p.a_tok_stride + hv * D + lane * 4);
         const int64_t c = static_cast<int64_t>(hv) * D + lane * 4;
         float4 g;
-        g.x = __expf(log_decay(av.x + load_any(p.dt_bias, p.dt_bias_dtype, c + 0), A_log, p.gate,
+        g.x = fast_exp(log_decay(av.x + load_any(p.dt_bias, p.dt_bias_dtype, c + 0), A_log, p.gate,
                                p.softplus_beta, p.softplus_threshold, p.lower_bound));
-        g.y = __expf(log_decay(av.y + load_any(p.dt_bias, p.dt_bias_dtype, c + 1), A_log, p.gate,
+        g.y = fast_exp(log_decay(av.y + load_any(p.dt_bias, p.dt_bias_dtype, c + 1), A_log, p.gate,
                                p.softplus_beta, p.softplus_threshold, p.lower_bound));
-        g.z = __expf(log_decay(av.z + load_any(p.dt_bias, p.dt_bias_dtype, c + 2), A_log, p.gate,
+        g.z = fast_exp(log_decay(av.z + load_any(p.dt_bias, p.dt_bias_dtype, c + 2), A_log, p.gate,
                                p.softplus_beta, p.softplus_threshold, p.lower_bound));
-        g.w = __expf(log_decay(av.w + load_any(p.dt_bias, p.dt_bias_dtype, c + 3), A_log, p.gate,
+        g.w = fast_exp(log_decay(av.w + load_any(p.dt_bias, p.dt_bias_dtype, c + 3), A_log, p.gate,
                                p.softplus_beta, p.softplus_threshold, p.lower_bound));
         reinterpret_cast<float4*>(s_gam + s * D)[lane] = g;
       } else if (lane == 0) {
         const float x = to_f32(ga[tok * p.a_tok_stride + hv]) + load_any(p.dt_bias, p.dt_bias_dtype, hv);
-        s_gam[s] = __expf(log_decay(x, A_log, p.gate, p.softplus_beta, p.softplus_threshold, p.lower_bound));
+        s_gam[s] = fast_exp(log_decay(x, A_log, p.gate, p.softplus_beta, p.softplus_threshold, p.lower_bound));
       }
       if (lane == 0) s_beta[s] = sigmoidf_fast(to_f32(gb[tok * p.b_tok_stride + hv]));
       for (int i = lane; i < BV; i += 32) s_v[s * BV + i] = kind == 1 ? 0.0f : to_f32(gv[tok * p.v_tok_stride + i]);

@@ -88,13 +88,13 @@ __global__ void __launch_bounds__(NT, 2) klast_rows_kernel(const pla_b200_klast_
     const float A_log = load_any(p.A_log, p.A_log_dtype, hv);
     const int64_t c = static_cast<int64_t>(hv) * D + lane * 4;
     float4 g;
-    g.x = __expf(log_decay(x.x + load_any(p.dt_bias, p.dt_bias_dtype, c + 0), A_log, p.gate, p.softplus_beta,
+    g.x = fast_exp(log_decay(x.x + load_any(p.dt_bias, p.dt_bias_dtype, c + 0), A_log, p.gate, p.softplus_beta,
                            p.softplus_threshold, p.lower_bound));
-    g.y = __expf(log_decay(x.y + load_any(p.dt_bias, p.dt_bias_dtype, c + 1), A_log, p.gate, p.softplus_beta,
+    g.y = fast_exp(log_decay(x.y + load_any(p.dt_bias, p.dt_bias_dtype, c + 1), A_log, p.gate, p.softplus_beta,
                            p.softplus_threshold, p.lower_bound));
-    g.z = __expf(log_decay(x.z + load_any(p.dt_bias, p.dt_bias_dtype, c + 2), A_log, p.gate, p.softplus_beta,
+    g.z = fast_exp(log_decay(x.z + load_any(p.dt_bias, p.dt_bias_dtype, c + 2), A_log, p.gate, p.softplus_beta,
                            p.softplus_threshold, p.lower_bound));
-    g.w = __expf(log_decay(x.w + load_any(p.dt_bias, p.dt_bias_dtype, c + 3), A_log, p.gate, p.softplus_beta,
+    g.w = fast_exp(log_decay(x.w + load_any(p.dt_bias, p.dt_bias_dtype, c + 3), A_log, p.gate, p.softplus_beta,
                            p.softplus_threshold, p.lower_bound));
     reinterpret_cast<float4*>(sh.gam)[lane] = g;
   }
@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(NT, 2) klast_rows_kernel(const pla_b200_klast_
   if constexpr (!IS_KDA) {
     const float x = to_f32(static_cast<const act_t*>(p.a)[tok * p.a_tok_stride + hv]) +
                     load_any(p.dt_bias, p.dt_bias_dtype, hv);
-    gs = __expf(log_decay(x, load_any(p.A_log, p.A_log_dtype, hv), p.gate, p.softplus_beta, p.softplus_threshold,
+    gs = fast_exp(log_decay(x, load_any(p.A_log, p.A_log_dtype, hv), p.gate, p.softplus_beta, p.softplus_threshold,
                           p.lower_bound));
   }
   const float beta = sigmoidf_fast(to_f32(static_cast<const act_t*>(p.b)[tok * p.b_tok_stride + hv]));

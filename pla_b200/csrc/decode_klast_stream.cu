@@ -303,12 +303,12 @@ __global__ void __launch_bounds__(NWARP * 32, 1) klast_stream_kernel(const pla_b
           const int64_t c0 = static_cast<int64_t>(cur.hv) * D + L::col4(e, j);
 #pragma unroll
           for (int c = 0; c < 4; ++c)
-            gg[4 * e + c] = __expf(log_decay(av[c] + load_any(p.dt_bias, p.dt_bias_dtype, c0 + c), A_log, p.gate,
+            gg[4 * e + c] = fast_exp(log_decay(av[c] + load_any(p.dt_bias, p.dt_bias_dtype, c0 + c), A_log, p.gate,
                                              p.softplus_beta, p.softplus_threshold, p.lower_bound));
         }
       } else {
         const float x = to_f32(raw.a) + load_any(p.dt_bias, p.dt_bias_dtype, cur.hv);
-        gs = __expf(log_decay(x, A_log, p.gate, p.softplus_beta, p.softplus_threshold, p.lower_bound));
+        gs = fast_exp(log_decay(x, A_log, p.gate, p.softplus_beta, p.softplus_threshold, p.lower_bound));
       }
       const float beta = sigmoidf_fast(to_f32(raw.b));
       uint32_t vcur[UPT];  // this task's v rows, still 16-bit (raw is refilled part way through)

@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(NT) vlast_kernel(const pla_b200_vlast_args p) 
   const float A_log = load_any(p.A_log, p.A_log_dtype, hv);
   const float xg = to_f32(static_cast<const act_t*>(p.a)[tok * HV + hv]) +
                    to_f32(static_cast<const act_t*>(p.dt_bias)[hv]);
-  const float gamma = __expf(log_decay(xg, A_log, PLA_B200_GATE_SOFTPLUS, p.softplus_beta, p.softplus_threshold, 0.0f));
+  const float gamma = fast_exp(log_decay(xg, A_log, PLA_B200_GATE_SOFTPLUS, p.softplus_beta, p.softplus_threshold, 0.0f));
   const float beta = sigmoidf_fast(to_f32(static_cast<const act_t*>(p.b)[tok * HV + hv]));
   const float4 vv = load4(static_cast<const act_t*>(p.v) + (tok * HV + hv) * D + lane * 4);
   __syncthreads();  // s_q / s_k ready, mbarriers initialised for everyone

@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(MT, 3) kda_mega_fused_kernel(const pla_b200_kd
   if (tid < D) {
     const float q = conv(0), k = conv(1);
     const float x = to_f32(static_cast<const act_t*>(p.raw_g)[static_cast<int64_t>(b) * dim + ch]) + p.dt_bias[ch];
-    sh.gam[c] = __expf(log_decay(x, p.A_log[h], p.gate, 1.0f, 20.0f, p.lower_bound));
+    sh.gam[c] = fast_exp(log_decay(x, p.A_log[h], p.gate, 1.0f, 20.0f, p.lower_bound));
     sh.q[c] = q;
     sh.k[c] = k;
     const float sq = warp_sum(q * q), sk = warp_sum(k * k);

@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(VNT, 2) kda_verify_kernel(const pla_b200_kda_v
         rg[static_cast<int64_t>(t) * D] = gk;
         sh.q[s][c] = ca;
         sh.k[s][c] = cb;
-        sh.gam[s][c] = __expf(gk);
+        sh.gam[s][c] = fast_exp(gk);
         const float sq = warp_sum(ca * ca), sk = warp_sum(cb * cb);
         if (lane == 0) {
           sh.part[s][0][warp] = sq;
@@ -450,7 +450,7 @@ __global__ void __launch_bounds__(VNT, 3) kda_verify_window_kernel(const pla_b20
         rg[static_cast<int64_t>(t) * D] = gk;
         sh.q[t][c] = ca;
         sh.k[t][c] = cb;
-        sh.gam[t][c] = __expf(gk);
+        sh.gam[t][c] = fast_exp(gk);
         const float sq = warp_sum(ca * ca), sk = warp_sum(cb * cb);
         if (lane == 0) {
           sh.part[t][0][warp] = sq;
@@ -695,7 +695,7 @@ __device__ void fold_cta(const pla_b200_kda_commit_args& p, int cta, Smem& sh) {
       const int64_t rec = (rec0 + t0 + s) * D;
       const float kf = __bfloat162float(rawk[rec + tid]);
       sh.k[s][tid] = kf;
-      sh.gam[s][tid] = __expf(gate[rec + tid]);
+      sh.gam[s][tid] = fast_exp(gate[rec + tid]);
       const float sk = warp_sum(kf * kf);
       if (lane == 0) sh.part[s][1][warp] = sk;
       if (tid < BV) sh.v[s][tid] = __bfloat162float(rawv[rec + row0 + tid]);
@@ -802,7 +802,7 @@ __device__ void fold_tile(const TileFold& f, TileSmem& sh) {
     if (tid < D) {
       const float kf = __bfloat162float(f.rawk[s * D + tid]);
       sh.k[s][tid] = kf;
-      sh.gam[s][tid] = __expf(f.gate[s * D + tid]);
+      sh.gam[s][tid] = fast_exp(f.gate[s * D + tid]);
       const float sk = warp_sum(kf * kf);
       if (lane == 0) sh.part[s][warp] = sk;
     } else {
@@ -954,7 +954,7 @@ __global__ void __launch_bounds__(NT) fold_layers_kernel(const pla_b200_kda_fold
       const int64_t rec = static_cast<int64_t>(t0 + s) * D;
       const float kf = __bfloat162float(rawk[rec + tid]);
       sh.k[s][tid] = kf;
-      sh.gam[s][tid] = __expf(gate[rec + tid]);
+      sh.gam[s][tid] = fast_exp(gate[rec + tid]);
       const float sk = warp_sum(kf * kf);
       if (lane == 0) sh.part[s][1][warp] = sk;
       if (tid < BV) sh.v[s][tid] = __bfloat162float(rawv[rec + row0 + tid]);

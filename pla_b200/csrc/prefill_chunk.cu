@@ -399,15 +399,15 @@ __global__ void __launch_bounds__(PREP_THREADS, 4) gdn_chunk_prepare_kernel(cons
       // vectors for the chain
       float* vec = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, hv) + TM_BYTES + PM_BYTES);
       const float g_last = __shfl_sync(0xffffffffu, s1, 31);
-      const float e0 = __expf(s0), e1 = __expf(s1);
+      const float e0 = fast_exp(s0), e1 = fast_exp(s1);
       vec[lane] = b2[0] * e0;            // W = beta V - (beta e^G) (Kn S): one multiply-add per element in the chain
       vec[lane + 32] = b2[1] * e1;
       vec[C + lane] = b2[0];
       vec[C + lane + 32] = b2[1];
       vec[2 * C + lane] = e0;
       vec[2 * C + lane + 32] = e1;
-      vec[3 * C + lane] = __expf(g_last - s0);
-      vec[3 * C + lane + 32] = __expf(g_last - s1);
+      vec[3 * C + lane] = fast_exp(g_last - s0);
+      vec[3 * C + lane + 32] = fast_exp(g_last - s1);
     }
     if (!have_d0) {
       const bool ok = mbar_wait(&sh.bar[1], ((PREP_PARTS - 1) >> 1) & 1, 1u << 20);   // the last slice's MMAs (and, in order, all before)
@@ -634,7 +634,7 @@ __global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(
         *reinterpret_cast<unsigned short*>(&raw) = gs[t * (STG * 2) + shf + c];
         G += log_decay(to_f32(raw) + dtb, A_log, p.gate_kind, 1.0f, 20.0f, p.lower_bound);
       }
-      sh.dm[t * DM_PITCH + c] = __expf(G);
+      sh.dm[t * DM_PITCH + c] = fast_exp(G);
     }
     sh.part[blk][c] = G;
     if (G < -80.0f && p.status != nullptr) atomicOr(p.status, PLA_B200_DEV_DECAY_RANGE);
@@ -648,14 +648,14 @@ __global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(
     auto ref = [&](int a) { return (a > 0 ? b0 : 0.f) + (a > 1 ? b1 : 0.f) + (a > 2 ? b2 : 0.f); };
     const float total = b0 + b1 + b2 + b3;
     if (which < 4) {
-      sh.erb[which][c] = __expf(ref(which));
+      sh.erb[which][c] = fast_exp(ref(which));
       if (which == 0) sh.gc[c] = total;
     } else if (which < 8) {
-      sh.egc[which - 4][c] = __expf(total - ref(which - 4));
+      sh.egc[which - 4][c] = fast_exp(total - ref(which - 4));
     } else {
       const int f = which - 8;                       // (a, b): (1,0) (2,0) (2,1) (3,0) (3,1) (3,2)
       const int a = f < 1 ? 1 : f < 3 ? 2 : 3, b = f - a * (a - 1) / 2;
-      sh.fab[f][c] = __expf(ref(a) - ref(b));
+      sh.fab[f][c] = fast_exp(ref(a) - ref(b));
     }
   }
   __syncthreads();  // also: the staged gate rows (aliased with the B images) are fully consumed
@@ -743,7 +743,7 @@ __global__ void __launch_bounds__(KDA_PREP_THREADS, 1) kda_chunk_prepare_kernel(
   if (tid >= 128 && tid < 256) {
     float* vec = reinterpret_cast<float*>(ws + ws_vblob(p.max_chunks, p.H, p.HV, gc, h) + TM_BYTES + PM_BYTES);
     const int c = tid - 128;
-    vec[2 * C + c] = __expf(sh.gc[c]);
+    vec[2 * C + c] = fast_exp(sh.gc[c]);
     if (c < C) {
       vec[c] = sh.beta[c];               // the decay is folded into the operands: W = beta V - beta (K+ S)
       vec[C + c] = sh.beta[c];
