@@ -55,7 +55,7 @@ WORKLOAD = "config1: GDN decode B=256 Hqk=16 HV=32 d=128, fp32 k-last pool 1024 
 # kernel ends). Reported for that workload only (smaller launches leave a larger share of their writes in L2).
 TRAFFIC_BYTES_FULL_LAUNCH = 541260885 + 479420075
 # The same sum over the kernels of one config-3 prefill step (prepare, inverse, chain: one launch each), from profiles/.
-PREFILL_TRAFFIC_BYTES = 4_084_852_736
+PREFILL_TRAFFIC_BYTES = 4_081_566_208
 PREFILL_FLOP_PER_TOKEN_HV = 133803     # chunk-equivalent tensor work per token and value head
 PREFILL_FLOP_PER_TOKEN_HQK = 32768     # ... and per q/k head (K K^T and Q K^T)
 
